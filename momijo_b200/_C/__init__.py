@@ -1,0 +1,191 @@
+"""ctypes bindings for the native libraries (``libmomijo_b200.so`` and ``libmomijo_host.so``).
+
+Every exported symbol has a C ABI; tensors are passed as raw device pointers together with the
+current CUDA stream. ``lib()`` raises if the CUDA library is missing: on a machine with a GPU
+the hand-written kernels are the only execution path, there is no silent fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_double, c_float, c_int, c_longlong, c_ulonglong, c_void_p
+from pathlib import Path
+
+_HERE = Path(__file__).resolve().parent
+_LIB = None
+_HOST = None
+
+# Number of device kernels launched through this module (bench.py reports it).
+launches = 0
+
+P, I, L, F = c_void_p, c_int, c_longlong, c_float
+
+# name -> (argtypes, kernels launched per call)
+_SIGS = {
+    "mmj_gemm_bf16": ([P, L, I, P, L, I, P, L, I, I, I, I, P, P, L, P, L, P, I, P, P], 1),
+    "mmj_gemm_bf16_grouped": ([P, L, P, L, I, I, I, P, L, I, I, I, I, P, L, P, P, P, I, P, P], 1),
+    "mmj_gemm_bf16_allgather": ([P, P, I, P, L, L, I, P, L, I, I, I, I, P, P, L, P, L, I, I, I, P,
+                                 P, I, I, P, P], 1),
+    "mmj_gemm_bf16_reduce_scatter": ([P, L, P, L, I, P, L, L, I, I, I, I, I, I, P, P], 1),
+    "mmj_norm_fwd": ([P, P, P, P, P, P, P, P, I, I, F, I, P], 1),
+    "mmj_norm_bwd_parts": ([I], 0),
+    "mmj_norm_bwd": ([P, P, P, P, P, P, P, P, P, P, I, I, I, I, P], 2),
+    "mmj_act_fwd": ([P, P, L, I, F, P], 1),
+    "mmj_act_bwd": ([P, P, P, L, I, F, P], 1),
+    "mmj_swiglu_fwd": ([P, P, L, I, P], 1),
+    "mmj_swiglu_bwd": ([P, P, P, L, I, P], 1),
+    "mmj_rope": ([P, P, L, L, I, I, I, I, F, P], 1),
+    "mmj_embedding_fwd": ([P, P, P, P, L, I, I, I, P], 1),
+    "mmj_embedding_bwd": ([P, P, P, P, L, I, I, I, I, P], 2),
+    "mmj_colsum_splits": ([I], 0),
+    "mmj_colsum_bf16": ([P, L, P, P, P, I, I, I, P], 2),
+    "mmj_cast_f32_to_bf16": ([P, P, L, P], 1),
+    "mmj_cast_bf16_to_f32": ([P, P, L, P], 1),
+    "mmj_cast_f32_to_bf16_2d": ([P, L, P, L, L, I, P], 1),
+    "mmj_fill": ([P, c_double, L, I, P], 1),
+    "mmj_axpby_bf16": ([P, P, F, F, L, P], 1),
+    "mmj_transpose2d": ([P, P, I, I, I, P], 1),
+    "mmj_one_hot_f32": ([P, P, L, I, P], 1),
+    "mmj_where_f32": ([P, P, P, P, L, P], 1),
+    "mmj_dropout_f32": ([P, P, P, L, F, c_ulonglong, P], 1),
+    "mmj_dropout_bf16": ([P, P, L, F, c_ulonglong, P], 1),
+    "mmj_pack_nchw": ([P, P, I, I, I, I, I, P], 1),
+    "mmj_ce_fwd_bwd": ([P, L, I, P, P, L, F, L, I, P], 1),
+    "mmj_ce_vp_stats": ([P, L, I, L, P, P, P, P, L, P], 1),
+    "mmj_ce_vp_grad": ([P, L, I, L, P, P, P, L, F, P], 1),
+    "mmj_reduce_mean": ([P, P, L, F, P], 1),
+    "mmj_adamw": ([P, I, P, P, P, P, L, F, F, F, F, F, F, F, F, P, P, P], 1),
+    "mmj_sgd": ([P, I, P, P, P, L, F, F, F, F, P], 1),
+    "mmj_sqnorm_parts": ([], 0),
+    "mmj_sqnorm": ([P, I, L, P, P, P, I, P], 2),
+    "mmj_attn_fwd": ([P, L, I, P, L, I, P, L, I, P, L, I, P, I, I, I, I, I, F, I, P, P], 1),
+    "mmj_attn_bwd": ([P, L, I, P, L, I, P, L, I, P, L, I, P, L, I, P, P, P, L, I, P, L, I, P, L, I,
+                      I, I, I, I, I, F, I, P, P], 2),
+}
+
+_OPTIONAL = {}
+
+
+def lib_path() -> Path:
+    return _HERE / "libmomijo_b200.so"
+
+
+def host_lib_path() -> Path:
+    return _HERE / "libmomijo_host.so"
+
+
+def available() -> bool:
+    return lib_path().exists()
+
+
+def register(name, argtypes, kernels=1, restype=c_int):
+    """Register one more exported function (used by modules that own extra kernels)."""
+    _SIGS[name] = (argtypes, kernels)
+    _OPTIONAL[name] = restype
+    if _LIB is not None:
+        _bind(_LIB, name)
+
+
+def _bind(lib, name):
+    argtypes, _ = _SIGS[name]
+    try:
+        fn = getattr(lib, name)
+    except AttributeError:
+        return
+    fn.argtypes = argtypes
+    fn.restype = _OPTIONAL.get(name, c_int)
+
+
+def lib():
+    """The CUDA kernel library (built on demand when nvcc is present)."""
+    global _LIB
+    if _LIB is None:
+        if not lib_path().exists():
+            from . import build as _build
+
+            _build.build()
+        _LIB = ctypes.CDLL(str(lib_path()))
+        for name in _SIGS:
+            _bind(_LIB, name)
+        _LIB.mmj_mix64.argtypes = [c_ulonglong]
+        _LIB.mmj_mix64.restype = c_ulonglong
+    return _LIB
+
+
+def host():
+    """The host-side C++ runtime library."""
+    global _HOST
+    if _HOST is None:
+        if not host_lib_path().exists():
+            from . import build as _build
+
+            _build.build()
+        _HOST = ctypes.CDLL(str(host_lib_path()))
+    return _HOST
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def call(name: str, *args):
+    """Call an exported launcher, count its kernels and raise on a non-zero return code."""
+    global launches
+    fn = getattr(lib(), name)
+    rc = fn(*args)
+    launches += _SIGS[name][1]
+    if rc != 0:
+        raise NativeError(f"{name} failed with code {rc}")
+    return rc
+
+
+def ptr(t):
+    """Device (or host) pointer of a torch tensor, None -> NULL."""
+    return None if t is None else t.data_ptr()
+
+
+def current_stream():
+    import torch
+
+    return torch.cuda.current_stream().cuda_stream
+
+
+_STATUS = {}
+
+
+def status_tensor(device=None):
+    """Per-device int32[4] status word that kernels fill when a bounded wait runs out."""
+    import torch
+
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    t = _STATUS.get(dev)
+    if t is None:
+        t = torch.zeros(4, dtype=torch.int32, device=dev)
+        _STATUS[dev] = t
+    return t
+
+
+STATUS_NAMES = {
+    0: "ok", 1: "timeout: TMA bytes never landed", 2: "timeout: no free shared-memory stage",
+    3: "timeout: accumulator never completed", 4: "timeout: no free accumulator",
+    5: "timeout: flag never arrived", 6: "timeout: cross-GPU barrier", 7: "bad argument",
+}
+
+
+class DeviceTimeout(RuntimeError):
+    """A bounded device-side wait expired; the kernel returned and the context is usable."""
+
+
+def check_status(device=None, reset=True):
+    """Synchronise and raise DeviceTimeout if any kernel recorded an error since the last check."""
+    import torch
+
+    t = status_tensor(device)
+    torch.cuda.synchronize(t.device)
+    vals = t.tolist()
+    if vals[0] != 0:
+        if reset:
+            t.zero_()
+        raise DeviceTimeout(
+            f"{STATUS_NAMES.get(vals[0], vals[0])} (detail={vals[1]}, block={vals[2]}, thread={vals[3]})")
+    return vals

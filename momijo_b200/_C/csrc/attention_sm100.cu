@@ -1,0 +1,737 @@
+// Flash-style attention forward and backward on tcgen05 tensor cores (causal or full, MHA and
+// GQA, head_dim 64 or 128), with Q/K/V/dO tiles staged by TMA (128-byte swizzle) and every
+// matrix product accumulated in tensor memory.
+//
+// Forward, one CTA per (128 query rows, head, batch):
+//   S = Q K^T in TMEM -> softmax warps read one row per thread (no shuffles needed), keep the
+//   running max / sum, write P (bf16) into shared memory in the swizzled K-major layout ->
+//   O_part = P V in TMEM -> threads fold O_part into a register accumulator.
+// Backward, one CTA per (128 key rows, kv head, batch), looping over the query blocks (and,
+// for GQA, over the query heads of the group):
+//   S^T = K Q^T and dP^T = V dO^T (TMEM) -> threads rebuild P^T = exp(S^T*scale - lse) and
+//   dS^T = P^T o (dP^T - delta), write both to shared memory -> dV += P^T dO, dK += dS^T Q
+//   (TMEM, accumulated over the whole loop), dQ = dS K (TMEM, then fp32 red.add to global).
+// The tiles loaded once by TMA serve both as K-major and as MN-major operands: a 128-row tile
+// whose rows are 128 swizzled bytes is the canonical layout of either, read with a different
+// descriptor.
+//
+// The reference attention is a forward-only scalar loop that builds one score row at a time
+// (legacy/src/momijo/learn/nn/attention.mojo:122-161); softmax is the default normaliser here.
+#include "common.cuh"
+
+namespace mmj {
+
+constexpr int kAttnThreads = 192;
+constexpr int kPanelBytes = 128 * 128;  // 128 rows x 64 bf16
+
+struct AttnParams {
+  int B, T, Hq, Hkv;
+  int q_col0, k_col0, v_col0;  // column of head 0 inside the Q / K / V tensor maps
+  float scale;                 // softmax scale (1/sqrt(D))
+  int causal;
+  // forward outputs
+  __nv_bfloat16* O;
+  long long ldo;
+  float* lse;  // [B, Hq, T]
+  // backward
+  const float* delta;  // [B, Hq, T]
+  float* dQ;           // fp32 accumulator [B*T, ld_dq]
+  long long ld_dq;
+  __nv_bfloat16* dK;
+  __nv_bfloat16* dV;
+  long long ld_dk, ld_dv;
+  int dk_col0, dv_col0, dq_col0, o_col0;
+  int* status;
+};
+
+// K-major operand descriptor for k-step `k` (16 elements each) of a tile made of 64-column panels.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile_addr, int k) {
+  return make_smem_desc(tile_addr + (uint32_t)(k >> 2) * kPanelBytes + (uint32_t)(k & 3) * 32, 16,
+                        1024);
+}
+// MN-major operand descriptor: rows are the contraction index, 16 rows per k-step.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_addr, int k) {
+  return make_smem_desc(tile_addr + (uint32_t)k * 2048, kPanelBytes, 1024);
+}
+
+// Write 32 consecutive columns [col0, col0+32) of row r into a 128 x 128 bf16 tile stored as
+// two 64-column panels with the 128-byte swizzle (16-byte chunk index ^= row & 7).
+__device__ __forceinline__ void store_chunk_sw128(uint8_t* tile, int r, int col0,
+                                                  const float (&v)[32]) {
+  uint8_t* rowp = tile + (col0 >> 6) * kPanelBytes + r * 128;
+  const int cbase = (col0 & 63) >> 3;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 q;
+    q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
+    q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+    q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+    q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+    const int phys = (cbase + i) ^ (r & 7);
+    *reinterpret_cast<uint4*>(rowp + phys * 16) = q;
+  }
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c),
+               "f"(d)
+               : "memory");
+}
+
+// =============================================================================================
+// Forward
+// =============================================================================================
+template <int D>
+__global__ void __launch_bounds__(kAttnThreads, (D == 64) ? 2 : 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+  constexpr int NP = D / 64;             // 64-column panels per tile
+  constexpr int kTile = NP * kPanelBytes;
+  constexpr uint32_t kTmemCols = 256;
+  constexpr uint32_t kColS = 0, kColO = 128;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + kTile;      // 2 stages
+  uint8_t* sV = sK + 2 * kTile;  // 2 stages
+  uint8_t* sP = sV + 2 * kTile;  // 128 x 128 bf16
+
+  __shared__ __align__(8) uint64_t q_full, s_full, p_full, o_full;
+  __shared__ __align__(8) uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_qb = (p.T + 127) / 128;
+  const int qb = num_qb - 1 - (int)blockIdx.x;  // heaviest (latest) query blocks first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hkv = h / (p.Hq / p.Hkv);
+  const int q0 = qb * 128;
+  int kv_end = p.causal ? min(p.T, q0 + 128) : p.T;
+  const int nkv = (kv_end + 127) / 128;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&q_full, 1);
+    mbar_init(&s_full, 1);
+    mbar_init(&p_full, 4);
+    mbar_init(&o_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(&q_full, kTile);
+#pragma unroll
+      for (int pn = 0; pn < NP; ++pn)
+        tma_load_3d(sQ + pn * kPanelBytes, &tmQ, &q_full, p.q_col0 + h * D + pn * 64, q0, b);
+      for (int j = 0; j < nkv; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_empty[s], ph ^ 1, &abort_flag, p.status, kTimeoutEmpty, j)) break;
+        mbar_expect_tx(&k_full[s], kTile);
+#pragma unroll
+        for (int pn = 0; pn < NP; ++pn)
+          tma_load_3d(sK + s * kTile + pn * kPanelBytes, &tmK, &k_full[s],
+                      p.k_col0 + hkv * D + pn * 64, j * 128, b);
+        if (!mbar_wait(&v_empty[s], ph ^ 1, &abort_flag, p.status, kTimeoutEmpty, 100 + j)) break;
+        mbar_expect_tx(&v_full[s], kTile);
+#pragma unroll
+        for (int pn = 0; pn < NP; ++pn)
+          tma_load_3d(sV + s * kTile + pn * kPanelBytes, &tmV, &v_full[s],
+                      p.v_col0 + hkv * D + pn * 64, j * 128, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);
+      const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
+      bool ok = mbar_wait(&q_full, 0, &abort_flag, p.status, kTimeoutFull, -1);
+      auto issue_s = [&](int j) -> bool {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_full[s], ph, &abort_flag, p.status, kTimeoutFull, j)) return false;
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sK + s * kTile);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_bf16_ss(tmem_base + kColS, desc_kmajor(aQ, k), desc_kmajor(aK, k), idesc_s,
+                       k > 0 ? 1u : 0u);
+        umma_commit(&k_empty[s]);
+        umma_commit(&s_full);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < nkv && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&p_full, j & 1, &abort_flag, p.status, kTimeoutFlag, j)) break;
+        if (!mbar_wait(&v_full[s], ph, &abort_flag, p.status, kTimeoutFull, 100 + j)) break;
+        tc_fence_after();
+        const uint32_t aV = smem_u32(sV + s * kTile);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_bf16_ss(tmem_base + kColO, desc_kmajor(aP, k), desc_mnmajor(aV, k), idesc_o,
+                       k > 0 ? 1u : 0u);
+        umma_commit(&v_empty[s]);
+        umma_commit(&o_full);
+        if (j + 1 < nkv) ok = issue_s(j + 1);
+      }
+    }
+  } else {
+    // ---------------- softmax / output warps: one query row per thread ----------------
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int q_idx = q0 + row;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const float c = p.scale * 1.4426950408889634f;
+    float m = -INFINITY, l = 0.f;
+    float o[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) o[d] = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nkv; ++j) {
+      if (!mbar_wait(&s_full, j & 1, &abort_flag, p.status, kTimeoutTmemFull, j)) { ok = false; break; }
+      tc_fence_after();
+      const int kv0 = j * 128;
+      const bool need_mask = (p.causal && (kv0 + 127 > q0)) || (kv0 + 128 > p.T);
+      float mx = m;
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_lane + kColS + cc * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(r[i]);
+          if (need_mask) {
+            const int kv = kv0 + cc * 32 + i;
+            if (kv >= p.T || (p.causal && kv > q_idx)) s = -INFINITY;
+          }
+          mx = fmaxf(mx, s);
+        }
+      }
+      const float m_use = (mx == -INFINITY) ? 0.f : mx;
+      const float alpha = exp2f((m - m_use) * c);
+      const float mc = m_use * c;
+      float rowsum = 0.f;
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_lane + kColS + cc * 32, r);
+        tmem_ld_wait();
+        float pv[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(r[i]);
+          float e = exp2f(s * c - mc);
+          if (need_mask) {
+            const int kv = kv0 + cc * 32 + i;
+            if (kv >= p.T || (p.causal && kv > q_idx)) e = 0.f;
+          }
+          // the MMA consumes bf16 probabilities; sum the same rounded values
+          e = __bfloat162float(__float2bfloat16(e));
+          pv[i] = e;
+          rowsum += e;
+        }
+        store_chunk_sw128(sP, row, cc * 32, pv);
+      }
+      l = l * alpha + rowsum;
+      m = mx;
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full);
+#pragma unroll
+      for (int d = 0; d < D; ++d) o[d] *= alpha;
+      if (!mbar_wait(&o_full, j & 1, &abort_flag, p.status, kTimeoutTmemFull, 100 + j)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int cc = 0; cc < D / 32; ++cc) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_lane + kColO + cc * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[cc * 32 + i] += __uint_as_float(r[i]);
+      }
+    }
+    if (ok && q_idx < p.T) {
+      const float inv = (l > 0.f) ? 1.0f / l : 0.f;
+      __nv_bfloat16* dst = p.O + ((long long)b * p.T + q_idx) * p.ldo + p.o_col0 + h * D;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        uint4 q;
+        q.x = pack_bf16x2(o[8 * i + 0] * inv, o[8 * i + 1] * inv);
+        q.y = pack_bf16x2(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
+        q.z = pack_bf16x2(o[8 * i + 4] * inv, o[8 * i + 5] * inv);
+        q.w = pack_bf16x2(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
+        reinterpret_cast<uint4*>(dst)[i] = q;
+      }
+      if (p.lse != nullptr)
+        p.lse[((long long)b * p.Hq + h) * p.T + q_idx] =
+            (l > 0.f) ? (m * p.scale + __logf(l)) : -INFINITY;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// =============================================================================================
+// Backward
+// =============================================================================================
+// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; one warp per (row, head).
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ O, long long ldo, int o_col0,
+                                  const __nv_bfloat16* __restrict__ dO, long long lddo, int do_col0,
+                                  float* __restrict__ delta, int B, int T, int H, int D) {
+  const long long gw = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)B * T * H;
+  if (gw >= total) return;
+  const int h = (int)(gw % H);
+  const long long bt = gw / H;
+  const __nv_bfloat16* o = O + bt * ldo + o_col0 + h * D;
+  const __nv_bfloat16* g = dO + bt * lddo + do_col0 + h * D;
+  float s = 0.f;
+  for (int d = lane * 2; d < D; d += 64) {
+    float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + d));
+    float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(g + d));
+    s += a.x * c.x + a.y * c.y;
+  }
+  s = warp_sum(s);
+  if (lane == 0) {
+    const long long b = bt / T, t = bt - b * T;
+    delta[(b * H + h) * T + t] = s;
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                const AttnParams p) {
+  constexpr int NP = D / 64;
+  constexpr int kTile = NP * kPanelBytes;
+  constexpr int kStages = (D == 64) ? 2 : 1;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kColSt = 0, kColdPt = 128, kColdV = 256, kColdK = 256 + D;
+  constexpr bool kAliasdQ = (D == 128);
+  constexpr uint32_t kColdQ = kAliasdQ ? 0u : (256u + 2u * D);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~(uintptr_t)1023);
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + kTile;
+  uint8_t* sQ = sV + kTile;               // kStages
+  uint8_t* sdO = sQ + kStages * kTile;    // kStages
+  uint8_t* sPt = sdO + kStages * kTile;   // 128 x 128 bf16
+  uint8_t* sdSt = sPt + 2 * kPanelBytes;  // 128 x 128 bf16
+
+  __shared__ __align__(8) uint64_t kv_full, s_full, p_full, dq_full, dq_read;
+  __shared__ __align__(8) uint64_t qdo_full[2], qdo_empty[2];
+  __shared__ float s_lse[128], s_delta[128];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int jb = blockIdx.x;  // key block
+  const int hkv = blockIdx.y, b = blockIdx.z;
+  const int group = p.Hq / p.Hkv;
+  const int num_qb = (p.T + 127) / 128;
+  const int kv0 = jb * 128;
+  const int i_begin = p.causal ? jb : 0;
+  const int n_i = num_qb - i_begin;   // query blocks per head
+  const int n_iter = n_i * group;     // (query head in group) x (query block)
+
+  if (threadIdx.x == 0) {
+    mbar_init(&kv_full, 1);
+    mbar_init(&s_full, 1);
+    mbar_init(&p_full, 4);
+    mbar_init(&dq_full, 1);
+    mbar_init(&dq_read, 4);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&qdo_full[s], 1);
+      mbar_init(&qdo_empty[s], 1);
+    }
+    abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+    prefetch_tmap(&tmdO);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(&kv_full, 2 * kTile);
+#pragma unroll
+      for (int pn = 0; pn < NP; ++pn) {
+        tma_load_3d(sK + pn * kPanelBytes, &tmK, &kv_full, p.k_col0 + hkv * D + pn * 64, kv0, b);
+        tma_load_3d(sV + pn * kPanelBytes, &tmV, &kv_full, p.v_col0 + hkv * D + pn * 64, kv0, b);
+      }
+      for (int it = 0; it < n_iter; ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1;
+        const int hq = hkv * group + it / n_i;
+        const int qi = i_begin + it % n_i;
+        if (!mbar_wait(&qdo_empty[s], ph ^ 1, &abort_flag, p.status, kTimeoutEmpty, it)) break;
+        mbar_expect_tx(&qdo_full[s], 2 * kTile);
+#pragma unroll
+        for (int pn = 0; pn < NP; ++pn) {
+          tma_load_3d(sQ + s * kTile + pn * kPanelBytes, &tmQ, &qdo_full[s],
+                      p.q_col0 + hq * D + pn * 64, qi * 128, b);
+          tma_load_3d(sdO + s * kTile + pn * kPanelBytes, &tmdO, &qdo_full[s],
+                      p.o_col0 + hq * D + pn * 64, qi * 128, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_st = make_idesc_bf16(128, 128, 0, 0);  // K/V (K-major) x Q/dO (K-major)
+      const uint32_t idesc_dkv = make_idesc_bf16(128, D, 0, 1);   // P^T/dS^T (K-major) x dO/Q (MN)
+      const uint32_t idesc_dq = make_idesc_bf16(128, D, 1, 1);    // dS^T as MN-major A x K (MN)
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aPt = smem_u32(sPt),
+                     adSt = smem_u32(sdSt);
+      bool ok = mbar_wait(&kv_full, 0, &abort_flag, p.status, kTimeoutFull, -1);
+      auto issue_scores = [&](int it) -> bool {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1;
+        if (!mbar_wait(&qdo_full[s], ph, &abort_flag, p.status, kTimeoutFull, it)) return false;
+        if (kAliasdQ && it > 0) {
+          // dQ of the previous iteration shares the S^T columns: wait until it has been read
+          if (!mbar_wait(&dq_read, (it - 1) & 1, &abort_flag, p.status, kTimeoutFlag, it))
+            return false;
+        }
+        tc_fence_after();
+        const uint32_t aQ = smem_u32(sQ + s * kTile), adO = smem_u32(sdO + s * kTile);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_bf16_ss(tmem_base + kColSt, desc_kmajor(aK, k), desc_kmajor(aQ, k), idesc_st,
+                       k > 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_bf16_ss(tmem_base + kColdPt, desc_kmajor(aV, k), desc_kmajor(adO, k), idesc_st,
+                       k > 0 ? 1u : 0u);
+        umma_commit(&s_full);
+        return true;
+      };
+      if (ok && n_iter > 0) ok = issue_scores(0);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int s = it % kStages;
+        if (!mbar_wait(&p_full, it & 1, &abort_flag, p.status, kTimeoutFlag, it)) break;
+        tc_fence_after();
+        const uint32_t aQ = smem_u32(sQ + s * kTile), adO = smem_u32(sdO + s * kTile);
+        // dV += P^T dO ; dK += dS^T Q   (contraction over the 128 query rows)
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_bf16_ss(tmem_base + kColdV, desc_kmajor(aPt, k), desc_mnmajor(adO, k), idesc_dkv,
+                       (it > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_bf16_ss(tmem_base + kColdK, desc_kmajor(adSt, k), desc_mnmajor(aQ, k), idesc_dkv,
+                       (it > 0 || k > 0) ? 1u : 0u);
+        // dQ = dS K  (contraction over the 128 key rows; dS^T tile read as an MN-major A)
+        if (!kAliasdQ && it > 0) {
+          if (!mbar_wait(&dq_read, (it - 1) & 1, &abort_flag, p.status, kTimeoutFlag, it)) break;
+          tc_fence_after();
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_bf16_ss(tmem_base + kColdQ, desc_mnmajor(adSt, k), desc_mnmajor(aK, k), idesc_dq,
+                       k > 0 ? 1u : 0u);
+        umma_commit(&qdo_empty[s]);
+        umma_commit(&dq_full);
+        if (it + 1 < n_iter) ok = issue_scores(it + 1);
+      }
+    }
+  } else {
+    // ---------------- compute warps: one key row per thread ----------------
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;  // key row inside the block
+    const int kv_idx = kv0 + row;
+    const int ctid = threadIdx.x - 64;  // 0..127
+    const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const float c = p.scale * 1.4426950408889634f;
+    const float l2e = 1.4426950408889634f;
+    bool ok = true;
+    for (int it = 0; it < n_iter; ++it) {
+      const int hq = hkv * group + it / n_i;
+      const int qi = i_begin + it % n_i;
+      const int qbase = qi * 128;
+      // stage lse / delta of this query block (previous iteration's readers are past p_full)
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      {
+        const int q = qbase + ctid;
+        const long long off = ((long long)b * p.Hq + hq) * p.T + q;
+        s_lse[ctid] = (q < p.T) ? p.lse[off] * l2e : 0.f;
+        s_delta[ctid] = (q < p.T) ? p.delta[off] : 0.f;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!mbar_wait(&s_full, it & 1, &abort_flag, p.status, kTimeoutTmemFull, it)) { ok = false; break; }
+      tc_fence_after();
+      const bool need_mask = (p.causal && (qbase < kv0 + 127)) || (qbase + 128 > p.T) ||
+                             (kv0 + 128 > p.T);
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32(t_lane + kColSt + cc * 32, rs);
+        tmem_ld_32x32(t_lane + kColdPt + cc * 32, rp);
+        tmem_ld_wait();
+        float pt[32], ds[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int qc = cc * 32 + i;
+          float e = exp2f(__uint_as_float(rs[i]) * c - s_lse[qc]);
+          if (need_mask) {
+            const int q = qbase + qc;
+            if (q >= p.T || kv_idx >= p.T || (p.causal && kv_idx > q)) e = 0.f;
+          }
+          pt[i] = e;
+          ds[i] = e * (__uint_as_float(rp[i]) - s_delta[qc]);
+        }
+        store_chunk_sw128(sPt, row, cc * 32, pt);
+        store_chunk_sw128(sdSt, row, cc * 32, ds);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full);
+      // dQ of this iteration: rows are queries here (lane = query row)
+      if (!mbar_wait(&dq_full, it & 1, &abort_flag, p.status, kTimeoutTmemFull, 100 + it)) { ok = false; break; }
+      tc_fence_after();
+      {
+        const int q = qbase + row;
+        float* dst = p.dQ + ((long long)b * p.T + q) * p.ld_dq + p.dq_col0 + hq * D;
+#pragma unroll
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_lane + kColdQ + cc * 32, r);
+          tmem_ld_wait();
+          if (q < p.T) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              red_add_v4(dst + cc * 32 + 4 * i, __uint_as_float(r[4 * i + 0]) * p.scale,
+                         __uint_as_float(r[4 * i + 1]) * p.scale,
+                         __uint_as_float(r[4 * i + 2]) * p.scale,
+                         __uint_as_float(r[4 * i + 3]) * p.scale);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&dq_read);
+    }
+    // all MMAs into dV / dK have completed once the last dq_full has been seen
+    if (ok && kv_idx < p.T && n_iter > 0) {
+      __nv_bfloat16* dk = p.dK + ((long long)b * p.T + kv_idx) * p.ld_dk + p.dk_col0 + hkv * D;
+      __nv_bfloat16* dv = p.dV + ((long long)b * p.T + kv_idx) * p.ld_dv + p.dv_col0 + hkv * D;
+#pragma unroll
+      for (int cc = 0; cc < D / 32; ++cc) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_lane + kColdV + cc * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 q;
+          q.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+          q.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+          q.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+          q.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+          reinterpret_cast<uint4*>(dv + cc * 32)[i] = q;
+        }
+        tmem_ld_32x32(t_lane + kColdK + cc * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 q;
+          q.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]) * p.scale, __uint_as_float(r[8 * i + 1]) * p.scale);
+          q.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * p.scale, __uint_as_float(r[8 * i + 3]) * p.scale);
+          q.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * p.scale, __uint_as_float(r[8 * i + 5]) * p.scale);
+          q.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * p.scale, __uint_as_float(r[8 * i + 7]) * p.scale);
+          reinterpret_cast<uint4*>(dk + cc * 32)[i] = q;
+        }
+      }
+    } else if (ok && kv_idx < p.T && n_iter == 0) {
+      // no query block attends to this key block: gradients are zero
+      __nv_bfloat16* dk = p.dK + ((long long)b * p.T + kv_idx) * p.ld_dk + p.dk_col0 + hkv * D;
+      __nv_bfloat16* dv = p.dV + ((long long)b * p.T + kv_idx) * p.ld_dv + p.dv_col0 + hkv * D;
+      for (int i = 0; i < D / 8; ++i) {
+        reinterpret_cast<uint4*>(dk)[i] = make_uint4(0, 0, 0, 0);
+        reinterpret_cast<uint4*>(dv)[i] = make_uint4(0, 0, 0, 0);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn attn_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(f);
+  }
+  return fn;
+}
+
+// [B, T, cols] bf16 view with row stride ld: dims {cols, T, B}, box {64, 128, 1}.
+static int make_tmap_btc(CUtensorMap* out, const void* base, int B, int T, long long cols,
+                         long long ld) {
+  EncodeTiledFn fn = attn_encode_fn();
+  if (fn == nullptr) return -1;
+  if (ld % 8 || ((uintptr_t)base & 15)) return -2;
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)T, (cuuint64_t)B};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)ld * 2 * (cuuint64_t)T};
+  cuuint32_t box[3] = {64, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return (r == CUDA_SUCCESS) ? 0 : (int)r;
+}
+
+}  // namespace mmj
+
+using namespace mmj;
+
+// q/k/v: [B*T, ld*] bf16 matrices in which head h of Q starts at column q_col0 + h*D (same for
+// K/V with Hkv heads). O: [B*T, ldo] with head h at o_col0 + h*D. lse: [B, Hq, T] fp32.
+MMJ_API int mmj_attn_fwd(const void* q, long long ldq, int q_col0, const void* k, long long ldk,
+                         int k_col0, const void* v, long long ldv, int v_col0, void* O,
+                         long long ldo, int o_col0, float* lse, int B, int T, int Hq, int Hkv,
+                         int D, float scale, int causal, int* status, void* stream) {
+  if (D != 64 && D != 128) return -10;
+  if (Hkv <= 0 || Hq % Hkv) return -11;
+  if (ldo % 8 || o_col0 % 8) return -12;
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = make_tmap_btc(&tq, q, B, T, ldq, ldq))) return rc;
+  if ((rc = make_tmap_btc(&tk, k, B, T, ldk, ldk))) return rc;
+  if ((rc = make_tmap_btc(&tv, v, B, T, ldv, ldv))) return rc;
+  AttnParams p = {};
+  p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
+  p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
+  p.scale = scale; p.causal = causal;
+  p.O = (__nv_bfloat16*)O; p.ldo = ldo; p.o_col0 = o_col0;
+  p.lse = lse;
+  p.status = status;
+  dim3 grid((T + 127) / 128, Hq, B);
+  static bool attr64 = false, attr128 = false;
+  if (D == 64) {
+    const int smem = 5 * kPanelBytes + 2 * kPanelBytes + 1024;
+    if (!attr64) {
+      cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      attr64 = true;
+    }
+    attn_fwd_kernel<64><<<grid, kAttnThreads, smem, (cudaStream_t)stream>>>(tq, tk, tv, p);
+  } else {
+    const int smem = 5 * 2 * kPanelBytes + 2 * kPanelBytes + 1024;
+    if (!attr128) {
+      cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      attr128 = true;
+    }
+    attn_fwd_kernel<128><<<grid, kAttnThreads, smem, (cudaStream_t)stream>>>(tq, tk, tv, p);
+  }
+  return (int)cudaGetLastError();
+}
+
+// dQ_accum: fp32 [B*T, ld_dq], must be zero on entry (the kernel adds into it).
+// delta: fp32 scratch [B, Hq, T] (filled here). dK/dV: bf16 outputs.
+MMJ_API int mmj_attn_bwd(const void* q, long long ldq, int q_col0, const void* k, long long ldk,
+                         int k_col0, const void* v, long long ldv, int v_col0, const void* O,
+                         long long ldo, int o_col0, const void* dO, long long lddo, int do_col0,
+                         const float* lse, float* delta, float* dQ_accum, long long ld_dq,
+                         int dq_col0, void* dK, long long ld_dk, int dk_col0, void* dV,
+                         long long ld_dv, int dv_col0, int B, int T, int Hq, int Hkv, int D,
+                         float scale, int causal, int* status, void* stream) {
+  if (D != 64 && D != 128) return -10;
+  if (Hkv <= 0 || Hq % Hkv) return -11;
+  if (ld_dk % 8 || ld_dv % 8 || dk_col0 % 8 || dv_col0 % 8 || ld_dq % 4 || dq_col0 % 4) return -12;
+  CUtensorMap tq, tk, tv, tdo;
+  int rc;
+  if ((rc = make_tmap_btc(&tq, q, B, T, ldq, ldq))) return rc;
+  if ((rc = make_tmap_btc(&tk, k, B, T, ldk, ldk))) return rc;
+  if ((rc = make_tmap_btc(&tv, v, B, T, ldv, ldv))) return rc;
+  if ((rc = make_tmap_btc(&tdo, dO, B, T, lddo, lddo))) return rc;
+  {
+    const long long warps = (long long)B * T * Hq;
+    const int threads = 256;
+    const long long blocks = (warps * 32 + threads - 1) / threads;
+    attn_delta_kernel<<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)O, ldo, o_col0, (const __nv_bfloat16*)dO, lddo, do_col0, delta, B, T,
+        Hq, D);
+  }
+  AttnParams p = {};
+  p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
+  p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
+  p.o_col0 = do_col0;  // the dO map is addressed with o_col0 inside the kernel
+  p.scale = scale; p.causal = causal;
+  p.lse = const_cast<float*>(lse);
+  p.delta = delta;
+  p.dQ = dQ_accum; p.ld_dq = ld_dq; p.dq_col0 = dq_col0;
+  p.dK = (__nv_bfloat16*)dK; p.ld_dk = ld_dk; p.dk_col0 = dk_col0;
+  p.dV = (__nv_bfloat16*)dV; p.ld_dv = ld_dv; p.dv_col0 = dv_col0;
+  p.status = status;
+  dim3 grid((T + 127) / 128, Hkv, B);
+  static bool attr64 = false, attr128 = false;
+  if (D == 64) {
+    const int smem = (2 + 2 * 2) * kPanelBytes + 4 * kPanelBytes + 1024;
+    if (!attr64) {
+      cudaFuncSetAttribute(attn_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      attr64 = true;
+    }
+    attn_bwd_kernel<64><<<grid, kAttnThreads, smem, (cudaStream_t)stream>>>(tq, tk, tv, tdo, p);
+  } else {
+    const int smem = (2 + 2) * 2 * kPanelBytes + 4 * kPanelBytes + 1024;
+    if (!attr128) {
+      cudaFuncSetAttribute(attn_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      attr128 = true;
+    }
+    attn_bwd_kernel<128><<<grid, kAttnThreads, smem, (cudaStream_t)stream>>>(tq, tk, tv, tdo, p);
+  }
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,736 @@
+// bf16 GEMM on the 5th-generation tensor cores: D[M,N] = op(A) * op(B)^T-style products with
+// fp32 accumulation in tensor memory (TMEM), operands staged in shared memory by TMA with a
+// 128-byte swizzle, issued by one thread per CTA (tcgen05.mma), persistent over output tiles.
+//
+// Warp roles inside a 192-thread CTA:
+//   warp 0      TMA producer (one lane)
+//   warp 1      TMEM allocator + MMA issuer (one lane)
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (one output row per thread), apply the
+//               fused epilogue (bias / GELU / GELU' / residual / SiLU / scale / accumulate),
+//               store bf16 or fp32
+// Two accumulators (2 x 256 TMEM columns) let the epilogue of tile i overlap the main loop
+// of tile i+1.
+//
+// The same kernel also carries the fused communication paths:
+//   * gathered operand: extra CTAs pull peer shards over NVLink into local memory and publish
+//     per-tile flags that the TMA producer waits on (all-gather -> GEMM);
+//   * scattered result: the epilogue stores each row block straight into the memory of the
+//     rank that owns it (GEMM -> reduce-scatter, summed by the owner afterwards);
+//   * grouped mode for MoE experts (per-tile group table, tile count read from the device).
+//
+// This replaces the reference's scalar one-thread-per-output kernels
+// (legacy/src/momijo/tensor/gpu/runtime.mojo:52-119) and its CPU matmul loops
+// (legacy/src/momijo/tensor/broadcast.mojo:1612, legacy/src/momijo/tensor/indexing.mojo:2702).
+#include "common.cuh"
+#include "gemm_sm100.cuh"
+
+#include <mutex>
+
+namespace mmj {
+
+constexpr int kThreads = 192;
+constexpr int kAStageBytes = kGemmBM * kGemmBK * 2;  // 16 KiB
+constexpr int kTmemCols = 512;
+constexpr int kAccCols = 256;
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Bounded wait until *flag >= want. Returns false on timeout / abort.
+__device__ __forceinline__ bool wait_flag_ge(const int* flag, int want, bool sys_scope,
+                                             volatile int* abort_flag, int* status, int detail) {
+  int v = sys_scope ? ld_acquire_sys(flag) : ld_acquire_gpu(flag);
+  if (v >= want) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t it = 0;
+  while (true) {
+    v = sys_scope ? ld_acquire_sys(flag) : ld_acquire_gpu(flag);
+    if (v >= want) return true;
+    __nanosleep(64);
+    if (((++it) & 0x3f) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > MMJ_WAIT_BUDGET_NS) {
+        *abort_flag = 1;
+        report(status, kTimeoutFlag, detail);
+        return false;
+      }
+    }
+  }
+}
+
+struct TileCoord {
+  int m_tile, n_tile;
+};
+
+__device__ __forceinline__ TileCoord tile_of(int t, int num_m, int num_n, const GemmParams& p) {
+  // n fastest: concurrently running CTAs share A rows and sweep B (weights stay in L2).
+  int m_lin = t / num_n;
+  int n_lin = t - m_lin * num_n;
+  TileCoord c;
+  c.m_tile = m_lin + p.m_tile_rot;
+  if (c.m_tile >= num_m) c.m_tile -= num_m;
+  c.n_tile = n_lin + p.n_tile_rot;
+  if (c.n_tile >= num_n) c.n_tile -= num_n;
+  return c;
+}
+
+template <bool kOutF32>
+__device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const uint32_t (&acc)[32],
+                                                     int row, int col0) {
+  // One thread owns 32 consecutive columns [col0, col0+32) of output row `row`.
+  const int epi = p.epi;
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]);
+
+  const bool full = p.vec_ok && (col0 + 32 <= p.N);
+  if (epi & kEpiBias) {
+    const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0;
+    if (full) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 q = __ldg(reinterpret_cast<const uint4*>(b) + i);
+        float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z),
+               f3 = unpack_bf16x2(q.w);
+        v[8 * i + 0] += f0.x; v[8 * i + 1] += f0.y; v[8 * i + 2] += f1.x; v[8 * i + 3] += f1.y;
+        v[8 * i + 4] += f2.x; v[8 * i + 5] += f2.y; v[8 * i + 6] += f3.x; v[8 * i + 7] += f3.y;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < p.N) v[i] += __bfloat162float(b[i]);
+    }
+  }
+  if (epi & kEpiGelu) {
+    __nv_bfloat16* d2 = reinterpret_cast<__nv_bfloat16*>(p.D2) + (long long)row * p.ldd2 + col0;
+    if (full) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 q;
+        q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
+        q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+        q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+        q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+        reinterpret_cast<uint4*>(d2)[i] = q;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < p.N) d2[i] = __float2bfloat16(v[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+  }
+  if (epi & kEpiSilu) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.0f + __expf(-v[i]));
+  }
+  if (epi & (kEpiDGelu | kEpiAddAux | kEpiMulAux)) {
+    const __nv_bfloat16* a =
+        reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)row * p.ldaux + col0;
+    float x[32];
+    if (full) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 q = reinterpret_cast<const uint4*>(a)[i];
+        float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z),
+               f3 = unpack_bf16x2(q.w);
+        x[8 * i + 0] = f0.x; x[8 * i + 1] = f0.y; x[8 * i + 2] = f1.x; x[8 * i + 3] = f1.y;
+        x[8 * i + 4] = f2.x; x[8 * i + 5] = f2.y; x[8 * i + 6] = f3.x; x[8 * i + 7] = f3.y;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) x[i] = (col0 + i < p.N) ? __bfloat162float(a[i]) : 0.f;
+    }
+    if (epi & kEpiDGelu) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] *= gelu_tanh_grad(x[i]);
+    } else if (epi & kEpiMulAux) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] *= x[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] += x[i];
+    }
+  }
+  if (epi & kEpiRowScale) {
+    const float s = p.row_scale[row];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] *= s;
+  }
+
+  // Destination row: local, or the owner's staging slot for the reduce-scatter epilogue.
+  long long off;
+  void* base = p.D;
+  if (epi & kEpiScatterPeers) {
+    int owner = row / p.rows_per_rank;
+    int lrow = row - owner * p.rows_per_rank;
+    base = p.peer_D[owner];
+    off = (long long)p.rank * p.slot_stride + (long long)lrow * p.ldd + col0;
+  } else {
+    off = (long long)row * p.ldd + col0;
+  }
+
+  if (kOutF32) {
+    float* d = reinterpret_cast<float*>(base) + off;
+    if (full) {
+      if (epi & kEpiAccumulate) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float4 o = reinterpret_cast<float4*>(d)[i];
+          v[4 * i + 0] += o.x; v[4 * i + 1] += o.y; v[4 * i + 2] += o.z; v[4 * i + 3] += o.w;
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        reinterpret_cast<float4*>(d)[i] =
+            make_float4(v[4 * i + 0], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < p.N) d[i] = (epi & kEpiAccumulate) ? d[i] + v[i] : v[i];
+    }
+  } else {
+    __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(base) + off;
+    if (full) {
+      if (epi & kEpiAccumulate) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 q = reinterpret_cast<uint4*>(d)[i];
+          float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z),
+                 f3 = unpack_bf16x2(q.w);
+          v[8 * i + 0] += f0.x; v[8 * i + 1] += f0.y; v[8 * i + 2] += f1.x; v[8 * i + 3] += f1.y;
+          v[8 * i + 4] += f2.x; v[8 * i + 5] += f2.y; v[8 * i + 6] += f3.x; v[8 * i + 7] += f3.y;
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 q;
+        q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
+        q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+        q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+        q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+        reinterpret_cast<uint4*>(d)[i] = q;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < p.N) {
+          float o = (epi & kEpiAccumulate) ? __bfloat162float(d[i]) : 0.f;
+          d[i] = __float2bfloat16(v[i] + o);
+        }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
+                         const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte swizzled tiles need 1024-byte aligned bases.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[kGemmMaxStages];
+  __shared__ __align__(8) uint64_t empty_bar[kGemmMaxStages];
+  __shared__ __align__(8) uint64_t tfull_bar[2];
+  __shared__ __align__(8) uint64_t tempty_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int gemm_ctas = (p.gemm_ctas > 0) ? p.gemm_ctas : (int)gridDim.x;
+
+  // ---------------- communication CTAs: pull peer shards, publish per-tile flags ----------
+  // One thread per CTA drives bulk asynchronous copies (peer memory -> shared memory ->
+  // local memory) through a ring of 32 KiB buffers, so that ~190 KiB per CTA stay in flight
+  // over NVLink without occupying the other threads. No multicast is involved.
+  if ((int)blockIdx.x >= gemm_ctas) {
+    constexpr int kNBuf = 6;
+    constexpr int kBufBytes = 32 * 1024;
+    if (threadIdx.x == 0) {
+      abort_flag = 0;
+      for (int b = 0; b < kNBuf; ++b) mbar_init(&full_bar[b], 1);
+      mbar_fence_init();
+      const int n_comm = (int)gridDim.x - gemm_ctas;
+      const int cid = (int)blockIdx.x - gemm_ctas;
+      const int tiles_per_shard = (int)((p.shard_bytes + p.tile_bytes - 1) / p.tile_bytes);
+      const int total = p.world * tiles_per_shard;
+      uint32_t issued = 0, drained = 0;  // chunk counters over the ring
+      bool ok = true;
+      for (int i = cid; i < total && ok; i += n_comm) {
+        const int hop = i / tiles_per_shard;
+        const int tt = i - hop * tiles_per_shard;
+        int sr = p.rank + hop;
+        if (sr >= p.world) sr -= p.world;
+        if (p.peer_ready != nullptr && sr != p.rank)
+          ok = wait_flag_ge(p.peer_ready + sr, p.ready_epoch, true, &abort_flag, p.status, 100 + sr);
+        if (!ok) break;
+        const long long off = (long long)tt * p.tile_bytes;
+        long long nbytes = p.shard_bytes - off;
+        if (nbytes > p.tile_bytes) nbytes = p.tile_bytes;
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(p.peer_src[sr]) + off;
+        uint8_t* dst =
+            reinterpret_cast<uint8_t*>(p.gather_dst) + (long long)sr * p.shard_bytes + off;
+        if (src != dst) {
+          const int nchunks = (int)((nbytes + kBufBytes - 1) / kBufBytes);
+          int next_load = 0;
+          for (int c = 0; c < nchunks && ok; ++c) {
+            // keep up to kNBuf loads in flight
+            while (next_load < nchunks && issued - drained < (uint32_t)kNBuf) {
+              const int b = issued % kNBuf;
+              const long long co = (long long)next_load * kBufBytes;
+              const uint32_t sz = (uint32_t)((nbytes - co < kBufBytes) ? (nbytes - co) : kBufBytes);
+              mbar_expect_tx(&full_bar[b], sz);
+              asm volatile(
+                  "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                  ::"r"(smem_u32(smem + (size_t)b * kBufBytes)), "l"(src + co), "r"(sz),
+                  "r"(smem_u32(&full_bar[b]))
+                  : "memory");
+              ++issued;
+              ++next_load;
+            }
+            const int b = drained % kNBuf;
+            const uint32_t par = (drained / kNBuf) & 1u;
+            if (!mbar_wait(&full_bar[b], par, &abort_flag, p.status, kTimeoutFull, 1000 + c)) {
+              ok = false;
+              break;
+            }
+            const long long co = (long long)c * kBufBytes;
+            const uint32_t sz = (uint32_t)((nbytes - co < kBufBytes) ? (nbytes - co) : kBufBytes);
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst + co),
+                         "r"(smem_u32(smem + (size_t)b * kBufBytes)), "r"(sz)
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            // the buffer may be refilled once the store has read it
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            ++drained;
+          }
+          // all bytes of this piece written before its flag is published
+          asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        }
+        if (!ok) break;
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __threadfence();
+        st_release_gpu(p.flags_rw + sr * tiles_per_shard + tt, p.ready_epoch);
+      }
+      // never leave with loads in flight into this CTA's shared memory
+      while (drained < issued) {
+        const int b = drained % kNBuf;
+        const uint32_t par = (drained / kNBuf) & 1u;
+        int local_abort = 0;
+        if (!mbar_wait(&full_bar[b], par, &local_abort, p.status, kTimeoutFull, 2000)) break;
+        ++drained;
+      }
+    }
+    return;
+  }
+
+  // ---------------- GEMM CTAs --------------------------------------------------------------
+  const int bn = p.bn;
+  const int stages = p.stages;
+  const int b_stage_bytes = bn * kGemmBK * 2;
+  const int stage_bytes = kAStageBytes + b_stage_bytes;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  const int num_m = (p.num_m_tiles_dev != nullptr) ? *p.num_m_tiles_dev
+                                                   : (p.M + kGemmBM - 1) / kGemmBM;
+  const int num_n = (p.N + bn - 1) / bn;
+  const int num_k = (p.K + kGemmBK - 1) / kGemmBK;
+  const int num_tiles = num_m * num_n;
+
+  if (num_k > 0) {
+    if (warp == 0) {
+      // ======================= TMA producer =======================
+      if (lane == 0) {
+        int s = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gemm_ctas) {
+          const TileCoord tc = tile_of(t, num_m, num_n, p);
+          const int m0 = tc.m_tile * kGemmBM;
+          const int n0 = tc.n_tile * bn;
+          const int g = (p.tile_group != nullptr) ? p.tile_group[tc.m_tile] : 0;
+          const int b_row_base = g * p.b_group_rows;
+          if (p.flag_mode == 1) {
+            ok = wait_flag_ge(p.ready_flags + tc.m_tile, p.ready_epoch, false, &abort_flag,
+                              p.status, tc.m_tile);
+            asm volatile("fence.proxy.async;" ::: "memory");
+          } else if (p.flag_mode == 2) {
+            ok = wait_flag_ge(p.ready_flags + tc.n_tile, p.ready_epoch, false, &abort_flag,
+                              p.status, tc.n_tile);
+            asm volatile("fence.proxy.async;" ::: "memory");
+          }
+          if (!ok) break;
+          for (int kb = 0; kb < num_k; ++kb) {
+            if (!mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, p.status, kTimeoutEmpty, kb)) {
+              ok = false;
+              break;
+            }
+            uint8_t* sA = smem + (size_t)s * stage_bytes;
+            uint8_t* sB = sA + kAStageBytes;
+            mbar_expect_tx(&full_bar[s], (uint32_t)stage_bytes);
+            const int k0 = kb * kGemmBK;
+            if (!p.a_mn) {
+              tma_load_2d(sA, &tmA, &full_bar[s], k0, m0);
+            } else {
+              tma_load_2d(sA, &tmA, &full_bar[s], m0, k0);
+              tma_load_2d(sA + 8192, &tmA, &full_bar[s], m0 + 64, k0);
+            }
+            if (!p.b_mn) {
+              tma_load_2d(sB, &tmB, &full_bar[s], k0, b_row_base + n0);
+            } else {
+              for (int j = 0; j < bn / 64; ++j)
+                tma_load_2d(sB + j * 8192, &tmB, &full_bar[s], n0 + 64 * j, b_row_base + k0);
+            }
+            if (++s == stages) { s = 0; ph ^= 1; }
+          }
+        }
+      }
+    } else if (warp == 1) {
+      // ======================= MMA issuer =======================
+      if (lane == 0) {
+        const uint32_t idesc = make_idesc_bf16(kGemmBM, bn, p.a_mn, p.b_mn);
+        const uint32_t a_lbo = p.a_mn ? 8192u : 16u;
+        const uint32_t b_lbo = p.b_mn ? 8192u : 16u;
+        const uint32_t a_kstep = p.a_mn ? 2048u : 32u;
+        const uint32_t b_kstep = p.b_mn ? 2048u : 32u;
+        int s = 0;
+        uint32_t ph = 0;
+        int acc = 0;
+        uint32_t acc_ph = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gemm_ctas) {
+          if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, &abort_flag, p.status, kTimeoutTmemEmpty,
+                         t)) {
+            break;
+          }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kAccCols);
+          for (int kb = 0; kb < num_k; ++kb) {
+            if (!mbar_wait(&full_bar[s], ph, &abort_flag, p.status, kTimeoutFull, kb)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t a_base = smem_u32(smem + (size_t)s * stage_bytes);
+            const uint32_t b_base = a_base + kAStageBytes;
+#pragma unroll
+            for (int k = 0; k < kGemmBK / 16; ++k) {
+              const uint64_t da = make_smem_desc(a_base + k * a_kstep, a_lbo, 1024);
+              const uint64_t db = make_smem_desc(b_base + k * b_kstep, b_lbo, 1024);
+              umma_bf16_ss(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            }
+            umma_commit(&empty_bar[s]);  // frees the smem stage once these MMAs retire
+            if (++s == stages) { s = 0; ph ^= 1; }
+          }
+          if (!ok) break;
+          umma_commit(&tfull_bar[acc]);  // accumulator complete
+          if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+        }
+      }
+    } else {
+      // ======================= epilogue warps =======================
+      const int quad = warp & 3;  // TMEM lane quadrant this warp may access
+      int acc = 0;
+      uint32_t acc_ph = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gemm_ctas) {
+        const TileCoord tc = tile_of(t, num_m, num_n, p);
+        const int m0 = tc.m_tile * kGemmBM;
+        const int n0 = tc.n_tile * bn;
+        if (!mbar_wait(&tfull_bar[acc], acc_ph, &abort_flag, p.status, kTimeoutTmemFull, t)) break;
+        tc_fence_after();
+        const int row = m0 + quad * 32 + lane;
+        const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kAccCols);
+        for (int c = 0; c < bn / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + (uint32_t)(c * 32), r);
+          tmem_ld_wait();
+          const int col0 = n0 + c * 32;
+          if (row < p.M && col0 < p.N) {
+            if (p.epi & kEpiOutF32)
+              epilogue_store_chunk<true>(p, r, row, col0);
+            else
+              epilogue_store_chunk<false>(p, r, row, col0);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+        if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(f);
+  });
+  return fn;
+}
+
+// 2-D bf16 tensor map: `inner` contiguous elements, `outer` rows `row_stride_elems` apart.
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
+                      uint64_t row_stride_elems, uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_elems * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return (r == CUDA_SUCCESS) ? 0 : (int)r;
+}
+
+static int g_sm_count = 0;
+static int sm_count() {
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (g_sm_count <= 0) g_sm_count = 148;
+  }
+  return g_sm_count;
+}
+
+static bool g_attr_set = false;
+
+int launch_gemm(GemmParams& p, const void* A, long long lda, long long a_rows, const void* B,
+                long long ldb, long long b_rows, int comm_ctas, cudaStream_t stream) {
+  if (p.M <= 0 || p.N <= 0) return 0;
+  if ((lda % 8) != 0 || (ldb % 8) != 0) return -2;
+  {
+    // 16-byte vector accesses in the epilogue need aligned bases and leading dimensions.
+    const int out_elems = (p.epi & kEpiOutF32) ? 4 : 8;
+    bool ok = (p.ldd % out_elems == 0) && (((uintptr_t)p.D & 15) == 0);
+    if (p.epi & kEpiScatterPeers)
+      for (int r = 0; r < p.world; ++r) ok = ok && (((uintptr_t)p.peer_D[r] & 15) == 0);
+    if (p.epi & kEpiScatterPeers) ok = ok && (p.slot_stride % out_elems == 0);
+    if (p.epi & kEpiBias) ok = ok && (((uintptr_t)p.bias & 15) == 0);
+    if (p.epi & kEpiGelu) ok = ok && (p.ldd2 % 8 == 0) && (((uintptr_t)p.D2 & 15) == 0);
+    if (p.epi & (kEpiDGelu | kEpiAddAux | kEpiMulAux))
+      ok = ok && (p.ldaux % 8 == 0) && (((uintptr_t)p.aux & 15) == 0);
+    p.vec_ok = ok ? 1 : 0;
+  }
+  if (((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -3;
+  if (p.bn != 64 && p.bn != 128 && p.bn != 256) return -4;
+  CUtensorMap tmA, tmB;
+  int rc;
+  // A: K-major [a_rows(M), K] or MN-major [a_rows(K), M]
+  if (!p.a_mn)
+    rc = make_tmap_bf16_2d(&tmA, A, (uint64_t)p.K, (uint64_t)a_rows, (uint64_t)lda, 64, 128);
+  else
+    rc = make_tmap_bf16_2d(&tmA, A, (uint64_t)p.M, (uint64_t)a_rows, (uint64_t)lda, 64, 64);
+  if (rc) return rc;
+  if (!p.b_mn)
+    rc = make_tmap_bf16_2d(&tmB, B, (uint64_t)p.K, (uint64_t)b_rows, (uint64_t)ldb, 64,
+                           (uint32_t)p.bn);
+  else
+    rc = make_tmap_bf16_2d(&tmB, B, (uint64_t)p.N, (uint64_t)b_rows, (uint64_t)ldb, 64, 64);
+  if (rc) return rc;
+
+  const int stage_bytes = kAStageBytes + p.bn * kGemmBK * 2;
+  int stages = (200 * 1024) / stage_bytes;
+  if (stages > kGemmMaxStages) stages = kGemmMaxStages;
+  p.stages = stages;
+  const int smem_bytes = stages * stage_bytes + 1024;
+  if (!g_attr_set) {
+    cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         220 * 1024);
+    g_attr_set = true;
+  }
+  const int num_m = (p.M + kGemmBM - 1) / kGemmBM;
+  const int num_n = (p.N + p.bn - 1) / p.bn;
+  long long tiles = (long long)num_m * num_n;
+  int gemm_ctas = sm_count() - comm_ctas;
+  if (gemm_ctas < 1) gemm_ctas = 1;
+  if (tiles < gemm_ctas) gemm_ctas = (int)tiles;
+  p.gemm_ctas = gemm_ctas;
+  gemm_bf16_tcgen05_kernel<<<gemm_ctas + comm_ctas, kThreads, smem_bytes, stream>>>(tmA, tmB, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace mmj
+
+using namespace mmj;
+
+// Plain / fused-epilogue GEMM.
+//   a_mn = 0: A is [M, K] row-major (lda);  a_mn = 1: A is [K, M] row-major (lda)
+//   b_mn = 0: B is [N, K] row-major (ldb);  b_mn = 1: B is [K, N] row-major (ldb)
+//   D[M, N] (ldd) = A_op * B_op^T-style contraction over K, then the epilogue flags in `epi`.
+MMJ_API int mmj_gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long ldb,
+                          int b_mn, void* D, long long ldd, int M, int N, int K, int epi,
+                          const void* bias, const void* aux, long long ldaux, void* D2,
+                          long long ldd2, const float* row_scale, int bn, int* status,
+                          void* stream) {
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K;
+  p.a_mn = a_mn; p.b_mn = b_mn;
+  p.bn = bn;
+  p.epi = epi;
+  p.D = D; p.ldd = ldd;
+  p.D2 = D2; p.ldd2 = ldd2;
+  p.bias = bias; p.aux = aux; p.ldaux = ldaux;
+  p.row_scale = row_scale;
+  p.status = status;
+  return launch_gemm(p, A, lda, a_mn ? K : M, B, ldb, b_mn ? K : N, 0, (cudaStream_t)stream);
+}
+
+// Grouped GEMM for MoE experts: rows of A are sorted by expert and every expert's segment
+// starts on a 128-row boundary. tile_group[m_tile] names the expert of each row tile;
+// num_m_tiles_dev (device int) is the number of row tiles in use. B holds `groups` weight
+// matrices stacked along its row dimension, b_group_rows rows each.
+MMJ_API int mmj_gemm_bf16_grouped(const void* A, long long lda, const void* B, long long ldb,
+                                  int b_mn, int groups, int b_group_rows, void* D, long long ldd,
+                                  int M_cap, int N, int K, int epi, const void* aux,
+                                  long long ldaux, const float* row_scale, const int* tile_group,
+                                  const int* num_m_tiles_dev, int bn, int* status, void* stream) {
+  GemmParams p = {};
+  p.M = M_cap; p.N = N; p.K = K;
+  p.a_mn = 0; p.b_mn = b_mn;
+  p.bn = bn;
+  p.epi = epi;
+  p.D = D; p.ldd = ldd;
+  p.aux = aux; p.ldaux = ldaux;
+  p.row_scale = row_scale;
+  p.status = status;
+  p.tile_group = tile_group;
+  p.b_group_rows = b_group_rows;
+  p.num_m_tiles_dev = num_m_tiles_dev;
+  return launch_gemm(p, A, lda, M_cap, B, ldb, (long long)groups * b_group_rows, 0,
+                     (cudaStream_t)stream);
+}
+
+// All-gather fused into the GEMM. One operand (A when gather_a != 0, else B) is the
+// concatenation along rows of `world` equal shards that live on different GPUs.
+// `gathered` is the local full-size buffer (the GEMM reads it through TMA); comm CTAs copy
+// each peer shard from peer_src[r] into it in `granule_rows`-row pieces (128 for A, bn for B)
+// and publish flags[piece] = epoch, which the TMA producer waits on (bounded). peer_ready
+// (may be null) is the local signal pad where rank r stores `epoch` once its shard is final.
+MMJ_API int mmj_gemm_bf16_allgather(const void* const* peer_src, void* gathered, int gather_a,
+                                    const void* other, long long ld_gathered, long long ld_other,
+                                    int other_mn, void* D, long long ldd, int M, int N, int K,
+                                    int epi, const void* bias, const void* aux, long long ldaux,
+                                    void* D2, long long ldd2, int bn, int world, int rank,
+                                    int* flags, const int* peer_ready, int epoch, int comm_ctas,
+                                    int* status, void* stream) {
+  if (world < 1 || world > kMaxPeers) return -5;
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K;
+  p.bn = bn;
+  p.epi = epi;
+  p.D = D; p.ldd = ldd;
+  p.D2 = D2; p.ldd2 = ldd2;
+  p.bias = bias; p.aux = aux; p.ldaux = ldaux;
+  p.status = status;
+  p.world = world; p.rank = rank;
+  p.ready_flags = flags; p.flags_rw = flags;
+  p.peer_ready = peer_ready;
+  p.ready_epoch = epoch;
+  p.gather_dst = gathered;
+  for (int r = 0; r < world; ++r) p.peer_src[r] = peer_src[r];
+  const long long rows = gather_a ? M : N;
+  if (rows % world) return -6;
+  const long long shard_rows = rows / world;
+  const int granule = gather_a ? kGemmBM : bn;
+  if (shard_rows % granule) return -7;
+  p.shard_bytes = shard_rows * ld_gathered * 2;
+  p.tile_bytes = (long long)granule * ld_gathered * 2;
+  if (gather_a) {
+    p.flag_mode = 1;
+    p.a_mn = 0; p.b_mn = other_mn;
+    p.m_tile_rot = (int)(rank * (shard_rows / granule));
+    return launch_gemm(p, gathered, ld_gathered, M, other, ld_other, other_mn ? K : N, comm_ctas,
+                       (cudaStream_t)stream);
+  } else {
+    p.flag_mode = 2;
+    p.a_mn = other_mn; p.b_mn = 0;
+    p.n_tile_rot = (int)(rank * (shard_rows / granule));
+    return launch_gemm(p, other, ld_other, other_mn ? K : M, gathered, ld_gathered, N, comm_ctas,
+                       (cudaStream_t)stream);
+  }
+}
+
+// GEMM whose result is reduce-scattered over rows: rank `rank` computes a partial D[M, N];
+// rows [r*M/world, (r+1)*M/world) are stored into rank r's staging buffer peer_stage[r] at
+// slot `rank` (slot_stride elements apart). Each owner later sums its `world` slots
+// (mmj_reduce_slots_bf16). Rows are visited starting after the local block so that ranks
+// write to different owners at the same time.
+MMJ_API int mmj_gemm_bf16_reduce_scatter(const void* A, long long lda, const void* B,
+                                         long long ldb, int b_mn, void* const* peer_stage,
+                                         long long ldd, long long slot_stride, int M, int N, int K,
+                                         int bn, int world, int rank, int* status, void* stream) {
+  if (world < 1 || world > kMaxPeers) return -5;
+  if (M % world) return -6;
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K;
+  p.a_mn = 0; p.b_mn = b_mn;
+  p.bn = bn;
+  p.epi = kEpiScatterPeers;
+  p.ldd = ldd;
+  p.status = status;
+  p.world = world; p.rank = rank;
+  p.rows_per_rank = M / world;
+  p.slot_stride = slot_stride;
+  for (int r = 0; r < world; ++r) p.peer_D[r] = peer_stage[r];
+  p.D = peer_stage[rank];
+  const int num_m = (M + kGemmBM - 1) / kGemmBM;
+  p.m_tile_rot = (int)(((long long)(rank + 1) % world) * p.rows_per_rank / kGemmBM) % num_m;
+  return launch_gemm(p, A, lda, M, B, ldb, b_mn ? K : N, 0, (cudaStream_t)stream);
+}

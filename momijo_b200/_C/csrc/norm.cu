@@ -1,0 +1,287 @@
+// LayerNorm and RMSNorm forward/backward for bf16 activations (fp32 statistics).
+//
+// One CTA per row; each thread keeps up to kVPT 16-byte vectors (8 bf16) of the row in
+// registers, so a row is read from HBM exactly once per pass. The forward can fuse the
+// residual add that precedes the norm (writes the updated residual stream too). The backward
+// is persistent over rows: each CTA keeps its partial dgamma/dbeta in registers, writes one
+// partial row per CTA into a scratch buffer, and a second kernel folds the partials.
+//
+// Replaces the reference's LayerNorm1d, which forms mean/variance with matmul-by-ones on the
+// CPU (legacy/src/momijo/learn/nn/layernorm.mojo:27-37). RMSNorm has no counterpart in the
+// reference; it follows the same layer style.
+#include "common.cuh"
+
+namespace mmj {
+
+constexpr int kNormMaxVPT = 2;
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  uint4 q = *reinterpret_cast<const uint4*>(p);
+  float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y), c = unpack_bf16x2(q.z),
+         d = unpack_bf16x2(q.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  uint4 q;
+  q.x = pack_bf16x2(f[0], f[1]);
+  q.y = pack_bf16x2(f[2], f[3]);
+  q.z = pack_bf16x2(f[4], f[5]);
+  q.w = pack_bf16x2(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = q;
+}
+
+// Block-wide sum of two values. `red` holds 2*32 floats.
+__device__ __forceinline__ float2 block_sum2(float a, float b, float* red) {
+  a = warp_sum(a);
+  b = warp_sum(b);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) { red[warp] = a; red[32 + warp] = b; }
+  __syncthreads();
+  float x = (lane < nw) ? red[lane] : 0.f;
+  float y = (lane < nw) ? red[32 + lane] : 0.f;
+  x = warp_sum(x);
+  y = warp_sum(y);
+  return make_float2(x, y);
+}
+
+// mode: 0 = LayerNorm (gamma, beta), 1 = RMSNorm (gamma only)
+template <int VPT>
+__global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                const __nv_bfloat16* __restrict__ res,  // optional residual in
+                                __nv_bfloat16* __restrict__ res_out,    // optional x + res out
+                                const __nv_bfloat16* __restrict__ gamma,
+                                const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ y,
+                                float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows,
+                                int C, float eps, int mode) {
+  __shared__ float red[64];
+  const int nvec = C >> 3;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    float v[VPT][8];
+    float s = 0.f, ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int vi = threadIdx.x + i * blockDim.x;
+      if (vi < nvec) {
+        load8(x + (size_t)row * C + vi * 8, v[i]);
+        if (res != nullptr) {
+          float r[8];
+          load8(res + (size_t)row * C + vi * 8, r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] += r[j];
+          // the normalised input is the bf16-rounded residual stream
+          if (res_out != nullptr) {
+            store8(res_out + (size_t)row * C + vi * 8, v[i]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[i][j] = __bfloat162float(__float2bfloat16(v[i][j]));
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { s += v[i][j]; ss += v[i][j] * v[i][j]; }
+      }
+    }
+    float2 t = block_sum2(s, ss, red);
+    float mean = 0.f, rstd;
+    if (mode == 0) {
+      mean = t.x / C;
+      // second pass over registers for a numerically safe variance
+      float d2 = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int vi = threadIdx.x + i * blockDim.x;
+        if (vi < nvec) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { float d = v[i][j] - mean; d2 += d * d; }
+        }
+      }
+      float2 t2 = block_sum2(d2, 0.f, red);
+      rstd = rsqrtf(t2.x / C + eps);
+    } else {
+      rstd = rsqrtf(t.y / C + eps);
+    }
+    if (threadIdx.x == 0) {
+      if (mean_out != nullptr) mean_out[row] = mean;
+      rstd_out[row] = rstd;
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int vi = threadIdx.x + i * blockDim.x;
+      if (vi < nvec) {
+        float g[8], o[8];
+        load8(gamma + vi * 8, g);
+        if (mode == 0 && beta != nullptr) {
+          float b[8];
+          load8(beta + vi * 8, b);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * g[j] + b[j];
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * g[j];
+        }
+        store8(y + (size_t)row * C + vi * 8, o);
+      }
+    }
+  }
+}
+
+// dx = rstd * (dy*g - mean_c(dy*g) - xhat * mean_c(dy*g*xhat))        (LayerNorm)
+// dx = rstd * (dy*g - xhat * mean_c(dy*g*xhat))                          (RMSNorm)
+// Optional dres_in is added to dx (gradient arriving through the residual branch).
+template <int VPT>
+__global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                const __nv_bfloat16* __restrict__ x,
+                                const __nv_bfloat16* __restrict__ gamma,
+                                const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                                const __nv_bfloat16* __restrict__ dres_in,
+                                __nv_bfloat16* __restrict__ dx, float* __restrict__ partial_dg,
+                                float* __restrict__ partial_db, int rows, int C, int mode) {
+  __shared__ float red[64];
+  const int nvec = C >> 3;
+  float dg[VPT][8], db[VPT][8], g[VPT][8];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int vi = threadIdx.x + i * blockDim.x;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { dg[i][j] = 0.f; db[i][j] = 0.f; g[i][j] = 0.f; }
+    if (vi < nvec) load8(gamma + vi * 8, g[i]);
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float mean = (mode == 0) ? mean_in[row] : 0.f;
+    const float rstd = rstd_in[row];
+    float xh[VPT][8], gy[VPT][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int vi = threadIdx.x + i * blockDim.x;
+      if (vi < nvec) {
+        float xv[8], dyv[8];
+        load8(x + (size_t)row * C + vi * 8, xv);
+        load8(dy + (size_t)row * C + vi * 8, dyv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = (xv[j] - mean) * rstd;
+          gy[i][j] = dyv[j] * g[i][j];
+          s1 += gy[i][j];
+          s2 += gy[i][j] * xh[i][j];
+          dg[i][j] += dyv[j] * xh[i][j];
+          db[i][j] += dyv[j];
+        }
+      }
+    }
+    float2 t = block_sum2(s1, s2, red);
+    const float m1 = (mode == 0) ? t.x / C : 0.f;
+    const float m2 = t.y / C;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int vi = threadIdx.x + i * blockDim.x;
+      if (vi < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (gy[i][j] - m1 - xh[i][j] * m2);
+        if (dres_in != nullptr) {
+          float r[8];
+          load8(dres_in + (size_t)row * C + vi * 8, r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += r[j];
+        }
+        store8(dx + (size_t)row * C + vi * 8, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int vi = threadIdx.x + i * blockDim.x;
+    if (vi < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        partial_dg[(size_t)blockIdx.x * C + vi * 8 + j] = dg[i][j];
+        if (partial_db != nullptr) partial_db[(size_t)blockIdx.x * C + vi * 8 + j] = db[i][j];
+      }
+    }
+  }
+}
+
+// Fold `nparts` partial rows into bf16 gradients (optionally accumulating into existing ones).
+__global__ void norm_bwd_finalize_kernel(const float* __restrict__ partial_dg,
+                                         const float* __restrict__ partial_db,
+                                         __nv_bfloat16* __restrict__ dgamma,
+                                         __nv_bfloat16* __restrict__ dbeta, int nparts, int C,
+                                         int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float a = 0.f, b = 0.f;
+  for (int p = 0; p < nparts; ++p) {
+    a += partial_dg[(size_t)p * C + c];
+    if (partial_db != nullptr) b += partial_db[(size_t)p * C + c];
+  }
+  if (accumulate) {
+    a += __bfloat162float(dgamma[c]);
+    if (dbeta != nullptr) b += __bfloat162float(dbeta[c]);
+  }
+  dgamma[c] = __float2bfloat16(a);
+  if (dbeta != nullptr && partial_db != nullptr) dbeta[c] = __float2bfloat16(b);
+}
+
+static inline int norm_threads(int C, int vpt) {
+  int nvec = C / 8;
+  int t = (nvec + vpt - 1) / vpt;
+  t = ((t + 31) / 32) * 32;
+  return t < 32 ? 32 : t;
+}
+
+}  // namespace mmj
+
+using namespace mmj;
+
+// rows x C, C % 8 == 0, C <= 16384. mode 0 LayerNorm, 1 RMSNorm.
+MMJ_API int mmj_norm_fwd(const void* x, const void* res, void* res_out, const void* gamma,
+                         const void* beta, void* y, float* mean, float* rstd, int rows, int C,
+                         float eps, int mode, void* stream) {
+  if (C % 8 != 0 || C > 8 * 1024 * kNormMaxVPT) return -1;
+  if (rows <= 0) return 0;
+  const int vpt = (C / 8 > 1024) ? 2 : 1;
+  const int threads = norm_threads(C, vpt);
+  const int grid = rows;
+  auto xs = (const __nv_bfloat16*)x;
+  if (vpt == 1)
+    norm_fwd_kernel<1><<<grid, threads, 0, (cudaStream_t)stream>>>(
+        xs, (const __nv_bfloat16*)res, (__nv_bfloat16*)res_out, (const __nv_bfloat16*)gamma,
+        (const __nv_bfloat16*)beta, (__nv_bfloat16*)y, mean, rstd, rows, C, eps, mode);
+  else
+    norm_fwd_kernel<2><<<grid, threads, 0, (cudaStream_t)stream>>>(
+        xs, (const __nv_bfloat16*)res, (__nv_bfloat16*)res_out, (const __nv_bfloat16*)gamma,
+        (const __nv_bfloat16*)beta, (__nv_bfloat16*)y, mean, rstd, rows, C, eps, mode);
+  return (int)cudaGetLastError();
+}
+
+// Number of partial rows the backward writes (scratch must hold nparts * C floats, twice for
+// LayerNorm).
+MMJ_API int mmj_norm_bwd_parts(int rows) {
+  int n = 148 * 4;
+  return rows < n ? rows : n;
+}
+
+MMJ_API int mmj_norm_bwd(const void* dy, const void* x, const void* gamma, const float* mean,
+                         const float* rstd, const void* dres_in, void* dx, void* dgamma,
+                         void* dbeta, float* scratch, int rows, int C, int mode, int accumulate,
+                         void* stream) {
+  if (C % 8 != 0 || C > 8 * 1024 * kNormMaxVPT) return -1;
+  if (rows <= 0) return 0;
+  const int vpt = (C / 8 > 1024) ? 2 : 1;
+  const int threads = norm_threads(C, vpt);
+  const int nparts = mmj_norm_bwd_parts(rows);
+  float* pdg = scratch;
+  float* pdb = (mode == 0 && dbeta != nullptr) ? scratch + (size_t)nparts * C : nullptr;
+  if (vpt == 1)
+    norm_bwd_kernel<1><<<nparts, threads, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, mean, rstd,
+        (const __nv_bfloat16*)dres_in, (__nv_bfloat16*)dx, pdg, pdb, rows, C, mode);
+  else
+    norm_bwd_kernel<2><<<nparts, threads, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, mean, rstd,
+        (const __nv_bfloat16*)dres_in, (__nv_bfloat16*)dx, pdg, pdb, rows, C, mode);
+  norm_bwd_finalize_kernel<<<(C + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+      pdg, pdb, (__nv_bfloat16*)dgamma, (__nv_bfloat16*)dbeta, nparts, C, accumulate);
+  return (int)cudaGetLastError();
+}

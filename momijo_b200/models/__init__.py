@@ -1,0 +1,2 @@
+"""Model families assembled from the kernel front ends."""
+from .gpt2 import GPT2, GPT2Config  # noqa: F401

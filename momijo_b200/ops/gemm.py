@@ -1,0 +1,144 @@
+"""bf16 GEMM front end for the tcgen05 kernel (``csrc/gemm_sm100.cu``).
+
+``gemm(a, b)`` contracts over K with either operand stored K-major (``[rows, K]``) or MN-major
+(``[K, rows]``), which covers forward (``x @ W.T``), input-gradient (``dy @ W``) and
+weight-gradient (``dy.T @ x``) products without materialising a transpose. The epilogue flags
+fuse bias, GELU (keeping the pre-activation), GELU', residual add, SiLU, element-wise and
+per-row scaling, fp32 output and accumulation into the destination.
+
+On CPU tensors the same contract is evaluated with plain torch in fp32 (used by the CPU tests);
+on CUDA tensors only the native kernel runs.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _C
+
+EPI_BIAS = 1
+EPI_GELU = 2
+EPI_DGELU = 4
+EPI_ADD_AUX = 8
+EPI_OUT_F32 = 16
+EPI_ACCUMULATE = 32
+EPI_SILU = 64
+EPI_MUL_AUX = 128
+EPI_SCATTER_PEERS = 256
+EPI_ROW_SCALE = 512
+
+
+def _gelu_tanh(x):
+    return torch.nn.functional.gelu(x, approximate="tanh")
+
+
+def _gelu_tanh_grad(x):
+    k0, k1 = 0.7978845608028654, 0.044715
+    u = k0 * (x + k1 * x ** 3)
+    t = torch.tanh(u)
+    return 0.5 * (1 + t) + 0.5 * x * (1 - t * t) * k0 * (1 + 3 * k1 * x * x)
+
+
+def pick_bn(M: int, N: int) -> int:
+    """N tile width: 256 keeps the MMA at its widest; narrower tiles for narrow outputs."""
+    if N <= 64:
+        return 64
+    if N <= 128:
+        return 128
+    sms = 148
+    best, best_cost = 256, None
+    for bn in (256, 128):
+        tiles = -(-M // 128) * -(-N // bn)
+        waves = -(-tiles // sms)
+        cost = waves * bn * (1.0 if bn == 256 else 1.12)  # narrow tiles re-read A more often
+        if best_cost is None or cost < best_cost:
+            best, best_cost = bn, cost
+    return best
+
+
+def _check_2d(t, name):
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{name} must be 2-D with unit inner stride, got shape {tuple(t.shape)} "
+                         f"strides {t.stride()}")
+    if t.dtype != torch.bfloat16:
+        raise TypeError(f"{name} must be bfloat16, got {t.dtype}")
+
+
+def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_f32=False, accumulate=False, bias=None,
+         gelu=False, pre_out=None, dgelu_aux=None, add_aux=None, mul_aux=None, silu=False,
+         row_scale=None, bn=None):
+    """D[M, N] = contraction over K of A and B, followed by the fused epilogue.
+
+    a: ``[M, K]`` (or ``[K, M]`` when ``a_mn``); b: ``[N, K]`` (or ``[K, N]`` when ``b_mn``).
+    """
+    _check_2d(a, "a")
+    _check_2d(b, "b")
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    if K != Kb:
+        raise ValueError(f"contraction mismatch: {K} vs {Kb}")
+    aux = dgelu_aux if dgelu_aux is not None else (add_aux if add_aux is not None else mul_aux)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32 if out_f32 else torch.bfloat16, device=a.device)
+        accumulate = False
+    else:
+        out_f32 = out.dtype == torch.float32
+        if out.dim() != 2 or out.shape[0] != M or out.shape[1] != N or out.stride(1) != 1:
+            raise ValueError("bad out shape")
+    if gelu and pre_out is None:
+        pre_out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+
+    if not a.is_cuda:
+        A = (a.t() if a_mn else a).float()
+        Bm = (b if b_mn else b.t()).float()
+        v = A @ Bm
+        if bias is not None:
+            v = v + bias.float()
+        if gelu:
+            pre_out.copy_(v.to(torch.bfloat16))
+            v = _gelu_tanh(v)
+        if silu:
+            v = torch.nn.functional.silu(v)
+        if dgelu_aux is not None:
+            v = v * _gelu_tanh_grad(dgelu_aux.float())
+        elif mul_aux is not None:
+            v = v * mul_aux.float()
+        elif add_aux is not None:
+            v = v + add_aux.float()
+        if row_scale is not None:
+            v = v * row_scale.float()[:, None]
+        if accumulate:
+            v = v + out.float()
+        out.copy_(v.to(out.dtype))
+        return (out, pre_out) if gelu else out
+
+    epi = 0
+    if bias is not None:
+        epi |= EPI_BIAS
+    if gelu:
+        epi |= EPI_GELU
+    if silu:
+        epi |= EPI_SILU
+    if dgelu_aux is not None:
+        epi |= EPI_DGELU
+    elif mul_aux is not None:
+        epi |= EPI_MUL_AUX
+    elif add_aux is not None:
+        epi |= EPI_ADD_AUX
+    if out_f32:
+        epi |= EPI_OUT_F32
+    if accumulate:
+        epi |= EPI_ACCUMULATE
+    if row_scale is not None:
+        epi |= EPI_ROW_SCALE
+    if aux is not None:
+        _check_2d(aux, "aux")
+    if N % 8 != 0 and out.stride(0) % 8 != 0:
+        raise ValueError("output leading dimension must be a multiple of 8 elements")
+    if bn is None:
+        bn = pick_bn(M, N)
+    _C.call("mmj_gemm_bf16", _C.ptr(a), a.stride(0), int(a_mn), _C.ptr(b), b.stride(0), int(b_mn),
+            _C.ptr(out), out.stride(0), M, N, K, epi, _C.ptr(bias), _C.ptr(aux),
+            aux.stride(0) if aux is not None else 0, _C.ptr(pre_out),
+            pre_out.stride(0) if pre_out is not None else 0, _C.ptr(row_scale), bn,
+            _C.ptr(_C.status_tensor(a.device)), _C.current_stream())
+    return (out, pre_out) if gelu else out

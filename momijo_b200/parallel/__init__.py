@@ -1,0 +1,3 @@
+"""Process groups, peer-memory runtime and the parallel wrappers (DDP / ZeRO / TP / EP / PP)."""
+from .flat import FlatParams, FlatLayout  # noqa: F401
+from .zero import ShardedDataParallel, AdamWConfig  # noqa: F401

@@ -1,0 +1,3 @@
+"""Timing, clock sampling and misc helpers."""
+from .clocks import ClockSampler  # noqa: F401
+from .timing import cuda_time_ms, max_over_ranks  # noqa: F401
