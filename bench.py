@@ -147,7 +147,7 @@ def build_torch(cfg, world, local):
             for b in s.blocks:
                 x = b(x)
             logits = F.linear(s.lnf(x), s.wte.weight)[..., :cfg.vocab_size]
-            return F.cross_entropy(logits.float().view(-1, cfg.vocab_size), tgt.view(-1))
+            return F.cross_entropy(logits.float().reshape(-1, cfg.vocab_size), tgt.reshape(-1))
 
     torch.manual_seed(1234)
     net = Net().cuda()

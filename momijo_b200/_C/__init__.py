@@ -24,8 +24,8 @@ P, I, L, F = c_void_p, c_int, c_longlong, c_float
 _SIGS = {
     "mmj_gemm_bf16": ([P, L, I, P, L, I, P, L, I, I, I, I, P, P, L, P, L, P, I, P, P], 1),
     "mmj_gemm_bf16_grouped": ([P, L, P, L, I, I, I, P, L, I, I, I, I, P, L, P, P, P, I, P, P], 1),
-    "mmj_gemm_bf16_allgather": ([P, P, I, P, L, L, I, P, L, I, I, I, I, P, P, L, P, L, I, I, I, P,
-                                 P, I, I, P, P], 1),
+    "mmj_gemm_bf16_allgather": ([P, P, I, P, L, L, I, P, L, I, I, I, I, P, P, L, P, L, I, I, I, L,
+                                 L, P, P, I, I, P, P], 1),
     "mmj_gemm_bf16_reduce_scatter": ([P, L, P, L, I, P, L, L, I, I, I, I, I, I, P, P], 1),
     "mmj_norm_fwd": ([P, P, P, P, P, P, P, P, I, I, F, I, P], 1),
     "mmj_norm_bwd_parts": ([I], 0),
@@ -61,6 +61,19 @@ _SIGS = {
     "mmj_attn_fwd": ([P, L, I, P, L, I, P, L, I, P, L, I, P, I, I, I, I, I, F, I, P, P], 1),
     "mmj_attn_bwd": ([P, L, I, P, L, I, P, L, I, P, L, I, P, L, I, P, P, P, L, I, P, L, I, P, L, I,
                       I, I, I, I, I, F, I, P, P], 2),
+    "mmj_barrier": ([P, I, I, I, I, P, P], 1),
+    "mmj_signal_peers": ([P, I, I, I, I, P], 1),
+    "mmj_wait_flag": ([P, I, P, P], 1),
+    "mmj_rs_adamw": ([P, P, P, P, P, P, P, L, L, F, F, F, F, F, F, F, F, I, I, I, I, P, P, P, P], 1),
+    "mmj_allgather_ranges": ([P, P, L, P, I, I, I, I, I, P, P], 1),
+    "mmj_allreduce_bf16": ([P, P, P, L, F, I, I, I, I, P, P, P, P], 1),
+    "mmj_reduce_slots_bf16": ([P, P, L, P, P, L, I, I, I, I, P, P], 1),
+    "mmj_moe_count": ([P, P, I, I, P, P, I, I, I, I, P, P], 1),
+    "mmj_moe_offsets": ([P, I, I, I, P, P, P, P, P, I, P], 1),
+    "mmj_moe_zero_pad": ([P, I, P, I, I, P], 1),
+    "mmj_moe_gate_grad": ([P, P, P, P, P, I, I, I, I, I, P], 1),
+    "mmj_moe_dispatch": ([P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P, P], 1),
+    "mmj_moe_combine": ([P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P], 1),
 }
 
 _OPTIONAL = {}

@@ -211,7 +211,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     for (int d = 0; d < D; ++d) o[d] = 0.f;
     bool ok = true;
     for (int j = 0; j < nkv; ++j) {
-      if (!mbar_wait(&s_full, j & 1, &abort_flag, p.status, kTimeoutTmemFull, j)) { ok = false; break; }
+      if (!mbar_wait_warp(&s_full, j & 1, &abort_flag, p.status, kTimeoutTmemFull, j)) { ok = false; break; }
       tc_fence_after();
       const int kv0 = j * 128;
       const bool need_mask = (p.causal && (kv0 + 127 > q0)) || (kv0 + 128 > p.T);
@@ -264,7 +264,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (lane == 0) mbar_arrive(&p_full);
 #pragma unroll
       for (int d = 0; d < D; ++d) o[d] *= alpha;
-      if (!mbar_wait(&o_full, j & 1, &abort_flag, p.status, kTimeoutTmemFull, 100 + j)) { ok = false; break; }
+      if (!mbar_wait_warp(&o_full, j & 1, &abort_flag, p.status, kTimeoutTmemFull, 100 + j)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll
       for (int cc = 0; cc < D / 32; ++cc) {
@@ -295,7 +295,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
 }
 
 // =============================================================================================
@@ -351,7 +354,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   __shared__ __align__(8) uint64_t kv_full, s_full, p_full, dq_full, dq_read;
   __shared__ __align__(8) uint64_t qdo_full[2], qdo_empty[2];
-  __shared__ float s_lse[128], s_delta[128];
+  __shared__ float s_lse[2][128], s_delta[2][128];
+  __shared__ __align__(8) uint64_t stat_full;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -371,6 +375,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(&p_full, 4);
     mbar_init(&dq_full, 1);
     mbar_init(&dq_read, 4);
+    mbar_init(&stat_full, 128);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&qdo_full[s], 1);
       mbar_init(&qdo_empty[s], 1);
@@ -488,16 +493,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int hq = hkv * group + it / n_i;
       const int qi = i_begin + it % n_i;
       const int qbase = qi * 128;
-      // stage lse / delta of this query block (previous iteration's readers are past p_full)
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      // stage lse / delta of this query block in a double buffer; an mbarrier (bounded wait)
+      // rather than a named barrier, so that an aborting warp can never strand the others
+      float* lse_s = s_lse[it & 1];
+      float* delta_s = s_delta[it & 1];
       {
         const int q = qbase + ctid;
         const long long off = ((long long)b * p.Hq + hq) * p.T + q;
-        s_lse[ctid] = (q < p.T) ? p.lse[off] * l2e : 0.f;
-        s_delta[ctid] = (q < p.T) ? p.delta[off] : 0.f;
+        lse_s[ctid] = (q < p.T) ? p.lse[off] * l2e : 0.f;
+        delta_s[ctid] = (q < p.T) ? p.delta[off] : 0.f;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (!mbar_wait(&s_full, it & 1, &abort_flag, p.status, kTimeoutTmemFull, it)) { ok = false; break; }
+      mbar_arrive(&stat_full);
+      if (!mbar_wait_warp(&stat_full, it & 1, &abort_flag, p.status, kTimeoutFlag, 500 + it)) { ok = false; break; }
+      if (!mbar_wait_warp(&s_full, it & 1, &abort_flag, p.status, kTimeoutTmemFull, it)) { ok = false; break; }
       tc_fence_after();
       const bool need_mask = (p.causal && (qbase < kv0 + 127)) || (qbase + 128 > p.T) ||
                              (kv0 + 128 > p.T);
@@ -511,13 +519,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const int qc = cc * 32 + i;
-          float e = exp2f(__uint_as_float(rs[i]) * c - s_lse[qc]);
+          float e = exp2f(__uint_as_float(rs[i]) * c - lse_s[qc]);
           if (need_mask) {
             const int q = qbase + qc;
             if (q >= p.T || kv_idx >= p.T || (p.causal && kv_idx > q)) e = 0.f;
           }
           pt[i] = e;
-          ds[i] = e * (__uint_as_float(rp[i]) - s_delta[qc]);
+          ds[i] = e * (__uint_as_float(rp[i]) - delta_s[qc]);
         }
         store_chunk_sw128(sPt, row, cc * 32, pt);
         store_chunk_sw128(sdSt, row, cc * 32, ds);
@@ -527,7 +535,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full);
       // dQ of this iteration: rows are queries here (lane = query row)
-      if (!mbar_wait(&dq_full, it & 1, &abort_flag, p.status, kTimeoutTmemFull, 100 + it)) { ok = false; break; }
+      if (!mbar_wait_warp(&dq_full, it & 1, &abort_flag, p.status, kTimeoutTmemFull, 100 + it)) { ok = false; break; }
       tc_fence_after();
       {
         const int q = qbase + row;
@@ -552,7 +560,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (lane == 0) mbar_arrive(&dq_read);
     }
     // all MMAs into dV / dK have completed once the last dq_full has been seen
-    if (ok && kv_idx < p.T && n_iter > 0) {
+    // tcgen05.ld is warp-collective: the condition around it must be warp-uniform; only the
+    // global stores are predicated per row.
+    const bool warp_ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+    const bool row_ok = kv_idx < p.T;
+    if (warp_ok && n_iter > 0) {
       __nv_bfloat16* dk = p.dK + ((long long)b * p.T + kv_idx) * p.ld_dk + p.dk_col0 + hkv * D;
       __nv_bfloat16* dv = p.dV + ((long long)b * p.T + kv_idx) * p.ld_dv + p.dv_col0 + hkv * D;
 #pragma unroll
@@ -567,7 +579,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           q.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
           q.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
           q.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
-          reinterpret_cast<uint4*>(dv + cc * 32)[i] = q;
+          if (row_ok) reinterpret_cast<uint4*>(dv + cc * 32)[i] = q;
         }
         tmem_ld_32x32(t_lane + kColdK + cc * 32, r);
         tmem_ld_wait();
@@ -578,10 +590,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           q.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * p.scale, __uint_as_float(r[8 * i + 3]) * p.scale);
           q.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * p.scale, __uint_as_float(r[8 * i + 5]) * p.scale);
           q.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * p.scale, __uint_as_float(r[8 * i + 7]) * p.scale);
-          reinterpret_cast<uint4*>(dk + cc * 32)[i] = q;
+          if (row_ok) reinterpret_cast<uint4*>(dk + cc * 32)[i] = q;
         }
       }
-    } else if (ok && kv_idx < p.T && n_iter == 0) {
+    } else if (warp_ok && row_ok && n_iter == 0) {
       // no query block attends to this key block: gradients are zero
       __nv_bfloat16* dk = p.dK + ((long long)b * p.T + kv_idx) * p.ld_dk + p.dk_col0 + hkv * D;
       __nv_bfloat16* dv = p.dV + ((long long)b * p.T + kv_idx) * p.ld_dv + p.dv_col0 + hkv * D;
@@ -594,7 +606,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -604,6 +619,8 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+void ensure_context();  // gemm_sm100.cu
 
 static EncodeTiledFn attn_encode_fn() {
   static EncodeTiledFn fn = nullptr;
@@ -623,6 +640,7 @@ static int make_tmap_btc(CUtensorMap* out, const void* base, int B, int T, long 
                          long long ld) {
   EncodeTiledFn fn = attn_encode_fn();
   if (fn == nullptr) return -1;
+  ensure_context();
   if (ld % 8 || ((uintptr_t)base & 15)) return -2;
   cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)T, (cuuint64_t)B};
   cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)ld * 2 * (cuuint64_t)T};

@@ -114,6 +114,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
   }
 }
 
+// Warp-collective form: every lane waits, then the warp agrees on the outcome, so that code
+// following the wait (tcgen05.ld and other .sync.aligned instructions) stays convergent even when
+// a timeout or an abort is observed by only some lanes.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity,
+                                               volatile int* abort_flag, int* status, int code,
+                                               int detail) {
+  const bool ok = mbar_wait(bar, parity, abort_flag, status, code, detail);
+  return __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+}
+
 // ---- TMA -----------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");

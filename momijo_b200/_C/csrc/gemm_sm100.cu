@@ -74,9 +74,17 @@ struct TileCoord {
 };
 
 __device__ __forceinline__ TileCoord tile_of(int t, int num_m, int num_n, const GemmParams& p) {
-  // n fastest: concurrently running CTAs share A rows and sweep B (weights stay in L2).
-  int m_lin = t / num_n;
-  int n_lin = t - m_lin * num_n;
+  // n fastest by default: concurrently running CTAs share A rows and sweep B (weights stay in
+  // L2). With a gathered B operand the order is m fastest, so that the first waves only need
+  // the B tiles that are already local.
+  int m_lin, n_lin;
+  if (p.flag_mode == 2) {
+    n_lin = t / num_m;
+    m_lin = t - n_lin * num_m;
+  } else {
+    m_lin = t / num_n;
+    n_lin = t - m_lin * num_n;
+  }
   TileCoord c;
   c.m_tile = m_lin + p.m_tile_rot;
   if (c.m_tile >= num_m) c.m_tile -= num_m;
@@ -265,65 +273,73 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       mbar_fence_init();
       const int n_comm = (int)gridDim.x - gemm_ctas;
       const int cid = (int)blockIdx.x - gemm_ctas;
-      const int tiles_per_shard = (int)((p.shard_bytes + p.tile_bytes - 1) / p.tile_bytes);
-      const int total = p.world * tiles_per_shard;
+      const int ntiles = (int)((p.gather_total_bytes + p.tile_bytes - 1) / p.tile_bytes);
+      const int rot = (p.flag_mode == 1) ? p.m_tile_rot : p.n_tile_rot;
       uint32_t issued = 0, drained = 0;  // chunk counters over the ring
       bool ok = true;
-      for (int i = cid; i < total && ok; i += n_comm) {
-        const int hop = i / tiles_per_shard;
-        const int tt = i - hop * tiles_per_shard;
-        int sr = p.rank + hop;
-        if (sr >= p.world) sr -= p.world;
-        if (p.peer_ready != nullptr && sr != p.rank)
-          ok = wait_flag_ge(p.peer_ready + sr, p.ready_epoch, true, &abort_flag, p.status, 100 + sr);
-        if (!ok) break;
-        const long long off = (long long)tt * p.tile_bytes;
-        long long nbytes = p.shard_bytes - off;
-        if (nbytes > p.tile_bytes) nbytes = p.tile_bytes;
-        const uint8_t* src = reinterpret_cast<const uint8_t*>(p.peer_src[sr]) + off;
-        uint8_t* dst =
-            reinterpret_cast<uint8_t*>(p.gather_dst) + (long long)sr * p.shard_bytes + off;
-        if (src != dst) {
-          const int nchunks = (int)((nbytes + kBufBytes - 1) / kBufBytes);
-          int next_load = 0;
-          for (int c = 0; c < nchunks && ok; ++c) {
-            // keep up to kNBuf loads in flight
-            while (next_load < nchunks && issued - drained < (uint32_t)kNBuf) {
-              const int b = issued % kNBuf;
-              const long long co = (long long)next_load * kBufBytes;
+      for (int i = cid; i < ntiles && ok; i += n_comm) {
+        int t = i + rot;  // same visiting order as the GEMM CTAs consume tiles
+        if (t >= ntiles) t -= ntiles;
+        long long lo = (long long)t * p.tile_bytes;
+        long long hi = lo + p.tile_bytes;
+        if (hi > p.gather_total_bytes) hi = p.gather_total_bytes;
+        // a tile may straddle shard boundaries: copy it owner by owner
+        while (lo < hi && ok) {
+          const long long abs_off = p.gather_flat_off + lo;
+          const int owner = (int)(abs_off / p.shard_bytes);
+          long long seg_hi = (long long)(owner + 1) * p.shard_bytes - p.gather_flat_off;
+          if (seg_hi > hi) seg_hi = hi;
+          if (owner != p.rank && owner < p.world) {
+            if (p.peer_ready != nullptr)
+              ok = wait_flag_ge(p.peer_ready + owner, p.ready_epoch, true, &abort_flag, p.status,
+                                100 + owner);
+            if (!ok) break;
+            const long long nbytes = seg_hi - lo;
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.peer_src[owner]) + lo;
+            uint8_t* dst = reinterpret_cast<uint8_t*>(p.gather_dst) + lo;
+            const int nchunks = (int)((nbytes + kBufBytes - 1) / kBufBytes);
+            int next_load = 0;
+            for (int c = 0; c < nchunks && ok; ++c) {
+              // keep up to kNBuf loads in flight
+              while (next_load < nchunks && issued - drained < (uint32_t)kNBuf) {
+                const int b = issued % kNBuf;
+                const long long co = (long long)next_load * kBufBytes;
+                const uint32_t sz =
+                    (uint32_t)((nbytes - co < kBufBytes) ? (nbytes - co) : kBufBytes);
+                mbar_expect_tx(&full_bar[b], sz);
+                asm volatile(
+                    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                    ::"r"(smem_u32(smem + (size_t)b * kBufBytes)), "l"(src + co), "r"(sz),
+                    "r"(smem_u32(&full_bar[b]))
+                    : "memory");
+                ++issued;
+                ++next_load;
+              }
+              const int b = drained % kNBuf;
+              const uint32_t par = (drained / kNBuf) & 1u;
+              if (!mbar_wait(&full_bar[b], par, &abort_flag, p.status, kTimeoutFull, 1000 + c)) {
+                ok = false;
+                break;
+              }
+              const long long co = (long long)c * kBufBytes;
               const uint32_t sz = (uint32_t)((nbytes - co < kBufBytes) ? (nbytes - co) : kBufBytes);
-              mbar_expect_tx(&full_bar[b], sz);
-              asm volatile(
-                  "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                  ::"r"(smem_u32(smem + (size_t)b * kBufBytes)), "l"(src + co), "r"(sz),
-                  "r"(smem_u32(&full_bar[b]))
-                  : "memory");
-              ++issued;
-              ++next_load;
+              asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst + co),
+                           "r"(smem_u32(smem + (size_t)b * kBufBytes)), "r"(sz)
+                           : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+              // the buffer may be refilled once the store has read it
+              asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+              ++drained;
             }
-            const int b = drained % kNBuf;
-            const uint32_t par = (drained / kNBuf) & 1u;
-            if (!mbar_wait(&full_bar[b], par, &abort_flag, p.status, kTimeoutFull, 1000 + c)) {
-              ok = false;
-              break;
-            }
-            const long long co = (long long)c * kBufBytes;
-            const uint32_t sz = (uint32_t)((nbytes - co < kBufBytes) ? (nbytes - co) : kBufBytes);
-            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst + co),
-                         "r"(smem_u32(smem + (size_t)b * kBufBytes)), "r"(sz)
-                         : "memory");
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-            // the buffer may be refilled once the store has read it
-            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-            ++drained;
+            // all bytes of this piece written before the tile's flag is published
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
           }
-          // all bytes of this piece written before its flag is published
-          asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+          lo = seg_hi;
         }
         if (!ok) break;
         asm volatile("fence.proxy.async;" ::: "memory");
         __threadfence();
-        st_release_gpu(p.flags_rw + sr * tiles_per_shard + tt, p.ready_epoch);
+        st_release_gpu(p.flags_rw + t, p.ready_epoch);
       }
       // never leave with loads in flight into this CTA's shared memory
       while (drained < issued) {
@@ -471,7 +487,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         const TileCoord tc = tile_of(t, num_m, num_n, p);
         const int m0 = tc.m_tile * kGemmBM;
         const int n0 = tc.n_tile * bn;
-        if (!mbar_wait(&tfull_bar[acc], acc_ph, &abort_flag, p.status, kTimeoutTmemFull, t)) break;
+        if (!mbar_wait_warp(&tfull_bar[acc], acc_ph, &abort_flag, p.status, kTimeoutTmemFull, t)) break;
         tc_fence_after();
         const int row = m0 + quad * 32 + lane;
         const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kAccCols);
@@ -498,7 +514,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   // ---------------- teardown ----------------
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -523,11 +542,22 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// The driver call below needs the primary context to be current on the calling thread; threads
+// that have only been handed a device ordinal (e.g. autograd workers) bind it on first use.
+void ensure_context() {
+  static thread_local bool ready = false;
+  if (!ready) {
+    cudaFree(0);
+    ready = true;
+  }
+}
+
 // 2-D bf16 tensor map: `inner` contiguous elements, `outer` rows `row_stride_elems` apart.
 int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
                       uint64_t row_stride_elems, uint32_t box_inner, uint32_t box_outer) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return -1;
+  ensure_context();
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {row_stride_elems * 2};
   cuuint32_t box[2] = {box_inner, box_outer};
@@ -668,6 +698,7 @@ MMJ_API int mmj_gemm_bf16_allgather(const void* const* peer_src, void* gathered,
                                     int other_mn, void* D, long long ldd, int M, int N, int K,
                                     int epi, const void* bias, const void* aux, long long ldaux,
                                     void* D2, long long ldd2, int bn, int world, int rank,
+                                    long long shard_bytes, long long flat_off_bytes,
                                     int* flags, const int* peer_ready, int epoch, int comm_ctas,
                                     int* status, void* stream) {
   if (world < 1 || world > kMaxPeers) return -5;
@@ -686,22 +717,29 @@ MMJ_API int mmj_gemm_bf16_allgather(const void* const* peer_src, void* gathered,
   p.gather_dst = gathered;
   for (int r = 0; r < world; ++r) p.peer_src[r] = peer_src[r];
   const long long rows = gather_a ? M : N;
-  if (rows % world) return -6;
-  const long long shard_rows = rows / world;
   const int granule = gather_a ? kGemmBM : bn;
-  if (shard_rows % granule) return -7;
-  p.shard_bytes = shard_rows * ld_gathered * 2;
   p.tile_bytes = (long long)granule * ld_gathered * 2;
+  p.gather_total_bytes = rows * ld_gathered * 2;
+  p.gather_flat_off = flat_off_bytes;
+  p.shard_bytes = shard_bytes;
+  if (shard_bytes <= 0 || (shard_bytes & 15) || (flat_off_bytes & 15)) return -6;
+  // first tile that holds local data (if any) is visited first
+  long long first_local = (long long)rank * shard_bytes - flat_off_bytes;
+  if (first_local < 0) first_local = 0;
+  int rot_tile = 0;
+  if (first_local < p.gather_total_bytes) rot_tile = (int)((first_local + p.tile_bytes - 1) / p.tile_bytes);
+  const int ntiles_g = (int)((p.gather_total_bytes + p.tile_bytes - 1) / p.tile_bytes);
+  if (rot_tile >= ntiles_g) rot_tile = 0;
   if (gather_a) {
     p.flag_mode = 1;
     p.a_mn = 0; p.b_mn = other_mn;
-    p.m_tile_rot = (int)(rank * (shard_rows / granule));
+    p.m_tile_rot = rot_tile;
     return launch_gemm(p, gathered, ld_gathered, M, other, ld_other, other_mn ? K : N, comm_ctas,
                        (cudaStream_t)stream);
   } else {
     p.flag_mode = 2;
     p.a_mn = other_mn; p.b_mn = 0;
-    p.n_tile_rot = (int)(rank * (shard_rows / granule));
+    p.n_tile_rot = rot_tile;
     return launch_gemm(p, other, ld_other, other_mn ? K : M, gathered, ld_gathered, N, comm_ctas,
                        (cudaStream_t)stream);
   }

@@ -63,8 +63,14 @@ struct GemmParams {
   int world, rank;
   const void* peer_src[kMaxPeers];  // peer_src[r]: base of rank r's shard (peer pointer)
   void* gather_dst;                 // local full buffer
-  long long shard_bytes;            // bytes per rank shard (contiguous rows)
-  long long tile_bytes;             // bytes per flag granule
+  // The gathered operand is a window [gather_flat_off, gather_flat_off + gather_total_bytes)
+  // of a flat symmetric buffer that is sharded in equal pieces of shard_bytes per rank: the
+  // byte at flat offset o is owned by rank o / shard_bytes. peer_src[r] points at the start of
+  // the window in rank r's memory.
+  long long shard_bytes;
+  long long gather_flat_off;
+  long long gather_total_bytes;
+  long long tile_bytes;             // bytes per flag granule (128 rows of A or bn rows of B)
   int* flags_rw;                    // same array as ready_flags, writable
   const int* peer_ready;            // local signal pad: peer_ready[r] >= ready_epoch => shard r final
 

@@ -1,0 +1,154 @@
+"""Per-kernel microbenchmarks with roofline fractions.
+
+    python -m momijo_b200.ops.bench_kernels --op gemm|attn|norm|ce|adamw|all [--small]
+
+Each kernel is timed with CUDA events on the launching stream after warm-up, with an L2-sized
+buffer rewritten between iterations. Achieved FLOP/s or bytes/s are reported against the measured
+peaks in MEASURED_PEAKS.json at the repository root (fallback 1.59 PFLOP/s, 6.65 TB/s). ``--small``
+runs one reduced case per op, sized for a profiler capture (a few hundred MB on the device).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+
+import torch
+
+from .. import ops
+from ..utils.timing import cuda_time_ms
+
+bf16 = torch.bfloat16
+
+
+def peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return p["bf16_tflops"] * 1e12, p["hbm_gbs"] * 1e9, "measured"
+    except Exception:
+        return 1.59e15, 6.65e12, "fallback"
+
+
+def bench_gemm(small):
+    flops_peak, _, tag = peaks()
+    shapes = [(2048, 2304, 768, False, False)] if small else [
+        (16384, 2304, 768, False, False), (16384, 768, 768, False, False),
+        (16384, 3072, 768, False, False), (16384, 768, 3072, False, False),
+        (16384, 50304, 768, False, False), (16384, 768, 50304, False, True),
+        (50304, 768, 16384, True, True), (3072, 768, 16384, True, True),
+        (8192, 8192, 8192, False, False), (32768, 4096, 4096, False, False),
+        (32768, 14336, 4096, False, False)]
+    rows = []
+    for M, N, K, a_mn, b_mn in shapes:
+        a = torch.randn((K, M) if a_mn else (M, K), device="cuda").to(bf16)
+        b = torch.randn((K, N) if b_mn else (N, K), device="cuda").to(bf16)
+        out = torch.empty(M, N, device="cuda", dtype=bf16)
+        med, best = cuda_time_ms(lambda: ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out), iters=5 if small else 10)
+        A = a.t() if a_mn else a
+        B = b if b_mn else b.t()
+        tmed, tbest = cuda_time_ms(lambda: torch.matmul(A, B, out=out), iters=5 if small else 10)
+        fl = 2.0 * M * N * K
+        rows.append({"op": "gemm", "M": M, "N": N, "K": K, "a_mn": a_mn, "b_mn": b_mn,
+                     "ms": med, "tflops": fl / med / 1e9, f"frac_of_{tag}_peak": fl / (med * 1e-3) / flops_peak,
+                     "cublas_ms": tmed, "vs_cublas": tmed / med})
+    return rows
+
+
+def bench_attn(small):
+    flops_peak, _, tag = peaks()
+    cfgs = [(2, 1024, 12, 12, 64)] if small else [(16, 1024, 12, 12, 64), (2, 4096, 32, 8, 128),
+                                                     (8, 4096, 16, 16, 128)]
+    rows = []
+    for B, T, Hq, Hkv, D in cfgs:
+        cols = (Hq + 2 * Hkv) * D
+        qkv = (torch.randn(B * T, cols, device="cuda")).to(bf16).requires_grad_(True)
+        dy = torch.randn(B * T, Hq * D, device="cuda").to(bf16)
+        f = lambda: ops.attention_packed(qkv, B, T, Hq, Hkv, D, causal=True)
+        med, _ = cuda_time_ms(f, iters=5 if small else 10)
+        out = f()
+        bmed, _ = cuda_time_ms(lambda: out.backward(dy, retain_graph=True), iters=5 if small else 10)
+        fl = 4.0 * B * Hq * T * T * D / 2
+        q = torch.randn(B, Hq, T, D, device="cuda", dtype=bf16, requires_grad=True)
+        k = torch.randn(B, Hkv, T, D, device="cuda", dtype=bf16, requires_grad=True)
+        v = torch.randn(B, Hkv, T, D, device="cuda", dtype=bf16, requires_grad=True)
+        sd = lambda: torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True,
+                                                                      enable_gqa=Hq != Hkv)
+        smed, _ = cuda_time_ms(sd, iters=5 if small else 10)
+        so = sd()
+        go = torch.randn_like(so)
+        sbmed, _ = cuda_time_ms(lambda: so.backward(go, retain_graph=True), iters=5 if small else 10)
+        rows.append({"op": "attn", "B": B, "T": T, "Hq": Hq, "Hkv": Hkv, "D": D, "fwd_ms": med,
+                     "fwd_tflops": fl / med / 1e9, f"fwd_frac_of_{tag}_peak": fl / (med * 1e-3) / flops_peak,
+                     "bwd_ms": bmed, "bwd_tflops": 2.5 * fl / bmed / 1e9,
+                     "sdpa_fwd_ms": smed, "sdpa_bwd_ms": sbmed})
+    return rows
+
+
+def bench_norm(small):
+    _, bw_peak, tag = peaks()
+    rows = []
+    for R, C in ([(16384, 768)] if small else [(16384, 768), (32768, 4096), (262144, 768)]):
+        x = torch.randn(R, C, device="cuda").to(bf16).requires_grad_(True)
+        g = torch.ones(C, device="cuda", dtype=bf16, requires_grad=True)
+        b = torch.zeros(C, device="cuda", dtype=bf16, requires_grad=True)
+        f = lambda: ops.layer_norm(x, g, b)
+        med, _ = cuda_time_ms(f)
+        y = f()
+        dy = torch.randn_like(y)
+        bmed, _ = cuda_time_ms(lambda: y.backward(dy, retain_graph=True))
+        by = 2.0 * R * C * 2
+        rows.append({"op": "layernorm", "rows": R, "C": C, "fwd_ms": med, "fwd_GBs": by / med / 1e6,
+                     f"fwd_frac_of_{tag}_bw": by / (med * 1e-3) / bw_peak, "bwd_ms": bmed,
+                     "bwd_GBs": 1.5 * by / bmed / 1e6})
+    return rows
+
+
+def bench_ce(small):
+    _, bw_peak, tag = peaks()
+    R, V = (2048, 50257) if small else (16384, 50257)
+    Vp = ops.pad_vocab(V)
+    logits = torch.randn(R, Vp, device="cuda").to(bf16)
+    tgt = torch.randint(0, V, (R,), device="cuda")
+    from .. import _C
+
+    lr = torch.empty(R, device="cuda")
+    f = lambda: _C.call("mmj_ce_fwd_bwd", _C.ptr(logits), Vp, V, _C.ptr(tgt), _C.ptr(lr), R, 1.0 / R,
+                        -100, 1, _C.current_stream())
+    med, _ = cuda_time_ms(f)
+    by = 2.0 * R * Vp * 2
+    return [{"op": "softmax_ce_fwd_bwd", "rows": R, "V": V, "ms": med, "GBs": by / med / 1e6,
+             f"frac_of_{tag}_bw": by / (med * 1e-3) / bw_peak}]
+
+
+def bench_adamw(small):
+    _, bw_peak, tag = peaks()
+    n = 16 * 1024 * 1024 if small else 124 * 1024 * 1024
+    g = torch.randn(n, device="cuda").to(bf16)
+    w, m, v = torch.randn(n, device="cuda"), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    p = torch.empty(n, device="cuda", dtype=bf16)
+    f = lambda: ops.adamw_flat(g, w, m, v, p, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8,
+                               weight_decay=0.1, step=3)
+    med, _ = cuda_time_ms(f)
+    by = n * (2 + 12 + 12 + 2)
+    return [{"op": "adamw", "n": n, "ms": med, "GBs": by / med / 1e6,
+             f"frac_of_{tag}_bw": by / (med * 1e-3) / bw_peak}]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="all")
+    ap.add_argument("--small", action="store_true")
+    a = ap.parse_args()
+    table = {"gemm": bench_gemm, "attn": bench_attn, "norm": bench_norm, "ce": bench_ce,
+             "adamw": bench_adamw}
+    for name, fn in table.items():
+        if a.op in ("all", name):
+            for r in fn(a.small):
+                print(json.dumps({k: (round(v, 4) if isinstance(v, float) else v) for k, v in r.items()}))
+
+
+if __name__ == "__main__":
+    main()

@@ -524,8 +524,10 @@ def softmax_cross_entropy(logits, targets, ignore_index=-100, reduction="mean"):
     l2 = logits.reshape(-1, V)
     t1 = targets.reshape(-1)
     n = l2.shape[0]
-    if l2.is_cuda and l2.dtype == bf16 and l2.stride(0) % 8 == 0 and l2.stride(1) == 1:
-        work = l2.clone()
+    if l2.is_cuda and l2.dtype == bf16:
+        work_buf = torch.empty((n, (V + 7) // 8 * 8), dtype=bf16, device=l2.device)
+        work = work_buf[:, :V]
+        work.copy_(l2)
         loss_row = torch.empty(n, dtype=torch.float32, device=l2.device)
         nvalid = n if reduction == "mean" else 1
         _C.call("mmj_ce_fwd_bwd", _C.ptr(work), work.stride(0), V, _C.ptr(t1), _C.ptr(loss_row), n,
@@ -533,7 +535,7 @@ def softmax_cross_entropy(logits, targets, ignore_index=-100, reduction="mean"):
         loss = torch.empty(1, dtype=torch.float32, device=l2.device)
         _C.call("mmj_reduce_mean", _C.ptr(loss_row), _C.ptr(loss), n, 1.0 / nvalid,
                 _C.current_stream())
-        return loss[0], work.view(logits.shape)
+        return loss[0], work.reshape(logits.shape)
     lf = l2.float()
     logp = torch.log_softmax(lf, dim=-1)
     valid = t1 != ignore_index

@@ -1,0 +1,41 @@
+"""Multi-GPU tests: peer-memory collectives and fused compute+communication kernels, run as one
+process per GPU (needs >= 2 GPUs). NVLS is switched off so that a rank ending early cannot
+disturb the others."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(scenarios, nproc=None, timeout=600):
+    n = nproc or min(torch.cuda.device_count(), 4)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+           "--master-addr", "127.0.0.1", "--master-port", "29533",
+           os.path.join(HERE, "mp_worker.py"), *scenarios]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0, out[-4000:]
+    for s in scenarios:
+        assert f"SCENARIO_OK {s}" in out, out[-4000:]
+
+
+def test_peer_allreduce_and_timeout_status():
+    _run(["allreduce", "timeout"])
+
+
+def test_zero_engine_matches_single_rank():
+    _run(["zero"])
+
+
+def test_fused_allgather_gemm_and_gemm_reduce_scatter():
+    _run(["ag_gemm", "gemm_rs"])
+
+
+def test_moe_dispatch_combine():
+    _run(["moe"])
