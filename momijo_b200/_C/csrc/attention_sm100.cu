@@ -89,14 +89,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   constexpr int kTile = NP * kPanelBytes;
   constexpr uint32_t kTmemCols = 256;
   constexpr uint32_t kColS = 0, kColO = 128;
+  // head_dim 64 keeps a single V stage so that two CTAs fit in one SM's shared memory (the
+  // second CTA's softmax then overlaps this CTA's MMAs); head_dim 128 runs one CTA per SM.
+  constexpr int VS = (D == 64) ? 1 : 2;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~(uintptr_t)1023);
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + kTile;      // 2 stages
-  uint8_t* sV = sK + 2 * kTile;  // 2 stages
-  uint8_t* sP = sV + 2 * kTile;  // 128 x 128 bf16
+  uint8_t* sV = sK + 2 * kTile;  // VS stages
+  uint8_t* sP = sV + VS * kTile;  // 128 x 128 bf16
 
   __shared__ __align__(8) uint64_t q_full, s_full, p_full, o_full;
   __shared__ __align__(8) uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
@@ -153,11 +156,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int pn = 0; pn < NP; ++pn)
           tma_load_3d(sK + s * kTile + pn * kPanelBytes, &tmK, &k_full[s],
                       p.k_col0 + hkv * D + pn * 64, j * 128, b);
-        if (!mbar_wait(&v_empty[s], ph ^ 1, &abort_flag, p.status, kTimeoutEmpty, 100 + j)) break;
-        mbar_expect_tx(&v_full[s], kTile);
+        const int sv = j % VS;
+        const uint32_t phv = (j / VS) & 1;
+        if (!mbar_wait(&v_empty[sv], phv ^ 1, &abort_flag, p.status, kTimeoutEmpty, 100 + j)) break;
+        mbar_expect_tx(&v_full[sv], kTile);
 #pragma unroll
         for (int pn = 0; pn < NP; ++pn)
-          tma_load_3d(sV + s * kTile + pn * kPanelBytes, &tmV, &v_full[s],
+          tma_load_3d(sV + sv * kTile + pn * kPanelBytes, &tmV, &v_full[sv],
                       p.v_col0 + hkv * D + pn * 64, j * 128, b);
       }
     }
@@ -183,19 +188,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       };
       if (ok) ok = issue_s(0);
       for (int j = 0; j < nkv && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+        const int sv = j % VS;
+        const uint32_t phv = (j / VS) & 1;
         if (!mbar_wait(&p_full, j & 1, &abort_flag, p.status, kTimeoutFlag, j)) break;
-        if (!mbar_wait(&v_full[s], ph, &abort_flag, p.status, kTimeoutFull, 100 + j)) break;
+        // P(j) written means S(j) has been consumed: the next score tile goes first, so that
+        // the softmax of block j+1 can start while P(j) V(j) is still running
+        if (j + 1 < nkv) ok = issue_s(j + 1);
+        if (!ok) break;
+        if (!mbar_wait(&v_full[sv], phv, &abort_flag, p.status, kTimeoutFull, 100 + j)) break;
         tc_fence_after();
-        const uint32_t aV = smem_u32(sV + s * kTile);
+        const uint32_t aV = smem_u32(sV + sv * kTile);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           umma_bf16_ss(tmem_base + kColO, desc_kmajor(aP, k), desc_mnmajor(aV, k), idesc_o,
                        k > 0 ? 1u : 0u);
-        umma_commit(&v_empty[s]);
+        umma_commit(&v_empty[sv]);
         umma_commit(&o_full);
-        if (j + 1 < nkv) ok = issue_s(j + 1);
       }
     }
   } else {
@@ -249,8 +257,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const int kv = kv0 + cc * 32 + i;
             if (kv >= p.T || (p.causal && kv > q_idx)) e = 0.f;
           }
-          // the MMA consumes bf16 probabilities; sum the same rounded values
-          e = __bfloat162float(__float2bfloat16(e));
           pv[i] = e;
           rowsum += e;
         }
@@ -262,8 +268,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full);
-#pragma unroll
-      for (int d = 0; d < D; ++d) o[d] *= alpha;
       if (!mbar_wait_warp(&o_full, j & 1, &abort_flag, p.status, kTimeoutTmemFull, 100 + j)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll
@@ -272,7 +276,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld_32x32(t_lane + kColO + cc * 32, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[cc * 32 + i] += __uint_as_float(r[i]);
+        for (int i = 0; i < 32; ++i)
+          o[cc * 32 + i] = fmaf(o[cc * 32 + i], alpha, __uint_as_float(r[i]));
       }
     }
     if (ok && q_idx < p.T) {
@@ -680,7 +685,7 @@ MMJ_API int mmj_attn_fwd(const void* q, long long ldq, int q_col0, const void* k
   dim3 grid((T + 127) / 128, Hq, B);
   static bool attr64 = false, attr128 = false;
   if (D == 64) {
-    const int smem = 5 * kPanelBytes + 2 * kPanelBytes + 1024;
+    const int smem = 4 * kPanelBytes + 2 * kPanelBytes + 1024;  // Q + 2 K + 1 V + P
     if (!attr64) {
       cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       attr64 = true;

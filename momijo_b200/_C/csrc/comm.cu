@@ -35,14 +35,18 @@ __device__ __forceinline__ void st_rel_sys(int* p, int v) {
 // Bounded wait for *flag >= want (system scope). false on timeout.
 __device__ __forceinline__ bool wait_sys_ge(const int* flag, int want, int* status, int detail) {
   if (ld_acq_sys(flag) >= want) return true;
-  const uint64_t t0 = globaltimer_ns();
+  uint64_t t0 = 0;  // %globaltimer is slow to read: start the clock only after many polls
   uint32_t it = 0;
   while (true) {
     if (ld_acq_sys(flag) >= want) return true;
-    __nanosleep(100);
-    if (((++it) & 0xff) == 0 && globaltimer_ns() - t0 > MMJ_WAIT_BUDGET_NS) {
-      report(status, kTimeoutBarrier, detail);
-      return false;
+    __nanosleep(64);
+    if (((++it) & 0xff) == 0) {
+      if (t0 == 0) {
+        t0 = globaltimer_ns();
+      } else if (globaltimer_ns() - t0 > MMJ_WAIT_BUDGET_NS) {
+        report(status, kTimeoutBarrier, detail);
+        return false;
+      }
     }
   }
 }

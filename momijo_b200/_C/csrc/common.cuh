@@ -98,13 +98,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           volatile int* abort_flag, int* status, int code,
                                           int detail) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  // Reading %globaltimer costs on the order of a microsecond, so the clock is only consulted
+  // after many failed polls; the common case (the phase completes within a few polls) never
+  // touches it.
+  uint64_t t0 = 0;
   uint32_t it = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (((++it) & 0x3f) == 0) {
+    if (((++it) & 0x3ff) == 0) {
       if (*abort_flag) return false;
+      if (t0 == 0) {
+        t0 = globaltimer_ns();
+        continue;
+      }
       if (globaltimer_ns() - t0 > MMJ_WAIT_BUDGET_NS) {
         *abort_flag = 1;
         report(status, code, detail);

@@ -52,14 +52,18 @@ __device__ __forceinline__ bool wait_flag_ge(const int* flag, int want, bool sys
                                              volatile int* abort_flag, int* status, int detail) {
   int v = sys_scope ? ld_acquire_sys(flag) : ld_acquire_gpu(flag);
   if (v >= want) return true;
-  const uint64_t t0 = globaltimer_ns();
+  uint64_t t0 = 0;  // %globaltimer is slow to read: start the clock only after many polls
   uint32_t it = 0;
   while (true) {
     v = sys_scope ? ld_acquire_sys(flag) : ld_acquire_gpu(flag);
     if (v >= want) return true;
-    __nanosleep(64);
-    if (((++it) & 0x3f) == 0) {
+    __nanosleep(32);
+    if (((++it) & 0xff) == 0) {
       if (*abort_flag) return false;
+      if (t0 == 0) {
+        t0 = globaltimer_ns();
+        continue;
+      }
       if (globaltimer_ns() - t0 > MMJ_WAIT_BUDGET_NS) {
         *abort_flag = 1;
         report(status, kTimeoutFlag, detail);
@@ -81,9 +85,20 @@ __device__ __forceinline__ TileCoord tile_of(int t, int num_m, int num_n, const 
   if (p.flag_mode == 2) {
     n_lin = t / num_m;
     m_lin = t - n_lin * num_m;
-  } else {
+  } else if (p.flag_mode == 1 || num_n <= 12) {
     m_lin = t / num_n;
     n_lin = t - m_lin * num_n;
+  } else {
+    // wide outputs: walk groups of 16 row tiles with n outer / m inner, so that one wave of
+    // CTAs covers a roughly square block of tiles and re-reads fewer operand panels from DRAM
+    constexpr int kGroupM = 16;
+    const int per_group = kGroupM * num_n;
+    const int g = t / per_group;
+    const int first_m = g * kGroupM;
+    const int rows_in_group = min(kGroupM, num_m - first_m);
+    const int r = t - g * per_group;
+    n_lin = r / rows_in_group;
+    m_lin = first_m + (r - n_lin * rows_in_group);
   }
   TileCoord c;
   c.m_tile = m_lin + p.m_tile_rot;

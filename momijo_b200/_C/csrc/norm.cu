@@ -208,12 +208,26 @@ __global__ void norm_bwd_finalize_kernel(const float* __restrict__ partial_dg,
                                          __nv_bfloat16* __restrict__ dgamma,
                                          __nv_bfloat16* __restrict__ dbeta, int nparts, int C,
                                          int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
+  // block (32, 8): 32 adjacent columns, the partial rows split over threadIdx.y
+  __shared__ float sa[8][33], sb[8][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float a = 0.f, b = 0.f;
-  for (int p = 0; p < nparts; ++p) {
-    a += partial_dg[(size_t)p * C + c];
-    if (partial_db != nullptr) b += partial_db[(size_t)p * C + c];
+  if (c < C) {
+    for (int p = threadIdx.y; p < nparts; p += 8) {
+      a += partial_dg[(size_t)p * C + c];
+      if (partial_db != nullptr) b += partial_db[(size_t)p * C + c];
+    }
+  }
+  sa[threadIdx.y][threadIdx.x] = a;
+  sb[threadIdx.y][threadIdx.x] = b;
+  __syncthreads();
+  if (threadIdx.y != 0 || c >= C) return;
+  a = 0.f;
+  b = 0.f;
+#pragma unroll
+  for (int y = 0; y < 8; ++y) {
+    a += sa[y][threadIdx.x];
+    b += sb[y][threadIdx.x];
   }
   if (accumulate) {
     a += __bfloat162float(dgamma[c]);
@@ -281,7 +295,7 @@ MMJ_API int mmj_norm_bwd(const void* dy, const void* x, const void* gamma, const
     norm_bwd_kernel<2><<<nparts, threads, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, mean, rstd,
         (const __nv_bfloat16*)dres_in, (__nv_bfloat16*)dx, pdg, pdb, rows, C, mode);
-  norm_bwd_finalize_kernel<<<(C + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+  norm_bwd_finalize_kernel<<<(C + 31) / 32, dim3(32, 8), 0, (cudaStream_t)stream>>>(
       pdg, pdb, (__nv_bfloat16*)dgamma, (__nv_bfloat16*)dbeta, nparts, C, accumulate);
   return (int)cudaGetLastError();
 }

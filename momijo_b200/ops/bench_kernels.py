@@ -34,7 +34,7 @@ def peaks():
 
 def bench_gemm(small):
     flops_peak, _, tag = peaks()
-    shapes = [(2048, 2304, 768, False, False)] if small else [
+    shapes = [(16384, 2304, 768, False, False), (8192, 8192, 4096, False, False)] if small else [
         (16384, 2304, 768, False, False), (16384, 768, 768, False, False),
         (16384, 3072, 768, False, False), (16384, 768, 3072, False, False),
         (16384, 50304, 768, False, False), (16384, 768, 50304, False, True),
