@@ -1,0 +1,108 @@
+"""Tensor losses (legacy/src/momijo/learn/losses/losses.mojo:46-273).
+
+``softmax_cross_entropy`` returns ``(loss, dlogits)`` in one call like the reference; on CUDA bf16
+logits it is the fused kernel of ``momijo_b200.ops``.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as tF
+
+from ... import ops
+
+
+def _reduce(x, reduction):
+    if reduction == "mean":
+        return x.mean()
+    if reduction == "sum":
+        return x.sum()
+    return x
+
+
+def cross_entropy_from_probs(probs, y_onehot, eps: float = 1e-7):
+    """-sum(y * log(clip(p))) / N  (losses.mojo:46)."""
+    p = probs.clamp(eps, 1.0 - eps)
+    return -(y_onehot * p.log()).sum() / probs.shape[0]
+
+
+def cross_entropy_from_logits(logits, y_onehot):
+    return -(y_onehot * torch.log_softmax(logits.float(), -1)).sum() / logits.shape[0]
+
+
+def softmax_cross_entropy(logits, y):
+    """``y`` is either one-hot ``[N, C]`` or class indices ``[N]``. Returns (loss, dlogits) with
+    ``dlogits = (softmax - onehot) / N`` (losses.mojo:72-85)."""
+    if y.dtype in (torch.int64, torch.int32) and y.dim() == logits.dim() - 1:
+        return ops.softmax_cross_entropy(logits, y.long())
+    probs = torch.softmax(logits.float(), -1)
+    loss = cross_entropy_from_probs(probs, y.float())
+    return loss, ((probs - y.float()) / logits.shape[0]).to(logits.dtype)
+
+
+def mse(pred, target, reduction="mean"):
+    return _reduce((pred - target) ** 2, reduction)
+
+
+def mae(pred, target, reduction="mean"):
+    return _reduce((pred - target).abs(), reduction)
+
+
+def huber(pred, target, delta=1.0, reduction="mean"):
+    d = (pred - target).abs()
+    return _reduce(torch.where(d <= delta, 0.5 * d * d, delta * (d - 0.5 * delta)), reduction)
+
+
+def smooth_l1(pred, target, beta=1.0, reduction="mean"):
+    d = (pred - target).abs()
+    return _reduce(torch.where(d < beta, 0.5 * d * d / beta, d - 0.5 * beta), reduction)
+
+
+def bce(probs, target, eps=1e-12, reduction="mean"):
+    p = probs.clamp(eps, 1 - eps)
+    return _reduce(-(target * p.log() + (1 - target) * (1 - p).log()), reduction)
+
+
+def bce_with_logits(logits, target, pos_weight=None, reduction="mean"):
+    """Stable form max(x,0) - x*t + log1p(exp(-|x|))."""
+    x = logits
+    loss = x.clamp_min(0) - x * target + torch.log1p(torch.exp(-x.abs()))
+    if pos_weight is not None:
+        loss = loss * (1 + (pos_weight - 1) * target)
+    return _reduce(loss, reduction)
+
+
+def kl_div(log_p, q, reduction="mean"):
+    """sum q * (log q - log_p)."""
+    return _reduce(torch.where(q > 0, q * (q.clamp_min(1e-38).log() - log_p), torch.zeros_like(q)), reduction)
+
+
+def nll_loss(log_probs, target, class_weight=None, reduction="mean"):
+    return tF.nll_loss(log_probs, target, weight=class_weight, reduction=reduction)
+
+
+def cross_entropy(logits, target, class_weight=None, reduction="mean"):
+    return tF.cross_entropy(logits.float(), target, weight=class_weight, reduction=reduction)
+
+
+def focal(logits, target, gamma=2.0, alpha=0.25, reduction="mean"):
+    p = torch.sigmoid(logits)
+    ce = bce_with_logits(logits, target, reduction="none")
+    pt = p * target + (1 - p) * (1 - target)
+    a = alpha * target + (1 - alpha) * (1 - target)
+    return _reduce(a * (1 - pt) ** gamma * ce, reduction)
+
+
+def dice(probs, target, eps=1e-6):
+    inter = (probs * target).sum()
+    return 1.0 - (2 * inter + eps) / (probs.sum() + target.sum() + eps)
+
+
+def triplet(anchor, positive, negative, margin=1.0, reduction="mean"):
+    dp = (anchor - positive).pow(2).sum(-1).sqrt()
+    dn = (anchor - negative).pow(2).sum(-1).sqrt()
+    return _reduce((dp - dn + margin).clamp_min(0), reduction)
+
+
+def cosine_embedding(a, b, y, margin=0.0, reduction="mean"):
+    cos = tF.cosine_similarity(a, b, dim=-1)
+    return _reduce(torch.where(y > 0, 1 - cos, (cos - margin).clamp_min(0)), reduction)

@@ -1,0 +1,18 @@
+"""``AvgPool2d(kernel_size, stride=(0,0)->kernel, padding=(0,0))``: averages over the in-bounds
+elements only (legacy/src/momijo/learn/nn/avgpool.mojo:9-57)."""
+import torch.nn.functional as tF
+
+from .module import Module
+from .functional import _pair
+
+
+class AvgPool2d(Module):
+    def __init__(self, kernel_size, stride=(0, 0), padding=(0, 0)):
+        super().__init__()
+        self.kernel_size = _pair(kernel_size)
+        s = _pair(stride)
+        self.stride = self.kernel_size if (s[0] == 0 or s[1] == 0) else s
+        self.padding = _pair(padding)
+
+    def forward(self, x, ctx=None):
+        return tF.avg_pool2d(x, self.kernel_size, self.stride, self.padding, count_include_pad=False)

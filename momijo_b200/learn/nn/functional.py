@@ -1,0 +1,120 @@
+"""Functional convolution / pooling helpers (NCHW).
+
+Names follow legacy/src/momijo/learn/nn/functional.mojo: ``im2col/col2im`` (:285-424),
+``conv2d_naive`` and ``conv2d`` (im2col + GEMM, :472), ``conv1d``, depthwise / pointwise /
+separable convolutions (:573-652), ``max_pool2d`` (:185), ``linear_mse_grads`` (:747). On CUDA
+bf16 tensors ``conv2d`` lowers to im2col followed by the tcgen05 GEMM of ``momijo_b200.ops``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Tuple
+
+import torch
+import torch.nn.functional as tF
+
+from ... import ops
+
+
+@dataclass
+class Conv2dConfig:
+    stride: Tuple[int, int] = (1, 1)
+    pad: Tuple[int, int] = (0, 0)
+    dilation: Tuple[int, int] = (1, 1)
+
+
+def _pair(v):
+    return (v, v) if isinstance(v, int) else tuple(v)
+
+
+def im2col(x, kernel, stride=(1, 1), pad=(0, 0)):
+    """[N, C, H, W] -> [N * OH * OW, C * kH * kW] (rows ordered n, oh, ow)."""
+    kernel, stride, pad = _pair(kernel), _pair(stride), _pair(pad)
+    cols = tF.unfold(x, kernel, padding=pad, stride=stride)  # [N, C*kH*kW, L]
+    return cols.transpose(1, 2).reshape(-1, cols.shape[1])
+
+
+def col2im(cols, x_shape, kernel, stride=(1, 1), pad=(0, 0)):
+    kernel, stride, pad = _pair(kernel), _pair(stride), _pair(pad)
+    N, C, H, W = x_shape
+    c = cols.reshape(N, -1, cols.shape[1]).transpose(1, 2)
+    return tF.fold(c, (H, W), kernel, padding=pad, stride=stride)
+
+
+def conv_out_size(h, k, s, p):
+    return (h + 2 * p - k) // s + 1
+
+
+def conv2d_naive(x, w, b=None, stride=(1, 1), pad=(0, 0)):
+    """Direct loops over the kernel window (reference semantics, for testing)."""
+    stride, pad = _pair(stride), _pair(pad)
+    N, C, H, W = x.shape
+    OC, _, kH, kW = w.shape
+    OH, OW = conv_out_size(H, kH, stride[0], pad[0]), conv_out_size(W, kW, stride[1], pad[1])
+    xp = tF.pad(x, (pad[1], pad[1], pad[0], pad[0]))
+    y = torch.zeros(N, OC, OH, OW, dtype=x.dtype, device=x.device)
+    for i in range(kH):
+        for j in range(kW):
+            patch = xp[:, :, i:i + stride[0] * OH:stride[0], j:j + stride[1] * OW:stride[1]]
+            y += torch.einsum("nchw,oc->nohw", patch, w[:, :, i, j])
+    if b is not None and b.numel():
+        y += b.view(1, -1, 1, 1)
+    return y
+
+
+def conv2d(x, w, b=None, stride=(1, 1), pad=(0, 0)):
+    """im2col + GEMM convolution; ``w`` is [OC, C, kH, kW]."""
+    stride, pad = _pair(stride), _pair(pad)
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        N, C, H, W = x.shape
+        OC, _, kH, kW = w.shape
+        OH, OW = conv_out_size(H, kH, stride[0], pad[0]), conv_out_size(W, kW, stride[1], pad[1])
+        K = C * kH * kW
+        Kp = (K + 7) // 8 * 8
+        cols = im2col(x, (kH, kW), stride, pad)
+        w2 = w.reshape(OC, K)
+        if Kp != K:  # TMA rows must be 16-byte multiples
+            cols = tF.pad(cols, (0, Kp - K))
+            w2 = tF.pad(w2, (0, Kp - K))
+        y = ops.linear(cols.contiguous(), w2.contiguous(), b if (b is not None and b.numel()) else None)
+        return y.reshape(N, OH, OW, OC).permute(0, 3, 1, 2).contiguous()
+    return tF.conv2d(x, w, b if (b is not None and b.numel()) else None, stride, pad)
+
+
+def conv1d(x, w, b=None, stride=1, pad=0):
+    return tF.conv1d(x, w, b, stride, pad)
+
+
+def depthwise_conv2d(x, w, b=None, stride=(1, 1), pad=(0, 0)):
+    """``w`` is [C, 1, kH, kW]."""
+    return tF.conv2d(x, w, b, _pair(stride), _pair(pad), groups=x.shape[1])
+
+
+def pointwise_conv2d(x, w, b=None):
+    """1x1 convolution; ``w`` is [OC, C] or [OC, C, 1, 1]."""
+    if w.dim() == 2:
+        w = w[:, :, None, None]
+    return conv2d(x, w, b)
+
+
+def separable_conv2d(x, w_depth, w_point, b=None, stride=(1, 1), pad=(0, 0)):
+    return pointwise_conv2d(depthwise_conv2d(x, w_depth, None, stride, pad), w_point, b)
+
+
+def max_pool2d(x, kernel, stride=(1, 1), pad=(0, 0)):
+    """Reference default stride is 1, not the kernel size (legacy/.../nn/conv.mojo:29-46)."""
+    return tF.max_pool2d(x, _pair(kernel), _pair(stride), _pair(pad))
+
+
+def linear_mse_grads(x, w, b, y_true):
+    """Gradients of mean((x W^T + b - y)^2) with respect to (W, b)."""
+    pred = x @ w.t() + b
+    diff = 2.0 * (pred - y_true) / pred.numel()
+    return diff.t() @ x, diff.sum(0)
+
+
+def rowwise_relu_normalize(s):
+    """max(0, s) / sum(max(0, s)) over the last dim: the reference attention's normaliser
+    (legacy/src/momijo/learn/nn/functional.mojo:674-694)."""
+    r = torch.relu(s)
+    return r / r.sum(-1, keepdim=True).clamp_min(1e-12)

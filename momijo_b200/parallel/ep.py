@@ -64,6 +64,15 @@ class MoEDispatcher:
         self.which = 0
         self._idx = None
 
+    def _ptrs_of(self, y):
+        for b, ptrs in zip(self.yout, self._y_ptrs):
+            if y is b or y.data_ptr() == b.data_ptr():
+                return ptrs
+        for b, ptrs in zip(self.recv, self._recv_ptrs):
+            if y is b or y.data_ptr() == b.data_ptr():
+                return ptrs
+        return self.comm.peer_ptrs(y)
+
     # -- buffers of the current call --
     def expert_out_buffer(self):
         return self.yout[self.which]
@@ -111,8 +120,7 @@ class MoEDispatcher:
         idx = self._idx
         n_tokens = idx.numel() // self.k if n_tokens is None else n_tokens
         out = torch.empty((n_tokens, self.H), dtype=bf16, device=c.device)
-        which = self.yout.index(y) if any(y is b for b in self.yout) else None
-        ptrs = self._y_ptrs[which] if which is not None else c.peer_ptrs(y)
+        ptrs = self._ptrs_of(y)
         gw = None if gate_w is None else gate_w.reshape(-1).contiguous().float()
         _C.call("mmj_moe_combine", c._sig_ptrs, ptrs, _C.ptr(idx), _C.ptr(self.src_row), _C.ptr(gw),
                 _C.ptr(out), _C.ptr(residual), n_tokens, self.k, self.H, self.E, c.world, c.rank,
@@ -125,8 +133,7 @@ class MoEDispatcher:
         idx = self._idx
         n_assign = idx.numel()
         dg = torch.empty(n_assign, dtype=torch.float32, device=c.device)
-        which = self.yout.index(y) if any(y is b for b in self.yout) else None
-        ptrs = self._y_ptrs[which] if which is not None else c.peer_ptrs(y)
+        ptrs = self._ptrs_of(y)
         _C.call("mmj_moe_gate_grad", ptrs, _C.ptr(dout), _C.ptr(idx), _C.ptr(self.src_row),
                 _C.ptr(dg), n_assign, self.k, self.H, self.E, c.world, _C.current_stream())
         return dg.view(-1, self.k)
