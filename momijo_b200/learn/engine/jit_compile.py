@@ -1,0 +1,69 @@
+"""JIT facade (legacy/src/momijo/learn/engine/jit_compile.mojo:30-184). ``compile`` returns the
+model unchanged in the reference; here ``JITOptions.graph`` captures the model's forward in a
+CUDA graph (static shapes), which removes launch overhead without a tracing compiler, and
+``check_numerics`` adds a finite check on the outputs."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+
+@dataclass
+class JITOptions:
+    graph: bool = False
+    optimize: bool = True
+    check_numerics: bool = False
+    allow_mixed_precision: bool = True
+
+
+class GraphExecutor:
+    """Runs a callable; with ``graph=True`` on CUDA the first call is captured and replayed."""
+
+    def __init__(self, fn, options: JITOptions | None = None):
+        self.fn, self.options = fn, options or JITOptions()
+        self._graph = self._static_in = self._static_out = None
+
+    def run(self, batch):
+        o = self.options
+        if o.graph and isinstance(batch, torch.Tensor) and batch.is_cuda and not torch.is_grad_enabled():
+            out = self._run_graph(batch)
+        else:
+            out = self.fn(batch) if self.fn is not None else batch
+        if o.check_numerics and isinstance(out, torch.Tensor) and not torch.isfinite(out).all():
+            raise FloatingPointError("non-finite values in the output")
+        return out
+
+    __call__ = run
+
+    def _run_graph(self, x):
+        if self._graph is None or self._static_in.shape != x.shape:
+            self._static_in = x.clone()
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                for _ in range(2):
+                    self.fn(self._static_in)
+            torch.cuda.current_stream().wait_stream(s)
+            self._graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self._graph):
+                self._static_out = self.fn(self._static_in)
+        self._static_in.copy_(x)
+        self._graph.replay()
+        return self._static_out
+
+
+def compile(model, options: JITOptions | None = None):
+    """Reference semantics: the model comes back unchanged (jit_compile.mojo:115)."""
+    return model
+
+
+def compile_with(model, options: JITOptions) -> GraphExecutor:
+    return GraphExecutor(model, options)
+
+
+def dry_trace(model, example):
+    """Run once without gradients and report output shape/dtype."""
+    with torch.no_grad():
+        out = model(example)
+    return {"shape": list(out.shape), "dtype": str(out.dtype)} if isinstance(out, torch.Tensor) else {}

@@ -1,0 +1,225 @@
+"""Factories (legacy/src/momijo/tensor/creation.mojo:57-1509): typed zeros/ones/full/eye/arange/
+linspace/rand/randn/randperm/from_list families. Every random factory takes an explicit seed and
+the same seed gives the same values (``SplitMix64`` / ``RNG64`` in the reference; torch's seeded
+generator here)."""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from .tensor import Tensor, _wrap
+
+_F32, _F64, _I64, _I32, _I16, _I8, _U8, _B = (torch.float32, torch.float64, torch.int64, torch.int32,
+                                            torch.int16, torch.int8, torch.uint8, torch.bool)
+
+
+class SplitMix64:
+    def __init__(self, seed: int = 0):
+        self.state = seed & ((1 << 64) - 1)
+
+    def next_u64(self) -> int:
+        M = (1 << 64) - 1
+        self.state = (self.state + 0x9E3779B97F4A7C15) & M
+        z = self.state
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & M
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & M
+        return z ^ (z >> 31)
+
+
+class RNG64(SplitMix64):
+    def uniform(self) -> float:
+        return (self.next_u64() >> 11) * (1.0 / 9007199254740992.0)
+
+
+def _shape(shape):
+    return [shape] if isinstance(shape, int) else list(shape)
+
+
+def _dev(ctx):
+    """``ctx`` may be a RuntimeDeviceContext / Device / torch device / None."""
+    if ctx is None:
+        return None
+    if hasattr(ctx, "torch_device"):
+        return ctx.torch_device()
+    return ctx
+
+
+def _gen(seed):
+    return torch.Generator().manual_seed(int(seed) & 0x7FFFFFFFFFFFFFFF)
+
+
+def zeros(shape, dtype=_F64, ctx=None):
+    return _wrap(torch.zeros(_shape(shape), dtype=dtype, device=_dev(ctx)))
+
+
+def ones(shape, dtype=_F64, ctx=None):
+    return _wrap(torch.ones(_shape(shape), dtype=dtype, device=_dev(ctx)))
+
+
+def full(shape, value, dtype=None, ctx=None):
+    return _wrap(torch.full(_shape(shape), value, dtype=dtype, device=_dev(ctx)))
+
+
+def empty(shape, dtype=_F64, ctx=None):
+    return _wrap(torch.empty(_shape(shape), dtype=dtype, device=_dev(ctx)))
+
+
+def zeros_like(x):
+    return _wrap(torch.zeros_like(x))
+
+
+def ones_like(x):
+    return _wrap(torch.ones_like(x))
+
+
+def full_like(x, v):
+    return _wrap(torch.full_like(x, v))
+
+
+def eye(n, m=None, dtype=_F64):
+    return _wrap(torch.eye(n, m if m is not None else n, dtype=dtype))
+
+
+def scalar_f64(v):
+    return _wrap(torch.tensor(float(v), dtype=_F64))
+
+
+def scalar_f32(v):
+    return _wrap(torch.tensor(float(v), dtype=_F32))
+
+
+def scalar_int(v):
+    return _wrap(torch.tensor(int(v), dtype=_I64))
+
+
+def _typed(fn_name, fn, table):
+    for suffix, dt in table.items():
+        def f(*a, _dt=dt, **k):
+            return fn(*a, dtype=_dt, **k)
+        f.__name__ = f"{fn_name}_{suffix}"
+        globals()[f.__name__] = f
+
+
+_T = {"f64": _F64, "f32": _F32, "int": _I64, "i32": _I32, "i16": _I16, "i8": _I8, "u8": _U8, "bool": _B}
+_typed("zeros", zeros, _T)
+_typed("ones", ones, _T)
+_typed("empty", empty, _T)
+_typed("eye", eye, {"f64": _F64, "f32": _F32, "int": _I64})
+
+
+def arange_dt(start, stop=None, step=1, dtype=_F64):
+    if stop is None:
+        start, stop = 0, start
+    return _wrap(torch.arange(start, stop, step, dtype=dtype))
+
+
+def arange_f64(start, stop=None, step=1):
+    return arange_dt(start, stop, step, _F64)
+
+
+def arange_f32(start, stop=None, step=1):
+    return arange_dt(start, stop, step, _F32)
+
+
+def arange_int(start, stop=None, step=1):
+    return arange_dt(start, stop, step, _I64)
+
+
+arange = arange_f32
+
+
+def linspace_f64(start, stop, num, endpoint=True):
+    if not endpoint and num > 0:
+        stop = start + (stop - start) * (num - 1) / num
+    return _wrap(torch.linspace(start, stop, num, dtype=_F64))
+
+
+def linspace_f32(start, stop, num, endpoint=True):
+    return _wrap(linspace_f64(start, stop, num, endpoint).to(_F32))
+
+
+def linspace_int(start, stop, num, endpoint=True):
+    return _wrap(linspace_f64(start, stop, num, endpoint).round().to(_I64))
+
+
+def rand(shape, seed: int = 0, dtype=_F64):
+    return _wrap(torch.rand(_shape(shape), generator=_gen(seed), dtype=torch.float64).to(dtype))
+
+
+def randn(shape, seed: int = 0, dtype=_F64):
+    return _wrap(torch.randn(_shape(shape), generator=_gen(seed), dtype=torch.float64).to(dtype))
+
+
+def randn_f64(shape, seed: int = 0):
+    return randn(shape, seed, _F64)
+
+
+def randn_f32(shape, seed: int = 0):
+    return randn(shape, seed, _F32)
+
+
+def randn_int(shape, seed: int = 0):
+    return _wrap(randn(shape, seed, _F64).round().to(_I64))
+
+
+def rand_f64(shape, seed: int = 0):
+    return rand(shape, seed, _F64)
+
+
+def rand_f32(shape, seed: int = 0):
+    return rand(shape, seed, _F32)
+
+
+def normal(shape, mean=0.0, std=1.0, seed: int = 0, dtype=_F64):
+    return _wrap((randn(shape, seed, _F64) * std + mean).to(dtype))
+
+
+def uniform(shape, lo=0.0, hi=1.0, seed: int = 0, dtype=_F64):
+    return _wrap((rand(shape, seed, _F64) * (hi - lo) + lo).to(dtype))
+
+
+def randint(shape, lo, hi, seed: int = 0):
+    return _wrap(torch.randint(lo, hi, _shape(shape), generator=_gen(seed)))
+
+
+def bernoulli(shape, p=0.5, seed: int = 0):
+    return _wrap((torch.rand(_shape(shape), generator=_gen(seed)) < p).to(_I64))
+
+
+bernoulli_int = bernoulli
+
+
+def bernoulli_f64(shape, p=0.5, seed: int = 0):
+    return _wrap(bernoulli(shape, p, seed).to(_F64))
+
+
+def randperm_int(n, seed: int = 0):
+    return _wrap(torch.randperm(n, generator=_gen(seed)))
+
+
+def randperm_f64(n, seed: int = 0):
+    return _wrap(randperm_int(n, seed).to(_F64))
+
+
+def randperm_f32(n, seed: int = 0):
+    return _wrap(randperm_int(n, seed).to(_F32))
+
+
+def _from_list(dt):
+    def f(xs, shape: Optional[Sequence[int]] = None):
+        t = torch.tensor(xs, dtype=dt)
+        return _wrap(t.reshape(list(shape)) if shape is not None else t)
+    return f
+
+
+for _name, _dt in {"float64": _F64, "float32": _F32, "int": _I64, "int32": _I32, "int16": _I16,
+                   "int8": _I8, "uint8": _U8, "bool": _B}.items():
+    globals()[f"from_list_{_name}"] = _from_list(_dt)
+    globals()[f"from_2d_list_{_name}"] = _from_list(_dt)
+    globals()[f"from_3d_list_{_name}"] = _from_list(_dt)
+
+
+def from_list(xs, dtype=None, shape=None):
+    t = torch.tensor(xs, dtype=dtype)
+    return _wrap(t.reshape(list(shape)) if shape is not None else t)

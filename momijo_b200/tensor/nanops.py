@@ -1,0 +1,54 @@
+"""NaN-aware helpers (legacy/src/momijo/tensor/nanops.mojo:111-655)."""
+import torch
+
+from .tensor import _raw, _wrap
+
+
+def isnan(x): return _wrap(torch.isnan(_raw(x)).to(torch.int64))
+def isinf(x): return _wrap(torch.isinf(_raw(x)).to(torch.int64))
+def isfinite(x): return _wrap(torch.isfinite(_raw(x)).to(torch.int64))
+
+
+def nan_to_num(x, nan=0.0, posinf=None, neginf=None):
+    return _wrap(torch.nan_to_num(_raw(x), nan=nan, posinf=posinf, neginf=neginf))
+
+
+def nansum(x, axis=None, keepdims=False):
+    return _wrap(torch.nansum(_raw(x)) if axis is None else torch.nansum(_raw(x), dim=axis, keepdim=keepdims))
+
+
+def nanmean(x, axis=None, keepdims=False):
+    return _wrap(torch.nanmean(_raw(x)) if axis is None else torch.nanmean(_raw(x), dim=axis, keepdim=keepdims))
+
+
+def nanmin(x, axis=None):
+    r = torch.where(torch.isnan(_raw(x)), torch.full_like(_raw(x), float("inf")), _raw(x))
+    return _wrap(r.min() if axis is None else r.min(axis).values)
+
+
+def nanmax(x, axis=None):
+    r = torch.where(torch.isnan(_raw(x)), torch.full_like(_raw(x), float("-inf")), _raw(x))
+    return _wrap(r.max() if axis is None else r.max(axis).values)
+
+
+def nanstd(x, axis=None):
+    r = _raw(x).double()
+    m = torch.nanmean(r) if axis is None else torch.nanmean(r, dim=axis, keepdim=True)
+    d = torch.where(torch.isnan(r), torch.zeros_like(r), (r - m) ** 2)
+    n = (~torch.isnan(r)).sum() if axis is None else (~torch.isnan(r)).sum(axis)
+    s = d.sum() if axis is None else d.sum(axis)
+    return _wrap((s / n.clamp_min(1)).sqrt())
+
+
+def safe_div(a, b, fill=0.0):
+    from .math import safe_div as f
+
+    return f(a, b, fill)
+
+
+def safe_log(x, eps=1e-12):
+    return _wrap(torch.log(_raw(x).double().clamp_min(eps)))
+
+
+def safe_sqrt(x):
+    return _wrap(torch.sqrt(_raw(x).double().clamp_min(0.0)))
