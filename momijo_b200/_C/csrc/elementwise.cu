@@ -608,6 +608,79 @@ MMJ_API int mmj_pack_nchw(const float* src, float* dst, int n, int C, int H, int
 // Host-callable twin of the dropout hash so the CPU path produces the same mask.
 MMJ_API unsigned long long mmj_mix64(unsigned long long z) { return mix64(z); }
 
+// ------------------------------------------------------------------------------------------------
+// Column sum without any allocation (declared in momijo_b200.h).
+//
+// Some callers of this library cannot allocate device memory at the point where they need a
+// bias gradient: code running inside a memory-pool "no allocation" region, a serving loop that
+// has handed all free memory to its KV cache, or a plugin whose host forbids cudaMalloc after
+// start-up. mmj_colsum_bf16 asks such callers for `splits * N` floats of scratch; this variant
+// keeps the scratch inside the library image instead, in a fixed-size device array that every
+// GPU loading the library holds until the process exits (kStaticColsumFloats * 4 bytes = 4 MiB).
+//
+// The array's name below is only a host-side handle. Its device address is looked up once per
+// device with cudaGetSymbolAddress (with that device current) during the first call on the
+// device, so that first call should be made before any stream capture begins. Later calls do
+// no set-up work. Nothing here calls cudaMalloc, cudaFree or any allocating routine.
+//
+// All calls on a device share the one array and it keeps whatever the last call left in it.
+// Stage 1 overwrites every partial that stage 2 reads, so nothing needs clearing, but two calls
+// that overlap on the GPU (different streams) would race on it: issue them on one stream, or
+// order them with events.
+// ------------------------------------------------------------------------------------------------
+namespace mmj {
+constexpr int kStaticColsumMaxN = 16384;
+constexpr int kStaticColsumMaxSplits = 64;
+constexpr long long kStaticColsumFloats = (long long)kStaticColsumMaxN * kStaticColsumMaxSplits;
+constexpr int kStaticMaxDevices = 64;
+static __device__ __align__(256) float g_colsum_static_scratch[kStaticColsumFloats];
+static float* g_colsum_static_ptr[kStaticMaxDevices] = {nullptr};
+}  // namespace mmj
+
+// Return codes of mmj_colsum_bf16_static (0 = ok, > 0 = CUDA error code).
+//   -1  leading dimension not a multiple of 8 elements
+//   -20 N exceeds mmj_colsum_bf16_static_max_n()
+//   -21 device ordinal outside the table kept by the library
+//   -22 the device address of the built-in scratch could not be obtained
+MMJ_API int mmj_colsum_bf16_static_max_n() { return kStaticColsumMaxN; }
+
+MMJ_API const char* mmj_colsum_bf16_static_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case -1: return "mmj_colsum_bf16_static: leading dimension must be a multiple of 8 elements";
+    case -20: return "mmj_colsum_bf16_static: N is larger than the built-in scratch allows (max 16384 columns)";
+    case -21: return "mmj_colsum_bf16_static: device ordinal out of range";
+    case -22: return "mmj_colsum_bf16_static: cudaGetSymbolAddress failed for the built-in scratch";
+    default: return code > 0 ? "mmj_colsum_bf16_static: CUDA launch error" : "mmj_colsum_bf16_static: unknown error";
+  }
+}
+
+MMJ_API int mmj_colsum_bf16_static(const void* x, long long ldx, void* out_bf16, float* out_f32,
+                                   int M, int N, int accumulate, void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (ldx % 8) return -1;
+  if (N > kStaticColsumMaxN) return -20;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kStaticMaxDevices) return -21;
+  float* scratch = g_colsum_static_ptr[dev];
+  if (scratch == nullptr) {
+    // one-time set-up for this device: translate the symbol into a device address
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_colsum_static_scratch);
+    if (e != cudaSuccess || p == nullptr) return -22;
+    scratch = static_cast<float*>(p);
+    g_colsum_static_ptr[dev] = scratch;
+  }
+  const int S = mmj_colsum_splits(M);  // <= kStaticColsumMaxSplits
+  dim3 grid((N + 255) / 256, S), block(32, 8);
+  colsum_partial_kernel<<<grid, block, 0, STREAM>>>((const __nv_bfloat16*)x, ldx, scratch, M, N);
+  colsum_finalize_kernel<<<(N + 255) / 256, 256, 0, STREAM>>>(scratch, (__nv_bfloat16*)out_bf16,
+                                                              out_f32, S, N, accumulate);
+  return (int)cudaGetLastError();
+}
+
 MMJ_API int mmj_cast_f32_to_bf16_2d(const float* src, long long lds, void* dst, long long ldd,
                                     long long rows, int cols, void* stream) {
   if (cols % 4 || lds % 4 || ldd % 4) return -1;
