@@ -212,6 +212,10 @@ def all_gather(x: torch.Tensor, dim: int = 0, group=None) -> torch.Tensor:
         return x
     W = dist.get_world_size(group)
     xs = _dev(x.contiguous())
+    if _STATE["backend"] == "gloo":
+        parts = [torch.empty_like(xs) for _ in range(W)]
+        dist.all_gather(parts, xs, group=group)
+        return torch.cat(parts, dim=dim)
     out = torch.empty((W,) + tuple(xs.shape), dtype=xs.dtype, device=xs.device)
     dist.all_gather_into_tensor(out, xs, group=group)
     return torch.cat(list(out.unbind(0)), dim=dim)

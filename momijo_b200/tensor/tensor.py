@@ -129,9 +129,8 @@ class Tensor(torch.Tensor):
             idx = idx.to_index()
         elif isinstance(idx, tuple):
             idx = tuple(j for i in idx for j in (i.to_index() if isinstance(i, S) else (i,)))
-        if isinstance(idx, torch.Tensor) and idx.dtype in (torch.int64, torch.int32) and False:
-            pass
-        return super().__getitem__(idx)
+        src, idx = _resolve_negative_steps(self, idx)
+        return torch.Tensor.__getitem__(src, idx)
 
     def __setitem__(self, idx, value):
         if isinstance(idx, S):
@@ -301,11 +300,15 @@ class Tensor(torch.Tensor):
     def nanmin(self, axis=None):
         """True nan-aware minimum (the reference's method calls ``nansum`` by mistake,
         tensor.mojo:3239-3261)."""
-        r = torch.where(torch.isnan(_raw(self)), torch.full_like(_raw(self), float("inf")), _raw(self))
+        r = _raw(self)
+        if r.dtype.is_floating_point:
+            r = torch.where(torch.isnan(r), torch.full_like(r, float("inf")), r)
         return _wrap(r.min() if axis is None else r.min(dim=axis).values)
 
     def nanmax(self, axis=None):
-        r = torch.where(torch.isnan(_raw(self)), torch.full_like(_raw(self), float("-inf")), _raw(self))
+        r = _raw(self)
+        if r.dtype.is_floating_point:
+            r = torch.where(torch.isnan(r), torch.full_like(r, float("-inf")), r)
         return _wrap(r.max() if axis is None else r.max(dim=axis).values)
 
     # ---- linear algebra -----------------------------------------------------------------------------
@@ -472,6 +475,34 @@ class Tensor(torch.Tensor):
 
 def _all_py_float32(data) -> bool:
     return False
+
+
+def _resolve_negative_steps(t, idx):
+    """torch has no negative-step slices: flip the affected axes and rewrite the slice so that the
+    result equals NumPy's (the reference normalises such slices itself, tensor.mojo:676-718)."""
+    keys = idx if isinstance(idx, tuple) else (idx,)
+    if not any(isinstance(k, slice) and k.step is not None and k.step < 0 for k in keys):
+        return t, idx
+    n_real = sum(1 for k in keys if k is not None and k is not Ellipsis)
+    out, dim, flips = [], 0, []
+    for k in keys:
+        if k is None:
+            out.append(k)
+            continue
+        if k is Ellipsis:
+            dim += t.dim() - n_real
+            out.append(k)
+            continue
+        if isinstance(k, slice) and k.step is not None and k.step < 0:
+            n = t.shape[dim]
+            start, stop, step = k.indices(n)
+            flips.append(dim)
+            out.append(slice(n - 1 - start, n - 1 - stop, -step))
+        else:
+            out.append(k)
+        dim += 1
+    src = torch.flip(t.as_subclass(torch.Tensor), flips).as_subclass(type(t))
+    return src, (tuple(out) if isinstance(idx, tuple) else out[0])
 
 
 def as_tensor(x) -> Tensor:
