@@ -201,7 +201,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           umma_bf16_ss(tmem_base + kColO, desc_kmajor(aP, k), desc_mnmajor(aV, k), idesc_o,
-                       k > 0 ? 1u : 0u);
+                       (j > 0 || k > 0) ? 1u : 0u);
         umma_commit(&v_empty[sv]);
         umma_commit(&o_full);
       }
@@ -213,88 +213,112 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int q_idx = q0 + row;
     const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
     const float c = p.scale * 1.4426950408889634f;
-    float m = -INFINITY, l = 0.f;
-    float o[D];
-#pragma unroll
-    for (int d = 0; d < D; ++d) o[d] = 0.f;
+    // The output accumulator stays in tensor memory (P V accumulates into it); it is rescaled
+    // in place only when the running row maximum grows by more than kTau (in the exp2 domain),
+    // so most iterations neither read nor write it. Probabilities are then bounded by 2^kTau,
+    // which bf16 / fp32 hold comfortably, and the final 1/l normalisation makes the result exact.
+    constexpr float kTau = 8.0f;
+    float m_used = -1.0e30f, l = 0.f;
     bool ok = true;
     for (int j = 0; j < nkv; ++j) {
       if (!mbar_wait_warp(&s_full, j & 1, &abort_flag, p.status, kTimeoutTmemFull, j)) { ok = false; break; }
       tc_fence_after();
       const int kv0 = j * 128;
       const bool need_mask = (p.causal && (kv0 + 127 > q0)) || (kv0 + 128 > p.T);
-      float mx = m;
+      uint32_t s[128];
+      tmem_ld_32x32(t_lane + kColS + 0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_ld_32x32(t_lane + kColS + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+      tmem_ld_32x32(t_lane + kColS + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
+      tmem_ld_32x32(t_lane + kColS + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
+      tmem_ld_wait();
+      if (need_mask) {
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_lane + kColS + cc * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(r[i]);
-          if (need_mask) {
-            const int kv = kv0 + cc * 32 + i;
-            if (kv >= p.T || (p.causal && kv > q_idx)) s = -INFINITY;
-          }
-          mx = fmaxf(mx, s);
+        for (int i = 0; i < 128; ++i) {
+          const int kv = kv0 + i;
+          if (kv >= p.T || (p.causal && kv > q_idx)) s[i] = 0xff800000u;  // -inf
         }
       }
-      const float m_use = (mx == -INFINITY) ? 0.f : mx;
-      const float alpha = exp2f((m - m_use) * c);
-      const float mc = m_use * c;
-      float rowsum = 0.f;
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 128; i += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(s[i + 0]));
+        mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      const bool grow = (mx - m_used) * c > kTau;  // false for fully masked rows (mx = -inf)
+      if (__any_sync(0xffffffffu, grow ? 1 : 0)) {
+        float alpha = 1.0f;
+        if (grow) {
+          alpha = exp2f((m_used - mx) * c);
+          l *= alpha;
+          m_used = mx;
+        }
+        if (j > 0) {
+          // P(j-1) V(j-1) must have landed before the accumulator is rescaled
+          if (!mbar_wait_warp(&o_full, (j - 1) & 1, &abort_flag, p.status, kTimeoutTmemFull, 100 + j)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int cc = 0; cc < D / 32; ++cc) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_lane + kColO + cc * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32(t_lane + kColO + cc * 32, r);
+          }
+          tmem_st_wait();
+        }
+      }
+      const float mc = m_used * c;
+      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_lane + kColS + cc * 32, r);
-        tmem_ld_wait();
-        float pv[32];
+        float(&pv)[32] = *reinterpret_cast<float(*)[32]>(&s[cc * 32]);  // exponentiate in place
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(r[i]);
-          float e = exp2f(s * c - mc);
-          if (need_mask) {
-            const int kv = kv0 + cc * 32 + i;
-            if (kv >= p.T || (p.causal && kv > q_idx)) e = 0.f;
-          }
-          pv[i] = e;
-          rowsum += e;
+        for (int i = 0; i < 32; i += 4) {
+          pv[i + 0] = exp2f(fmaf(pv[i + 0], c, -mc));
+          pv[i + 1] = exp2f(fmaf(pv[i + 1], c, -mc));
+          pv[i + 2] = exp2f(fmaf(pv[i + 2], c, -mc));
+          pv[i + 3] = exp2f(fmaf(pv[i + 3], c, -mc));
+          sum0 += pv[i + 0]; sum1 += pv[i + 1]; sum2 += pv[i + 2]; sum3 += pv[i + 3];
         }
         store_chunk_sw128(sP, row, cc * 32, pv);
       }
-      l = l * alpha + rowsum;
-      m = mx;
+      l += (sum0 + sum1) + (sum2 + sum3);
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full);
-      if (!mbar_wait_warp(&o_full, j & 1, &abort_flag, p.status, kTimeoutTmemFull, 100 + j)) { ok = false; break; }
+    }
+    // final: wait for the last P V, normalise and store
+    if (ok && nkv > 0)
+      ok = mbar_wait_warp(&o_full, (nkv - 1) & 1, &abort_flag, p.status, kTimeoutTmemFull, 999);
+    if (ok) {
       tc_fence_after();
+      const float inv = (l > 0.f) ? 1.0f / l : 0.f;
+      __nv_bfloat16* dst = p.O + ((long long)b * p.T + q_idx) * p.ldo + p.o_col0 + h * D;
 #pragma unroll
       for (int cc = 0; cc < D / 32; ++cc) {
         uint32_t r[32];
         tmem_ld_32x32(t_lane + kColO + cc * 32, r);
         tmem_ld_wait();
+        if (q_idx < p.T) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          o[cc * 32 + i] = fmaf(o[cc * 32 + i], alpha, __uint_as_float(r[i]));
+          for (int i = 0; i < 4; ++i) {
+            uint4 q;
+            q.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]) * inv, __uint_as_float(r[8 * i + 1]) * inv);
+            q.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv);
+            q.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv);
+            q.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv);
+            reinterpret_cast<uint4*>(dst + cc * 32)[i] = q;
+          }
+        }
       }
-    }
-    if (ok && q_idx < p.T) {
-      const float inv = (l > 0.f) ? 1.0f / l : 0.f;
-      __nv_bfloat16* dst = p.O + ((long long)b * p.T + q_idx) * p.ldo + p.o_col0 + h * D;
-#pragma unroll
-      for (int i = 0; i < D / 8; ++i) {
-        uint4 q;
-        q.x = pack_bf16x2(o[8 * i + 0] * inv, o[8 * i + 1] * inv);
-        q.y = pack_bf16x2(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
-        q.z = pack_bf16x2(o[8 * i + 4] * inv, o[8 * i + 5] * inv);
-        q.w = pack_bf16x2(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
-        reinterpret_cast<uint4*>(dst)[i] = q;
-      }
-      if (p.lse != nullptr)
+      if (q_idx < p.T && p.lse != nullptr)
         p.lse[((long long)b * p.Hq + h) * p.T + q_idx] =
-            (l > 0.f) ? (m * p.scale + __logf(l)) : -INFINITY;
+            (l > 0.f) ? (m_used * p.scale + __logf(l)) : -INFINITY;
     }
   }
 

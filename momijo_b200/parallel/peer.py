@@ -140,6 +140,25 @@ class PeerComm:
                 _C.ptr(self.status), _C.current_stream())
         return t
 
+    def all_gather_rows(self, full: torch.Tensor, site=None):
+        """``full`` is a symmetric [rows, cols] buffer whose local row block is filled; pull the
+        other ranks' blocks (entry barrier included, so every rank's block is final)."""
+        nbytes = full.numel() * full.element_size()
+        key = (full.data_ptr(), nbytes)
+        if not hasattr(self, "_agr"):
+            self._agr = {}
+            self._agr_slots = self.new_slots(self.world)
+        st = self._agr.get(key)
+        if st is None:
+            st = (self.peer_ptrs(full),
+                  torch.tensor([0, nbytes], dtype=torch.int64, device=self.device))
+            self._agr[key] = st
+        ptrs, ranges = st
+        _C.call("mmj_allgather_ranges", self._sig_ptrs, ptrs, nbytes // self.world, _C.ptr(ranges), 1,
+                self.world, self.rank, self._agr_slots, self.next_epoch(self._agr_slots),
+                _C.ptr(self.status), _C.current_stream())
+        return full
+
     # ---- ZeRO step (called by ShardedDataParallel) ----
     def reduce_scatter_adamw(self, sdp, lr: float):
         flat, o = sdp.flat, sdp.optim

@@ -1,0 +1,128 @@
+"""Pipeline parallelism: stage wrapper and the 1F1B schedule.
+
+The reference has no pipeline parallelism (``learn/data/pipeline.mojo`` is an input pipeline).
+Inter-stage activations and gradients travel over torch.distributed point-to-point (NCCL on GPUs,
+gloo on CPU) issued asynchronously: receives for the next micro-batch are posted before the
+current one is computed and sends are not waited on until their buffers are reused, so transfers
+overlap with compute. Inside a stage any module may be used, including tensor-parallel blocks.
+
+1F1B with ``S`` stages and ``m`` micro-batches: stage ``s`` runs ``S - 1 - s`` warm-up forwards,
+then alternates one forward / one backward, then drains the remaining backwards; at most
+``S - s`` activations are alive per stage and the bubble fraction is ``(S - 1) / (m + S - 1)``.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+
+def partition_layers(n_layers: int, n_stages: int) -> List[range]:
+    """Balanced contiguous split (earlier stages take the remainder)."""
+    base, rem = divmod(n_layers, n_stages)
+    out, s = [], 0
+    for i in range(n_stages):
+        n = base + (1 if i < rem else 0)
+        out.append(range(s, s + n))
+        s += n
+    return out
+
+
+class PipelineStage(nn.Module):
+    """One pipeline stage: ``module(x) -> y`` (the first stage gets the micro-batch input, the last
+    stage's output goes to the loss)."""
+
+    def __init__(self, module: nn.Module, stage: int, n_stages: int, prev_rank: Optional[int] = None,
+                 next_rank: Optional[int] = None, group=None):
+        super().__init__()
+        self.module, self.stage, self.n_stages = module, stage, n_stages
+        self.prev_rank, self.next_rank, self.group = prev_rank, next_rank, group
+        self.is_first, self.is_last = stage == 0, stage == n_stages - 1
+
+    def forward(self, x):
+        return self.module(x)
+
+
+class Schedule1F1B:
+    def __init__(self, stage: PipelineStage, n_micro: int, act_shape, act_dtype=torch.bfloat16, device=None):
+        self.stage, self.n_micro = stage, n_micro
+        self.act_shape, self.act_dtype = tuple(act_shape), act_dtype
+        self.device = device if device is not None else next(stage.parameters()).device
+        self._pending = []
+
+    # ---- p2p helpers ----
+    def _irecv(self, src):
+        buf = torch.empty(self.act_shape, dtype=self.act_dtype, device=self.device)
+        return buf, dist.irecv(buf, src=src, group=self.stage.group)
+
+    def _isend(self, t, dst):
+        t = t.contiguous()
+        self._pending.append((dist.isend(t, dst=dst, group=self.stage.group), t))
+        if len(self._pending) > 4:
+            w, _ = self._pending.pop(0)
+            w.wait()
+
+    def _drain(self):
+        for w, _ in self._pending:
+            w.wait()
+        self._pending = []
+
+    def run(self, micro_inputs=None, loss_fn: Optional[Callable] = None, micro_targets=None):
+        """Run one training step over ``n_micro`` micro-batches; gradients accumulate in the
+        parameters. Returns the mean loss on the last stage (None elsewhere)."""
+        st, m, S, s = self.stage, self.n_micro, self.stage.n_stages, self.stage.stage
+        warm = min(S - 1 - s, m)
+        saved = []          # (input, output) pairs awaiting their backward
+        losses = []
+        fwd_i = bwd_i = 0
+        next_act = self._irecv(st.prev_rank) if (not st.is_first and m > 0) else None
+
+        def forward_one():
+            nonlocal fwd_i, next_act
+            if st.is_first:
+                x = micro_inputs[fwd_i]
+            else:
+                buf, w = next_act
+                w.wait()
+                x = buf.requires_grad_(True)
+                next_act = self._irecv(st.prev_rank) if fwd_i + 1 < m else None
+            y = st(x)
+            if st.is_last:
+                loss = loss_fn(y, micro_targets[fwd_i]) if loss_fn is not None else y
+                losses.append(loss.detach())
+                saved.append((x, loss / m))
+            else:
+                self._isend(y.detach(), st.next_rank)
+                saved.append((x, y))
+            fwd_i += 1
+
+        def backward_one():
+            nonlocal bwd_i
+            x, y = saved.pop(0)
+            if st.is_last:
+                y.backward()
+            else:
+                g, w = self._irecv(st.next_rank)
+                w.wait()
+                y.backward(g)
+            if not st.is_first:
+                self._isend(x.grad, st.prev_rank)
+            bwd_i += 1
+
+        for _ in range(warm):
+            forward_one()
+        for _ in range(m - warm):
+            forward_one()
+            backward_one()
+        for _ in range(warm):
+            backward_one()
+        self._drain()
+        if st.is_last and losses:
+            return torch.stack([l.float() for l in losses]).mean()
+        return None
+
+    @staticmethod
+    def bubble_fraction(n_stages: int, n_micro: int) -> float:
+        return (n_stages - 1) / (n_micro + n_stages - 1)
