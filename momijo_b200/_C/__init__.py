@@ -24,6 +24,7 @@ P, I, L, F = c_void_p, c_int, c_longlong, c_float
 _SIGS = {
     "mmj_gemm_bf16": ([P, L, I, P, L, I, P, L, I, I, I, I, P, P, L, P, L, P, I, P, P], 1),
     "mmj_gemm_bf16_grouped": ([P, L, P, L, I, I, I, P, L, I, I, I, I, P, L, P, P, P, I, P, P], 1),
+    "mmj_gemm_bf16_grouped_k": ([P, L, P, L, P, L, I, I, I, I, P, I, I, I, P, P], 1),
     "mmj_gemm_bf16_allgather": ([P, P, I, P, L, L, I, P, L, I, I, I, I, P, P, L, P, L, I, I, I, L,
                                  L, P, P, I, I, P, P], 1),
     "mmj_gemm_bf16_reduce_scatter": ([P, L, P, L, I, P, L, L, I, I, I, I, I, I, P, P], 1),
@@ -69,7 +70,7 @@ _SIGS = {
     "mmj_allreduce_bf16": ([P, P, P, L, F, I, I, I, I, P, P, P, P], 1),
     "mmj_reduce_slots_bf16": ([P, P, L, P, P, L, I, I, I, I, P, P], 1),
     "mmj_moe_count": ([P, P, I, I, P, P, I, I, I, I, P, P], 1),
-    "mmj_moe_offsets": ([P, I, I, I, P, P, P, P, P, I, P], 1),
+    "mmj_moe_offsets": ([P, I, I, I, P, P, P, P, P, P, I, P], 1),
     "mmj_moe_zero_pad": ([P, I, P, I, I, P], 1),
     "mmj_moe_gate_grad": ([P, P, P, P, P, I, I, I, I, I, P], 1),
     "mmj_moe_dispatch": ([P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P, P], 1),

@@ -413,7 +413,7 @@ __global__ void __launch_bounds__(1024) moe_count_kernel(const MoeCountParams p)
 // tile_group / num_tiles describe THIS rank's recv buffer for the grouped GEMM.
 __global__ void moe_offsets_kernel(const int* counts, int world, int rank, int n_experts,
                                    int* seg_off, int* tile_group, int* num_tiles, int* total_rows,
-                                   int* pad_ranges, int max_tiles) {
+                                   int* pad_ranges, int* expert_ranges, int max_tiles) {
   if (threadIdx.x != 0) return;
   const int epr = n_experts / world;
   for (int d = 0; d < world; ++d) {
@@ -430,6 +430,8 @@ __global__ void moe_offsets_kernel(const int* counts, int world, int rank, int n
         for (int tI = start / 128; tI < padded / 128 && tI < max_tiles; ++tI) tile_group[tI] = le;
         pad_ranges[2 * le] = row;          // rows [row, padded) of this expert hold no token
         pad_ranges[2 * le + 1] = padded;
+        expert_ranges[2 * le] = start;     // rows [start, padded) belong to this expert
+        expert_ranges[2 * le + 1] = padded;
       }
       row = padded;
     }
@@ -704,9 +706,10 @@ MMJ_API int mmj_moe_count(void* const* sig, const int* expert_idx, int n_assign,
 }
 MMJ_API int mmj_moe_offsets(const int* counts, int world, int rank, int n_experts, int* seg_off,
                             int* tile_group, int* num_tiles, int* total_rows, int* pad_ranges,
-                            int max_tiles, void* stream) {
+                            int* expert_ranges, int max_tiles, void* stream) {
   moe_offsets_kernel<<<1, 32, 0, STREAM>>>(counts, world, rank, n_experts, seg_off, tile_group,
-                                           num_tiles, total_rows, pad_ranges, max_tiles);
+                                           num_tiles, total_rows, pad_ranges, expert_ranges,
+                                           max_tiles);
   return (int)cudaGetLastError();
 }
 // Zero the padding rows of a recv-layout buffer (rows that no token maps to), so that they add

@@ -77,6 +77,26 @@ struct TileCoord {
   int m_tile, n_tile;
 };
 
+// Contraction range of a tile. Plain GEMMs contract over [0, K); in grouped-K mode (expert
+// weight gradients) tile t belongs to group g = t / tiles_per_group and contracts over the rows
+// [group_k[2g], group_k[2g+1]) of both MN-major operands.
+struct KRange {
+  int g, tt, k_begin, nk;
+};
+__device__ __forceinline__ KRange krange_of(int t, int per_group, int num_k, const GemmParams& p) {
+  KRange r;
+  if (p.groups_k <= 0) {
+    r.g = 0; r.tt = t; r.k_begin = 0; r.nk = num_k;
+    return r;
+  }
+  r.g = t / per_group;
+  r.tt = t - r.g * per_group;
+  r.k_begin = p.group_k[2 * r.g];
+  const int k_end = p.group_k[2 * r.g + 1];
+  r.nk = (k_end > r.k_begin) ? (k_end - r.k_begin + kGemmBK - 1) / kGemmBK : 0;
+  return r;
+}
+
 __device__ __forceinline__ TileCoord tile_of(int t, int num_m, int num_n, const GemmParams& p) {
   // n fastest by default: concurrently running CTAs share A rows and sweep B (weights stay in
   // L2). With a gathered B operand the order is m fastest, so that the first waves only need
@@ -401,9 +421,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                                                    : (p.M + kGemmBM - 1) / kGemmBM;
   const int num_n = (p.N + bn - 1) / bn;
   const int num_k = (p.K + kGemmBK - 1) / kGemmBK;
-  const int num_tiles = num_m * num_n;
+  const int per_group = num_m * num_n;
+  const int num_tiles = (p.groups_k > 0) ? p.groups_k * per_group : per_group;
 
-  if (num_k > 0) {
+  if (num_k > 0 || p.groups_k > 0) {
     if (warp == 0) {
       // ======================= TMA producer =======================
       if (lane == 0) {
@@ -411,7 +432,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         uint32_t ph = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < num_tiles && ok; t += gemm_ctas) {
-          const TileCoord tc = tile_of(t, num_m, num_n, p);
+          const KRange kr = krange_of(t, per_group, num_k, p);
+          const TileCoord tc = tile_of(kr.tt, num_m, num_n, p);
           const int m0 = tc.m_tile * kGemmBM;
           const int n0 = tc.n_tile * bn;
           const int g = (p.tile_group != nullptr) ? p.tile_group[tc.m_tile] : 0;
@@ -426,7 +448,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             asm volatile("fence.proxy.async;" ::: "memory");
           }
           if (!ok) break;
-          for (int kb = 0; kb < num_k; ++kb) {
+          for (int kb = 0; kb < kr.nk; ++kb) {
             if (!mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, p.status, kTimeoutEmpty, kb)) {
               ok = false;
               break;
@@ -434,7 +456,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             uint8_t* sA = smem + (size_t)s * stage_bytes;
             uint8_t* sB = sA + kAStageBytes;
             mbar_expect_tx(&full_bar[s], (uint32_t)stage_bytes);
-            const int k0 = kb * kGemmBK;
+            const int k0 = kr.k_begin + kb * kGemmBK;
             if (!p.a_mn) {
               tma_load_2d(sA, &tmA, &full_bar[s], k0, m0);
             } else {
@@ -465,13 +487,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         uint32_t acc_ph = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < num_tiles && ok; t += gemm_ctas) {
+          const KRange kr = krange_of(t, per_group, num_k, p);
+          if (kr.nk == 0) continue;  // empty contraction: the epilogue writes zeros on its own
           if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, &abort_flag, p.status, kTimeoutTmemEmpty,
                          t)) {
             break;
           }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kAccCols);
-          for (int kb = 0; kb < num_k; ++kb) {
+          for (int kb = 0; kb < kr.nk; ++kb) {
             if (!mbar_wait(&full_bar[s], ph, &abort_flag, p.status, kTimeoutFull, kb)) {
               ok = false;
               break;
@@ -499,9 +523,30 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       int acc = 0;
       uint32_t acc_ph = 0;
       for (int t = blockIdx.x; t < num_tiles; t += gemm_ctas) {
-        const TileCoord tc = tile_of(t, num_m, num_n, p);
+        const KRange kr = krange_of(t, per_group, num_k, p);
+        const TileCoord tc = tile_of(kr.tt, num_m, num_n, p);
         const int m0 = tc.m_tile * kGemmBM;
         const int n0 = tc.n_tile * bn;
+        const int out_row0 = kr.g * p.M;  // grouped-K: group g writes rows [g*M, (g+1)*M)
+        if (kr.nk == 0) {
+          // nothing to contract (an expert without tokens): the result is zero
+          const int zrow = m0 + quad * 32 + lane;
+          if (zrow < p.M) {
+            uint32_t z[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) z[i] = 0u;
+            for (int c = 0; c < bn / 32; ++c) {
+              const int col0 = n0 + c * 32;
+              if (col0 < p.N) {
+                if (p.epi & kEpiOutF32)
+                  epilogue_store_chunk<true>(p, z, zrow + out_row0, col0);
+                else
+                  epilogue_store_chunk<false>(p, z, zrow + out_row0, col0);
+              }
+            }
+          }
+          continue;
+        }
         if (!mbar_wait_warp(&tfull_bar[acc], acc_ph, &abort_flag, p.status, kTimeoutTmemFull, t)) break;
         tc_fence_after();
         const int row = m0 + quad * 32 + lane;
@@ -513,9 +558,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           const int col0 = n0 + c * 32;
           if (row < p.M && col0 < p.N) {
             if (p.epi & kEpiOutF32)
-              epilogue_store_chunk<true>(p, r, row, col0);
+              epilogue_store_chunk<true>(p, r, row + out_row0, col0);
             else
-              epilogue_store_chunk<false>(p, r, row, col0);
+              epilogue_store_chunk<false>(p, r, row + out_row0, col0);
           }
         }
         tc_fence_before();
@@ -643,6 +688,7 @@ int launch_gemm(GemmParams& p, const void* A, long long lda, long long a_rows, c
   const int num_m = (p.M + kGemmBM - 1) / kGemmBM;
   const int num_n = (p.N + p.bn - 1) / p.bn;
   long long tiles = (long long)num_m * num_n;
+  if (p.groups_k > 0) tiles *= p.groups_k;
   int gemm_ctas = sm_count() - comm_ctas;
   if (gemm_ctas < 1) gemm_ctas = 1;
   if (tiles < gemm_ctas) gemm_ctas = (int)tiles;
@@ -786,4 +832,24 @@ MMJ_API int mmj_gemm_bf16_reduce_scatter(const void* A, long long lda, const voi
   const int num_m = (M + kGemmBM - 1) / kGemmBM;
   p.m_tile_rot = (int)(((long long)(rank + 1) % world) * p.rows_per_rank / kGemmBM) % num_m;
   return launch_gemm(p, A, lda, M, B, ldb, b_mn ? K : N, 0, (cudaStream_t)stream);
+}
+
+// Grouped-K GEMM for expert weight gradients: for every group g,
+//   D[g][M, N] = sum over rows k in [group_k[2g], group_k[2g+1]) of A[k, :M]^T B[k, :N]
+// with A: [rows, M] and B: [rows, N] row-major (both MN-major operands; rows outside every range
+// are never read, rows inside a range that hold no token must be zero). D is [groups, M, N].
+MMJ_API int mmj_gemm_bf16_grouped_k(const void* A, long long lda, const void* B, long long ldb,
+                                    void* D, long long ldd, int rows, int M, int N, int groups,
+                                    const int* group_k_dev, int out_f32, int accumulate, int bn,
+                                    int* status, void* stream) {
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = rows;
+  p.a_mn = 1; p.b_mn = 1;
+  p.bn = bn;
+  p.epi = (out_f32 ? kEpiOutF32 : 0) | (accumulate ? kEpiAccumulate : 0);
+  p.D = D; p.ldd = ldd;
+  p.status = status;
+  p.groups_k = groups;
+  p.group_k = group_k_dev;
+  return launch_gemm(p, A, lda, rows, B, ldb, rows, 0, (cudaStream_t)stream);
 }

@@ -46,6 +46,10 @@ struct GemmParams {
   int b_group_rows;
   // Number of valid 128-row tiles lives on the device (expert counts are only known there).
   const int* num_m_tiles_dev;
+  // Grouped-K mode: groups_k > 0 selects per-group contraction ranges group_k[2g], group_k[2g+1]
+  // (device array); the output of group g starts at row g * M.
+  const int* group_k;
+  int groups_k;
 
   // Gathered operand (all-gather fused into the GEMM): a tile may only be loaded once
   // ready_flags[tile] >= ready_epoch. flag_mode 0: off, 1: per 128-row tile of A,

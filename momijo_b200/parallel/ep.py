@@ -8,18 +8,22 @@ The reference has no mixture-of-experts code; the layer style follows its ``Line
              128-row aligned segment of its expert on the destination rank (the per-expert counts
              are exchanged first, also by peer stores, so no host synchronisation is needed);
   experts  : grouped tcgen05 GEMMs over the local experts (per-tile expert table, tile count
-             read from the device);
+             read from the device; weight gradients use the grouped-K mode);
   combine  : every token pulls its k expert outputs from the ranks that computed them and forms
              the router-weighted sum.
+
+The backward pass reuses the same kernels with the roles swapped: the gradient of combine is a
+dispatch of ``dout`` scaled by the router weights, the gradient of dispatch is an unweighted
+combine.
 """
 from __future__ import annotations
 
 import math
+from dataclasses import dataclass
 from typing import Optional
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as tF
 
 from .. import _C, ops
 from ..ops.gemm import EPI_MUL_AUX, EPI_ROW_SCALE, EPI_SILU
@@ -27,12 +31,30 @@ from ..ops.gemm import EPI_MUL_AUX, EPI_ROW_SCALE, EPI_SILU
 bf16 = torch.bfloat16
 
 
+@dataclass
+class Routing:
+    """Device-side routing state of one dispatch (kept for the combine and for the backward)."""
+    idx: torch.Tensor            # [n_assign] global expert of each (token, k)
+    local_pos: torch.Tensor      # [n_assign] position inside its (source rank, expert) run
+    src_row: torch.Tensor        # [n_assign] row inside the destination rank's buffer
+    seg_off: torch.Tensor        # [world, experts_per_rank, world]
+    tile_group: torch.Tensor     # [max_tiles] local expert of each 128-row tile
+    num_tiles: torch.Tensor      # [1]
+    total_rows: torch.Tensor     # [1]
+    pad_ranges: torch.Tensor     # [experts_per_rank, 2] rows holding no token
+    expert_ranges: torch.Tensor  # [experts_per_rank, 2] rows of each local expert (padded)
+    n_tokens: int = 0
+
+    def info(self):
+        return {"tile_group": self.tile_group, "num_tiles": self.num_tiles}
+
+
 class MoEDispatcher:
-    """Owns the symmetric buffers and signal slots of one MoE layer (or of several layers that
-    run strictly one after another)."""
+    """Symmetric buffers and signal slots shared by the MoE layers of a model (layers run one
+    after another; buffers rotate so a fast rank never overwrites rows a peer still reads)."""
 
     def __init__(self, comm, n_experts: int, top_k: int, hidden: int, max_tokens: int,
-                 capacity_factor: float = 2.0, n_buffers: int = 2):
+                 capacity_factor: float = 2.0, n_buffers: int = 4):
         self.comm = comm
         W = comm.world
         if n_experts % W:
@@ -40,136 +62,173 @@ class MoEDispatcher:
         self.E, self.k, self.H = n_experts, top_k, hidden
         self.epr = n_experts // W
         self.max_assign = max_tokens * top_k
-        avg_rows = max_tokens * top_k  # rows per rank when routing is balanced
-        self.cap_rows = int(math.ceil(capacity_factor * avg_rows / 128) * 128) + 128 * self.epr
+        self.cap_rows = int(math.ceil(capacity_factor * self.max_assign / 128) * 128) + 128 * self.epr
         self.max_tiles = self.cap_rows // 128
-        dev = comm.device
         self.counts = comm.alloc(W * n_experts, torch.int32)
-        self.recv = [comm.alloc(self.cap_rows * hidden, bf16).view(self.cap_rows, hidden)
-                     for _ in range(n_buffers)]
-        self.yout = [comm.alloc(self.cap_rows * hidden, bf16).view(self.cap_rows, hidden)
-                     for _ in range(n_buffers)]
         self._counts_ptrs = comm.peer_ptrs(self.counts)
-        self._recv_ptrs = [comm.peer_ptrs(b) for b in self.recv]
-        self._y_ptrs = [comm.peer_ptrs(b) for b in self.yout]
-        self.local_pos = torch.empty(self.max_assign, dtype=torch.int32, device=dev)
-        self.src_row = torch.empty(self.max_assign, dtype=torch.int32, device=dev)
-        self.seg_off = torch.empty(W * self.epr * W, dtype=torch.int32, device=dev)
-        self.tile_group = torch.zeros(self.max_tiles, dtype=torch.int32, device=dev)
-        self.num_tiles = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.total_rows = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.pad_ranges = torch.zeros(2 * self.epr, dtype=torch.int32, device=dev)
-        self.slots = comm.new_slots(3 * W)
+        self.bufs = [comm.alloc(self.cap_rows * hidden, bf16).view(self.cap_rows, hidden)
+                     for _ in range(n_buffers)]
+        self._ptrs = [comm.peer_ptrs(b) for b in self.bufs]
+        self._next = 0
+        self.slots = comm.new_slots(3 * W)   # count barrier | dispatch barrier | combine barrier
+        comm._epochs[self.slots + W] = 0
+        comm._epochs[self.slots + 2 * W] = 0
         self.ctr = comm.new_counter(1)
-        self.which = 0
-        self._idx = None
 
-    def _ptrs_of(self, y):
-        for b, ptrs in zip(self.yout, self._y_ptrs):
-            if y is b or y.data_ptr() == b.data_ptr():
-                return ptrs
-        for b, ptrs in zip(self.recv, self._recv_ptrs):
-            if y is b or y.data_ptr() == b.data_ptr():
-                return ptrs
-        return self.comm.peer_ptrs(y)
+    def next_buffer(self):
+        """A symmetric [cap_rows, H] buffer (recv layout) to dispatch into or to fill with expert
+        outputs; returns (tensor, peer pointer table)."""
+        i = self._next
+        self._next = (self._next + 1) % len(self.bufs)
+        return self.bufs[i], self._ptrs[i]
 
-    # -- buffers of the current call --
-    def expert_out_buffer(self):
-        return self.yout[self.which]
+    def ptrs_of(self, t):
+        for b, p in zip(self.bufs, self._ptrs):
+            if t.data_ptr() == b.data_ptr():
+                return p
+        return self.comm.peer_ptrs(t)
 
-    def dispatch(self, x, expert_idx, row_w: Optional[torch.Tensor] = None, reuse_routing=False):
-        """x: [n_tok, H] bf16; expert_idx: [n_tok, k] int32 (global expert ids).
-        Returns (recv buffer [cap_rows, H], info dict with the grouped-GEMM tile table).
-        With ``reuse_routing`` the counts/offsets of the previous call are kept (backward pass)."""
-        c = self.comm
-        W = c.world
-        n_assign = expert_idx.numel()
-        if n_assign > self.max_assign:
+    def route(self, expert_idx) -> Routing:
+        """Exchange per-expert counts with all ranks and derive every rank's segment offsets."""
+        c, W, dev = self.comm, self.comm.world, self.comm.device
+        idx = expert_idx.reshape(-1).to(torch.int32).contiguous()
+        n = idx.numel()
+        if n > self.max_assign:
             raise ValueError("more assignments than the dispatcher was sized for")
-        idx = expert_idx.reshape(-1).contiguous()
-        st = _C.ptr(c.status)
-        stream = _C.current_stream()
-        if not reuse_routing:
-            self.which = (self.which + 1) % len(self.recv)
-            ep = c.next_epoch(self.slots)
-            self._ep = ep
-            _C.call("mmj_moe_count", c._sig_ptrs, _C.ptr(idx), n_assign, self.E, self._counts_ptrs,
-                    _C.ptr(self.local_pos), W, c.rank, self.slots, ep, st, stream)
-            _C.call("mmj_moe_offsets", _C.ptr(self.counts), W, c.rank, self.E, _C.ptr(self.seg_off),
-                    _C.ptr(self.tile_group), _C.ptr(self.num_tiles), _C.ptr(self.total_rows),
-                    _C.ptr(self.pad_ranges), self.max_tiles, stream)
-            self._idx = idx
-        else:
-            ep = c.next_epoch(self.slots)
-            self._ep = ep
-        buf = self.recv[self.which]
-        _C.call("mmj_moe_zero_pad", _C.ptr(buf), self.H, _C.ptr(self.pad_ranges), self.epr,
-                self.cap_rows, stream)
-        _C.call("mmj_moe_dispatch", c._sig_ptrs, _C.ptr(x), _C.ptr(idx), _C.ptr(self.local_pos),
-                _C.ptr(self.seg_off), self._recv_ptrs[self.which], _C.ptr(self.src_row),
-                _C.ptr(row_w), self.cap_rows, n_assign, self.k, self.H, self.E, W, c.rank,
-                self.slots + W, ep, _C.ptr(self.ctr), st, stream)
-        info = {"tile_group": self.tile_group, "num_tiles": self.num_tiles,
-                "total_rows": self.total_rows}
-        return buf, info
+        i32 = lambda *s: torch.empty(*s, dtype=torch.int32, device=dev)
+        r = Routing(idx, i32(n), i32(n), i32(W * self.epr * W), torch.zeros(self.max_tiles, dtype=torch.int32, device=dev),
+                    i32(1), i32(1), i32(2 * self.epr), i32(2 * self.epr), n // self.k)
+        ep = c.next_epoch(self.slots)
+        st, stream = _C.ptr(c.status), _C.current_stream()
+        _C.call("mmj_moe_count", c._sig_ptrs, _C.ptr(idx), n, self.E, self._counts_ptrs, _C.ptr(r.local_pos),
+                W, c.rank, self.slots, ep, st, stream)
+        _C.call("mmj_moe_offsets", _C.ptr(self.counts), W, c.rank, self.E, _C.ptr(r.seg_off),
+                _C.ptr(r.tile_group), _C.ptr(r.num_tiles), _C.ptr(r.total_rows), _C.ptr(r.pad_ranges),
+                _C.ptr(r.expert_ranges), self.max_tiles, stream)
+        return r
 
-    def combine(self, y, gate_w, residual=None, n_tokens=None):
-        """out[token] = residual[token] + sum_k gate_w[token, k] * y[row(token, k)] where ``y`` is
-        a symmetric buffer in recv layout (``expert_out_buffer()``)."""
+    def dispatch(self, x, r: Routing, row_w: Optional[torch.Tensor] = None):
+        """Send every (token, k) row of ``x`` [n_tok, H] to its expert's segment; rows may be scaled
+        by ``row_w`` [n_assign]. Returns the local recv-layout buffer [cap_rows, H]."""
+        c, W = self.comm, self.comm.world
+        buf, ptrs = self.next_buffer()
+        stream = _C.current_stream()
+        ep = c.next_epoch(self.slots + W)
+        _C.call("mmj_moe_zero_pad", _C.ptr(buf), self.H, _C.ptr(r.pad_ranges), self.epr, self.cap_rows, stream)
+        rw = None if row_w is None else row_w.reshape(-1).float().contiguous()
+        _C.call("mmj_moe_dispatch", c._sig_ptrs, _C.ptr(x.contiguous()), _C.ptr(r.idx), _C.ptr(r.local_pos),
+                _C.ptr(r.seg_off), ptrs, _C.ptr(r.src_row), _C.ptr(rw), self.cap_rows, r.idx.numel(), self.k,
+                self.H, self.E, W, c.rank, self.slots + W, ep, _C.ptr(self.ctr), _C.ptr(c.status), stream)
+        return buf
+
+    def combine(self, y, r: Routing, gate_w=None, residual=None):
+        """out[token] = residual[token] + sum_k gate_w[token, k] * y[row(token, k)] where ``y`` is a
+        symmetric recv-layout buffer on every rank (``gate_w=None`` means weights of one)."""
         c = self.comm
-        idx = self._idx
-        n_tokens = idx.numel() // self.k if n_tokens is None else n_tokens
-        out = torch.empty((n_tokens, self.H), dtype=bf16, device=c.device)
-        ptrs = self._ptrs_of(y)
-        gw = None if gate_w is None else gate_w.reshape(-1).contiguous().float()
-        _C.call("mmj_moe_combine", c._sig_ptrs, ptrs, _C.ptr(idx), _C.ptr(self.src_row), _C.ptr(gw),
-                _C.ptr(out), _C.ptr(residual), n_tokens, self.k, self.H, self.E, c.world, c.rank,
-                self.slots + 2 * c.world, self._ep, _C.ptr(c.status), _C.current_stream())
+        out = torch.empty((r.n_tokens, self.H), dtype=bf16, device=c.device)
+        gw = None if gate_w is None else gate_w.reshape(-1).float().contiguous()
+        ep = c.next_epoch(self.slots + 2 * c.world)
+        _C.call("mmj_moe_combine", c._sig_ptrs, self.ptrs_of(y), _C.ptr(r.idx), _C.ptr(r.src_row), _C.ptr(gw),
+                _C.ptr(out), _C.ptr(residual), r.n_tokens, self.k, self.H, self.E, c.world, c.rank,
+                self.slots + 2 * c.world, ep, _C.ptr(c.status), _C.current_stream())
         return out
 
-    def gate_grad(self, y, dout):
-        """d gate_w[token, k] = <dout[token], y[row(token, k)]>."""
+    def gate_grad(self, y, dout, r: Routing):
+        """d gate_w[token, k] = <dout[token], y[row(token, k)]> (``y`` symmetric, final on all ranks)."""
         c = self.comm
-        idx = self._idx
-        n_assign = idx.numel()
-        dg = torch.empty(n_assign, dtype=torch.float32, device=c.device)
-        ptrs = self._ptrs_of(y)
-        _C.call("mmj_moe_gate_grad", ptrs, _C.ptr(dout), _C.ptr(idx), _C.ptr(self.src_row),
-                _C.ptr(dg), n_assign, self.k, self.H, self.E, c.world, _C.current_stream())
+        n = r.idx.numel()
+        dg = torch.empty(n, dtype=torch.float32, device=c.device)
+        _C.call("mmj_moe_gate_grad", self.ptrs_of(y), _C.ptr(dout.contiguous()), _C.ptr(r.idx), _C.ptr(r.src_row),
+                _C.ptr(dg), n, self.k, self.H, self.E, c.world, _C.current_stream())
         return dg.view(-1, self.k)
 
 
-def grouped_gemm(a, w, info, *, b_mn=False, out=None, epi_silu=False, mul_aux=None,
-                 row_scale=None, bn=128):
-    """Rows of ``a`` [cap_rows, K] are grouped by expert in 128-row tiles (``info``); ``w`` is
+def grouped_gemm(a, w, r: Routing, *, b_mn=False, out=None, mul_aux=None, bn=128):
+    """Rows of ``a`` [cap_rows, K] are grouped by expert in 128-row tiles; ``w`` is
     [n_local_experts, N, K] (or [n_local_experts, K, N] with ``b_mn``)."""
     G = w.shape[0]
-    if b_mn:
-        K, N = w.shape[1], w.shape[2]
-        group_rows = K
-    else:
-        N, K = w.shape[1], w.shape[2]
-        group_rows = N
+    K, N = (w.shape[1], w.shape[2]) if b_mn else (w.shape[2], w.shape[1])
     cap = a.shape[0]
     if out is None:
         out = torch.empty((cap, N), dtype=bf16, device=a.device)
-    epi = (EPI_SILU if epi_silu else 0) | (EPI_MUL_AUX if mul_aux is not None else 0) | (
-        EPI_ROW_SCALE if row_scale is not None else 0)
+    epi = EPI_MUL_AUX if mul_aux is not None else 0
     w2 = w.reshape(G * w.shape[1], w.shape[2])
     _C.call("mmj_gemm_bf16_grouped", _C.ptr(a), a.stride(0), _C.ptr(w2), w2.stride(0), int(b_mn), G,
-            group_rows, _C.ptr(out), out.stride(0), cap, N, K, epi, _C.ptr(mul_aux),
-            mul_aux.stride(0) if mul_aux is not None else 0, _C.ptr(row_scale),
-            _C.ptr(info["tile_group"]), _C.ptr(info["num_tiles"]), bn,
-            _C.ptr(_C.status_tensor(a.device)), _C.current_stream())
+            w.shape[1], _C.ptr(out), out.stride(0), cap, N, K, epi, _C.ptr(mul_aux),
+            mul_aux.stride(0) if mul_aux is not None else 0, None, _C.ptr(r.tile_group),
+            _C.ptr(r.num_tiles), bn, _C.ptr(_C.status_tensor(a.device)), _C.current_stream())
     return out
+
+
+def grouped_gemm_wgrad(dy, x, r: Routing, n_groups: int, out=None, accumulate=False, bn=128):
+    """dW[g] = dy_g^T x_g over the rows of each local expert; dy [cap, M], x [cap, N] -> [G, M, N]."""
+    cap, M = dy.shape
+    N = x.shape[1]
+    if out is None:
+        out = torch.empty((n_groups, M, N), dtype=bf16, device=dy.device)
+        accumulate = False
+    _C.call("mmj_gemm_bf16_grouped_k", _C.ptr(dy), dy.stride(0), _C.ptr(x), x.stride(0), _C.ptr(out), N, cap,
+            M, N, n_groups, _C.ptr(r.expert_ranges), int(out.dtype == torch.float32), int(accumulate), bn,
+            _C.ptr(_C.status_tensor(dy.device)), _C.current_stream())
+    return out
+
+
+class _ExpertsEP(torch.autograd.Function):
+    """dispatch -> grouped gate/up GEMM -> SwiGLU -> grouped down GEMM -> weighted combine."""
+
+    @staticmethod
+    def forward(ctx, x, gate_w, idx, w_gu, w_down, disp):
+        F = w_down.shape[2]
+        r = disp.route(idx)
+        recv = disp.dispatch(x, r)
+        gu = grouped_gemm(recv, w_gu, r)                         # [cap, 2F]
+        act = torch.empty((gu.shape[0], F), dtype=bf16, device=x.device)
+        _C.call("mmj_swiglu_fwd", _C.ptr(gu), _C.ptr(act), gu.shape[0], F, _C.current_stream())
+        ybuf, _ = disp.next_buffer()
+        grouped_gemm(act, w_down, r, out=ybuf)                   # [cap, H] symmetric
+        out = disp.combine(ybuf, r, gate_w)
+        # rows are kept as private copies: the symmetric buffers are reused by later layers
+        ctx.save_for_backward(x, gate_w, recv.clone(), gu, act, ybuf.clone(), w_gu, w_down)
+        ctx.r, ctx.disp, ctx.refs = r, disp, (w_gu, w_down)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from ..ops.functional import _wgrad_target
+
+        x, gate_w, recv, gu, act, y_saved, w_gu, w_down = ctx.saved_tensors
+        r, disp = ctx.r, ctx.disp
+        rw_gu, rw_down = ctx.refs
+        F = w_down.shape[2]
+        G = w_gu.shape[0]
+        dout = dout.contiguous()
+        # gradient of the router weights needs the (unweighted) expert outputs of every rank
+        ysym, _ = disp.next_buffer()
+        ysym.copy_(y_saved)
+        disp.comm.barrier()
+        dgate = disp.gate_grad(ysym, dout, r)
+        # gradient w.r.t. expert outputs: dispatch dout scaled by the router weights
+        dy = disp.dispatch(dout, r, row_w=gate_w)
+        dact = grouped_gemm(dy, w_down, r, b_mn=True)            # dy [cap,H] x w_down[e] [H,F]
+        buf, acc = _wgrad_target(rw_down)
+        dw_down = grouped_gemm_wgrad(dy, act, r, G, out=buf, accumulate=acc)
+        dgu = torch.empty_like(gu)
+        _C.call("mmj_swiglu_bwd", _C.ptr(gu), _C.ptr(dact), _C.ptr(dgu), gu.shape[0], F, _C.current_stream())
+        buf2, acc2 = _wgrad_target(rw_gu)
+        dw_gu = grouped_gemm_wgrad(dgu, recv, r, G, out=buf2, accumulate=acc2)
+        dxbuf, _ = disp.next_buffer()
+        grouped_gemm(dgu, w_gu, r, b_mn=True, out=dxbuf)         # dgu [cap,2F] x w_gu[e] [2F,H]
+        dx = disp.combine(dxbuf, r, None)
+        return (dx, dgate.to(gate_w.dtype), None, None if buf2 is not None else dw_gu,
+                None if buf is not None else dw_down, None)
 
 
 class TopKRouter(nn.Module):
     """Softmax router with top-k selection, renormalised weights and the load-balance auxiliary
-    loss  aux = E * sum_e f_e * P_e  (f_e: fraction of assignments, P_e: mean router probability)."""
+    loss ``aux = coef * E * sum_e f_e * P_e`` (f_e: fraction of assignments, P_e: mean router
+    probability)."""
 
-    def __init__(self, hidden: int, n_experts: int, top_k: int, aux_coef: float = 0.01,
-                 dtype=bf16):
+    def __init__(self, hidden: int, n_experts: int, top_k: int, aux_coef: float = 0.01, dtype=bf16):
         super().__init__()
         self.weight = nn.Parameter(torch.empty(n_experts, hidden, dtype=dtype))
         nn.init.normal_(self.weight, 0.0, 0.02)
@@ -186,3 +245,56 @@ class TopKRouter(nn.Module):
             f = f / idx.numel()
         aux = self.aux_coef * self.E * (f * probs.mean(0)).sum()
         return w, idx.int(), aux
+
+
+class MoELayer(nn.Module):
+    """Routed experts (SwiGLU, expert parallel) plus optional shared experts (dense SwiGLU)."""
+
+    def __init__(self, hidden: int, ffn: int, n_experts: int, top_k: int, n_shared: int = 0,
+                 aux_coef: float = 0.01, dispatcher: Optional[MoEDispatcher] = None, world: int = 1,
+                 rank: int = 0, dtype=bf16, init_std: float = 0.02):
+        super().__init__()
+        self.disp = dispatcher
+        self.world = dispatcher.comm.world if dispatcher is not None else world
+        self.rank = dispatcher.comm.rank if dispatcher is not None else rank
+        if n_experts % self.world:
+            raise ValueError("experts must divide evenly over ranks")
+        self.E, self.k, self.H, self.F = n_experts, top_k, hidden, ffn
+        self.epr = n_experts // self.world
+        self.router = TopKRouter(hidden, n_experts, top_k, aux_coef, dtype)
+        self.w_gu = nn.Parameter(torch.empty(self.epr, 2 * ffn, hidden, dtype=dtype))
+        self.w_down = nn.Parameter(torch.empty(self.epr, hidden, ffn, dtype=dtype))
+        nn.init.normal_(self.w_gu, 0.0, init_std)
+        nn.init.normal_(self.w_down, 0.0, init_std)
+        self.shared = None
+        if n_shared > 0:
+            from ..learn.nn.layers import SwiGLU
+
+            self.shared = SwiGLU(hidden, n_shared * ffn, dtype=dtype, init_std=init_std)
+
+    def forward(self, x):
+        """x: [n_tok, H] -> ([n_tok, H], aux loss)."""
+        w, idx, aux = self.router(x)
+        if self.disp is not None and x.is_cuda and x.dtype == bf16:
+            y = _ExpertsEP.apply(x, w, idx, self.w_gu, self.w_down, self.disp)
+        else:
+            y = self._experts_reference(x, w, idx)
+        if self.shared is not None:
+            y = y + self.shared(x)
+        return y, aux
+
+    def _experts_reference(self, x, w, idx):
+        """Dense evaluation with plain torch (single rank holds every expert); used on CPU."""
+        if self.world != 1:
+            raise RuntimeError("the reference path needs all experts on one rank")
+        out = torch.zeros_like(x, dtype=torch.float32)
+        for e in range(self.E):
+            sel = (idx == e)
+            tok, kk = torch.nonzero(sel, as_tuple=True)
+            if tok.numel() == 0:
+                continue
+            h = x[tok] @ self.w_gu[e].t().to(x.dtype)
+            g, u = h.chunk(2, -1)
+            y = (torch.nn.functional.silu(g) * u) @ self.w_down[e].t().to(x.dtype)
+            out.index_add_(0, tok, (y.float() * w[tok, kk].float()[:, None]))
+        return out.to(x.dtype)

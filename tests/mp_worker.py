@@ -150,18 +150,99 @@ def sc_moe(comm):
     gw = torch.rand(n_tok, k, device="cuda")
     disp = MoEDispatcher(comm, n_experts=E, top_k=k, hidden=H, max_tokens=n_tok)
     for it in range(2):
-        recv, info = disp.dispatch(x, idx)
+        r = disp.route(idx)
+        recv = disp.dispatch(x, r)
         # identity experts scaled by (global expert id + 1): check routing end to end
         epr = E // W
-        y = disp.expert_out_buffer()
-        tg = info["tile_group"][: int(info["num_tiles"].item())]
+        y, _ = disp.next_buffer()
+        tg = r.tile_group[: int(r.num_tiles.item())]
         scale = (tg.float() + 1 + R * epr).repeat_interleave(128)[:, None]
         rows = scale.shape[0]
         y[:rows] = (recv[:rows].float() * scale).to(bf16)
-        out = disp.combine(y, gw)
+        out = disp.combine(y, r, gw)
         torch.cuda.synchronize()
         ref = (x.float()[:, None, :] * (idx.float() + 1)[:, :, None] * gw[:, :, None]).sum(1)
         close(out, ref, 3e-2, "moe dispatch/combine")
+
+
+def sc_moe_layer(comm):
+    """Expert-parallel MoE layer (forward + backward) == dense single-rank evaluation."""
+    from momijo_b200.parallel.ep import MoEDispatcher, MoELayer
+
+    W, R = comm.world, comm.rank
+    H, F, E, k, n_tok = 256, 128, 4 * W, 2, 384
+    torch.manual_seed(5)
+    ref = MoELayer(H, F, E, k, n_shared=1, world=1).cuda()          # same weights on every rank
+    disp = MoEDispatcher(comm, n_experts=E, top_k=k, hidden=H, max_tokens=n_tok)
+    ep = MoELayer(H, F, E, k, n_shared=1, dispatcher=disp).cuda()
+    epr = E // W
+    with torch.no_grad():
+        ep.router.weight.copy_(ref.router.weight)
+        ep.w_gu.copy_(ref.w_gu[R * epr:(R + 1) * epr])
+        ep.w_down.copy_(ref.w_down[R * epr:(R + 1) * epr])
+        ep.shared.w_gu.copy_(ref.shared.w_gu)
+        ep.shared.w_down.copy_(ref.shared.w_down)
+    torch.manual_seed(100 + R)
+    x = torch.randn(n_tok, H, device="cuda").to(bf16)
+    dy = torch.randn(n_tok, H, device="cuda").to(bf16)
+    x1, x2 = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    y_ep, aux_ep = ep(x1)
+    (y_ep.float() * dy.float()).sum().backward()
+    y_rf, aux_rf = ref(x2)
+    (y_rf.float() * dy.float()).sum().backward()
+    torch.cuda.synchronize()
+    close(y_ep, y_rf, 4e-2, "moe layer output")
+    close(x1.grad, x2.grad, 6e-2, "moe layer dx")
+    close(ep.router.weight.grad, ref.router.weight.grad, 8e-2, "router grad")
+    for name in ("w_gu", "w_down"):
+        g = getattr(ref, name).grad.float().clone()
+        dist.all_reduce(g)                  # every rank's tokens contribute to an expert's gradient
+        close(getattr(ep, name).grad, g[R * epr:(R + 1) * epr], 8e-2, f"expert {name} grad")
+
+
+def sc_tp_llama(comm):
+    """Tensor-parallel Llama on the fused kernels == the same model on one rank."""
+    from momijo_b200.models import Llama, LlamaConfig
+    from momijo_b200.parallel.tp import TPContext
+
+    W, R = comm.world, comm.rank
+    cfg = LlamaConfig(vocab_size=1024, n_layer=2, d_model=256, n_head=4 * W // 2 * 2, n_kv_head=2 * W // 2,
+                      head_dim=64, d_ff=512 * W // 2, max_seq=256)
+    torch.manual_seed(0)
+    full = Llama(cfg, TPContext.single()).cuda()
+    tp = TPContext(comm=comm)
+    model = Llama(cfg, tp).cuda()
+    with torch.no_grad():
+        V = model.embed.vocab_local
+        model.embed.weight.copy_(full.embed.weight[R * V:(R + 1) * V])
+        model.final_norm.copy_(full.final_norm)
+        vl = model.v_local
+        model.lm_head.weight.copy_(full.lm_head.weight[R * vl:(R + 1) * vl])
+        for bt, bf in zip(model.blocks, full.blocks):
+            bt.attn_norm.copy_(bf.attn_norm)
+            bt.mlp_norm.copy_(bf.mlp_norm)
+            D, Hq, Hk = cfg.head_dim, cfg.n_head, cfg.n_kv_head
+            wq, wk, wv = bf.wqkv.weight.split([Hq * D, Hk * D, Hk * D])
+            bt.wqkv.weight.copy_(torch.cat([wq.chunk(W)[R], wk.chunk(W)[R], wv.chunk(W)[R]]))
+            bt.wo.weight.copy_(bf.wo.weight.chunk(W, dim=1)[R])
+            g, u = bf.w_gu.weight.chunk(2)
+            bt.w_gu.weight.copy_(torch.cat([g.chunk(W)[R], u.chunk(W)[R]]))
+            bt.w_down.weight.copy_(bf.w_down.weight.chunk(W, dim=1)[R])
+    tok = torch.randint(0, cfg.vocab_size, (2, 257), generator=torch.Generator().manual_seed(3)).cuda()
+    for it in range(2):
+        for m_ in (full, model):
+            for p_ in m_.parameters():
+                p_.grad = None
+        l_ref = full(tok[:, :-1], tok[:, 1:])
+        l_ref.backward()
+        l_tp = model(tok[:, :-1], tok[:, 1:])
+        l_tp.backward()
+        torch.cuda.synchronize()
+        assert abs(l_ref.item() - l_tp.item()) < 3e-2 * abs(l_ref.item()), (l_ref.item(), l_tp.item())
+        close(model.blocks[0].wo.weight.grad, full.blocks[0].wo.weight.grad.chunk(W, dim=1)[R], 8e-2, "wo grad")
+        close(model.blocks[1].w_gu.weight.grad,
+              torch.cat([c_.chunk(W)[R] for c_ in full.blocks[1].w_gu.weight.grad.chunk(2)]), 8e-2, "w_gu grad")
+        close(model.embed.weight.grad, full.embed.weight.grad[R * V:(R + 1) * V], 8e-2, "embedding grad")
 
 
 def sc_timeout(comm):
@@ -178,7 +259,8 @@ def sc_timeout(comm):
 
 
 SCENARIOS = {"allreduce": sc_allreduce, "zero": sc_zero, "ag_gemm": sc_ag_gemm,
-             "gemm_rs": sc_gemm_rs, "moe": sc_moe, "timeout": sc_timeout}
+             "gemm_rs": sc_gemm_rs, "moe": sc_moe, "moe_layer": sc_moe_layer, "tp_llama": sc_tp_llama,
+             "timeout": sc_timeout}
 
 
 def main():
@@ -186,7 +268,7 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    comm = PeerComm.from_default_group(heap_bytes=512 << 20)
+    comm = PeerComm.from_default_group(heap_bytes=1024 << 20)
     for name in names:
         SCENARIOS[name](comm)
         _C.check_status()

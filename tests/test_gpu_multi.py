@@ -37,5 +37,9 @@ def test_fused_allgather_gemm_and_gemm_reduce_scatter():
     _run(["ag_gemm", "gemm_rs"])
 
 
-def test_moe_dispatch_combine():
-    _run(["moe"])
+def test_moe_dispatch_combine_and_layer():
+    _run(["moe", "moe_layer"])
+
+
+def test_tensor_parallel_llama_matches_single_rank():
+    _run(["tp_llama"])
