@@ -1,0 +1,8 @@
+"""momijo.dataframe: pandas-like frames without pandas (CPU only)."""
+from .frame import (  # noqa: F401
+    DataFrame, Series, Column, Value, Index, MultiIndex, Bitmap, DType, int32, int64, float32, float64,
+    string, NaN, NoneStr, isna, series_from_list, Series_from_strings, series_index,
+)
+from .frame import bool_ as bool  # noqa: F401
+from .ops import *  # noqa: F401,F403
+from .ops import range, filter, where, copy, rename  # noqa: F401
