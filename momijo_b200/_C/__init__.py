@@ -60,6 +60,7 @@ _SIGS = {
     "mmj_sqnorm_parts": ([], 0),
     "mmj_sqnorm": ([P, I, L, P, P, P, I, P], 2),
     "mmj_attn_fwd": ([P, L, I, P, L, I, P, L, I, P, L, I, P, I, I, I, I, I, F, I, P, P], 1),
+    "mmj_attn_set_trace": ([P, L], 0),
     "mmj_attn_bwd": ([P, L, I, P, L, I, P, L, I, P, L, I, P, L, I, P, P, P, L, I, P, L, I, P, L, I,
                       I, I, I, I, I, F, I, P, P], 2),
     "mmj_barrier": ([P, I, I, I, I, P, P], 1),

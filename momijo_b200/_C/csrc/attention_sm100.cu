@@ -10,7 +10,8 @@
 // for GQA, over the query heads of the group):
 //   S^T = K Q^T and dP^T = V dO^T (TMEM) -> threads rebuild P^T = exp(S^T*scale - lse) and
 //   dS^T = P^T o (dP^T - delta), write both to shared memory -> dV += P^T dO, dK += dS^T Q
-//   (TMEM, accumulated over the whole loop), dQ = dS K (TMEM, then fp32 red.add to global).
+//   (TMEM, accumulated over the whole loop), dQ = dS K (TMEM, then a TMA reduce-add into the
+//   fp32 accumulator in global memory).
 // The tiles loaded once by TMA serve both as K-major and as MN-major operands: a 128-row tile
 // whose rows are 128 swizzled bytes is the canonical layout of either, read with a different
 // descriptor.
@@ -21,7 +22,10 @@
 
 namespace mmj {
 
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 192;     // forward: TMA warp, MMA warp, 4 softmax warps
+constexpr int kAttnBwdThreads = 448;  // backward: TMA warp, MMA warp, 8 compute warps, 4 dQ warps
+struct TrueTag { static constexpr bool value = true; };
+struct FalseTag { static constexpr bool value = false; };
 constexpr int kPanelBytes = 128 * 128;  // 128 rows x 64 bf16
 
 struct AttnParams {
@@ -42,6 +46,7 @@ struct AttnParams {
   long long ld_dk, ld_dv;
   int dk_col0, dv_col0, dq_col0, o_col0;
   int* status;
+  long long* trace;  // nullable; kTraceSlots stamps per CTA
 };
 
 // K-major operand descriptor for k-step `k` (16 elements each) of a tile made of 64-column panels.
@@ -72,10 +77,25 @@ __device__ __forceinline__ void store_chunk_sw128(uint8_t* tile, int r, int col0
   }
 }
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c),
-               "f"(d)
-               : "memory");
+// TMA reduce-add of a shared-memory box into a global tensor (element type from the map).
+// The x coordinate times the element size must be a multiple of 16 bytes; coordinates are
+// never negative here.
+__device__ __forceinline__ void tma_reduce_add_3d(const void* tmap, const void* smem_src, int c0,
+                                                  int c1, int c2) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.bulk_group [%0, {%2, %3, %4}], [%1];"
+      :
+      : "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_group_read0() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_group0() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 
 // =============================================================================================
@@ -94,8 +114,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   constexpr int VS = (D == 64) ? 1 : 2;
 
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~(uintptr_t)1023);
+  // (offset arithmetic on the __shared__ symbol, not an integer round trip, so that the compiler
+  // keeps the shared address space and emits shared rather than generic loads and stores)
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + kTile;      // 2 stages
   uint8_t* sV = sK + 2 * kTile;  // VS stages
@@ -333,60 +354,115 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 // =============================================================================================
 // Backward
 // =============================================================================================
-// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; one warp per (row, head).
+// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; D/8 lanes per (row, head), 16 bytes per
+// lane and tensor, so a warp covers 4 (head_dim 64) or 2 (head_dim 128) heads of a row at once.
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ O, long long ldo, int o_col0,
                                   const __nv_bfloat16* __restrict__ dO, long long lddo, int do_col0,
                                   float* __restrict__ delta, int B, int T, int H, int D) {
-  const long long gw = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
+  const int lp = D >> 3;  // lanes per item: 8 or 16
+  const long long gt = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long item = gt / lp;
+  const int sub = (int)(gt - item * lp);
   const long long total = (long long)B * T * H;
-  if (gw >= total) return;
-  const int h = (int)(gw % H);
-  const long long bt = gw / H;
-  const __nv_bfloat16* o = O + bt * ldo + o_col0 + h * D;
-  const __nv_bfloat16* g = dO + bt * lddo + do_col0 + h * D;
+  const bool live = item < total;
   float s = 0.f;
-  for (int d = lane * 2; d < D; d += 64) {
-    float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + d));
-    float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(g + d));
-    s += a.x * c.x + a.y * c.y;
+  int h = 0;
+  long long bt = 0;
+  if (live) {
+    h = (int)(item % H);
+    bt = item / H;
+    const uint4 a = *reinterpret_cast<const uint4*>(O + bt * ldo + o_col0 + h * D + sub * 8);
+    const uint4 c = *reinterpret_cast<const uint4*>(dO + bt * lddo + do_col0 + h * D + sub * 8);
+    const uint32_t av[4] = {a.x, a.y, a.z, a.w}, cv[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = unpack_bf16x2(av[i]), y = unpack_bf16x2(cv[i]);
+      s = fmaf(x.x, y.x, fmaf(x.y, y.y, s));
+    }
   }
-  s = warp_sum(s);
-  if (lane == 0) {
+  for (int o = lp >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (live && sub == 0) {
     const long long b = bt / T, t = bt - b * T;
     delta[(b * H + h) * T + t] = s;
   }
 }
 
+// Optional kernel timeline: when a trace buffer is installed, one compute thread and the MMA
+// thread of every CTA store clock64() stamps at their stage boundaries (64 slots per CTA).
+constexpr int kTraceSlots = 64;
+__device__ __forceinline__ void trace_stamp(long long* trace, int cta, int slot) {
+  if (trace != nullptr && slot < kTraceSlots) trace[(long long)cta * kTraceSlots + slot] = clock64();
+}
+
+struct BwdCtl {
+  uint64_t kv_full, s_full, p_full, pds_free, acc_full, stat_full;
+  uint64_t dq_full[2], dq_read[2];
+  uint64_t dq_staged, stage_free;
+  uint64_t qdo_full[4], qdo_empty[4];
+  float s_lse[2][128], s_delta[2][128];
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+
+// Backward kernel. Warp roles (14 warps): 0 = TMA producer, 1 = MMA issuer and TMEM owner,
+// 2..9 = compute (P^T and dS^T from S^T and dP^T, then the dK/dV epilogue), 10..13 = dQ drain
+// (TMEM -> registers -> swizzled fp32 staging tile -> TMA reduce-add into global; per-thread
+// red.global.add would spend one L1 sector slot per 16 bytes and starve the compute warps' own
+// shared-memory traffic). A warp reaches the 32 TMEM lanes of its quadrant (warp
+// index mod 4) only, so two compute warps share each quadrant and split the columns; two
+// compute warps per scheduler also hide each other's dependent-issue and TMEM-load latency.
 template <int D>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __launch_bounds__(kAttnBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                const AttnParams p) {
+                const __grid_constant__ CUtensorMap tmdQ, const AttnParams p) {
   constexpr int NP = D / 64;
   constexpr int kTile = NP * kPanelBytes;
-  constexpr int kStages = (D == 64) ? 2 : 1;
+  // head_dim 64: three Q/dO stages, so that a stage released by the MMAs of block i is refilled
+  // (about 1.5 us of TMA latency) before block i+2 needs it, and two dQ accumulators.
+  // head_dim 128 has shared memory for one stage and TMEM columns for one dQ that aliases S^T.
+  constexpr int kStages = (D == 64) ? 3 : 1;
+  constexpr bool kAliasdQ = (D == 128);
+  constexpr int kDQB = kAliasdQ ? 1 : 2;
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kColSt = 0, kColdPt = 128, kColdV = 256, kColdK = 256 + D;
-  constexpr bool kAliasdQ = (D == 128);
-  constexpr uint32_t kColdQ = kAliasdQ ? 0u : (256u + 2u * D);
+  constexpr uint32_t kColdQ = kAliasdQ ? 0u : (256u + 2u * D);  // + D per extra buffer
+  constexpr int kPdsBytes = 2 * kPanelBytes;                    // one 128 x 128 bf16 tile
 
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~(uintptr_t)1023);
+  // (offset arithmetic on the __shared__ symbol, not an integer round trip, so that the compiler
+  // keeps the shared address space and emits shared rather than generic loads and stores)
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* sK = smem;
   uint8_t* sV = sK + kTile;
-  uint8_t* sQ = sV + kTile;               // kStages
-  uint8_t* sdO = sQ + kStages * kTile;    // kStages
-  uint8_t* sPt = sdO + kStages * kTile;   // 128 x 128 bf16
-  uint8_t* sdSt = sPt + 2 * kPanelBytes;  // 128 x 128 bf16
+  uint8_t* sQ = sV + kTile;              // kStages
+  uint8_t* sdO = sQ + kStages * kTile;   // kStages
+  uint8_t* sPt = sdO + kStages * kTile;  // 128 x 128 bf16
+  uint8_t* sdSt = sPt + kPdsBytes;       // 128 x 128 bf16
+  uint8_t* sDQ = sdSt + kPdsBytes;       // 128 x 64 fp32: two 32-column panels, 128-byte swizzle
 
-  __shared__ __align__(8) uint64_t kv_full, s_full, p_full, dq_full, dq_read;
-  __shared__ __align__(8) uint64_t qdo_full[2], qdo_empty[2];
-  __shared__ float s_lse[2][128], s_delta[2][128];
-  __shared__ __align__(8) uint64_t stat_full;
-  __shared__ uint32_t tmem_slot;
-  __shared__ int abort_flag;
+  // Barriers and the lse / delta staging live behind the tiles in dynamic shared memory: with
+  // head_dim 64 the tiles alone take 224 KB, and a static segment in front of them would push
+  // the 1024-byte alignment padding over the per-CTA limit.
+  BwdCtl& ctl = *reinterpret_cast<BwdCtl*>(sDQ + 2 * kPanelBytes);
+  {
+    uint32_t dyn_bytes;
+    asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_bytes));
+    const uint32_t need = (uint32_t)(reinterpret_cast<uint8_t*>(&ctl) - smem_raw) + sizeof(BwdCtl);
+    if (need > dyn_bytes) {  // uniform over the CTA: nothing allocated yet, just leave
+      if (threadIdx.x == 0) report(p.status, kBadArgument, (int)need);
+      return;
+    }
+  }
+  uint64_t &kv_full = ctl.kv_full, &s_full = ctl.s_full, &p_full = ctl.p_full;
+  uint64_t &pds_free = ctl.pds_free, &acc_full = ctl.acc_full, &stat_full = ctl.stat_full;
+  uint64_t *dq_full = ctl.dq_full, *dq_read = ctl.dq_read;
+  uint64_t &dq_staged = ctl.dq_staged, &stage_free = ctl.stage_free;
+  uint64_t *qdo_full = ctl.qdo_full, *qdo_empty = ctl.qdo_empty;
+  float(*s_lse)[128] = ctl.s_lse;
+  float(*s_delta)[128] = ctl.s_delta;
+  uint32_t& tmem_slot = ctl.tmem_slot;
+  int& abort_flag = ctl.abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int jb = blockIdx.x;  // key block
@@ -397,15 +473,32 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int i_begin = p.causal ? jb : 0;
   const int n_i = num_qb - i_begin;   // query blocks per head
   const int n_iter = n_i * group;     // (query head in group) x (query block)
+  const int cta_lin = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+  const bool tracer = (threadIdx.x == 64);
+  if (tracer) {
+    trace_stamp(p.trace, cta_lin, 0);
+    if (p.trace) {
+      uint32_t smid;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+      p.trace[(long long)cta_lin * kTraceSlots + 1] = smid;
+      p.trace[(long long)cta_lin * kTraceSlots + 7] = n_iter;
+    }
+  }
 
   if (threadIdx.x == 0) {
     mbar_init(&kv_full, 1);
     mbar_init(&s_full, 1);
-    mbar_init(&p_full, 4);
-    mbar_init(&dq_full, 1);
-    mbar_init(&dq_read, 4);
+    mbar_init(&p_full, 8);
+    mbar_init(&pds_free, 1);
+    mbar_init(&acc_full, 1);
     mbar_init(&stat_full, 128);
+    mbar_init(&dq_staged, 4);
+    mbar_init(&stage_free, 1);
     for (int s = 0; s < 2; ++s) {
+      mbar_init(&dq_full[s], 1);
+      mbar_init(&dq_read[s], 4);
+    }
+    for (int s = 0; s < 4; ++s) {
       mbar_init(&qdo_full[s], 1);
       mbar_init(&qdo_empty[s], 1);
     }
@@ -415,6 +508,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     prefetch_tmap(&tmK);
     prefetch_tmap(&tmV);
     prefetch_tmap(&tmdO);
+    prefetch_tmap(&tmdQ);
   }
   if (warp == 1) {
     tmem_alloc(&tmem_slot, kTmemCols);
@@ -424,6 +518,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  if (tracer) trace_stamp(p.trace, cta_lin, 2);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -454,18 +549,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t idesc_st = make_idesc_bf16(128, 128, 0, 0);  // K/V (K-major) x Q/dO (K-major)
       const uint32_t idesc_dkv = make_idesc_bf16(128, D, 0, 1);   // P^T/dS^T (K-major) x dO/Q (MN)
       const uint32_t idesc_dq = make_idesc_bf16(128, D, 1, 1);    // dS^T as MN-major A x K (MN)
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aPt = smem_u32(sPt),
-                     adSt = smem_u32(sdSt);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
+      const uint32_t aPt = smem_u32(sPt), adSt = smem_u32(sdSt);
       bool ok = mbar_wait(&kv_full, 0, &abort_flag, p.status, kTimeoutFull, -1);
+      trace_stamp(p.trace, cta_lin, 3);
+      // S^T = K Q^T and dP^T = V dO^T of block `it` (the Q/dO stage must have landed)
       auto issue_scores = [&](int it) -> bool {
         const int s = it % kStages;
         const uint32_t ph = (it / kStages) & 1;
         if (!mbar_wait(&qdo_full[s], ph, &abort_flag, p.status, kTimeoutFull, it)) return false;
-        if (kAliasdQ && it > 0) {
-          // dQ of the previous iteration shares the S^T columns: wait until it has been read
-          if (!mbar_wait(&dq_read, (it - 1) & 1, &abort_flag, p.status, kTimeoutFlag, it))
-            return false;
-        }
         tc_fence_after();
         const uint32_t aQ = smem_u32(sQ + s * kTile), adO = smem_u32(sdO + s * kTile);
 #pragma unroll
@@ -482,8 +574,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (ok && n_iter > 0) ok = issue_scores(0);
       for (int it = 0; it < n_iter && ok; ++it) {
         const int s = it % kStages;
-        if (!mbar_wait(&p_full, it & 1, &abort_flag, p.status, kTimeoutFlag, it)) break;
+        const int qb = it % kDQB;
+        if (!mbar_wait(&p_full, it & 1, &abort_flag, p.status, kTimeoutFlag, it)) { ok = false; break; }
         tc_fence_after();
+        trace_stamp(p.trace, cta_lin, 8 + it * 6 + 5);
+        // S^T / dP^T of this block are consumed. With a dQ accumulator of its own the next
+        // block's scores can go first (its exponentials then overlap the MMAs below), provided
+        // its Q/dO stage has landed; otherwise they follow the gradient MMAs.
+        bool scores_issued = (it + 1 >= n_iter);
+        if (!kAliasdQ && !scores_issued) {
+          const int s1 = (it + 1) % kStages;
+          if (mbar_try_wait(&qdo_full[s1], ((it + 1) / kStages) & 1)) {
+            ok = issue_scores(it + 1);
+            scores_issued = true;
+          }
+        }
         const uint32_t aQ = smem_u32(sQ + s * kTile), adO = smem_u32(sdO + s * kTile);
         // dV += P^T dO ; dK += dS^T Q   (contraction over the 128 query rows)
 #pragma unroll
@@ -495,109 +600,145 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           umma_bf16_ss(tmem_base + kColdK, desc_kmajor(adSt, k), desc_mnmajor(aQ, k), idesc_dkv,
                        (it > 0 || k > 0) ? 1u : 0u);
         // dQ = dS K  (contraction over the 128 key rows; dS^T tile read as an MN-major A)
-        if (!kAliasdQ && it > 0) {
-          if (!mbar_wait(&dq_read, (it - 1) & 1, &abort_flag, p.status, kTimeoutFlag, it)) break;
+        if (!kAliasdQ && it >= kDQB) {
+          if (!mbar_wait(&dq_read[qb], ((it / kDQB) - 1) & 1, &abort_flag, p.status, kTimeoutFlag, 200 + it)) { ok = false; break; }
           tc_fence_after();
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_bf16_ss(tmem_base + kColdQ, desc_mnmajor(adSt, k), desc_mnmajor(aK, k), idesc_dq,
-                       k > 0 ? 1u : 0u);
+          umma_bf16_ss(tmem_base + kColdQ + qb * D, desc_mnmajor(adSt, k), desc_mnmajor(aK, k),
+                       idesc_dq, k > 0 ? 1u : 0u);
         umma_commit(&qdo_empty[s]);
-        umma_commit(&dq_full);
-        if (it + 1 < n_iter) ok = issue_scores(it + 1);
+        umma_commit(&pds_free);
+        umma_commit(&dq_full[qb]);
+        if (it + 1 == n_iter) umma_commit(&acc_full);
+        if (!scores_issued) {
+          if (kAliasdQ) {
+            // dQ shares the S^T columns: the next scores wait until dQ has been drained
+            if (!mbar_wait(&dq_read[0], it & 1, &abort_flag, p.status, kTimeoutFlag, 300 + it)) { ok = false; break; }
+            tc_fence_after();
+          }
+          ok = issue_scores(it + 1);
+        }
       }
     }
-  } else {
-    // ---------------- compute warps: one key row per thread ----------------
+  } else if (warp < 10) {
+    // ---------------- compute warps: one key row and half of the columns per thread --------
     const int quad = warp & 3;
-    const int row = quad * 32 + lane;  // key row inside the block
+    const int chalf = (warp - 2) >> 2;  // which half of the columns this warp handles
+    const int row = quad * 32 + lane;   // key row inside the block
     const int kv_idx = kv0 + row;
-    const int ctid = threadIdx.x - 64;  // 0..127
+    const int ctid = threadIdx.x - 64;  // 0..255; the first 128 also stage lse / delta
     const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
     const float c = p.scale * 1.4426950408889634f;
     const float l2e = 1.4426950408889634f;
     bool ok = true;
-    for (int it = 0; it < n_iter; ++it) {
-      const int hq = hkv * group + it / n_i;
-      const int qi = i_begin + it % n_i;
-      const int qbase = qi * 128;
-      // stage lse / delta of this query block in a double buffer; an mbarrier (bounded wait)
-      // rather than a named barrier, so that an aborting warp can never strand the others
-      float* lse_s = s_lse[it & 1];
-      float* delta_s = s_delta[it & 1];
-      {
-        const int q = qbase + ctid;
+
+    // lse / delta of query block `it` go to shared memory one iteration ahead: the global loads
+    // are issued at the top of iteration it-1 and stored at its end, so the wait on stat_full
+    // at the top of iteration `it` normally finds the phase complete.
+    float st_l = 0.f, st_d = 0.f;
+    auto stat_load = [&](int it) {
+      if (ctid < 128 && it < n_iter) {
+        const int hq = hkv * group + it / n_i;
+        const int q = (i_begin + it % n_i) * 128 + ctid;
         const long long off = ((long long)b * p.Hq + hq) * p.T + q;
-        lse_s[ctid] = (q < p.T) ? p.lse[off] * l2e : 0.f;
-        delta_s[ctid] = (q < p.T) ? p.delta[off] : 0.f;
+        st_l = (q < p.T) ? p.lse[off] * l2e : 0.f;
+        st_d = (q < p.T) ? p.delta[off] : 0.f;
       }
-      mbar_arrive(&stat_full);
+    };
+    auto stat_store = [&](int it) {
+      if (ctid < 128 && it < n_iter) {
+        s_lse[it & 1][ctid] = st_l;
+        s_delta[it & 1][ctid] = st_d;
+        mbar_arrive(&stat_full);
+      }
+    };
+    stat_load(0);
+    stat_store(0);
+
+    for (int it = 0; it < n_iter; ++it) {
+      const int qbase = (i_begin + it % n_i) * 128;
+      const float* lse_s = s_lse[it & 1];
+      const float* delta_s = s_delta[it & 1];
+      stat_load(it + 1);
       if (!mbar_wait_warp(&stat_full, it & 1, &abort_flag, p.status, kTimeoutFlag, 500 + it)) { ok = false; break; }
       if (!mbar_wait_warp(&s_full, it & 1, &abort_flag, p.status, kTimeoutTmemFull, it)) { ok = false; break; }
       tc_fence_after();
+      if (tracer) trace_stamp(p.trace, cta_lin, 8 + it * 6 + 0);
       const bool need_mask = (p.causal && (qbase < kv0 + 127)) || (qbase + 128 > p.T) ||
                              (kv0 + 128 > p.T);
-#pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
+      // Both variants are straight-line code (the mask is a select, not a branch), so that the
+      // 32 independent exp / multiply chains of a chunk interleave.
+      auto chunk = [&](auto masked_tag, int cc, float (&pt)[32], float (&ds)[32]) {
+        constexpr bool kMasked = decltype(masked_tag)::value;
+        const int col0 = chalf * 64 + cc * 32;
         uint32_t rs[32], rp[32];
-        tmem_ld_32x32(t_lane + kColSt + cc * 32, rs);
-        tmem_ld_32x32(t_lane + kColdPt + cc * 32, rp);
+        tmem_ld_32x32(t_lane + kColSt + col0, rs);
+        tmem_ld_32x32(t_lane + kColdPt + col0, rp);
         tmem_ld_wait();
-        float pt[32], ds[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int qc = cc * 32 + i;
-          float e = exp2f(__uint_as_float(rs[i]) * c - lse_s[qc]);
-          if (need_mask) {
-            const int q = qbase + qc;
-            if (q >= p.T || kv_idx >= p.T || (p.causal && kv_idx > q)) e = 0.f;
+        for (int i4 = 0; i4 < 8; ++i4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(&lse_s[col0 + 4 * i4]);
+          const float4 d4 = *reinterpret_cast<const float4*>(&delta_s[col0 + 4 * i4]);
+          const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+          const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int i = 4 * i4 + u;
+            float e = exp2f(fmaf(__uint_as_float(rs[i]), c, -ls[u]));
+            if (kMasked) {
+              const int q = qbase + col0 + i;
+              const bool dead = (q >= p.T) | (kv_idx >= p.T) | ((p.causal != 0) & (kv_idx > q));
+              e = dead ? 0.f : e;
+            }
+            pt[i] = e;
+            ds[i] = e * (__uint_as_float(rp[i]) - dl[u]);
           }
-          pt[i] = e;
-          ds[i] = e * (__uint_as_float(rp[i]) - delta_s[qc]);
         }
-        store_chunk_sw128(sPt, row, cc * 32, pt);
-        store_chunk_sw128(sdSt, row, cc * 32, ds);
+      };
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        float pt[32], ds[32];
+        if (need_mask) chunk(TrueTag{}, cc, pt, ds);
+        else chunk(FalseTag{}, cc, pt, ds);
+        if (tracer && cc == 0) trace_stamp(p.trace, cta_lin, 8 + it * 6 + 1);
+        if (cc == 0 && it > 0) {
+          // the gradient MMAs of the previous block read P^T / dS^T: they must have finished
+          if (!mbar_wait_warp(&pds_free, (it - 1) & 1, &abort_flag, p.status, kTimeoutFlag, 600 + it)) { ok = false; break; }
+        }
+        store_chunk_sw128(sPt, row, chalf * 64 + cc * 32, pt);
+        store_chunk_sw128(sdSt, row, chalf * 64 + cc * 32, ds);
       }
+      if (!ok) break;
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full);
-      // dQ of this iteration: rows are queries here (lane = query row)
-      if (!mbar_wait_warp(&dq_full, it & 1, &abort_flag, p.status, kTimeoutTmemFull, 100 + it)) { ok = false; break; }
-      tc_fence_after();
-      {
-        const int q = qbase + row;
-        float* dst = p.dQ + ((long long)b * p.T + q) * p.ld_dq + p.dq_col0 + hq * D;
-#pragma unroll
-        for (int cc = 0; cc < D / 32; ++cc) {
-          uint32_t r[32];
-          tmem_ld_32x32(t_lane + kColdQ + cc * 32, r);
-          tmem_ld_wait();
-          if (q < p.T) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              red_add_v4(dst + cc * 32 + 4 * i, __uint_as_float(r[4 * i + 0]) * p.scale,
-                         __uint_as_float(r[4 * i + 1]) * p.scale,
-                         __uint_as_float(r[4 * i + 2]) * p.scale,
-                         __uint_as_float(r[4 * i + 3]) * p.scale);
-          }
-        }
+      if (tracer) trace_stamp(p.trace, cta_lin, 8 + it * 6 + 2);
+      if (ctid < 128 && it + 1 < n_iter) {
+        // Every compute warp has passed its wait on stat_full(it) once p_full(it) completes;
+        // arriving for the next phase any earlier could complete it before a slow warp looked
+        // at this one. The scores of block it+1 need p_full(it) as well, so this costs nothing.
+        if (!mbar_wait_warp(&p_full, it & 1, &abort_flag, p.status, kTimeoutFlag, 800 + it)) { ok = false; break; }
+        stat_store(it + 1);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&dq_read);
     }
-    // all MMAs into dV / dK have completed once the last dq_full has been seen
+    // all MMAs into dV / dK have completed once acc_full fires
+    if (ok && n_iter > 0)
+      ok = mbar_wait_warp(&acc_full, 0, &abort_flag, p.status, kTimeoutTmemFull, 700);
+    tc_fence_after();
     // tcgen05.ld is warp-collective: the condition around it must be warp-uniform; only the
     // global stores are predicated per row.
     const bool warp_ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
     const bool row_ok = kv_idx < p.T;
+    if (tracer) trace_stamp(p.trace, cta_lin, 4);
     if (warp_ok && n_iter > 0) {
       __nv_bfloat16* dk = p.dK + ((long long)b * p.T + kv_idx) * p.ld_dk + p.dk_col0 + hkv * D;
       __nv_bfloat16* dv = p.dV + ((long long)b * p.T + kv_idx) * p.ld_dv + p.dv_col0 + hkv * D;
 #pragma unroll
-      for (int cc = 0; cc < D / 32; ++cc) {
+      for (int c2 = 0; c2 < D / 64; ++c2) {
+        const int cc = chalf * (D / 64) + c2;
         uint32_t r[32];
         tmem_ld_32x32(t_lane + kColdV + cc * 32, r);
         tmem_ld_wait();
@@ -626,20 +767,89 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // no query block attends to this key block: gradients are zero
       __nv_bfloat16* dk = p.dK + ((long long)b * p.T + kv_idx) * p.ld_dk + p.dk_col0 + hkv * D;
       __nv_bfloat16* dv = p.dV + ((long long)b * p.T + kv_idx) * p.ld_dv + p.dv_col0 + hkv * D;
-      for (int i = 0; i < D / 8; ++i) {
+      for (int i = chalf * (D / 16); i < (chalf + 1) * (D / 16); ++i) {
         reinterpret_cast<uint4*>(dk)[i] = make_uint4(0, 0, 0, 0);
         reinterpret_cast<uint4*>(dv)[i] = make_uint4(0, 0, 0, 0);
       }
     }
+  } else {
+    // ---------------- dQ drain warps: one query row per thread ----------------
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const bool elected = (threadIdx.x == 320);  // issues the TMA reductions; also the tracer
+    uint8_t* my_row = sDQ + row * 128;
+    int u = 0;  // staging-tile uses so far (D / 64 per query block)
+    bool ok = true;
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int qb = it % kDQB;
+      if (!mbar_wait_warp(&dq_full[qb], (it / kDQB) & 1, &abort_flag, p.status, kTimeoutTmemFull, 100 + it)) break;
+      tc_fence_after();
+      if (elected) trace_stamp(p.trace, cta_lin, 8 + it * 6 + 3);
+      const int hq = hkv * group + it / n_i;
+      const int q0 = (i_begin + it % n_i) * 128;
+#pragma unroll
+      for (int h2 = 0; h2 < D / 64; ++h2, ++u) {
+        uint32_t r[2][32];
+        tmem_ld_32x32(t_lane + kColdQ + qb * D + h2 * 64, r[0]);
+        tmem_ld_32x32(t_lane + kColdQ + qb * D + h2 * 64 + 32, r[1]);
+        tmem_ld_wait();
+        if (h2 == D / 64 - 1) {
+          // the accumulator is in registers: hand its TMEM columns back right away
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&dq_read[qb]);
+        }
+        // the previous reduction must have finished reading the staging tile
+        if (u > 0 && !mbar_wait_warp(&stage_free, (u - 1) & 1, &abort_flag, p.status, kTimeoutFlag, 900 + it)) { ok = false; break; }
+#pragma unroll
+        for (int pn = 0; pn < 2; ++pn) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 v;
+            v.x = __uint_as_float(r[pn][4 * j + 0]) * p.scale;
+            v.y = __uint_as_float(r[pn][4 * j + 1]) * p.scale;
+            v.z = __uint_as_float(r[pn][4 * j + 2]) * p.scale;
+            v.w = __uint_as_float(r[pn][4 * j + 3]) * p.scale;
+            *reinterpret_cast<float4*>(my_row + pn * kPanelBytes + ((j ^ (row & 7)) << 4)) = v;
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&dq_staged);
+        if (elected) {
+          if (!mbar_wait(&dq_staged, u & 1, &abort_flag, p.status, kTimeoutFlag, 1000 + it)) { ok = false; }
+          else {
+            // rows past T are clipped by the tensor map (3-D: columns, rows of one batch, batch)
+#pragma unroll
+            for (int pn = 0; pn < 2; ++pn)
+              tma_reduce_add_3d(&tmdQ, sDQ + pn * kPanelBytes,
+                                p.dq_col0 + hq * D + h2 * 64 + pn * 32, q0, b);
+            bulk_commit_group();
+            bulk_wait_group_read0();
+            mbar_arrive(&stage_free);
+          }
+        }
+        ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+        if (!ok) break;
+      }
+      if (elected) trace_stamp(p.trace, cta_lin, 8 + it * 6 + 4);
+    }
+    if (elected) bulk_wait_group0();  // reductions in flight finish before the CTA retires
   }
 
+  if (tracer) trace_stamp(p.trace, cta_lin, 5);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     __syncwarp();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (tracer) trace_stamp(p.trace, cta_lin, 6);
 }
+
+static long long* g_attn_trace = nullptr;
+static long long g_attn_trace_ctas = 0;
 
 // ---------------------------------------------------------------------------------------------
 // Host side
@@ -676,6 +886,22 @@ static int make_tmap_btc(CUtensorMap* out, const void* base, int B, int T, long 
   cuuint32_t box[3] = {64, 128, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return (r == CUDA_SUCCESS) ? 0 : (int)r;
+}
+
+// fp32 accumulator [B*T, ld] viewed as [B][T][ld]; boxes of 32 columns x 128 rows, 128-byte swizzle
+static int make_tmap_f32_btc(CUtensorMap* out, const void* base, int B, int T, long long ld) {
+  EncodeTiledFn fn = attn_encode_fn();
+  if (fn == nullptr) return -1;
+  ensure_context();
+  if (ld % 4 || ((uintptr_t)base & 15)) return -2;
+  cuuint64_t dims[3] = {(cuuint64_t)ld, (cuuint64_t)T, (cuuint64_t)B};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 4, (cuuint64_t)ld * 4 * (cuuint64_t)T};
+  cuuint32_t box[3] = {32, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return (r == CUDA_SUCCESS) ? 0 : (int)r;
@@ -726,6 +952,14 @@ MMJ_API int mmj_attn_fwd(const void* q, long long ldq, int q_col0, const void* k
   return (int)cudaGetLastError();
 }
 
+// Install (or clear, with nullptr) the timeline buffer of the backward kernel: int64
+// [ctas * 64]. Launches whose grid has more CTAs than `ctas` leave it untouched.
+MMJ_API int mmj_attn_set_trace(void* buf, long long ctas) {
+  g_attn_trace = reinterpret_cast<long long*>(buf);
+  g_attn_trace_ctas = buf ? ctas : 0;
+  return 0;
+}
+
 // dQ_accum: fp32 [B*T, ld_dq], must be zero on entry (the kernel adds into it).
 // delta: fp32 scratch [B, Hq, T] (filled here). dK/dV: bf16 outputs.
 MMJ_API int mmj_attn_bwd(const void* q, long long ldq, int q_col0, const void* k, long long ldk,
@@ -744,10 +978,14 @@ MMJ_API int mmj_attn_bwd(const void* q, long long ldq, int q_col0, const void* k
   if ((rc = make_tmap_btc(&tk, k, B, T, ldk, ldk))) return rc;
   if ((rc = make_tmap_btc(&tv, v, B, T, ldv, ldv))) return rc;
   if ((rc = make_tmap_btc(&tdo, dO, B, T, lddo, lddo))) return rc;
+  CUtensorMap tdq;
+  if (dq_col0 % 4) return -13;
+  if ((rc = make_tmap_f32_btc(&tdq, dQ_accum, B, T, ld_dq))) return rc;
   {
-    const long long warps = (long long)B * T * Hq;
+    if (((uintptr_t)O & 15) || (ldo & 7) || (o_col0 & 7) || (do_col0 & 7)) return -1;
+    const long long lanes = (long long)B * T * Hq * (D / 8);
     const int threads = 256;
-    const long long blocks = (warps * 32 + threads - 1) / threads;
+    const long long blocks = (lanes + threads - 1) / threads;
     attn_delta_kernel<<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)O, ldo, o_col0, (const __nv_bfloat16*)dO, lddo, do_col0, delta, B, T,
         Hq, D);
@@ -763,22 +1001,26 @@ MMJ_API int mmj_attn_bwd(const void* q, long long ldq, int q_col0, const void* k
   p.dK = (__nv_bfloat16*)dK; p.ld_dk = ld_dk; p.dk_col0 = dk_col0;
   p.dV = (__nv_bfloat16*)dV; p.ld_dv = ld_dv; p.dv_col0 = dv_col0;
   p.status = status;
+  p.trace = g_attn_trace;
   dim3 grid((T + 127) / 128, Hkv, B);
+  if (g_attn_trace && (long long)grid.x * grid.y * grid.z > g_attn_trace_ctas) p.trace = nullptr;
   static bool attr64 = false, attr128 = false;
   if (D == 64) {
-    const int smem = (2 + 2 * 2) * kPanelBytes + 4 * kPanelBytes + 1024;
+    // K,V + 3x(Q,dO) + P^T,dS^T + dQ staging = 224 KB of tiles; the control block and the alignment
+    // padding take what is left of the 227 KB a CTA may have (the kernel checks that they fit)
+    const int smem = 232448;
     if (!attr64) {
       cudaFuncSetAttribute(attn_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       attr64 = true;
     }
-    attn_bwd_kernel<64><<<grid, kAttnThreads, smem, (cudaStream_t)stream>>>(tq, tk, tv, tdo, p);
+    attn_bwd_kernel<64><<<grid, kAttnBwdThreads, smem, (cudaStream_t)stream>>>(tq, tk, tv, tdo, tdq, p);
   } else {
-    const int smem = (2 + 2) * 2 * kPanelBytes + 4 * kPanelBytes + 1024;
+    const int smem = 232448;  // 224 KB of tiles as well: K,V + Q,dO + P^T,dS^T + dQ staging
     if (!attr128) {
       cudaFuncSetAttribute(attn_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       attr128 = true;
     }
-    attn_bwd_kernel<128><<<grid, kAttnThreads, smem, (cudaStream_t)stream>>>(tq, tk, tv, tdo, p);
+    attn_bwd_kernel<128><<<grid, kAttnBwdThreads, smem, (cudaStream_t)stream>>>(tq, tk, tv, tdo, tdq, p);
   }
   return (int)cudaGetLastError();
 }

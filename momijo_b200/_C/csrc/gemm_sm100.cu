@@ -282,8 +282,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                          const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled tiles need 1024-byte aligned bases.
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~(uintptr_t)1023);
+  // (offset arithmetic on the __shared__ symbol, not an integer round trip, so that the compiler
+  // keeps the shared address space and emits shared rather than generic loads and stores)
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   __shared__ __align__(8) uint64_t full_bar[kGemmMaxStages];
   __shared__ __align__(8) uint64_t empty_bar[kGemmMaxStages];
   __shared__ __align__(8) uint64_t tfull_bar[2];
