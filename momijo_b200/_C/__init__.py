@@ -60,6 +60,16 @@ _SIGS = {
     "mmj_sqnorm_parts": ([], 0),
     "mmj_sqnorm": ([P, I, L, P, P, P, I, P], 2),
     "mmj_attn_fwd": ([P, L, I, P, L, I, P, L, I, P, L, I, P, I, I, I, I, I, F, I, P, P], 1),
+    "mmj_vis_resize": ([P, P, I, I, I, I, I, I, P], 1),
+    "mmj_vis_to_gray": ([P, P, L, I, I, P], 1),
+    "mmj_vis_swap_rb": ([P, P, L, I, P], 1),
+    "mmj_vis_sep_filter": ([P, P, I, I, I, P, I, I, P], 1),
+    "mmj_vis_deriv3": ([P, P, I, I, I, P], 1),
+    "mmj_vis_morph": ([P, P, I, I, I, I, I, P], 1),
+    "mmj_vis_warp": ([P, P, I, I, I, P, I, I, I, P], 1),
+    "mmj_vis_hist": ([P, L, I, I, P, P], 1),
+    "mmj_vis_lut": ([P, P, L, P, P], 1),
+    "mmj_vis_binary": ([P, P, P, L, I, F, F, F, P], 1),
     "mmj_attn_set_trace": ([P, L], 0),
     "mmj_attn_bwd": ([P, L, I, P, L, I, P, L, I, P, L, I, P, L, I, P, P, P, L, I, P, L, I, P, L, I,
                       I, I, I, I, I, F, I, P, P], 2),
