@@ -40,6 +40,11 @@ def parse():
     ap.add_argument("--micro-batch", type=int, default=16)
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--model", default="gpt2-small", choices=["gpt2-small", "gpt2-tiny"])
+    ap.add_argument("--config", default="gpt2", choices=["gpt2", "llama8b-tp", "moe16b-ep", "llama13b-pptp"],
+                    help="gpt2: the headline config (sharded data parallel). The others are the tensor-, "
+                         "expert- and pipeline-parallel configs; they need the GPUs named in their docstrings.")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="override the layer count (for smoke runs; the result is then marked 'reduced')")
     return ap.parse_args()
 
 
@@ -165,6 +170,186 @@ def build_torch(cfg, world, local):
     return net, opt
 
 
+def _pinned_batches(vocab, shape, seed, n=4):
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, shape, generator=g).pin_memory() for _ in range(n)]
+
+
+def setup_llama_tp(args, rank, world, local):
+    """Llama-3-8B shape (32L, d4096, 32q/8kv heads of 128, SwiGLU 14336, vocab 128256), seq 4096, global
+    batch 8 sequences, tensor parallel over all ranks with sequence parallelism; every rank feeds the same
+    tokens. Fused all-gather->GEMM and GEMM->reduce-scatter kernels over peer memory; AdamW (fp32 master)
+    on each rank's own weight shards."""
+    import torch
+    from momijo_b200 import ops
+    from momijo_b200.models import Llama, LlamaConfig
+    from momijo_b200.parallel import AdamWConfig, HybridEngine
+    from momijo_b200.parallel.tp import TPContext
+
+    cfg = LlamaConfig.llama3_8b()
+    if args.layers:
+        cfg.n_layer = args.layers
+    B, T = 8, cfg.max_seq
+    comm = None
+    if world > 1:
+        from momijo_b200.parallel.peer import PeerComm
+
+        comm = PeerComm.from_default_group(heap_bytes=12 << 30)
+    tp = TPContext(comm=comm) if comm is not None else TPContext.single()
+    torch.manual_seed(1234 + rank)
+    with torch.device("cuda"):
+        model = Llama(cfg, tp)
+    engine = HybridEngine(model, AdamWConfig(lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1), rep_comm=comm)
+    ops.assume_unit_loss_grad(True)
+    host_tok = _pinned_batches(cfg.vocab_size, (B, T + 1), 1000)   # same seed on every rank: same tokens
+    dev_tok = [t.cuda() for t in host_tok]
+
+    def step_device(i):
+        t = dev_tok[i % len(dev_tok)]
+        loss = engine(t[:, :-1], t[:, 1:])
+        loss.backward()
+        engine.step()
+        return loss
+
+    def step_e2e(i):
+        t = host_tok[i % len(host_tok)].cuda(non_blocking=True)
+        loss = engine(t[:, :-1], t[:, 1:])
+        loss.backward()
+        engine.step()
+        return float(loss)
+
+    info = {"tokens_per_step": B * T, "scaling": "strong", "flops_per_token": cfg.flops_per_token(T),
+            "h2d_bytes": B * (T + 1) * 8,
+            "config": {"model": f"llama-3-8b shape ({cfg.n_layer}L d4096 32q/8kv hd128 ff14336 vocab128256 seq4096)",
+                       "global_batch": B, "seq_len": T, "parallelism": f"tp{world}+sp",
+                       "optimizer": "AdamW fp32 master on local shards, step inside the timed region",
+                       "l2": "working set of tens of GB per step >> 126 MB L2; no flush"}}
+    return step_device, step_e2e, info
+
+
+def setup_moe_ep(args, rank, world, local):
+    """16B-class MoE (28L, d2048, 16 heads, 64 routed experts of FFN 1408 + 2 shared, top-6, aux 0.01, vocab
+    102400), seq 4096, micro-batch 4 per GPU: experts split over all ranks (fused dispatch / grouped GEMM /
+    combine over peer memory), attention and the other dense parameters data parallel with the fused
+    reduce-scatter + sharded AdamW."""
+    import torch
+    from momijo_b200 import ops
+    from momijo_b200.models import MoEConfig, MoEDecoder
+    from momijo_b200.parallel import AdamWConfig, HybridEngine
+
+    cfg = MoEConfig.moe_16b()
+    if args.layers:
+        cfg.n_layer = args.layers
+    B, T = 4, cfg.max_seq
+    comm = None
+    if world > 1:
+        from momijo_b200.parallel.peer import PeerComm
+
+        comm = PeerComm.from_default_group(heap_bytes=16 << 30)
+    torch.manual_seed(1234 + rank)
+    with torch.device("cuda"):
+        model = MoEDecoder(cfg, comm, max_tokens=B * T, capacity_factor=1.5)
+    experts = {id(p) for p in model.expert_parameters()}
+    dense = [p for p in model.parameters() if id(p) not in experts]
+    if world > 1:
+        # dense parameters start identical on every rank
+        import torch.distributed as dist
+        for p in dense:
+            dist.broadcast(p.data, 0)
+    engine = HybridEngine(model, AdamWConfig(lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1),
+                          dp_comm=comm, dp_params=dense if world > 1 else None,
+                          local_grad_scale=1.0 / world)
+    ops.assume_unit_loss_grad(False)   # the loss is cross-entropy + auxiliary term
+    host_tok = _pinned_batches(cfg.vocab_size, (B, T + 1), 1000 + rank)
+    dev_tok = [t.cuda() for t in host_tok]
+
+    def step_device(i):
+        t = dev_tok[i % len(dev_tok)]
+        loss = engine(t[:, :-1], t[:, 1:])
+        loss.backward()
+        engine.step()
+        return loss
+
+    def step_e2e(i):
+        t = host_tok[i % len(host_tok)].cuda(non_blocking=True)
+        loss = engine(t[:, :-1], t[:, 1:])
+        loss.backward()
+        engine.step()
+        return float(loss)
+
+    info = {"tokens_per_step": B * T * world, "scaling": "weak", "flops_per_token": cfg.flops_per_token(T),
+            "h2d_bytes": B * (T + 1) * 8,
+            "config": {"model": f"moe-16b shape ({cfg.n_layer}L d2048 16H 64 experts ff1408 top6 + 2 shared vocab102400 seq4096)",
+                       "global_batch": B * world, "seq_len": T, "parallelism": f"ep{world}+dp{world}-attention",
+                       "optimizer": "AdamW fp32 master (experts local, dense sharded), step inside the timed region",
+                       "l2": "working set of tens of GB per step >> 126 MB L2; no flush"}}
+    return step_device, step_e2e, info
+
+
+def setup_llama_pptp(args, rank, world, local):
+    """Llama-2-13B shape (40L, d5120, 40 heads, SwiGLU 13824, vocab 32000): 2 pipeline stages x 4-way tensor
+    parallel on 8 GPUs, 1F1B over 16 micro-batches of 1 x 4096 tokens; activations between stages go over
+    NCCL p2p, tensor parallelism uses the fused kernels inside each stage."""
+    import torch
+    import torch.distributed as dist
+    from momijo_b200 import ops
+    from momijo_b200.models import LlamaConfig
+    from momijo_b200.models.llama import LlamaStage
+    from momijo_b200.parallel import AdamWConfig, HybridEngine
+    from momijo_b200.parallel.peer import PeerComm
+    from momijo_b200.parallel.pp import PipelineStage, Schedule1F1B, partition_layers
+    from momijo_b200.parallel.tp import TPContext
+
+    if world % 2:
+        raise SystemExit("--config llama13b-pptp needs an even number of GPUs (2 pipeline stages)")
+    cfg = LlamaConfig.llama2_13b()
+    if args.layers:
+        cfg.n_layer = args.layers
+    S, TP = 2, world // 2
+    n_micro, T = 16, cfg.max_seq
+    stage_id, tp_rank = rank // TP, rank % TP
+    groups = [dist.new_group(list(range(s * TP, (s + 1) * TP))) for s in range(S)]
+    comm = PeerComm(groups[stage_id], heap_bytes=6 << 30) if TP > 1 else None
+    tp = TPContext(comm=comm) if comm is not None else TPContext.single()
+    layers = partition_layers(cfg.n_layer, S)[stage_id]
+    torch.manual_seed(1234 + rank)
+    with torch.device("cuda"):
+        module = LlamaStage(cfg, tp, layers, first=stage_id == 0, last=stage_id == S - 1)
+    module.batch_shape = (1, T)
+    engine = HybridEngine(module, AdamWConfig(lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1), rep_comm=comm)
+    ops.assume_unit_loss_grad(False)   # micro-batch losses are scaled by 1/n_micro
+    stage = PipelineStage(module, stage_id, S, prev_rank=rank - TP if stage_id > 0 else None,
+                          next_rank=rank + TP if stage_id < S - 1 else None)
+    sched = Schedule1F1B(stage, n_micro, (T // TP, cfg.d_model), torch.bfloat16, torch.device("cuda", local))
+    host_tok = _pinned_batches(cfg.vocab_size, (n_micro, T + 1), 1000)  # same tokens on every rank
+    dev_tok = [t.cuda() for t in host_tok]
+
+    def run(t):
+        inputs = [t[m:m + 1, :-1] for m in range(n_micro)]
+        targets = [t[m:m + 1, 1:] for m in range(n_micro)]
+        loss = sched.run(inputs if stage.is_first else None, module.loss if stage.is_last else None,
+                         targets if stage.is_last else None)
+        engine.step()
+        return loss
+
+    def step_device(i):
+        return run(dev_tok[i % len(dev_tok)])
+
+    def step_e2e(i):
+        loss = run(host_tok[i % len(host_tok)].cuda(non_blocking=True))
+        return float(loss) if loss is not None else None
+
+    info = {"tokens_per_step": n_micro * T, "scaling": "strong", "flops_per_token": cfg.flops_per_token(T),
+            "h2d_bytes": n_micro * (T + 1) * 8,
+            "config": {"model": f"llama-2-13b shape ({cfg.n_layer}L d5120 40H ff13824 vocab32000 seq4096)",
+                       "global_batch": n_micro, "seq_len": T, "parallelism": f"pp2 x tp{TP}, 1F1B, {n_micro} micro-batches",
+                       "optimizer": "AdamW fp32 master on local shards, step inside the timed region",
+                       "l2": "working set of tens of GB per step >> 126 MB L2; no flush"}}
+    return step_device, step_e2e, info
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -176,6 +361,14 @@ def main():
     from momijo_b200.utils import ClockSampler
 
     rank, world, local = init_dist(args.gpus)
+    if args.config != "gpt2":
+        if args.impl != "ours":
+            if rank == 0:
+                print(json.dumps({"impl": args.impl, "unavailable": f"no {args.impl} arm for --config {args.config}"}))
+            return 0
+        setup = {"llama8b-tp": setup_llama_tp, "moe16b-ep": setup_moe_ep, "llama13b-pptp": setup_llama_pptp}[args.config]
+        step_device, step_e2e, info = setup(args, rank, world, local)
+        return run_and_report(args, rank, world, local, step_device, step_e2e, info)
     cfg = GPT2Config.small() if args.model == "gpt2-small" else GPT2Config.tiny()
     B, T = args.micro_batch, min(args.seq, cfg.max_seq)
     tokens_per_step = B * T * world
@@ -222,6 +415,28 @@ def main():
             opt.zero_grad(set_to_none=True)
             return float(loss)
 
+    info = {
+        "tokens_per_step": tokens_per_step,
+        "scaling": "weak",
+        "flops_per_token": cfg.flops_per_token(T),
+        "h2d_bytes": B * (T + 1) * 8,
+        "config": {
+            "model": "gpt2-small (12L d768 12H ff3072 vocab50257 seq1024)" if args.model == "gpt2-small" else args.model,
+            "global_batch": B * world,
+            "seq_len": T,
+            "parallelism": "single" if world == 1 else f"zero3-dp{world}",
+            "optimizer": "AdamW fp32 master, step inside the timed region",
+            "l2": "per-step working set (0.25 GB weights + GBs of activations) >> 126 MB L2; no flush",
+        },
+    }
+    return run_and_report(args, rank, world, local, step_device, step_e2e, info)
+
+
+def run_and_report(args, rank, world, local, step_device, step_e2e, info):
+    import torch
+    from momijo_b200 import _C
+    from momijo_b200.utils import ClockSampler
+
     for i in range(max(args.warmup, 3)):
         last = step_device(i)
     torch.cuda.synchronize()
@@ -232,11 +447,12 @@ def main():
     launches = _C.launches - launches0
     ms_e2e = timed(step_e2e, args.steps, world)
     clocks = sampler.stop() if sampler is not None else None
-    loss_val = float(last)
+    loss_val = float(last) if last is not None else None
     if args.impl == "ours":
         _C.check_status()
 
     if rank == 0:
+        tokens_per_step = info["tokens_per_step"]
         tok_s = tokens_per_step / (ms / 1e3)
         tok_s_e2e = tokens_per_step / (ms_e2e / 1e3)
         out = {
@@ -248,31 +464,26 @@ def main():
             "warmup": max(args.warmup, 3),
             "ms_per_step": ms,
             "higher_is_better": True,
-            "scaling": "weak",
+            "scaling": info["scaling"],
             "vs_baseline": None,
             "dtype": "bf16",
             "data": "synthetic uniform-random tokens, random-init weights N(0,0.02)",
             "impl": args.impl,
-            "config": {
-                "model": "gpt2-small (12L d768 12H ff3072 vocab50257 seq1024)" if args.model == "gpt2-small" else args.model,
-                "global_batch": B * world,
-                "seq_len": T,
-                "parallelism": "single" if world == 1 else f"zero3-dp{world}",
-                "optimizer": "AdamW fp32 master, step inside the timed region",
-                "l2": "per-step working set (0.25 GB weights + GBs of activations) >> 126 MB L2; no flush",
-            },
+            "config": info["config"],
             "e2e": {
                 "value": tok_s_e2e,
                 "unit": "tokens/s",
                 "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": B * (T + 1) * 8,
+                "h2d_bytes_per_step": info["h2d_bytes"],
                 "d2h_bytes_per_step": 4,
             },
             "gpu_launches": launches if args.impl == "ours" else 0,
             "clocks": clocks,
             "final_loss": loss_val,
-            "model_tflops": cfg.flops_per_token(T) * tok_s / 1e12,
+            "model_tflops": info["flops_per_token"] * tok_s / 1e12,
         }
+        if args.layers:
+            out["reduced"] = f"layer count overridden to {args.layers}: not a result for the named model"
         print(json.dumps(out))
     if world > 1:
         import torch.distributed as dist

@@ -41,6 +41,7 @@ __device__ __forceinline__ bool wait_sys_ge(const int* flag, int want, int* stat
     if (ld_acq_sys(flag) >= want) return true;
     __nanosleep(64);
     if (((++it) & 0xff) == 0) {
+      if (status_failed(status)) return false;
       if (t0 == 0) {
         t0 = globaltimer_ns();
       } else if (globaltimer_ns() - t0 > MMJ_WAIT_BUDGET_NS) {

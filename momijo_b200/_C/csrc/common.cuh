@@ -37,6 +37,13 @@ __device__ __forceinline__ void report(int* status, int code, int detail) {
   }
 }
 
+// True once any kernel has recorded an error in this status word. Waits give up at once then: after
+// a first timeout every later kernel of the step would otherwise spend its own full budget, and a
+// step of several hundred launches would look like a hang.
+__device__ __forceinline__ bool status_failed(const int* status) {
+  return status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0;
+}
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -107,6 +114,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
     if (mbar_try_wait(bar, parity)) return true;
     if (((++it) & 0x3ff) == 0) {
       if (*abort_flag) return false;
+      if (status_failed(status)) {
+        *abort_flag = 1;
+        return false;
+      }
       if (t0 == 0) {
         t0 = globaltimer_ns();
         continue;

@@ -60,6 +60,10 @@ __device__ __forceinline__ bool wait_flag_ge(const int* flag, int want, bool sys
     __nanosleep(32);
     if (((++it) & 0xff) == 0) {
       if (*abort_flag) return false;
+      if (status_failed(status)) {
+        *abort_flag = 1;
+        return false;
+      }
       if (t0 == 0) {
         t0 = globaltimer_ns();
         continue;

@@ -67,6 +67,9 @@ class LlamaBlock(nn.Module):
         c, dt = cfg.d_model, cfg.dtype
         self.attn_norm = nn.Parameter(torch.ones(c, dtype=dt))
         self.mlp_norm = nn.Parameter(torch.ones(c, dtype=dt))
+        # held in full by every tensor-parallel rank, each of which sees 1/world of the rows
+        self.attn_norm.tp_replicated = True
+        self.mlp_norm.tp_replicated = True
         qkv_cols = (cfg.n_head + 2 * cfg.n_kv_head) * cfg.head_dim
         k = lambda n: (layer_id, n)
         self.wqkv = ColumnParallelLinear(c, qkv_cols, tp, bias=False, dtype=dt, init_std=cfg.init_std, key=k("qkv"))
@@ -103,6 +106,7 @@ class Llama(nn.Module):
         ids = range(cfg.n_layer) if layers is None else layers
         self.blocks = nn.ModuleList([LlamaBlock(cfg, self.tp, i) for i in ids])
         self.final_norm = nn.Parameter(torch.ones(cfg.d_model, dtype=dt))
+        self.final_norm.tp_replicated = True
         v_pad = (cfg.vocab_size + self.tp.world * 8 - 1) // (self.tp.world * 8) * (self.tp.world * 8)
         self.v_local = v_pad // self.tp.world
         self.lm_head = ColumnParallelLinear(cfg.d_model, v_pad, self.tp, bias=False, dtype=dt,
@@ -122,6 +126,50 @@ class Llama(nn.Module):
         logits = self.lm_head(h)                       # [M, V/W]
         if targets is None:
             return logits
+        start = self.tp.rank * self.v_local
+        valid = min(self.v_local, max(0, self.cfg.vocab_size - start))
+        return vocab_parallel_cross_entropy(logits, targets, start, valid, self.tp)
+
+
+class LlamaStage(nn.Module):
+    """One pipeline stage of a (tensor-parallel) Llama: a contiguous range of blocks, plus the
+    embedding on the first stage and the final norm / head / loss on the last one. Between stages the
+    residual stream travels as one [M/W, C] tensor per tensor-parallel rank (branch output already
+    added)."""
+
+    def __init__(self, cfg: LlamaConfig, tp: TPContext, layers: range, first: bool, last: bool):
+        super().__init__()
+        self.cfg, self.tp, self.first, self.last = cfg, tp, first, last
+        dt = cfg.dtype
+        self.embed = VocabParallelEmbedding(cfg.vocab_size, cfg.d_model, tp, dtype=dt, init_std=cfg.init_std) \
+            if first else None
+        self.blocks = nn.ModuleList([LlamaBlock(cfg, tp, i) for i in layers])
+        if last:
+            self.final_norm = nn.Parameter(torch.ones(cfg.d_model, dtype=dt))
+            self.final_norm.tp_replicated = True
+            v_pad = (cfg.vocab_size + tp.world * 8 - 1) // (tp.world * 8) * (tp.world * 8)
+            self.v_local = v_pad // tp.world
+            self.lm_head = ColumnParallelLinear(cfg.d_model, v_pad, tp, bias=False, dtype=dt,
+                                                init_std=cfg.init_std, key=("head",))
+        self.batch_shape = None  # (B, T) of a micro-batch; set by the caller on non-first stages
+
+    def forward(self, x):
+        if self.first:
+            B, T = x.shape
+            res = self.embed(x)
+        else:
+            B, T = self.batch_shape
+            res = x
+        delta = None
+        for blk in self.blocks:
+            delta, res = blk(delta, res, B, T)
+        if not self.last:
+            return res + delta if delta is not None else res
+        h, _ = ops.rms_norm(delta, self.final_norm, self.cfg.rms_eps, residual=res)
+        return h
+
+    def loss(self, h, targets):
+        logits = self.lm_head(h)
         start = self.tp.rank * self.v_local
         valid = min(self.v_local, max(0, self.cfg.vocab_size - start))
         return vocab_parallel_cross_entropy(logits, targets, start, valid, self.tp)

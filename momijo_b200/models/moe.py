@@ -39,6 +39,16 @@ class MoEConfig:
     def moe_16b():
         return MoEConfig()
 
+    def flops_per_token(self, seq: int) -> float:
+        """Forward + backward FLOPs per token (matrix products only; top-k routed + shared experts)."""
+        c, hd = self.d_model, self.n_head * self.head_dim
+        attn_proj = 2 * (3 * c * hd + hd * c)
+        experts = 2 * 3 * c * self.d_ff_expert * (self.top_k + self.n_shared)
+        router = 2 * c * self.n_experts
+        dense = (attn_proj + experts + router) * self.n_layer + 2 * c * self.vocab_size
+        attn = 2 * 2 * seq * hd * self.n_layer / 2
+        return 3.0 * (dense + attn)
+
     @staticmethod
     def tiny():
         return MoEConfig(vocab_size=1024, n_layer=2, d_model=256, n_head=4, head_dim=64, n_experts=8,

@@ -1,0 +1,92 @@
+"""Optimizer engines for models whose parameters are not all plain data-parallel replicas.
+
+``HybridEngine`` splits a module's parameters into
+
+* *sharded-local* parameters, of which every rank owns a different slice outright (tensor-parallel
+  weight shards, expert-parallel expert weights, the layers of one pipeline stage): updated by the
+  fused AdamW kernel on a local flat buffer, no gradient exchange;
+* *replicated-in-group* parameters that every rank of a tensor-parallel group holds in full but sees
+  only part of the gradient of (norm weights under sequence parallelism): their gradients are summed
+  over the group with the peer all-reduce kernel (or torch.distributed) before the local update;
+* optionally *data-parallel* parameters (the dense part of an expert-parallel model), which go through
+  ``ShardedDataParallel``: gradient reduce-scatter fused with the sharded AdamW, then the parameter
+  all-gather.
+
+The reference's wrappers stop at one level (``DDP.wrap`` legacy/src/momijo/learn/distributed/ddp.mojo:52-105,
+``ZeroStage1`` legacy/src/momijo/learn/distributed/sharding.mojo:121-184); this composes them the way a
+TP x PP x EP job needs.
+"""
+from __future__ import annotations
+
+from typing import Iterable, List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .zero import AdamWConfig, ShardedDataParallel
+
+
+def mark_replicated(params: Iterable[nn.Parameter]) -> None:
+    for p in params:
+        p.tp_replicated = True
+
+
+class HybridEngine(nn.Module):
+    def __init__(self, module: nn.Module, optim: Optional[AdamWConfig] = None, *, dp_comm=None,
+                 dp_params: Optional[List[nn.Parameter]] = None, rep_comm=None, rep_group=None,
+                 local_grad_scale: float = 1.0):
+        """``dp_params`` (with ``dp_comm``): parameters updated through the sharded data-parallel path;
+        everything else is local. ``rep_comm`` / ``rep_group``: where to sum the gradients of parameters
+        flagged ``tp_replicated`` (a ``PeerComm`` of the tensor-parallel group, or a process group)."""
+        super().__init__()
+        self.module = module
+        self.optim = optim or AdamWConfig()
+        dp_ids = {id(p) for p in (dp_params or [])}
+        local = [p for p in module.parameters() if p.requires_grad and id(p) not in dp_ids]
+        self.local = ShardedDataParallel(module, self.optim, stage=3, comm=None, params=local,
+                                         grad_scale=local_grad_scale) if local else None
+        self.dp = ShardedDataParallel(module, self.optim, stage=3, comm=dp_comm, params=list(dp_params)) \
+            if dp_params else None
+        self.rep_comm, self.rep_group = rep_comm, rep_group
+        self._rep = [p for p in local if getattr(p, "tp_replicated", False)]
+        self._rep_buf = None
+        if self._rep and self.local is not None and (rep_comm is not None or rep_group is not None):
+            self.local.pre_update_hook = self._sync_replicated
+
+    def forward(self, *a, **kw):
+        return self.module(*a, **kw)
+
+    def _sync_replicated(self, _sdp):
+        n = sum(p.numel() for p in self._rep)
+        if self.rep_comm is not None:
+            W = self.rep_comm.world
+            if W == 1:
+                return
+            if self._rep_buf is None:
+                pad = (n + 8 * W - 1) // (8 * W) * (8 * W)
+                self._rep_buf = self.rep_comm.alloc(pad, torch.bfloat16)
+            buf = self._rep_buf
+            off = 0
+            for p in self._rep:
+                buf[off:off + p.numel()].copy_(p.main_grad.reshape(-1))
+                off += p.numel()
+            self.rep_comm.all_reduce_(buf)
+        else:
+            buf = torch.cat([p.main_grad.reshape(-1) for p in self._rep])
+            dist.all_reduce(buf, group=self.rep_group)
+        off = 0
+        for p in self._rep:
+            p.main_grad.copy_(buf[off:off + p.numel()].view_as(p.main_grad))
+            off += p.numel()
+
+    def zero_grad(self):
+        for e in (self.local, self.dp):
+            if e is not None:
+                e.zero_grad()
+
+    def step(self, lr: Optional[float] = None):
+        if self.dp is not None:
+            self.dp.step(lr)
+        if self.local is not None:
+            self.local.step(lr)

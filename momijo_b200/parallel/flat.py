@@ -39,9 +39,10 @@ class FlatParams:
 
     def __init__(self, module: nn.Module, world: int = 1, rank: int = 0,
                  alloc: Optional[Callable[[int, torch.dtype, torch.device], torch.Tensor]] = None,
-                 dtype: torch.dtype = torch.bfloat16, device=None):
+                 dtype: torch.dtype = torch.bfloat16, device=None, params: Optional[List[nn.Parameter]] = None):
+        source = list(params) if params is not None else list(module.parameters())
         seen, params = set(), []
-        for p in module.parameters():
+        for p in source:
             if id(p) not in seen and p.requires_grad:
                 seen.add(id(p))
                 params.append(p)

@@ -45,6 +45,15 @@ class PipelineStage(nn.Module):
         return self.module(x)
 
 
+class _Works:
+    def __init__(self, works):
+        self.works = list(works)
+
+    def wait(self):
+        for w in self.works:
+            w.wait()
+
+
 class Schedule1F1B:
     def __init__(self, stage: PipelineStage, n_micro: int, act_shape, act_dtype=torch.bfloat16, device=None):
         self.stage, self.n_micro = stage, n_micro
@@ -53,13 +62,17 @@ class Schedule1F1B:
         self._pending = []
 
     # ---- p2p helpers ----
+    # Every transfer goes through ``batch_isend_irecv`` (a batch of one): with an eagerly initialised
+    # NCCL group, bare isend / irecv calls are serialised like collectives of the whole group.
     def _irecv(self, src):
         buf = torch.empty(self.act_shape, dtype=self.act_dtype, device=self.device)
-        return buf, dist.irecv(buf, src=src, group=self.stage.group)
+        works = dist.batch_isend_irecv([dist.P2POp(dist.irecv, buf, src, self.stage.group)])
+        return buf, _Works(works)
 
     def _isend(self, t, dst):
         t = t.contiguous()
-        self._pending.append((dist.isend(t, dst=dst, group=self.stage.group), t))
+        works = dist.batch_isend_irecv([dist.P2POp(dist.isend, t, dst, self.stage.group)])
+        self._pending.append((_Works(works), t))
         if len(self._pending) > 4:
             w, _ = self._pending.pop(0)
             w.wait()

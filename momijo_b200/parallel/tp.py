@@ -54,7 +54,8 @@ class TPContext:
     def __init__(self, group=None, comm=None, single: bool = False):
         import torch.distributed as dist
 
-        self.group = group
+        # collectives of the generic path must stay inside the peer communicator's own group
+        self.group = group if group is not None else (comm.group if comm is not None else None)
         self.comm = comm
         if single:
             self.world, self.rank = 1, 0

@@ -36,7 +36,10 @@ class AdamWConfig:
 
 class ShardedDataParallel(nn.Module):
     def __init__(self, module: nn.Module, optim: Optional[AdamWConfig] = None, stage: int = 3,
-                 comm=None, grad_clip: Optional[float] = None):
+                 comm=None, grad_clip: Optional[float] = None, params=None, grad_scale: float = 1.0):
+        """``params``: restrict the wrapper to these parameters of ``module`` (default: all of them).
+        ``grad_scale``: constant applied to the gradients of a single-rank wrapper (a rank that owns
+        its shard outright but whose loss is a per-rank mean needs 1/world here)."""
         super().__init__()
         self.module = module
         self.optim = optim or AdamWConfig()
@@ -46,7 +49,9 @@ class ShardedDataParallel(nn.Module):
         self.rank = comm.rank if comm is not None else 0
         self.grad_clip = grad_clip
         alloc = comm.alloc if comm is not None else None
-        self.flat = FlatParams(module, self.world, self.rank, alloc=alloc)
+        self.flat = FlatParams(module, self.world, self.rank, alloc=alloc, params=params)
+        self.grad_scale = grad_scale
+        self.pre_update_hook = None  # called after gradients are final in the flat buffer, before the update
         dev = self.flat.param.device
         n = self.flat.layout.shard
         a, b = self.flat.layout.shard_range(self.rank)
@@ -74,9 +79,11 @@ class ShardedDataParallel(nn.Module):
         o = self.optim
         lr = o.lr if lr is None else lr
         self.flat.zero_untouched()
+        if self.pre_update_hook is not None:
+            self.pre_update_hook(self)
         self.step_count += 1
         if self.world == 1:
-            grad_scale = 1.0
+            grad_scale = self.grad_scale
             gs_dev = None
             if self.grad_clip is not None:
                 ops.sq_norm(self.flat.grad, out=self.gnorm_sq)
