@@ -250,7 +250,7 @@ def setup_moe_ep(args, rank, world, local):
         comm = PeerComm.from_default_group(heap_bytes=16 << 30)
     torch.manual_seed(1234 + rank)
     with torch.device("cuda"):
-        model = MoEDecoder(cfg, comm, max_tokens=B * T, capacity_factor=1.5)
+        model = MoEDecoder(cfg, comm, max_tokens=B * T, capacity_factor=2.0)
     experts = {id(p) for p in model.expert_parameters()}
     dense = [p for p in model.parameters() if id(p) not in experts]
     if world > 1:

@@ -429,16 +429,17 @@ __global__ void moe_offsets_kernel(const int* counts, int world, int rank, int n
       const int padded = (row + 127) / 128 * 128;
       if (d == rank) {
         for (int tI = start / 128; tI < padded / 128 && tI < max_tiles; ++tI) tile_group[tI] = le;
-        pad_ranges[2 * le] = row;          // rows [row, padded) of this expert hold no token
-        pad_ranges[2 * le + 1] = padded;
-        expert_ranges[2 * le] = start;     // rows [start, padded) belong to this expert
-        expert_ranges[2 * le + 1] = padded;
+        const int cap = max_tiles * 128;   // rows past the buffer's capacity are dropped
+        pad_ranges[2 * le] = min(row, cap);          // rows [row, padded) of this expert hold no token
+        pad_ranges[2 * le + 1] = min(padded, cap);
+        expert_ranges[2 * le] = min(start, cap);     // rows [start, padded) belong to this expert
+        expert_ranges[2 * le + 1] = min(padded, cap);
       }
       row = padded;
     }
     if (d == rank) {
       *num_tiles = min(row / 128, max_tiles);
-      *total_rows = row;
+      *total_rows = min(row, max_tiles * 128);
     }
   }
 }
@@ -464,6 +465,10 @@ __global__ void __launch_bounds__(256) moe_gate_grad_kernel(const MoeGateGradPar
   const int a = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (a >= p.n_assign) return;
   const int d = p.expert_idx[a] / p.epr;
+  if (p.src_row_of[a] < 0) {  // dropped at capacity
+    if (lane == 0) p.dgate[a] = 0.f;
+    return;
+  }
   const uint4* yr = reinterpret_cast<const uint4*>(p.y[d] + (long long)p.src_row_of[a] * p.H);
   const uint4* gr = reinterpret_cast<const uint4*>(p.dout + (long long)(a / p.top_k) * p.H);
   float s = 0.f;
@@ -505,11 +510,11 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const MoeDispatchPara
     const int e = p.expert_idx[a];
     const int d = e / epr, le = e - d * epr;
     const int row = p.seg_off[(d * epr + le) * W + p.t.rank] + p.local_pos[a];
-    if (lane == 0) p.src_row_of[a] = row;
-    if (row >= p.cap_rows) {  // over capacity: drop the row and report it
-      if (lane == 0) report(p.status, kBadArgument, row);
+    if (row >= p.cap_rows) {  // over capacity: the assignment is dropped (contributes nothing)
+      if (lane == 0) p.src_row_of[a] = -1;
       continue;
     }
+    if (lane == 0) p.src_row_of[a] = row;
     const uint4* s = reinterpret_cast<const uint4*>(p.x + (long long)(a / p.top_k) * p.H);
     uint4* dst = reinterpret_cast<uint4*>(p.recv[d] + (long long)row * p.H);
     if (p.row_w == nullptr) {
@@ -557,6 +562,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombineParams
       for (int k = 0; k < p.top_k; ++k) {
         const int a = tk * p.top_k + k;
         const int d = p.expert_idx[a] / epr;
+        if (p.src_row_of[a] < 0) continue;  // dropped at capacity
         const float w = (p.gate_w != nullptr) ? p.gate_w[a] : 1.0f;
         float f[8];
         bf16x8_to_f32(*reinterpret_cast<const uint4*>(p.y[d] + (long long)p.src_row_of[a] * p.H + c * 8), f);

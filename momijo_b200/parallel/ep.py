@@ -187,8 +187,10 @@ class _ExpertsEP(torch.autograd.Function):
         ybuf, _ = disp.next_buffer()
         grouped_gemm(act, w_down, r, out=ybuf)                   # [cap, H] symmetric
         out = disp.combine(ybuf, r, gate_w)
-        # rows are kept as private copies: the symmetric buffers are reused by later layers
-        ctx.save_for_backward(x, gate_w, recv.clone(), gu, act, ybuf.clone(), w_gu, w_down)
+        # The symmetric buffers are reused by later layers, and private copies of the dispatched rows
+        # and of the expert outputs would cost two [cap_rows, H] tensors per layer; the backward pass
+        # dispatches x again and recomputes the expert outputs from `act` instead.
+        ctx.save_for_backward(x, gate_w, gu, act, w_gu, w_down)
         ctx.r, ctx.disp, ctx.refs = r, disp, (w_gu, w_down)
         return out
 
@@ -196,7 +198,7 @@ class _ExpertsEP(torch.autograd.Function):
     def backward(ctx, dout):
         from ..ops.functional import _wgrad_target
 
-        x, gate_w, recv, gu, act, y_saved, w_gu, w_down = ctx.saved_tensors
+        x, gate_w, gu, act, w_gu, w_down = ctx.saved_tensors
         r, disp = ctx.r, ctx.disp
         rw_gu, rw_down = ctx.refs
         F = w_down.shape[2]
@@ -204,7 +206,7 @@ class _ExpertsEP(torch.autograd.Function):
         dout = dout.contiguous()
         # gradient of the router weights needs the (unweighted) expert outputs of every rank
         ysym, _ = disp.next_buffer()
-        ysym.copy_(y_saved)
+        grouped_gemm(act, w_down, r, out=ysym)
         disp.comm.barrier()
         dgate = disp.gate_grad(ysym, dout, r)
         # gradient w.r.t. expert outputs: dispatch dout scaled by the router weights
@@ -214,6 +216,7 @@ class _ExpertsEP(torch.autograd.Function):
         dw_down = grouped_gemm_wgrad(dy, act, r, G, out=buf, accumulate=acc)
         dgu = torch.empty_like(gu)
         _C.call("mmj_swiglu_bwd", _C.ptr(gu), _C.ptr(dact), _C.ptr(dgu), gu.shape[0], F, _C.current_stream())
+        recv = disp.dispatch(x, r)                               # the forward's expert inputs again
         buf2, acc2 = _wgrad_target(rw_gu)
         dw_gu = grouped_gemm_wgrad(dgu, recv, r, G, out=buf2, accumulate=acc2)
         dxbuf, _ = disp.next_buffer()

@@ -27,7 +27,7 @@ _ALIGN = 1024
 class PeerComm:
     """Symmetric heap + signal slots shared by the ranks of one process group (one node)."""
 
-    SLOTS = 4096
+    SLOTS = 65536
 
     def __init__(self, group=None, heap_bytes: Optional[int] = None, use_multicast: bool = False):
         import torch.distributed._symmetric_memory as symm

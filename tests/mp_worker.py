@@ -245,6 +245,27 @@ def sc_tp_llama(comm):
         close(model.embed.weight.grad, full.embed.weight.grad[R * V:(R + 1) * V], 8e-2, "embedding grad")
 
 
+def sc_moe_drop(comm):
+    """Assignments beyond the receive buffer's capacity are dropped, not an error: the layer still runs
+    forward and backward, outputs stay finite and the status word stays clean."""
+    from momijo_b200.parallel.ep import MoEDispatcher, MoELayer
+
+    W = comm.world
+    H, F, E, k, n_tok = 256, 128, 4 * W, 2, 512
+    torch.manual_seed(7)
+    disp = MoEDispatcher(comm, n_experts=E, top_k=k, hidden=H, max_tokens=n_tok, capacity_factor=0.4)
+    ep = MoELayer(H, F, E, k, n_shared=0, dispatcher=disp).cuda()
+    x = torch.randn(n_tok, H, device="cuda").to(bf16).requires_grad_(True)
+    y, aux = ep(x)
+    (y.float().sum() + aux).backward()
+    torch.cuda.synchronize()
+    assert comm.status[0].item() == 0, comm.status.tolist()
+    assert torch.isfinite(y.float()).all() and torch.isfinite(x.grad.float()).all()
+    # some tokens lost all their experts' contributions or kept them: both kinds must exist
+    zero_rows = (y.float().abs().sum(-1) == 0).sum().item()
+    assert 0 < zero_rows < n_tok, zero_rows
+
+
 def sc_timeout(comm):
     """A wait on a flag that nobody sets returns an error status; the context stays usable."""
     slot = comm.new_slots(1)
@@ -260,7 +281,7 @@ def sc_timeout(comm):
 
 SCENARIOS = {"allreduce": sc_allreduce, "zero": sc_zero, "ag_gemm": sc_ag_gemm,
              "gemm_rs": sc_gemm_rs, "moe": sc_moe, "moe_layer": sc_moe_layer, "tp_llama": sc_tp_llama,
-             "timeout": sc_timeout}
+             "moe_drop": sc_moe_drop, "timeout": sc_timeout}
 
 
 def main():

@@ -38,7 +38,7 @@ def test_fused_allgather_gemm_and_gemm_reduce_scatter():
 
 
 def test_moe_dispatch_combine_and_layer():
-    _run(["moe", "moe_layer"])
+    _run(["moe", "moe_layer", "moe_drop"])
 
 
 def test_tensor_parallel_llama_matches_single_rank():
