@@ -91,8 +91,12 @@ _SIGS = {
 _OPTIONAL = {}
 
 
+DEBUG_BOUNDS = os.environ.get("MOMIJO_DEBUG_BOUNDS", "0") == "1"
+
+
 def lib_path() -> Path:
-    return _HERE / "libmomijo_b200.so"
+    """``libmomijo_b200.so``, or the bounds-checked build when MOMIJO_DEBUG_BOUNDS=1."""
+    return _HERE / ("libmomijo_b200_dbg.so" if DEBUG_BOUNDS else "libmomijo_b200.so")
 
 
 def host_lib_path() -> Path:
@@ -153,15 +157,52 @@ class NativeError(RuntimeError):
     pass
 
 
+_NVTX = os.environ.get("MOMIJO_NVTX", "0") == "1"
+
+
 def call(name: str, *args):
-    """Call an exported launcher, count its kernels and raise on a non-zero return code."""
+    """Call an exported launcher, count its kernels and raise on a non-zero return code. With
+    ``MOMIJO_NVTX=1`` every call is wrapped in an NVTX range named after the launcher, so that a
+    timeline tool shows which front-end call produced which kernels."""
     global launches
     fn = getattr(lib(), name)
-    rc = fn(*args)
+    if _NVTX:
+        import torch
+
+        torch.cuda.nvtx.range_push(name)
+        try:
+            rc = fn(*args)
+        finally:
+            torch.cuda.nvtx.range_pop()
+    else:
+        rc = fn(*args)
     launches += _SIGS[name][1]
     if rc != 0:
         raise NativeError(f"{name} failed with code {rc}")
     return rc
+
+
+BOUNDS_SITES = {1: "embedding forward: token id", 2: "embedding backward: token id", 3: "cross-entropy: target id"}
+
+
+def debug_bounds():
+    """Read (and clear) the out-of-range records of the bounds-checked build: a list of dicts with
+    ``unit, count, site, block, thread, index, limit``. ``count == -1`` means a normal build."""
+    import torch
+
+    torch.cuda.synchronize()
+    out = []
+    for unit, fn in (("elementwise", "mmj_debug_bounds_elementwise"), ("loss", "mmj_debug_bounds_loss")):
+        buf = (ctypes.c_longlong * 6)()
+        f = getattr(lib(), fn)
+        f.argtypes = [ctypes.POINTER(ctypes.c_longlong)]
+        f.restype = c_int
+        rc = f(buf)
+        if rc != 0:
+            raise NativeError(f"{fn} failed with code {rc}")
+        out.append({"unit": unit, "count": buf[0], "site": BOUNDS_SITES.get(buf[1], buf[1]), "block": buf[2],
+                    "thread": buf[3], "index": buf[4], "limit": buf[5]})
+    return out
 
 
 def ptr(t):

@@ -54,9 +54,16 @@ def _run(cmd, verbose):
     return r.stdout + r.stderr
 
 
-def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> dict:
-    """Compile all sources; returns {'cuda': path, 'host': path, 'log': str}."""
-    OBJ.mkdir(exist_ok=True)
+def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False,
+          debug_bounds: bool = None) -> dict:
+    """Compile all sources; returns {'cuda': path, 'host': path, 'log': str}. ``debug_bounds`` (default:
+    the MOMIJO_DEBUG_BOUNDS environment variable) builds the bounds-checked variant of the kernel library
+    beside the normal one (``libmomijo_b200_dbg.so``, own object directory)."""
+    if debug_bounds is None:
+        debug_bounds = os.environ.get("MOMIJO_DEBUG_BOUNDS", "0") == "1"
+    obj_dir = HERE / "build_dbg" if debug_bounds else OBJ
+    lib_cuda = HERE / "libmomijo_b200_dbg.so" if debug_bounds else LIB_CUDA
+    obj_dir.mkdir(exist_ok=True)
     headers = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
     cu = sorted(CSRC.glob("*.cu"))
     cpp = sorted(CSRC.glob("*.cpp"))
@@ -64,17 +71,19 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
     log = []
 
     def compile_cu(src: Path):
-        obj = OBJ / (src.stem + ".o")
+        obj = obj_dir / (src.stem + ".o")
         if not force and _newer(obj, [src, *headers]):
             return obj
         flags = list(NVCC_FLAGS)
+        if debug_bounds:
+            flags += ["-DMMJ_DEBUG_BOUNDS"]
         if ptxas_info:
             flags += ["-Xptxas", "-v"]
         log.append(_run([nvcc, *flags, "-c", src, "-o", obj], verbose))
         return obj
 
     def compile_cpp(src: Path):
-        obj = OBJ / (src.stem + ".host.o")
+        obj = obj_dir / (src.stem + ".host.o")
         if not force and _newer(obj, [src, *headers]):
             return obj
         log.append(_run(["g++", "-O3", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-pthread",
@@ -85,12 +94,12 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
         cu_objs = list(ex.map(compile_cu, cu))
         cpp_objs = list(ex.map(compile_cpp, cpp))
 
-    if cu_objs and (force or not _newer(LIB_CUDA, cu_objs)):
-        log.append(_run([nvcc, "-shared", "-o", LIB_CUDA, *cu_objs, "-cudart", "static",
+    if cu_objs and (force or not _newer(lib_cuda, cu_objs)):
+        log.append(_run([nvcc, "-shared", "-o", lib_cuda, *cu_objs, "-cudart", "static",
                          "-gencode", "arch=compute_100a,code=sm_100a"], verbose))
     if cpp_objs and (force or not _newer(LIB_HOST, cpp_objs)):
         log.append(_run(["g++", "-shared", "-pthread", "-o", LIB_HOST, *cpp_objs], verbose))
-    return {"cuda": str(LIB_CUDA), "host": str(LIB_HOST), "log": "\n".join(log)}
+    return {"cuda": str(lib_cuda), "host": str(LIB_HOST), "log": "\n".join(log)}
 
 
 if __name__ == "__main__":

@@ -71,6 +71,43 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// ---- bounds-checked debug build -----------------------------------------------------------
+// With -DMMJ_DEBUG_BOUNDS (MOMIJO_DEBUG_BOUNDS=1 at build time) data-dependent indices go through
+// index_ok(): the first violation of a translation unit is recorded as (count, site, block, thread,
+// index, limit) and the access is skipped or clamped by the caller; nothing traps. The host reads and
+// clears the record through the reader each translation unit defines with MMJ_BOUNDS_READER.
+#ifdef MMJ_DEBUG_BOUNDS
+static __device__ long long g_bounds_err[6];
+__device__ __forceinline__ bool index_ok(long long idx, long long limit, int site) {
+  if (idx >= 0 && idx < limit) return true;
+  if (atomicAdd(reinterpret_cast<unsigned long long*>(&g_bounds_err[0]), 1ULL) == 0ULL) {
+    g_bounds_err[1] = site;
+    g_bounds_err[2] = blockIdx.x;
+    g_bounds_err[3] = threadIdx.x;
+    g_bounds_err[4] = idx;
+    g_bounds_err[5] = limit;
+  }
+  return false;
+}
+#define MMJ_BOUNDS_READER(fn)                                                     \
+  MMJ_API int fn(long long* out6) {                                               \
+    cudaError_t e = cudaMemcpyFromSymbol(out6, g_bounds_err, sizeof(long long) * 6); \
+    if (e != cudaSuccess) return (int)e;                                          \
+    const long long zero[6] = {0, 0, 0, 0, 0, 0};                                 \
+    return (int)cudaMemcpyToSymbol(g_bounds_err, zero, sizeof(zero));             \
+  }
+#else
+__device__ __forceinline__ bool index_ok(long long idx, long long limit, int) {
+  return idx >= 0 && idx < limit;
+}
+#define MMJ_BOUNDS_READER(fn)                      \
+  MMJ_API int fn(long long* out6) {                \
+    for (int i = 0; i < 6; ++i) out6[i] = 0;       \
+    out6[0] = -1; /* not a debug build */          \
+    return 0;                                      \
+  }
+#endif
+
 // ---- mbarrier ------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));

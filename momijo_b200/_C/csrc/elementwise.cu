@@ -166,8 +166,7 @@ __global__ void embedding_fwd_kernel(const long long* __restrict__ tok,
     const long long r = i / c8;
     const int c = (int)(i - r * c8) * 8;
     long long t = tok[r];
-    if (t < 0) t = 0;
-    if (t >= vocab) t = vocab - 1;
+    if (!index_ok(t, vocab, /*site=*/1)) t = t < 0 ? 0 : vocab - 1;  // clamp (recorded in debug builds)
     float a[8];
     ld8(wte + t * C + c, a);
     if (wpe != nullptr) {
@@ -192,7 +191,7 @@ __global__ void embedding_bwd_wte_kernel(const long long* __restrict__ tok,
     const long long r = i / c2;
     const int c = (int)(i - r * c2) * 2;
     long long t = tok[r];
-    if (t < 0 || t >= vocab) continue;
+    if (!index_ok(t, vocab, /*site=*/2)) continue;
     __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(dout + r * C + c);
     atomicAdd(reinterpret_cast<__nv_bfloat162*>(dwte + t * C + c), v);
   }
@@ -689,3 +688,5 @@ MMJ_API int mmj_cast_f32_to_bf16_2d(const float* src, long long lds, void* dst, 
       src, lds, (__nv_bfloat16*)dst, ldd, rows, cols);
   return (int)cudaGetLastError();
 }
+
+MMJ_BOUNDS_READER(mmj_debug_bounds_elementwise)

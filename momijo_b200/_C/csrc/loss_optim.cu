@@ -47,7 +47,7 @@ __global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long 
   __nv_bfloat16* g = logits + row * ld;
   const int nvec = (int)(ld >> 3);  // ld % 8 == 0
   const long long tgt = targets[row];
-  const bool ignored = (tgt == ignore_index) || tgt < 0 || tgt >= V;
+  const bool ignored = (tgt == ignore_index) || !index_ok(tgt, V, /*site=*/3);
 
   float mx = -INFINITY;
   for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
@@ -391,3 +391,5 @@ MMJ_API int mmj_sqnorm(const void* x, int dtype, long long n, float* scratch, fl
   sqnorm_finalize_kernel<<<1, 256, 0, STREAM>>>(scratch, parts, out, accumulate);
   return (int)cudaGetLastError();
 }
+
+MMJ_BOUNDS_READER(mmj_debug_bounds_loss)

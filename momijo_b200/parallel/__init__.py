@@ -2,3 +2,4 @@
 from .flat import FlatParams, FlatLayout  # noqa: F401
 from .zero import ShardedDataParallel, AdamWConfig  # noqa: F401
 from .engine import HybridEngine, mark_replicated  # noqa: F401
+from .ddp import DistributedDataParallel  # noqa: F401

@@ -210,3 +210,26 @@ def test_attention(B, T, Hq, Hkv, D, causal):
                      ("dv", slice((Hq + Hkv) * D, cols))]:
         err = ((gq[:, sl] - rq[:, sl]).abs().max() / rq[:, sl].abs().max()).item()
         assert err < 4e-2, f"{name} relative max error {err}"
+
+
+def test_debug_bounds_build_records_bad_index(tmp_path):
+    """The bounds-checked build records an out-of-range token id (and still clamps it); run in a child
+    process because the library variant is chosen at import time."""
+    import subprocess, sys, os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import torch\n"
+        "from momijo_b200 import _C, ops\n"
+        "assert _C.DEBUG_BOUNDS\n"
+        "w = torch.randn(64, 32, device='cuda').to(torch.bfloat16)\n"
+        "tok = torch.tensor([[1, 2, 99, 3]], device='cuda')\n"
+        "y = ops.embedding(tok, w)\n"
+        "rec = _C.debug_bounds()\n"
+        "e = [r for r in rec if r['unit'] == 'elementwise'][0]\n"
+        "assert e['count'] > 0 and e['index'] == 99 and e['limit'] == 64, rec\n"
+        "assert torch.equal(y.reshape(-1, 32)[2], w[63])\n"
+        "assert all(r['count'] == 0 for r in _C.debug_bounds())\n"
+        "print('BOUNDS_OK')\n")
+    env = dict(os.environ, MOMIJO_DEBUG_BOUNDS="1", PYTHONPATH=root)
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert "BOUNDS_OK" in out.stdout, out.stdout + out.stderr
