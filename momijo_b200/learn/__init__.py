@@ -58,3 +58,10 @@ from .distributed import (  # noqa: F401
     DataParallel, DistributedDataParallel, ShardRange, partition_1d, ZeroStage1, ReduceOp,
     all_gather, reduce_scatter, all_to_all, send, recv, ShardedDataParallel,
 )
+from ..tensor import Tensor  # noqa: F401,E402
+from ..tensor.autograd import GradContext, GradTensor, no_grad_begin, no_grad_end  # noqa: F401,E402
+from ..parallel.tp import ColumnParallelLinear, RowParallelLinear, VocabParallelEmbedding  # noqa: F401,E402
+from ..parallel.ep import TopKRouter, MoELayer  # noqa: F401,E402
+from ..parallel.pp import PipelineStage, Schedule1F1B  # noqa: F401,E402
+from ..parallel.config import ParallelConfig  # noqa: F401,E402
+from ..parallel.engine import HybridEngine  # noqa: F401,E402

@@ -162,6 +162,9 @@ def allreduce(x, op=ReduceOp.SUM, group=None):
     return _back(tt, kind, x)
 
 
+all_reduce = allreduce
+
+
 def allreduce_sum(x, group=None):
     return allreduce(x, ReduceOp.SUM, group)
 

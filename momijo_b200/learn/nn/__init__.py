@@ -13,3 +13,4 @@ from .attention import MultiHeadAttention  # noqa: F401
 from .transformer import EncoderLayer, DecoderLayer, TinyTransformer  # noqa: F401
 from .rnn import GRU  # noqa: F401
 from . import functional, activations, pool, init, regularizers  # noqa: F401
+from ..api.sequential import Sequential as NNSequential  # noqa: F401,E402
