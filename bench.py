@@ -17,7 +17,8 @@ than the 126 MB L2, so no explicit L2 flush is needed between iterations.
 
 ``--impl reference`` must run the unmodified reference; it is pure Mojo with no build files and
 no Mojo toolchain exists in this image, so that arm reports ``unavailable``. ``--impl torch``
-runs the same model as stock PyTorch (cuBLAS + SDPA, FSDP for N > 1) for orientation.
+runs the same model as stock PyTorch (cuBLAS + SDPA, FSDP for N > 1) for orientation; for
+``--config llama8b-tp`` and ``moe16b-ep`` it runs the arms in ``bench_torch.py``.
 """
 from __future__ import annotations
 
@@ -350,6 +351,47 @@ def setup_llama_pptp(args, rank, world, local):
     return step_device, step_e2e, info
 
 
+def setup_torch_arm(args, rank, world, local):
+    """Stock-PyTorch arm of the tensor- and expert-parallel configs (``bench_torch.py``): same shapes, batch
+    sizes and token streams as the native setups, NCCL collectives, cuBLAS, SDPA, fused AdamW on fp32
+    parameters under bf16 autocast."""
+    import torch
+    import torch.distributed as dist
+    from bench_torch import TorchLlamaTP, TorchMoEEP, make_step
+    from momijo_b200.models import LlamaConfig, MoEConfig
+
+    tp = args.config == "llama8b-tp"
+    cfg = LlamaConfig.llama3_8b() if tp else MoEConfig.moe_16b()
+    if args.layers:
+        cfg.n_layer = args.layers
+    B, T = (8, cfg.max_seq) if tp else (4, cfg.max_seq)
+    torch.manual_seed(1234 + rank)
+    with torch.device("cuda"):
+        model = TorchLlamaTP(cfg) if tp else TorchMoEEP(cfg)
+    if not tp and world > 1:
+        for p in model.dense_params:
+            dist.broadcast(p.data, 0)
+    step = make_step(model, "tp" if tp else "ep", "cuda")
+    host_tok = _pinned_batches(cfg.vocab_size, (B, T + 1), 1000 if tp else 1000 + rank)
+    dev_tok = [t.cuda() for t in host_tok]
+
+    def step_device(i):
+        return step(dev_tok[i % len(dev_tok)])
+
+    def step_e2e(i):
+        return float(step(host_tok[i % len(host_tok)].cuda(non_blocking=True)))
+
+    name = (f"llama-3-8b shape ({cfg.n_layer}L d4096 32q/8kv hd128 ff14336 vocab128256 seq4096)" if tp else
+            f"moe-16b shape ({cfg.n_layer}L d2048 16H 64 experts ff1408 top6 + 2 shared vocab102400 seq4096)")
+    info = {"tokens_per_step": B * T * (1 if tp else world), "scaling": "strong" if tp else "weak",
+            "flops_per_token": cfg.flops_per_token(T), "h2d_bytes": B * (T + 1) * 8,
+            "config": {"model": name, "global_batch": B * (1 if tp else world), "seq_len": T,
+                       "parallelism": (f"tp{world}+sp" if tp else f"ep{world}+dp{world}-attention") + " (torch.distributed, cuBLAS, SDPA)",
+                       "optimizer": "torch.optim.AdamW(fused) on fp32 parameters, bf16 autocast, step inside the timed region",
+                       "l2": "working set of tens of GB per step >> 126 MB L2; no flush"}}
+    return step_device, step_e2e, info
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -362,6 +404,9 @@ def main():
 
     rank, world, local = init_dist(args.gpus)
     if args.config != "gpt2":
+        if args.impl == "torch" and args.config in ("llama8b-tp", "moe16b-ep"):
+            step_device, step_e2e, info = setup_torch_arm(args, rank, world, local)
+            return run_and_report(args, rank, world, local, step_device, step_e2e, info)
         if args.impl != "ours":
             if rank == 0:
                 print(json.dumps({"impl": args.impl, "unavailable": f"no {args.impl} arm for --config {args.config}"}))

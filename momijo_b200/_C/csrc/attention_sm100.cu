@@ -98,6 +98,13 @@ __device__ __forceinline__ void bulk_wait_group0() {
   asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 
+// Optional kernel timeline: when a trace buffer is installed, one compute (or softmax) thread and the
+// MMA thread of every CTA store clock64() stamps at their stage boundaries (64 slots per CTA).
+constexpr int kTraceSlots = 64;
+__device__ __forceinline__ void trace_stamp(long long* trace, int cta, int slot) {
+  if (trace != nullptr && slot < kTraceSlots) trace[(long long)cta * kTraceSlots + slot] = clock64();
+}
+
 // =============================================================================================
 // Forward
 // =============================================================================================
@@ -135,6 +142,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int q0 = qb * 128;
   int kv_end = p.causal ? min(p.T, q0 + 128) : p.T;
   const int nkv = (kv_end + 127) / 128;
+  const int cta_lin = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+  const bool tracer = (threadIdx.x == 64);
+  if (tracer) {
+    trace_stamp(p.trace, cta_lin, 0);
+    if (p.trace) {
+      uint32_t smid;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+      p.trace[(long long)cta_lin * kTraceSlots + 1] = smid;
+      p.trace[(long long)cta_lin * kTraceSlots + 7] = nkv;
+    }
+  }
 
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
@@ -161,6 +179,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  if (tracer) trace_stamp(p.trace, cta_lin, 2);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -212,6 +231,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int sv = j % VS;
         const uint32_t phv = (j / VS) & 1;
         if (!mbar_wait(&p_full, j & 1, &abort_flag, p.status, kTimeoutFlag, j)) break;
+        trace_stamp(p.trace, cta_lin, 8 + j * 6 + 3);
         // P(j) written means S(j) has been consumed: the next score tile goes first, so that
         // the softmax of block j+1 can start while P(j) V(j) is still running
         if (j + 1 < nkv) ok = issue_s(j + 1);
@@ -244,6 +264,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     for (int j = 0; j < nkv; ++j) {
       if (!mbar_wait_warp(&s_full, j & 1, &abort_flag, p.status, kTimeoutTmemFull, j)) { ok = false; break; }
       tc_fence_after();
+      if (tracer) trace_stamp(p.trace, cta_lin, 8 + j * 6 + 0);
       const int kv0 = j * 128;
       const bool need_mask = (p.causal && (kv0 + 127 > q0)) || (kv0 + 128 > p.T);
       uint32_t s[128];
@@ -252,6 +273,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tmem_ld_32x32(t_lane + kColS + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
       tmem_ld_32x32(t_lane + kColS + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
       tmem_ld_wait();
+      if (tracer) trace_stamp(p.trace, cta_lin, 8 + j * 6 + 1);
       if (need_mask) {
 #pragma unroll
         for (int i = 0; i < 128; ++i) {
@@ -292,6 +314,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tmem_st_wait();
         }
       }
+      // P(j-1) V(j-1) reads the P tile that is about to be overwritten: it must have finished. (It
+      // was issued after S(j) and takes a fraction of the time spent above, so this wait is normally
+      // already satisfied; without it the order would only be a matter of timing.)
+      if (j > 0) {
+        if (!mbar_wait_warp(&o_full, (j - 1) & 1, &abort_flag, p.status, kTimeoutTmemFull, 200 + j)) { ok = false; break; }
+      }
       const float mc = m_used * c;
       float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll
@@ -312,7 +340,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full);
+      if (tracer) trace_stamp(p.trace, cta_lin, 8 + j * 6 + 2);
     }
+    if (tracer) trace_stamp(p.trace, cta_lin, 4);
     // final: wait for the last P V, normalise and store
     if (ok && nkv > 0)
       ok = mbar_wait_warp(&o_full, (nkv - 1) & 1, &abort_flag, p.status, kTimeoutTmemFull, 999);
@@ -343,12 +373,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   }
 
+  if (tracer) trace_stamp(p.trace, cta_lin, 5);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     __syncwarp();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (tracer) trace_stamp(p.trace, cta_lin, 6);
 }
 
 // =============================================================================================
@@ -385,13 +417,6 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ O, long long
     const long long b = bt / T, t = bt - b * T;
     delta[(b * H + h) * T + t] = s;
   }
-}
-
-// Optional kernel timeline: when a trace buffer is installed, one compute thread and the MMA
-// thread of every CTA store clock64() stamps at their stage boundaries (64 slots per CTA).
-constexpr int kTraceSlots = 64;
-__device__ __forceinline__ void trace_stamp(long long* trace, int cta, int slot) {
-  if (trace != nullptr && slot < kTraceSlots) trace[(long long)cta * kTraceSlots + slot] = clock64();
 }
 
 struct BwdCtl {
@@ -933,6 +958,7 @@ MMJ_API int mmj_attn_fwd(const void* q, long long ldq, int q_col0, const void* k
   p.lse = lse;
   p.status = status;
   dim3 grid((T + 127) / 128, Hq, B);
+  p.trace = (g_attn_trace && (long long)grid.x * grid.y * grid.z <= g_attn_trace_ctas) ? g_attn_trace : nullptr;
   static bool attr64 = false, attr128 = false;
   if (D == 64) {
     const int smem = 4 * kPanelBytes + 2 * kPanelBytes + 1024;  // Q + 2 K + 1 V + P
@@ -952,8 +978,8 @@ MMJ_API int mmj_attn_fwd(const void* q, long long ldq, int q_col0, const void* k
   return (int)cudaGetLastError();
 }
 
-// Install (or clear, with nullptr) the timeline buffer of the backward kernel: int64
-// [ctas * 64]. Launches whose grid has more CTAs than `ctas` leave it untouched.
+// Install (or clear, with nullptr) the timeline buffer of the attention kernels: int64
+// [ctas * 64], written by whichever of them is launched next. Launches whose grid has more CTAs than `ctas` leave it untouched.
 MMJ_API int mmj_attn_set_trace(void* buf, long long ctas) {
   g_attn_trace = reinterpret_cast<long long*>(buf);
   g_attn_trace_ctas = buf ? ctas : 0;

@@ -60,8 +60,22 @@ from .distributed import (  # noqa: F401
 )
 from ..tensor import Tensor  # noqa: F401,E402
 from ..tensor.autograd import GradContext, GradTensor, no_grad_begin, no_grad_end  # noqa: F401,E402
-from ..parallel.tp import ColumnParallelLinear, RowParallelLinear, VocabParallelEmbedding  # noqa: F401,E402
-from ..parallel.ep import TopKRouter, MoELayer  # noqa: F401,E402
-from ..parallel.pp import PipelineStage, Schedule1F1B  # noqa: F401,E402
-from ..parallel.config import ParallelConfig  # noqa: F401,E402
-from ..parallel.engine import HybridEngine  # noqa: F401,E402
+
+# Names that live in momijo_b200.parallel are resolved on first use: that package imports parts of this
+# one (the collective facade), so importing it here at module load would be circular.
+_PARALLEL_NAMES = {
+    "ColumnParallelLinear": "tp", "RowParallelLinear": "tp", "VocabParallelEmbedding": "tp",
+    "TopKRouter": "ep", "MoELayer": "ep", "PipelineStage": "pp", "Schedule1F1B": "pp",
+    "ParallelConfig": "config", "HybridEngine": "engine",
+}
+
+
+def __getattr__(name):
+    mod = _PARALLEL_NAMES.get(name)
+    if mod is None:
+        raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+    import importlib
+
+    value = getattr(importlib.import_module(f"..parallel.{mod}", __name__), name)
+    globals()[name] = value
+    return value
