@@ -40,6 +40,7 @@ _SIGS = {
     "mmj_embedding_bwd": ([P, P, P, P, L, I, I, I, I, P], 2),
     "mmj_colsum_splits": ([I], 0),
     "mmj_colsum_bf16": ([P, L, P, P, P, I, I, I, P], 2),
+    "mmj_splitk_reduce": ([P, L, I, P, L, I, P], 1),
     "mmj_cast_f32_to_bf16": ([P, P, L, P], 1),
     "mmj_cast_bf16_to_f32": ([P, P, L, P], 1),
     "mmj_cast_f32_to_bf16_2d": ([P, L, P, L, L, I, P], 1),

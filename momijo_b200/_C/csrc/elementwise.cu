@@ -279,6 +279,28 @@ __global__ void colsum_finalize_kernel(const float* __restrict__ scratch,
   }
 }
 
+// ---- split-K reduction: out[i] (+)= sum_s parts[s][i]  (fp32 slabs -> bf16) ---------------------
+__global__ void splitk_reduce_kernel(const float* __restrict__ parts, long long slab, int S,
+                                     __nv_bfloat16* __restrict__ out, long long n, int accumulate) {
+  for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8; i < n;
+       i += (long long)gridDim.x * blockDim.x * 8) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int s = 0; s < S; ++s) {
+      const float4 a = *reinterpret_cast<const float4*>(parts + s * slab + i);
+      const float4 b = *reinterpret_cast<const float4*>(parts + s * slab + i + 4);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+      acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    if (accumulate) {
+      float old[8];
+      ld8(out + i, old);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += old[j];
+    }
+    st8(out + i, acc);
+  }
+}
+
 // ---- casts, fills, axpy ------------------------------------------------------------------------
 __global__ void cast_f32_to_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y,
                                         long long n) {
@@ -530,6 +552,16 @@ MMJ_API int mmj_colsum_bf16(const void* x, long long ldx, void* out_bf16, float*
   colsum_partial_kernel<<<grid, block, 0, STREAM>>>((const __nv_bfloat16*)x, ldx, scratch, M, N);
   colsum_finalize_kernel<<<(N + 255) / 256, 256, 0, STREAM>>>(scratch, (__nv_bfloat16*)out_bf16,
                                                               out_f32, S, N, accumulate);
+  return (int)cudaGetLastError();
+}
+
+// Sum S fp32 slabs of n elements (slab stride `slab`, n a multiple of 8) into a bf16 vector.
+MMJ_API int mmj_splitk_reduce(const float* parts, long long slab, int S, void* out, long long n,
+                              int accumulate, void* stream) {
+  if (n == 0) return 0;
+  if (n % 8 || slab % 4 || S < 1) return -1;
+  splitk_reduce_kernel<<<grid_for(n / 8, 256), 256, 0, STREAM>>>(parts, slab, S, (__nv_bfloat16*)out, n,
+                                                                accumulate);
   return (int)cudaGetLastError();
 }
 

@@ -55,6 +55,55 @@ def pick_bn(M: int, N: int) -> int:
     return best
 
 
+_SPLITK = {"ranges": {}, "scratch": None, "enabled": True, "force": None}
+
+
+def plan_split_k(M: int, N: int, K: int, bn: int = 128):
+    """Number of K splits for a weight-gradient shaped product (small M x N, long K): the output has
+    too few 128 x bn tiles to occupy 148 SMs, so the contraction is cut into S ranges whose partial
+    products run as separate tiles and are summed afterwards. Returns 1 when splitting does not pay."""
+    if _SPLITK["force"] is not None:
+        return max(1, int(_SPLITK["force"]))
+    tiles = -(-M // 128) * -(-N // bn)
+    if not _SPLITK["enabled"] or K < 4096 or tiles >= 148:
+        return 1
+    best, best_cost = 1, None
+    for S in range(1, 17):
+        if K // S < 1024:
+            break
+        waves = -(-(tiles * S) // 148)
+        cost = waves * (K / S) + 600.0 * (S > 1) + 40.0 * S   # fixed cost of the reduction pass
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = S, cost
+    return best
+
+
+def _split_ranges(K: int, S: int, device):
+    key = (K, S, str(device))
+    r = _SPLITK["ranges"].get(key)
+    if r is None:
+        step = -(-K // S)
+        step = (step + 127) // 128 * 128
+        edges = [min(i * step, K) for i in range(S + 1)]
+        r = torch.tensor([v for i in range(S) for v in (edges[i], edges[i + 1])], dtype=torch.int32, device=device)
+        _SPLITK["ranges"][key] = r
+    return r
+
+
+def _gemm_split_k(a, b, out, accumulate, M, N, K, S, bn):
+    """a: [K, M], b: [K, N] (both MN-major). Partial products as fp32 slabs, then one reduction pass."""
+    need = S * M * N
+    sc = _SPLITK["scratch"]
+    if sc is None or sc.numel() < need or sc.device != a.device:
+        sc = torch.empty(need, dtype=torch.float32, device=a.device)
+        _SPLITK["scratch"] = sc
+    _C.call("mmj_gemm_bf16_grouped_k", _C.ptr(a), a.stride(0), _C.ptr(b), b.stride(0), _C.ptr(sc), N, K, M, N, S,
+            _C.ptr(_split_ranges(K, S, a.device)), 1, 0, bn, _C.ptr(_C.status_tensor(a.device)),
+            _C.current_stream())
+    _C.call("mmj_splitk_reduce", _C.ptr(sc), M * N, S, _C.ptr(out), M * N, int(accumulate), _C.current_stream())
+    return out
+
+
 def _check_2d(t, name):
     if t.dim() != 2 or t.stride(1) != 1:
         raise ValueError(f"{name} must be 2-D with unit inner stride, got shape {tuple(t.shape)} "
@@ -134,6 +183,11 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_f32=False, accumulate=Fa
         _check_2d(aux, "aux")
     if N % 8 != 0 and out.stride(0) % 8 != 0:
         raise ValueError("output leading dimension must be a multiple of 8 elements")
+    if (a_mn and b_mn and epi in (0, EPI_ACCUMULATE) and out.is_contiguous() and (M * N) % 8 == 0
+            and M % 8 == 0 and N % 8 == 0):
+        S = plan_split_k(M, N, K, 128)
+        if S > 1:
+            return _gemm_split_k(a, b, out, accumulate, M, N, K, S, 128)
     if bn is None:
         bn = pick_bn(M, N)
     _C.call("mmj_gemm_bf16", _C.ptr(a), a.stride(0), int(a_mn), _C.ptr(b), b.stride(0), int(b_mn),
