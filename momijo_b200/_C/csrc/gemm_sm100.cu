@@ -397,7 +397,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   const int bn = p.bn;
   const int stages = p.stages;
   const int b_stage_bytes = bn * kGemmBK * 2;
-  const int stage_bytes = kAStageBytes + b_stage_bytes;
+  // Tall tiles (bm2): 256 rows per tile as two 128-row sub-tiles that share each B stage, which
+  // halves the B bytes pulled from L2 per FLOP. With bn = 256 the two accumulators take all 512
+  // TMEM columns, so the epilogue of a tile no longer overlaps the next tile's main loop.
+  const int subs = p.bm2 ? 2 : 1;
+  const int bm = kGemmBM * subs;
+  const int a_bytes = kAStageBytes * subs;
+  const int stage_bytes = a_bytes + b_stage_bytes;
+  const int n_acc = (subs * bn > kAccCols) ? 1 : 2;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -423,7 +430,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   const uint32_t tmem_base = tmem_slot;
 
   const int num_m = (p.num_m_tiles_dev != nullptr) ? *p.num_m_tiles_dev
-                                                   : (p.M + kGemmBM - 1) / kGemmBM;
+                                                   : (p.M + bm - 1) / bm;
   const int num_n = (p.N + bn - 1) / bn;
   const int num_k = (p.K + kGemmBK - 1) / kGemmBK;
   const int per_group = num_m * num_n;
@@ -439,7 +446,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         for (int t = blockIdx.x; t < num_tiles && ok; t += gemm_ctas) {
           const KRange kr = krange_of(t, per_group, num_k, p);
           const TileCoord tc = tile_of(kr.tt, num_m, num_n, p);
-          const int m0 = tc.m_tile * kGemmBM;
+          const int m0 = tc.m_tile * bm;
           const int n0 = tc.n_tile * bn;
           const int g = (p.tile_group != nullptr) ? p.tile_group[tc.m_tile] : 0;
           const int b_row_base = g * p.b_group_rows;
@@ -459,14 +466,18 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
               break;
             }
             uint8_t* sA = smem + (size_t)s * stage_bytes;
-            uint8_t* sB = sA + kAStageBytes;
+            uint8_t* sB = sA + a_bytes;
             mbar_expect_tx(&full_bar[s], (uint32_t)stage_bytes);
             const int k0 = kr.k_begin + kb * kGemmBK;
-            if (!p.a_mn) {
-              tma_load_2d(sA, &tmA, &full_bar[s], k0, m0);
-            } else {
-              tma_load_2d(sA, &tmA, &full_bar[s], m0, k0);
-              tma_load_2d(sA + 8192, &tmA, &full_bar[s], m0 + 64, k0);
+            for (int sub = 0; sub < subs; ++sub) {
+              uint8_t* sAs = sA + sub * kAStageBytes;
+              const int ms = m0 + sub * kGemmBM;
+              if (!p.a_mn) {
+                tma_load_2d(sAs, &tmA, &full_bar[s], k0, ms);
+              } else {
+                tma_load_2d(sAs, &tmA, &full_bar[s], ms, k0);
+                tma_load_2d(sAs + 8192, &tmA, &full_bar[s], ms + 64, k0);
+              }
             }
             if (!p.b_mn) {
               tma_load_2d(sB, &tmB, &full_bar[s], k0, b_row_base + n0);
@@ -500,6 +511,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kAccCols);
+          const uint32_t d_tmem1 = d_tmem + (uint32_t)bn;  // second sub-tile of a tall tile
           for (int kb = 0; kb < kr.nk; ++kb) {
             if (!mbar_wait(&full_bar[s], ph, &abort_flag, p.status, kTimeoutFull, kb)) {
               ok = false;
@@ -507,19 +519,23 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             }
             tc_fence_after();
             const uint32_t a_base = smem_u32(smem + (size_t)s * stage_bytes);
-            const uint32_t b_base = a_base + kAStageBytes;
+            const uint32_t b_base = a_base + (uint32_t)a_bytes;
 #pragma unroll
             for (int k = 0; k < kGemmBK / 16; ++k) {
               const uint64_t da = make_smem_desc(a_base + k * a_kstep, a_lbo, 1024);
               const uint64_t db = make_smem_desc(b_base + k * b_kstep, b_lbo, 1024);
               umma_bf16_ss(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+              if (subs == 2) {
+                const uint64_t da1 = make_smem_desc(a_base + kAStageBytes + k * a_kstep, a_lbo, 1024);
+                umma_bf16_ss(d_tmem1, da1, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+              }
             }
             umma_commit(&empty_bar[s]);  // frees the smem stage once these MMAs retire
             if (++s == stages) { s = 0; ph ^= 1; }
           }
           if (!ok) break;
           umma_commit(&tfull_bar[acc]);  // accumulator complete
-          if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+          if (++acc == n_acc) { acc = 0; acc_ph ^= 1; }
         }
       }
     } else {
@@ -530,12 +546,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       for (int t = blockIdx.x; t < num_tiles; t += gemm_ctas) {
         const KRange kr = krange_of(t, per_group, num_k, p);
         const TileCoord tc = tile_of(kr.tt, num_m, num_n, p);
-        const int m0 = tc.m_tile * kGemmBM;
+        const int m0 = tc.m_tile * bm;
         const int n0 = tc.n_tile * bn;
         const int out_row0 = kr.g * p.M;  // grouped-K: group g writes rows [g*M, (g+1)*M)
         if (kr.nk == 0) {
           // nothing to contract (an expert without tokens): the result is zero
-          const int zrow = m0 + quad * 32 + lane;
+          for (int sub = 0; sub < subs; ++sub) {
+          const int zrow = m0 + sub * kGemmBM + quad * 32 + lane;
           if (zrow < p.M) {
             uint32_t z[32];
 #pragma unroll
@@ -550,28 +567,32 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
               }
             }
           }
+          }
           continue;
         }
         if (!mbar_wait_warp(&tfull_bar[acc], acc_ph, &abort_flag, p.status, kTimeoutTmemFull, t)) break;
         tc_fence_after();
-        const int row = m0 + quad * 32 + lane;
-        const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kAccCols);
-        for (int c = 0; c < bn / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(t_row + (uint32_t)(c * 32), r);
-          tmem_ld_wait();
-          const int col0 = n0 + c * 32;
-          if (row < p.M && col0 < p.N) {
-            if (p.epi & kEpiOutF32)
-              epilogue_store_chunk<true>(p, r, row + out_row0, col0);
-            else
-              epilogue_store_chunk<false>(p, r, row + out_row0, col0);
+        for (int sub = 0; sub < subs; ++sub) {
+          const int row = m0 + sub * kGemmBM + quad * 32 + lane;
+          const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) +
+                                 (uint32_t)(acc * kAccCols + sub * bn);
+          for (int c = 0; c < bn / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_row + (uint32_t)(c * 32), r);
+            tmem_ld_wait();
+            const int col0 = n0 + c * 32;
+            if (row < p.M && col0 < p.N) {
+              if (p.epi & kEpiOutF32)
+                epilogue_store_chunk<true>(p, r, row + out_row0, col0);
+              else
+                epilogue_store_chunk<false>(p, r, row + out_row0, col0);
+            }
           }
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty_bar[acc]);
-        if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+        if (++acc == n_acc) { acc = 0; acc_ph ^= 1; }
       }
     }
   }
@@ -680,7 +701,8 @@ int launch_gemm(GemmParams& p, const void* A, long long lda, long long a_rows, c
     rc = make_tmap_bf16_2d(&tmB, B, (uint64_t)p.N, (uint64_t)b_rows, (uint64_t)ldb, 64, 64);
   if (rc) return rc;
 
-  const int stage_bytes = kAStageBytes + p.bn * kGemmBK * 2;
+  if (p.bm2 && (p.flag_mode != 0 || p.tile_group != nullptr || (p.epi & kEpiScatterPeers))) return -5;
+  const int stage_bytes = kAStageBytes * (p.bm2 ? 2 : 1) + p.bn * kGemmBK * 2;
   int stages = (200 * 1024) / stage_bytes;
   if (stages > kGemmMaxStages) stages = kGemmMaxStages;
   p.stages = stages;
@@ -690,7 +712,8 @@ int launch_gemm(GemmParams& p, const void* A, long long lda, long long a_rows, c
                          220 * 1024);
     g_attr_set = true;
   }
-  const int num_m = (p.M + kGemmBM - 1) / kGemmBM;
+  const int bm = kGemmBM * (p.bm2 ? 2 : 1);
+  const int num_m = (p.M + bm - 1) / bm;
   const int num_n = (p.N + p.bn - 1) / p.bn;
   long long tiles = (long long)num_m * num_n;
   if (p.groups_k > 0) tiles *= p.groups_k;
@@ -718,7 +741,8 @@ MMJ_API int mmj_gemm_bf16(const void* A, long long lda, int a_mn, const void* B,
   GemmParams p = {};
   p.M = M; p.N = N; p.K = K;
   p.a_mn = a_mn; p.b_mn = b_mn;
-  p.bn = bn;
+  p.bn = bn & 0xfff;          // bit 12 of `bn` asks for 256-row tiles
+  p.bm2 = (bn >> 12) & 1;
   p.epi = epi;
   p.D = D; p.ldd = ldd;
   p.D2 = D2; p.ldd2 = ldd2;
@@ -850,7 +874,8 @@ MMJ_API int mmj_gemm_bf16_grouped_k(const void* A, long long lda, const void* B,
   GemmParams p = {};
   p.M = M; p.N = N; p.K = rows;
   p.a_mn = 1; p.b_mn = 1;
-  p.bn = bn;
+  p.bn = bn & 0xfff;          // bit 12 of `bn` asks for 256-row tiles
+  p.bm2 = (bn >> 12) & 1;
   p.epi = (out_f32 ? kEpiOutF32 : 0) | (accumulate ? kEpiAccumulate : 0);
   p.D = D; p.ldd = ldd;
   p.status = status;

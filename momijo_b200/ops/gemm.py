@@ -25,6 +25,7 @@ EPI_SILU = 64
 EPI_MUL_AUX = 128
 EPI_SCATTER_PEERS = 256
 EPI_ROW_SCALE = 512
+TALL = 1 << 12   # or-ed into the tile width: 256-row tiles (two 128-row MMAs per B stage)
 
 
 def _gelu_tanh(x):
@@ -58,24 +59,52 @@ def pick_bn(M: int, N: int) -> int:
 _SPLITK = {"ranges": {}, "scratch": None, "enabled": True, "force": None}
 
 
-def plan_split_k(M: int, N: int, K: int, bn: int = 128):
-    """Number of K splits for a weight-gradient shaped product (small M x N, long K): the output has
-    too few 128 x bn tiles to occupy 148 SMs, so the contraction is cut into S ranges whose partial
-    products run as separate tiles and are summed afterwards. Returns 1 when splitting does not pay."""
+# Measured cost of one 64-deep K block of a tile, in SM cycles (B200, operands streamed from L2/HBM):
+# the taller / wider the tile, the fewer operand bytes it pulls per FLOP.
+_KBLOCK_CYCLES = {(128, False): 850.0, (256, False): 1100.0, (128, True): 1230.0, (256, True): 2100.0}
+
+
+def plan_wgrad(M: int, N: int, K: int):
+    """(splits, tile width, tall) for a weight-gradient shaped product dW[M, N] = sum_k dy[k, M] x[k, N]
+    (small output, long contraction). The output alone has too few tiles to occupy 148 SMs, so the
+    contraction is cut into S ranges whose partial products run as separate tiles (fp32 slabs) and are
+    summed by one reduction pass. Returns S = 1 when the plain kernel is the better choice."""
     if _SPLITK["force"] is not None:
-        return max(1, int(_SPLITK["force"]))
-    tiles = -(-M // 128) * -(-N // bn)
-    if not _SPLITK["enabled"] or K < 4096 or tiles >= 148:
-        return 1
-    best, best_cost = 1, None
-    for S in range(1, 17):
-        if K // S < 1024:
-            break
-        waves = -(-(tiles * S) // 148)
-        cost = waves * (K / S) + 600.0 * (S > 1) + 40.0 * S   # fixed cost of the reduction pass
-        if best_cost is None or cost < best_cost - 1e-9:
-            best, best_cost = S, cost
+        f = _SPLITK["force"]
+        return f if isinstance(f, tuple) else (max(1, int(f)), 128, False)
+    plain_tiles = -(-M // 128) * -(-N // 128)
+    if not _SPLITK["enabled"] or K < 4096 or plain_tiles >= 2 * 148:
+        return 1, 128, False
+    best, best_cost = (1, 128, False), None
+    for (bn, tall), kcyc in _KBLOCK_CYCLES.items():
+        if bn > max(128, N) or (tall and M < 256):
+            continue
+        tiles = -(-M // (256 if tall else 128)) * -(-N // bn)
+        for S in range(1, 17):
+            if K // S < 1024:
+                break
+            waves = -(-(tiles * S) // 148)
+            cost = waves * (K / S / 64.0) * kcyc
+            if S > 1 or tall:
+                cost += 5700.0 + S * M * N * 0.0026    # reduction pass: launch + slab traffic
+            if best_cost is None or cost < best_cost - 1e-6:
+                best, best_cost = (S, bn, tall), cost
+    S, bn, tall = best
+    if S == 1 and tall:      # a single range needs no slabs: fall back to the plain kernel
+        return 1, 128, False
     return best
+
+
+def plan_split_k(M: int, N: int, K: int, bn: int = 128):
+    return plan_wgrad(M, N, K)[0]
+
+
+def pick_tall(M: int, N: int, K: int) -> bool:
+    """256 x 256 tiles for plain products with a long contraction and enough tiles to fill the GPU
+    several times over: they pull a third less operand data per FLOP than 128 x 256 tiles, at the price
+    of an epilogue that no longer overlaps the next tile's main loop (which is why short contractions
+    keep the 128-row tiles)."""
+    return K >= 4096 and M >= 256 and N >= 256 and (-(-M // 256)) * (-(-N // 256)) >= 3 * 148
 
 
 def _split_ranges(K: int, S: int, device):
@@ -90,7 +119,7 @@ def _split_ranges(K: int, S: int, device):
     return r
 
 
-def _gemm_split_k(a, b, out, accumulate, M, N, K, S, bn):
+def _gemm_split_k(a, b, out, accumulate, M, N, K, S, bn, tall=False):
     """a: [K, M], b: [K, N] (both MN-major). Partial products as fp32 slabs, then one reduction pass."""
     need = S * M * N
     sc = _SPLITK["scratch"]
@@ -98,7 +127,8 @@ def _gemm_split_k(a, b, out, accumulate, M, N, K, S, bn):
         sc = torch.empty(need, dtype=torch.float32, device=a.device)
         _SPLITK["scratch"] = sc
     _C.call("mmj_gemm_bf16_grouped_k", _C.ptr(a), a.stride(0), _C.ptr(b), b.stride(0), _C.ptr(sc), N, K, M, N, S,
-            _C.ptr(_split_ranges(K, S, a.device)), 1, 0, bn, _C.ptr(_C.status_tensor(a.device)),
+            _C.ptr(_split_ranges(K, S, a.device)), 1, 0, bn | (TALL if tall else 0),
+            _C.ptr(_C.status_tensor(a.device)),
             _C.current_stream())
     _C.call("mmj_splitk_reduce", _C.ptr(sc), M * N, S, _C.ptr(out), M * N, int(accumulate), _C.current_stream())
     return out
@@ -114,7 +144,7 @@ def _check_2d(t, name):
 
 def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_f32=False, accumulate=False, bias=None,
          gelu=False, pre_out=None, dgelu_aux=None, add_aux=None, mul_aux=None, silu=False,
-         row_scale=None, bn=None):
+         row_scale=None, bn=None, tall=False):
     """D[M, N] = contraction over K of A and B, followed by the fused epilogue.
 
     a: ``[M, K]`` (or ``[K, M]`` when ``a_mn``); b: ``[N, K]`` (or ``[K, N]`` when ``b_mn``).
@@ -185,14 +215,17 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_f32=False, accumulate=Fa
         raise ValueError("output leading dimension must be a multiple of 8 elements")
     if (a_mn and b_mn and epi in (0, EPI_ACCUMULATE) and out.is_contiguous() and (M * N) % 8 == 0
             and M % 8 == 0 and N % 8 == 0):
-        S = plan_split_k(M, N, K, 128)
+        S, sbn, stall = plan_wgrad(M, N, K)
         if S > 1:
-            return _gemm_split_k(a, b, out, accumulate, M, N, K, S, 128)
+            return _gemm_split_k(a, b, out, accumulate, M, N, K, S, sbn, stall)
     if bn is None:
-        bn = pick_bn(M, N)
+        if not tall and pick_tall(M, N, K):
+            bn, tall = 256, True
+        else:
+            bn = pick_bn(M, N)
     _C.call("mmj_gemm_bf16", _C.ptr(a), a.stride(0), int(a_mn), _C.ptr(b), b.stride(0), int(b_mn),
             _C.ptr(out), out.stride(0), M, N, K, epi, _C.ptr(bias), _C.ptr(aux),
             aux.stride(0) if aux is not None else 0, _C.ptr(pre_out),
-            pre_out.stride(0) if pre_out is not None else 0, _C.ptr(row_scale), bn,
+            pre_out.stride(0) if pre_out is not None else 0, _C.ptr(row_scale), bn | (TALL if tall else 0),
             _C.ptr(_C.status_tensor(a.device)), _C.current_stream())
     return (out, pre_out) if gelu else out
