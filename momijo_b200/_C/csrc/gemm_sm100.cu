@@ -2,14 +2,14 @@
 // fp32 accumulation in tensor memory (TMEM), operands staged in shared memory by TMA with a
 // 128-byte swizzle, issued by one thread per CTA (tcgen05.mma), persistent over output tiles.
 //
-// Warp roles inside a 192-thread CTA:
+// Warp roles inside a 320-thread CTA:
 //   warp 0      TMA producer (one lane)
 //   warp 1      TMEM allocator + MMA issuer (one lane)
-//   warps 2..5  epilogue: tcgen05.ld the accumulator (one output row per thread), apply the
-//               fused epilogue (bias / GELU / GELU' / residual / SiLU / scale / accumulate),
-//               store bf16 or fp32
+//   warps 2..9  epilogue: tcgen05.ld the accumulator (one output row per thread, two warps per
+//               TMEM lane quadrant taking alternate 32-column chunks), apply the fused epilogue
+//               (bias / GELU / GELU' / residual / SiLU / scale / accumulate), store bf16 or fp32
 // Two accumulators (2 x 256 TMEM columns) let the epilogue of tile i overlap the main loop
-// of tile i+1.
+// of tile i+1. Tiles are 128 rows tall, or 256 (two MMAs per B stage) for long contractions.
 //
 // The same kernel also carries the fused communication paths:
 //   * gathered operand: extra CTAs pull peer shards over NVLink into local memory and publish
@@ -28,7 +28,8 @@
 
 namespace mmj {
 
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = (2 + kEpiWarps) * 32;  // TMA producer warp, MMA warp, epilogue warps
 constexpr int kAStageBytes = kGemmBM * kGemmBK * 2;  // 16 KiB
 constexpr int kTmemCols = 512;
 constexpr int kAccCols = 256;
@@ -413,7 +414,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 4);
+      mbar_init(&tempty_bar[a], kEpiWarps);
     }
     abort_flag = 0;
     mbar_fence_init();
@@ -540,7 +541,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       }
     } else {
       // ======================= epilogue warps =======================
-      const int quad = warp & 3;  // TMEM lane quadrant this warp may access
+      // Eight epilogue warps: two per TMEM lane quadrant (a warp reaches the 32 lanes of quadrant
+      // warp % 4 only), taking alternate 32-column chunks. With four warps the fused GELU / GELU'
+      // epilogues of the K = 768 products took longer than the next tile's main loop.
+      const int quad = warp & 3;
+      const int chalf = (warp - 2) >> 2;
       int acc = 0;
       uint32_t acc_ph = 0;
       for (int t = blockIdx.x; t < num_tiles; t += gemm_ctas) {
@@ -557,7 +562,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             uint32_t z[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) z[i] = 0u;
-            for (int c = 0; c < bn / 32; ++c) {
+            for (int c = chalf; c < bn / 32; c += 2) {
               const int col0 = n0 + c * 32;
               if (col0 < p.N) {
                 if (p.epi & kEpiOutF32)
@@ -576,7 +581,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           const int row = m0 + sub * kGemmBM + quad * 32 + lane;
           const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) +
                                  (uint32_t)(acc * kAccCols + sub * bn);
-          for (int c = 0; c < bn / 32; ++c) {
+          for (int c = chalf; c < bn / 32; c += 2) {
             uint32_t r[32];
             tmem_ld_32x32(t_row + (uint32_t)(c * 32), r);
             tmem_ld_wait();
