@@ -315,7 +315,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       const int n_comm = (int)gridDim.x - gemm_ctas;
       const int cid = (int)blockIdx.x - gemm_ctas;
       const int ntiles = (int)((p.gather_total_bytes + p.tile_bytes - 1) / p.tile_bytes);
-      const int rot = (p.flag_mode == 1) ? p.m_tile_rot : p.n_tile_rot;
+      const int rot = p.comm_rot;
       uint32_t issued = 0, drained = 0;  // chunk counters over the ring
       bool ok = true;
       for (int i = cid; i < ntiles && ok; i += n_comm) {
@@ -452,8 +452,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           const int g = (p.tile_group != nullptr) ? p.tile_group[tc.m_tile] : 0;
           const int b_row_base = g * p.b_group_rows;
           if (p.flag_mode == 1) {
-            ok = wait_flag_ge(p.ready_flags + tc.m_tile, p.ready_epoch, false, &abort_flag,
-                              p.status, tc.m_tile);
+            // flags are per 128-row granule of the gathered operand: a tall tile needs two
+            const int n_gran = (p.M + kGemmBM - 1) / kGemmBM;
+            for (int sub = 0; sub < subs && ok; ++sub) {
+              const int gt = tc.m_tile * subs + sub;
+              if (gt < n_gran)
+                ok = wait_flag_ge(p.ready_flags + gt, p.ready_epoch, false, &abort_flag, p.status, gt);
+            }
             asm volatile("fence.proxy.async;" ::: "memory");
           } else if (p.flag_mode == 2) {
             ok = wait_flag_ge(p.ready_flags + tc.n_tile, p.ready_epoch, false, &abort_flag,
@@ -706,7 +711,7 @@ int launch_gemm(GemmParams& p, const void* A, long long lda, long long a_rows, c
     rc = make_tmap_bf16_2d(&tmB, B, (uint64_t)p.N, (uint64_t)b_rows, (uint64_t)ldb, 64, 64);
   if (rc) return rc;
 
-  if (p.bm2 && (p.flag_mode != 0 || p.tile_group != nullptr || (p.epi & kEpiScatterPeers))) return -5;
+  if (p.bm2 && p.tile_group != nullptr) return -5;
   const int stage_bytes = kAStageBytes * (p.bm2 ? 2 : 1) + p.bn * kGemmBK * 2;
   int stages = (200 * 1024) / stage_bytes;
   if (stages > kGemmMaxStages) stages = kGemmMaxStages;
@@ -799,7 +804,9 @@ MMJ_API int mmj_gemm_bf16_allgather(const void* const* peer_src, void* gathered,
   if (world < 1 || world > kMaxPeers) return -5;
   GemmParams p = {};
   p.M = M; p.N = N; p.K = K;
-  p.bn = bn;
+  p.bn = bn & 0xfff;          // bit 12 of `bn` asks for 256-row tiles
+  p.bm2 = (bn >> 12) & 1;
+  bn = p.bn;
   p.epi = epi;
   p.D = D; p.ldd = ldd;
   p.D2 = D2; p.ldd2 = ldd2;
@@ -828,12 +835,14 @@ MMJ_API int mmj_gemm_bf16_allgather(const void* const* peer_src, void* gathered,
   if (gather_a) {
     p.flag_mode = 1;
     p.a_mn = 0; p.b_mn = other_mn;
-    p.m_tile_rot = rot_tile;
+    p.comm_rot = rot_tile;
+    p.m_tile_rot = p.bm2 ? rot_tile / 2 : rot_tile;
     return launch_gemm(p, gathered, ld_gathered, M, other, ld_other, other_mn ? K : N, comm_ctas,
                        (cudaStream_t)stream);
   } else {
     p.flag_mode = 2;
     p.a_mn = other_mn; p.b_mn = 0;
+    p.comm_rot = rot_tile;
     p.n_tile_rot = rot_tile;
     return launch_gemm(p, other, ld_other, other_mn ? K : M, gathered, ld_gathered, N, comm_ctas,
                        (cudaStream_t)stream);
@@ -854,7 +863,8 @@ MMJ_API int mmj_gemm_bf16_reduce_scatter(const void* A, long long lda, const voi
   GemmParams p = {};
   p.M = M; p.N = N; p.K = K;
   p.a_mn = 0; p.b_mn = b_mn;
-  p.bn = bn;
+  p.bn = bn & 0xfff;          // bit 12 of `bn` asks for 256-row tiles
+  p.bm2 = (bn >> 12) & 1;
   p.epi = kEpiScatterPeers;
   p.ldd = ldd;
   p.status = status;
@@ -863,8 +873,9 @@ MMJ_API int mmj_gemm_bf16_reduce_scatter(const void* A, long long lda, const voi
   p.slot_stride = slot_stride;
   for (int r = 0; r < world; ++r) p.peer_D[r] = peer_stage[r];
   p.D = peer_stage[rank];
-  const int num_m = (M + kGemmBM - 1) / kGemmBM;
-  p.m_tile_rot = (int)(((long long)(rank + 1) % world) * p.rows_per_rank / kGemmBM) % num_m;
+  const int bm = kGemmBM * (p.bm2 ? 2 : 1);
+  const int num_m = (M + bm - 1) / bm;
+  p.m_tile_rot = (int)(((long long)(rank + 1) % world) * p.rows_per_rank / bm) % num_m;
   return launch_gemm(p, A, lda, M, B, ldb, b_mn ? K : N, 0, (cudaStream_t)stream);
 }
 

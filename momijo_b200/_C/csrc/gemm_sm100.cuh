@@ -28,6 +28,7 @@ struct GemmParams {
   int a_mn, b_mn;  // 0: operand is K-major ([rows, K]); 1: MN-major ([K, rows])
   int bn;          // N tile: 64, 128 or 256
   int bm2;         // 1: tiles are 256 rows tall (two 128-row MMAs share every B stage)
+  int comm_rot;    // first gather granule the communication CTAs visit (granule units)
   int stages;
   int epi;
   int vec_ok;  // epilogue may use 16-byte vector accesses

@@ -11,7 +11,7 @@ import ctypes
 import torch
 
 from .. import _C
-from .gemm import pick_bn, EPI_BIAS, EPI_GELU, EPI_ADD_AUX
+from .gemm import TALL, pick_tall, pick_bn, EPI_BIAS, EPI_GELU, EPI_ADD_AUX
 
 bf16 = torch.bfloat16
 
@@ -43,7 +43,7 @@ def signal_shard_ready(site: FusedSite, epoch: int):
 
 
 def allgather_gemm(site: FusedSite, gathered, other, *, gather_a=True, other_mn=False, out=None,
-                   bias=None, gelu=False, pre_out=None, add_aux=None, bn=None, comm_ctas=16,
+                   bias=None, gelu=False, pre_out=None, add_aux=None, bn=None, comm_ctas=8, tall=None,
                    signal=True, shard_bytes=None, flat_off_bytes=0, wait_peers=True):
     """D = A @ B^T where one operand is the row-wise concatenation of per-rank shards.
 
@@ -65,7 +65,9 @@ def allgather_gemm(site: FusedSite, gathered, other, *, gather_a=True, other_mn=
         N = rows
         M = other.shape[1] if other_mn else other.shape[0]
     if bn is None:
-        bn = pick_bn(M, N)
+        if tall is None:
+            tall = pick_tall(M, N, K) and M % 256 == 0 and (not gather_a or (rows // c.world) % 256 == 0)
+        bn = 256 if tall else pick_bn(M, N)
         if not gather_a:
             while (rows // c.world) % bn and bn > 64:
                 bn //= 2
@@ -86,24 +88,26 @@ def allgather_gemm(site: FusedSite, gathered, other, *, gather_a=True, other_mn=
             _C.ptr(other), gathered.stride(0), other.stride(0), int(other_mn), _C.ptr(out),
             out.stride(0), M, N, K, epi, _C.ptr(bias), _C.ptr(add_aux),
             add_aux.stride(0) if add_aux is not None else 0, _C.ptr(pre_out),
-            pre_out.stride(0) if pre_out is not None else 0, bn, c.world, c.rank,
+            pre_out.stride(0) if pre_out is not None else 0, bn | (TALL if tall else 0), c.world, c.rank,
             shard_bytes, flat_off_bytes, _C.ptr(site.flags), peer_ready, site.epoch, comm_ctas,
             _C.ptr(c.status), _C.current_stream())
     return (out, pre_out) if gelu else out
 
 
-def gemm_reduce_scatter(site: FusedSite, a, b, stage, out, *, b_mn=False, residual=None, bn=None):
+def gemm_reduce_scatter(site: FusedSite, a, b, stage, out, *, b_mn=False, residual=None, bn=None, tall=None):
     """out[M/world, N] = reduce-scatter over ranks of (a @ b^T); ``stage`` is a symmetric
     [world, M/world, N] bf16 staging buffer (one slot per source rank)."""
     c = site.comm
     M, K = a.shape
     N = b.shape[1] if b_mn else b.shape[0]
     if bn is None:
-        bn = pick_bn(M, N)
+        if tall is None:
+            tall = pick_tall(M, N, K) and M % 256 == 0
+        bn = 256 if tall else pick_bn(M, N)
     rows = M // c.world
     site.epoch += 1
     _C.call("mmj_gemm_bf16_reduce_scatter", _C.ptr(a), a.stride(0), _C.ptr(b), b.stride(0),
-            int(b_mn), site.peer_ptrs(stage), N, rows * N, M, N, K, bn, c.world, c.rank,
+            int(b_mn), site.peer_ptrs(stage), N, rows * N, M, N, K, bn | (TALL if tall else 0), c.world, c.rank,
             _C.ptr(c.status), _C.current_stream())
     _C.call("mmj_reduce_slots_bf16", c._sig_ptrs, _C.ptr(stage), rows * N, _C.ptr(out),
             _C.ptr(residual), rows * N, c.world, c.rank, site.slots + c.world, site.epoch,
