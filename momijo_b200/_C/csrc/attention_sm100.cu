@@ -127,10 +127,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + kTile;      // 2 stages
   uint8_t* sV = sK + 2 * kTile;  // VS stages
-  uint8_t* sP = sV + VS * kTile;  // 128 x 128 bf16
+  // head_dim 128 (one CTA per SM) has room for two P tiles, so the softmax of block j+1 need not
+  // wait for P(j) V(j); head_dim 64 keeps one (its second CTA on the SM fills the gap)
+  constexpr int PB = (D == 64) ? 1 : 2;
+  constexpr int kPTile = 2 * kPanelBytes;
+  uint8_t* sP = sV + VS * kTile;  // PB tiles of 128 x 128 bf16
 
   __shared__ __align__(8) uint64_t q_full, s_full, p_full, o_full;
-  __shared__ __align__(8) uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+  __shared__ __align__(8) uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2], p_free[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -164,6 +168,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
+      mbar_init(&p_free[s], 1);
     }
     abort_flag = 0;
     mbar_fence_init();
@@ -241,9 +246,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t aV = smem_u32(sV + sv * kTile);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_bf16_ss(tmem_base + kColO, desc_kmajor(aP, k), desc_mnmajor(aV, k), idesc_o,
+          umma_bf16_ss(tmem_base + kColO, desc_kmajor(aP + (uint32_t)((j % PB) * kPTile), k), desc_mnmajor(aV, k), idesc_o,
                        (j > 0 || k > 0) ? 1u : 0u);
         umma_commit(&v_empty[sv]);
+        umma_commit(&p_free[j % PB]);  // this P tile may be overwritten
         umma_commit(&o_full);
       }
     }
@@ -317,8 +323,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // P(j-1) V(j-1) reads the P tile that is about to be overwritten: it must have finished. (It
       // was issued after S(j) and takes a fraction of the time spent above, so this wait is normally
       // already satisfied; without it the order would only be a matter of timing.)
-      if (j > 0) {
-        if (!mbar_wait_warp(&o_full, (j - 1) & 1, &abort_flag, p.status, kTimeoutTmemFull, 200 + j)) { ok = false; break; }
+      // (one barrier per P tile: each sees one completion per use of its tile, so a wait for the
+      // previous use can never be overtaken by a later phase)
+      if (j >= PB) {
+        if (!mbar_wait_warp(&p_free[j % PB], ((j / PB) - 1) & 1, &abort_flag, p.status, kTimeoutTmemFull, 200 + j)) { ok = false; break; }
       }
       const float mc = m_used * c;
       float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
@@ -333,7 +341,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           pv[i + 3] = exp2f(fmaf(pv[i + 3], c, -mc));
           sum0 += pv[i + 0]; sum1 += pv[i + 1]; sum2 += pv[i + 2]; sum3 += pv[i + 3];
         }
-        store_chunk_sw128(sP, row, cc * 32, pv);
+        store_chunk_sw128(sP + (j % PB) * kPTile, row, cc * 32, pv);
       }
       l += (sum0 + sum1) + (sum2 + sum3);
       fence_proxy_async_smem();
@@ -968,7 +976,7 @@ MMJ_API int mmj_attn_fwd(const void* q, long long ldq, int q_col0, const void* k
     }
     attn_fwd_kernel<64><<<grid, kAttnThreads, smem, (cudaStream_t)stream>>>(tq, tk, tv, p);
   } else {
-    const int smem = 5 * 2 * kPanelBytes + 2 * kPanelBytes + 1024;
+    const int smem = 5 * 2 * kPanelBytes + 2 * 2 * kPanelBytes + 1024;  // Q + 2 K + 2 V + 2 P
     if (!attr128) {
       cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       attr128 = true;
