@@ -266,6 +266,61 @@ def sc_moe_drop(comm):
     assert 0 < zero_rows < n_tok, zero_rows
 
 
+def sc_determinism(comm):
+    """Every fused collective, run twice on the same inputs, gives bitwise identical results (a missing
+    acquire / release on a signal flag shows up here long before it shows up as a wrong number)."""
+    from momijo_b200.ops.fused_comm import FusedSite, allgather_gemm, gemm_reduce_scatter
+    from momijo_b200.parallel.ep import MoEDispatcher
+
+    W, R = comm.world, comm.rank
+    torch.manual_seed(11 + R)
+    n = 8 * W * 4096
+    src = torch.randn(n, device="cuda").to(bf16)
+    t = comm.alloc(n, bf16)
+    outs = []
+    for _ in range(2):
+        t.copy_(src)
+        torch.cuda.synchronize(); dist.barrier()
+        comm.all_reduce_(t)
+        torch.cuda.synchronize(); dist.barrier()
+        outs.append(t.clone())
+    assert torch.equal(outs[0], outs[1]), "all-reduce"
+    M, N, K = 256 * W, 384, 512
+    torch.manual_seed(3)
+    full = torch.randn(M, K, device="cuda").to(bf16)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(bf16)
+    site, site2 = FusedSite(comm), FusedSite(comm)
+    xa = comm.alloc(M * K, bf16).view(M, K)
+    stage = comm.alloc(M * N, bf16)
+    rows = M // W
+    res = []
+    for _ in range(2):
+        xa.zero_()
+        xa[R * rows:(R + 1) * rows].copy_(full[R * rows:(R + 1) * rows])
+        torch.cuda.synchronize(); dist.barrier()
+        y = allgather_gemm(site, xa, w, gather_a=True, comm_ctas=4)
+        o = torch.empty(rows, N, dtype=bf16, device="cuda")
+        gemm_reduce_scatter(site2, full, w, stage, o)
+        torch.cuda.synchronize(); dist.barrier()
+        res.append((y.clone(), o.clone()))
+    assert torch.equal(res[0][0], res[1][0]), "all-gather -> gemm"
+    assert torch.equal(res[0][1], res[1][1]), "gemm -> reduce-scatter"
+    n_tok, H, E, k = 256, 256, 4 * W, 2
+    x = torch.randn(n_tok, H, device="cuda").to(bf16)
+    idx = torch.rand(n_tok, E, device="cuda").topk(k, dim=-1).indices.int()
+    gw = torch.rand(n_tok, k, device="cuda")
+    disp = MoEDispatcher(comm, n_experts=E, top_k=k, hidden=H, max_tokens=n_tok)
+    mo = []
+    for _ in range(2):
+        r = disp.route(idx)
+        recv = disp.dispatch(x, r)
+        y, _ = disp.next_buffer()
+        y.copy_(recv)
+        mo.append(disp.combine(y, r, gw).clone())
+        torch.cuda.synchronize(); dist.barrier()
+    assert torch.equal(mo[0], mo[1]), "moe dispatch / combine"
+
+
 def sc_timeout(comm):
     """A wait on a flag that nobody sets returns an error status; the context stays usable."""
     slot = comm.new_slots(1)
@@ -281,7 +336,7 @@ def sc_timeout(comm):
 
 SCENARIOS = {"allreduce": sc_allreduce, "zero": sc_zero, "ag_gemm": sc_ag_gemm,
              "gemm_rs": sc_gemm_rs, "moe": sc_moe, "moe_layer": sc_moe_layer, "tp_llama": sc_tp_llama,
-             "moe_drop": sc_moe_drop, "timeout": sc_timeout}
+             "moe_drop": sc_moe_drop, "determinism": sc_determinism, "timeout": sc_timeout}
 
 
 def main():

@@ -43,3 +43,7 @@ def test_moe_dispatch_combine_and_layer():
 
 def test_tensor_parallel_llama_matches_single_rank():
     _run(["tp_llama"])
+
+
+def test_fused_collectives_are_deterministic():
+    _run(["determinism"])
