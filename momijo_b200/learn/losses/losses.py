@@ -29,6 +29,11 @@ def cross_entropy_from_logits(logits, y_onehot):
     return -(y_onehot * torch.log_softmax(logits.float(), -1)).sum() / logits.shape[0]
 
 
+def softmax(x, axis: int = -1):
+    """Row softmax (legacy/src/momijo/learn/losses/losses.mojo re-exports the tensor softmax)."""
+    return torch.softmax(x.float(), axis).to(x.dtype) if x.is_floating_point() else torch.softmax(x.float(), axis)
+
+
 def softmax_cross_entropy(logits, y):
     """``y`` is either one-hot ``[N, C]`` or class indices ``[N]``. Returns (loss, dlogits) with
     ``dlogits = (softmax - onehot) / N`` (losses.mojo:72-85)."""

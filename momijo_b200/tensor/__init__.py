@@ -9,7 +9,7 @@ from .creation import arange_f32 as arange  # noqa: F401
 from .axis import moveaxis, moveaxes, swapaxes, roll, reduce_along_axis, ReduceSpec, cumsum, cumprod, quantile, percentile, median  # noqa: F401
 from .transform import (  # noqa: F401
     pad, fliplr, flipud, flip, sliding_window, sliding_window_step, transpose, transpose2d, reshape,
-    reshape_infer, resize_like_with_pad, reshape_like, stack, cat, permute, contiguous, view, repeat,
+    reshape_infer, resize_like_with_pad, reshape_like, stack, cat, concat, concatenate, permute, contiguous, view, repeat,
     tile, flatten, expand, as_strided, upsample_nearest, upsample_bilinear, downsample_mean, dilate,
     split_sizes, chunk, unbind, squeeze, unsqueeze,
 )

@@ -46,6 +46,9 @@ def matmul(a, b):
         return _wrap(fb)
     if not a.dtype.is_floating_point and not b.dtype.is_floating_point:
         a, b = a.float(), b.float()  # Int @ Int -> Float32
+    elif a.dtype != b.dtype:
+        dt = torch.result_type(a, b)     # mixed operands meet at the promoted type
+        a, b = a.to(dt), b.to(dt)
     if (a.is_cuda and a.dtype == torch.bfloat16 and b.dim() == 2 and b.dtype == torch.bfloat16
             and a.stride(1) == 1 and b.stride(1) == 1 and a.stride(0) % 8 == 0 and b.stride(0) % 8 == 0):
         from .. import ops

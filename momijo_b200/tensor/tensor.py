@@ -68,6 +68,19 @@ class S:
         return tuple(out)
 
 
+class _Shape(tuple):
+    """Shape tuple that can also be called: the reference spells it ``x.shape()``."""
+
+    def __call__(self):
+        return list(self)
+
+    def numel(self) -> int:
+        n = 1
+        for v in self:
+            n *= v
+        return n
+
+
 class Tensor(torch.Tensor):
     # ---- construction -----------------------------------------------------------------------
     @staticmethod
@@ -90,6 +103,21 @@ class Tensor(torch.Tensor):
         pass
 
     # ---- metadata ----------------------------------------------------------------------------
+    @property
+    def shape(self):
+        return _Shape(torch.Tensor.shape.__get__(self))
+
+    def transpose(self, *dims):
+        """``transpose()`` swaps the last two axes (the reference's 2-D transpose); with arguments it is
+        torch's ``transpose(dim0, dim1)``; more than two arguments permute."""
+        if len(dims) == 0:
+            return self if self.dim() < 2 else torch.Tensor.transpose(self, -2, -1)
+        if len(dims) == 1 and isinstance(dims[0], (list, tuple)):
+            return self.permute(*dims[0])
+        if len(dims) > 2:
+            return self.permute(*dims)
+        return torch.Tensor.transpose(self, *dims)
+
     def numel_(self) -> int:
         return self.numel()
 
@@ -511,3 +539,25 @@ def as_tensor(x) -> Tensor:
     if isinstance(x, torch.Tensor):
         return x.as_subclass(Tensor)
     return Tensor(x)
+
+
+# Code written against the reference often does ``from momijo.tensor import tensor`` and then calls
+# ``tensor.randn([4, 10])``, ``tensor.matmul(a, b)``, ``tensor.maximum_scalar(x, 0.0)``
+# (legacy/src/momijo/learn/examples/learn/*.mojo). Names that are not defined in this module are looked
+# up in the package (creation, math, transform, ... re-exports) and then as ``Tensor`` methods.
+def __getattr__(name):
+    if name.startswith("__"):
+        raise AttributeError(name)
+    import importlib
+
+    pkg = importlib.import_module(__package__)
+    if name in pkg.__dict__:
+        return pkg.__dict__[name]
+    if hasattr(Tensor, name):
+        meth = getattr(Tensor, name)
+
+        def free(x, *a, **kw):
+            return meth(as_tensor(x), *a, **kw)
+        free.__name__ = name
+        return free
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -175,6 +175,10 @@ def cat(xs, axis: int = 0):
     return _wrap(torch.cat([_raw(v) for v in xs], axis))
 
 
+concat = cat          # the reference's examples spell it both ways
+concatenate = cat
+
+
 def split_sizes(x, sizes, axis: int = 0):
     return [_wrap(v) for v in torch.split(_raw(x), list(sizes), axis)]
 
