@@ -296,6 +296,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   __shared__ __align__(8) uint64_t tempty_bar[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  // per-warp staging for the scatter epilogue: 32 rows x 64 bytes, rows 80 bytes apart (conflict free)
+  __shared__ __align__(16) uint8_t epi_stage[kEpiWarps][32 * 80];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -591,7 +593,38 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             tmem_ld_32x32(t_row + (uint32_t)(c * 32), r);
             tmem_ld_wait();
             const int col0 = n0 + c * 32;
-            if (row < p.M && col0 < p.N) {
+            if ((p.epi & kEpiScatterPeers) && p.vec_ok && col0 + 32 <= p.N) {
+              // Stores into a peer's memory travel over NVLink: transpose the chunk through shared
+              // memory so that four neighbouring lanes write 64 contiguous bytes of one row (one
+              // thread per row would send 16-byte pieces).
+              uint8_t* st = epi_stage[warp - 2];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                uint4 q;
+                q.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+                q.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+                q.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+                q.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+                *reinterpret_cast<uint4*>(st + lane * 80 + i * 16) = q;
+              }
+              __syncwarp();
+              const int row_base = m0 + sub * kGemmBM + quad * 32;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int rr = 8 * i + (lane >> 2);
+                const uint4 q = *reinterpret_cast<const uint4*>(st + rr * 80 + (lane & 3) * 16);
+                const int grow = row_base + rr;
+                if (grow < p.M) {
+                  const int owner = grow / p.rows_per_rank;
+                  const int lrow = grow - owner * p.rows_per_rank;
+                  __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.peer_D[owner]) +
+                                     (long long)p.rank * p.slot_stride + (long long)lrow * p.ldd + col0 +
+                                     (lane & 3) * 8;
+                  *reinterpret_cast<uint4*>(d) = q;
+                }
+              }
+              __syncwarp();
+            } else if (row < p.M && col0 < p.N) {
               if (p.epi & kEpiOutF32)
                 epilogue_store_chunk<true>(p, r, row + out_row0, col0);
               else
@@ -676,6 +709,7 @@ static int sm_count() {
 }
 
 static bool g_attr_set = false;
+static int g_max_dyn_smem = 0;
 
 int launch_gemm(GemmParams& p, const void* A, long long lda, long long a_rows, const void* B,
                 long long ldb, long long b_rows, int comm_ctas, cudaStream_t stream) {
@@ -718,10 +752,17 @@ int launch_gemm(GemmParams& p, const void* A, long long lda, long long a_rows, c
   p.stages = stages;
   const int smem_bytes = stages * stage_bytes + 1024;
   if (!g_attr_set) {
-    cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         220 * 1024);
+    // static shared memory (barriers, the scatter staging) counts against the same 227 KB
+    cudaFuncAttributes fa;
+    cudaError_t e = cudaFuncGetAttributes(&fa, gemm_bf16_tcgen05_kernel);
+    if (e != cudaSuccess) return (int)e;
+    g_max_dyn_smem = 232448 - (int)fa.sharedSizeBytes;
+    e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             g_max_dyn_smem);
+    if (e != cudaSuccess) return (int)e;
     g_attr_set = true;
   }
+  if (smem_bytes > g_max_dyn_smem) return -6;
   const int bm = kGemmBM * (p.bm2 ? 2 : 1);
   const int num_m = (p.M + bm - 1) / bm;
   const int num_n = (p.N + p.bn - 1) / p.bn;

@@ -45,7 +45,10 @@ def timed(fn, iters=10, warm=3):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--small", action="store_true")
+    ap.add_argument("--only", default="all_reduce,zero,tp,moe",
+                    help="comma list of sections: all_reduce, zero, tp (all-gather->GEMM, GEMM->reduce-scatter), moe")
     args = ap.parse_args()
+    only = set(args.only.split(","))
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -67,7 +70,7 @@ def main():
 
     frac = (W - 1) / W
     # ---- all-reduce (two-shot, peer loads) ----
-    for mb in ([16] if args.small else [64, 512]):
+    for mb in ([] if "all_reduce" not in only else [16] if args.small else [64, 512]):
         n = mb * (1 << 20) // 2
         t = comm.alloc(n, bf16)
         t.fill_(1.0)
@@ -79,7 +82,7 @@ def main():
              roofline_ms=link_bytes / LINK * 1e3, frac_of_roofline=link_bytes / LINK * 1e3 / ms, nccl_ms=ms_nccl)
 
     # ---- ZeRO step: reduce-scatter + AdamW in one kernel, then parameter all-gather ----
-    for n_param in ([8 << 20] if args.small else [130023424, 1 << 30]):
+    for n_param in ([] if "zero" not in only else [8 << 20] if args.small else [130023424, 1 << 30]):
         class Box(torch.nn.Module):
             def __init__(s):
                 super().__init__()
@@ -113,50 +116,51 @@ def main():
              frac_of_roofline=roof / ms, nccl_rs_adamw_ag_ms=ms_nccl)
         del sdp, g, gs, pfull, master, m1, v1
 
-    # ---- all-gather -> GEMM and GEMM -> reduce-scatter (Llama-8B MLP shapes at this world size) ----
-    M = 2048 * W if args.small else 32768
-    C = 1024 if args.small else 4096
-    Fl = (4096 if args.small else 14336) // W
-    site = FusedSite(comm)
-    xa = comm.alloc(M * C, bf16).view(M, C)
-    xa.normal_()
-    w_gu = (torch.randn(2 * Fl, C, device="cuda") * 0.02).to(bf16)
-    out = torch.empty(M, 2 * Fl, dtype=bf16, device="cuda")
-    ms = timed(lambda: allgather_gemm(site, xa, w_gu, gather_a=True, out=out))
-    fl = 2.0 * M * 2 * Fl * C
-    link_bytes = frac * M * C * 2
-    roof = max(fl / flops_peak, link_bytes / LINK) * 1e3
-    ms_gemm = timed(lambda: ops.gemm(xa, w_gu, out=out))
-    xs = xa[R * (M // W):(R + 1) * (M // W)].clone()
-    xfull = torch.empty(M, C, dtype=bf16, device="cuda")
+    if "tp" in only:
+        # ---- all-gather -> GEMM and GEMM -> reduce-scatter (Llama-8B MLP shapes at this world size) ----
+        M = 2048 * W if args.small else 32768
+        C = 1024 if args.small else 4096
+        Fl = (4096 if args.small else 14336) // W
+        site = FusedSite(comm)
+        xa = comm.alloc(M * C, bf16).view(M, C)
+        xa.normal_()
+        w_gu = (torch.randn(2 * Fl, C, device="cuda") * 0.02).to(bf16)
+        out = torch.empty(M, 2 * Fl, dtype=bf16, device="cuda")
+        ms = timed(lambda: allgather_gemm(site, xa, w_gu, gather_a=True, out=out))
+        fl = 2.0 * M * 2 * Fl * C
+        link_bytes = frac * M * C * 2
+        roof = max(fl / flops_peak, link_bytes / LINK) * 1e3
+        ms_gemm = timed(lambda: ops.gemm(xa, w_gu, out=out))
+        xs = xa[R * (M // W):(R + 1) * (M // W)].clone()
+        xfull = torch.empty(M, C, dtype=bf16, device="cuda")
 
-    def nccl_ag_gemm():
-        dist.all_gather_into_tensor(xfull, xs)
-        torch.matmul(xfull, w_gu.t(), out=out)
-    ms_nccl = timed(nccl_ag_gemm)
-    emit(op="allgather->gemm", M=M, N=2 * Fl, K=C, world=W, ms=ms, tflops=fl / ms / 1e9, roofline_ms=roof,
-         frac_of_roofline=roof / ms, local_gemm_only_ms=ms_gemm, nccl_allgather_plus_cublas_ms=ms_nccl)
+        def nccl_ag_gemm():
+            dist.all_gather_into_tensor(xfull, xs)
+            torch.matmul(xfull, w_gu.t(), out=out)
+        ms_nccl = timed(nccl_ag_gemm)
+        emit(op="allgather->gemm", M=M, N=2 * Fl, K=C, world=W, ms=ms, tflops=fl / ms / 1e9, roofline_ms=roof,
+             frac_of_roofline=roof / ms, local_gemm_only_ms=ms_gemm, nccl_allgather_plus_cublas_ms=ms_nccl)
 
-    site2 = FusedSite(comm)
-    a = (torch.randn(M, Fl, device="cuda")).to(bf16)
-    w_down = (torch.randn(C, Fl, device="cuda") * 0.02).to(bf16)
-    stage = comm.alloc(M * C, bf16)
-    o = torch.empty(M // W, C, dtype=bf16, device="cuda")
-    ms = timed(lambda: gemm_reduce_scatter(site2, a, w_down, stage, o))
-    fl = 2.0 * M * C * Fl
-    roof = max(fl / flops_peak, link_bytes / LINK) * 1e3
-    full = torch.empty(M, C, dtype=bf16, device="cuda")
+        site2 = FusedSite(comm)
+        a = (torch.randn(M, Fl, device="cuda")).to(bf16)
+        w_down = (torch.randn(C, Fl, device="cuda") * 0.02).to(bf16)
+        stage = comm.alloc(M * C, bf16)
+        o = torch.empty(M // W, C, dtype=bf16, device="cuda")
+        ms = timed(lambda: gemm_reduce_scatter(site2, a, w_down, stage, o))
+        fl = 2.0 * M * C * Fl
+        roof = max(fl / flops_peak, link_bytes / LINK) * 1e3
+        full = torch.empty(M, C, dtype=bf16, device="cuda")
 
-    def nccl_gemm_rs():
-        torch.matmul(a, w_down.t(), out=full)
-        dist.reduce_scatter_tensor(o, full)
-    ms_nccl = timed(nccl_gemm_rs)
-    emit(op="gemm->reduce_scatter", M=M, N=C, K=Fl, world=W, ms=ms, tflops=fl / ms / 1e9, roofline_ms=roof,
-         frac_of_roofline=roof / ms, cublas_plus_nccl_reduce_scatter_ms=ms_nccl)
+        def nccl_gemm_rs():
+            torch.matmul(a, w_down.t(), out=full)
+            dist.reduce_scatter_tensor(o, full)
+        ms_nccl = timed(nccl_gemm_rs)
+        emit(op="gemm->reduce_scatter", M=M, N=C, K=Fl, world=W, ms=ms, tflops=fl / ms / 1e9, roofline_ms=roof,
+             frac_of_roofline=roof / ms, cublas_plus_nccl_reduce_scatter_ms=ms_nccl)
 
     # ---- MoE dispatch / combine at the 16B shape (top-6 of 64 experts, hidden 2048, 16384 tokens per rank) ----
     n_tok, H, E, k = (2048, 1024, 8 * W, 2) if args.small else (16384, 2048, 64, 6)
-    if E % W == 0:
+    if E % W == 0 and "moe" in only:
         torch.manual_seed(50 + R)
         x = torch.randn(n_tok, H, device="cuda").to(bf16)
         idx = torch.rand(n_tok, E, device="cuda").topk(k, dim=-1).indices.int()
