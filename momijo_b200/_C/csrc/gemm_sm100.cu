@@ -133,10 +133,36 @@ __device__ __forceinline__ TileCoord tile_of(int t, int num_m, int num_n, const 
   return c;
 }
 
+// Stores a 32-row x 32-column bf16 chunk (lane = row, v = its 32 columns) through a per-warp
+// staging area so that four neighbouring lanes write 64 contiguous bytes of one row: full 32-byte
+// sectors per request instead of 32 half-sector pieces. `tile` points at (first row, first column).
+__device__ __forceinline__ void staged_store_bf16(uint8_t* st, int lane, const float (&v)[32],
+                                                  __nv_bfloat16* tile, long long ld) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 q;
+    q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
+    q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+    q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+    q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+    *reinterpret_cast<uint4*>(st + lane * 80 + i * 16) = q;
+  }
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int rr = 8 * i + (lane >> 2);
+    const uint4 q = *reinterpret_cast<const uint4*>(st + rr * 80 + (lane & 3) * 16);
+    *reinterpret_cast<uint4*>(tile + rr * ld + (lane & 3) * 8) = q;
+  }
+  __syncwarp();
+}
+
 template <bool kOutF32>
 __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const uint32_t (&acc)[32],
-                                                     int row, int col0) {
-  // One thread owns 32 consecutive columns [col0, col0+32) of output row `row`.
+                                                     int row, int col0, uint8_t* st = nullptr,
+                                                     int lane = 0) {
+  // One thread owns 32 consecutive columns [col0, col0+32) of output row `row`. With `st` set the
+  // whole warp is here (32 valid rows, lane = row offset) and full chunks leave through it.
   const int epi = p.epi;
   float v[32];
 #pragma unroll
@@ -162,7 +188,9 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const 
   }
   if (epi & kEpiGelu) {
     __nv_bfloat16* d2 = reinterpret_cast<__nv_bfloat16*>(p.D2) + (long long)row * p.ldd2 + col0;
-    if (full) {
+    if (full && st != nullptr) {
+      staged_store_bf16(st, lane, v, d2 - (long long)lane * p.ldd2, p.ldd2);
+    } else if (full) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         uint4 q;
@@ -251,7 +279,9 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const 
     }
   } else {
     __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(base) + off;
-    if (full) {
+    if (full && st != nullptr && !(epi & (kEpiAccumulate | kEpiScatterPeers))) {
+      staged_store_bf16(st, lane, v, d - (long long)lane * p.ldd, p.ldd);
+    } else if (full) {
       if (epi & kEpiAccumulate) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -628,7 +658,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
               if (p.epi & kEpiOutF32)
                 epilogue_store_chunk<true>(p, r, row + out_row0, col0);
               else
-                epilogue_store_chunk<false>(p, r, row + out_row0, col0);
+                epilogue_store_chunk<false>(
+                    p, r, row + out_row0, col0,
+                    (m0 + sub * kGemmBM + quad * 32 + 32 <= p.M) ? epi_stage[warp - 2] : nullptr, lane);
             }
           }
         }
