@@ -225,12 +225,15 @@ __global__ void embedding_bwd_wpe_kernel(const __nv_bfloat16* __restrict__ dout,
 }
 
 // ---- column sums: out[n] = sum_m x[m, n]  (bias gradients) -----------------------------------
-// Stage 1: grid (ceil(N/256), S); block (32, 8). Each thread sums 8 columns over its rows and
-// the block writes one partial row into scratch[S, N]. Stage 2 folds the S partial rows.
+// Stage 1: grid (ceil(N/64), S); 256 threads as 8 column groups x 32 row lanes. Each thread sums 8
+// columns over its rows (a warp reads four 128-byte row pieces per load) and the block writes one
+// partial row into scratch[S, N]. Narrow column strips keep several CTAs on every SM even for
+// N = 768, where 256-column strips left most of the load latency exposed. Stage 2 folds the S rows.
 __global__ void colsum_partial_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                                       float* __restrict__ scratch, int M, int N) {
-  __shared__ float sm[8][32][9];
-  const int col = (blockIdx.x * 32 + threadIdx.x) * 8;
+  __shared__ float sm[8][64];
+  const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
+  const int col = (blockIdx.x * 8 + tx) * 8;
   const int S = gridDim.y;
   const int rows_per = (M + S - 1) / S;
   const int r0 = blockIdx.y * rows_per;
@@ -238,38 +241,54 @@ __global__ void colsum_partial_kernel(const __nv_bfloat16* __restrict__ x, long 
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (col < N) {
     if (col + 8 <= N) {
-      for (int r = r0 + threadIdx.y; r < r1; r += 8) {
+#pragma unroll 4
+      for (int r = r0 + ty; r < r1; r += 32) {
         float f[8];
         ld8(x + (size_t)r * ldx + col, f);
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] += f[j];
       }
     } else {
-      for (int r = r0 + threadIdx.y; r < r1; r += 8)
+      for (int r = r0 + ty; r < r1; r += 32)
         for (int j = 0; j < 8; ++j)
           if (col + j < N) acc[j] += __bfloat162float(x[(size_t)r * ldx + col + j]);
     }
   }
+  // fold the four row lanes of a warp, then the eight warps
 #pragma unroll
-  for (int j = 0; j < 8; ++j) sm[threadIdx.y][threadIdx.x][j] = acc[j];
+  for (int j = 0; j < 8; ++j) {
+    acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 8);
+    acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 16);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane < 8) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sm[warp][lane * 8 + j] = acc[j];
+  }
   __syncthreads();
-  if (threadIdx.y == 0 && col < N) {
+  if (threadIdx.x < 64) {
+    const int c = blockIdx.x * 64 + threadIdx.x;
+    float t = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float s = 0.f;
-#pragma unroll
-      for (int y = 0; y < 8; ++y) s += sm[y][threadIdx.x][j];
-      if (col + j < N) scratch[(size_t)blockIdx.y * N + col + j] = s;
-    }
+    for (int w = 0; w < 8; ++w) t += sm[w][threadIdx.x];
+    if (c < N) scratch[(size_t)blockIdx.y * N + c] = t;
   }
 }
+// block (32, 8): 32 adjacent columns, the partial rows split over threadIdx.y
 __global__ void colsum_finalize_kernel(const float* __restrict__ scratch,
                                        __nv_bfloat16* __restrict__ out_bf16,
                                        float* __restrict__ out_f32, int S, int N, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= N) return;
+  __shared__ float sm[8][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float s = 0.f;
-  for (int p = 0; p < S; ++p) s += scratch[(size_t)p * N + c];
+  if (c < N)
+    for (int p = threadIdx.y; p < S; p += 8) s += scratch[(size_t)p * N + c];
+  sm[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y != 0 || c >= N) return;
+  s = 0.f;
+#pragma unroll
+  for (int y = 0; y < 8; ++y) s += sm[y][threadIdx.x];
   if (out_bf16 != nullptr) {
     if (accumulate) s += __bfloat162float(out_bf16[c]);
     out_bf16[c] = __float2bfloat16(s);
@@ -548,9 +567,9 @@ MMJ_API int mmj_colsum_bf16(const void* x, long long ldx, void* out_bf16, float*
   if (M <= 0 || N <= 0) return 0;
   if (ldx % 8) return -1;
   const int S = mmj_colsum_splits(M);
-  dim3 grid((N + 255) / 256, S), block(32, 8);
-  colsum_partial_kernel<<<grid, block, 0, STREAM>>>((const __nv_bfloat16*)x, ldx, scratch, M, N);
-  colsum_finalize_kernel<<<(N + 255) / 256, 256, 0, STREAM>>>(scratch, (__nv_bfloat16*)out_bf16,
+  dim3 grid((N + 63) / 64, S);
+  colsum_partial_kernel<<<grid, 256, 0, STREAM>>>((const __nv_bfloat16*)x, ldx, scratch, M, N);
+  colsum_finalize_kernel<<<(N + 31) / 32, dim3(32, 8), 0, STREAM>>>(scratch, (__nv_bfloat16*)out_bf16,
                                                               out_f32, S, N, accumulate);
   return (int)cudaGetLastError();
 }
@@ -705,9 +724,9 @@ MMJ_API int mmj_colsum_bf16_static(const void* x, long long ldx, void* out_bf16,
     g_colsum_static_ptr[dev] = scratch;
   }
   const int S = mmj_colsum_splits(M);  // <= kStaticColsumMaxSplits
-  dim3 grid((N + 255) / 256, S), block(32, 8);
-  colsum_partial_kernel<<<grid, block, 0, STREAM>>>((const __nv_bfloat16*)x, ldx, scratch, M, N);
-  colsum_finalize_kernel<<<(N + 255) / 256, 256, 0, STREAM>>>(scratch, (__nv_bfloat16*)out_bf16,
+  dim3 grid((N + 63) / 64, S);
+  colsum_partial_kernel<<<grid, 256, 0, STREAM>>>((const __nv_bfloat16*)x, ldx, scratch, M, N);
+  colsum_finalize_kernel<<<(N + 31) / 32, dim3(32, 8), 0, STREAM>>>(scratch, (__nv_bfloat16*)out_bf16,
                                                               out_f32, S, N, accumulate);
   return (int)cudaGetLastError();
 }

@@ -21,6 +21,11 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
          d = unpack_bf16x2(q.w);
   f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
 }
+__device__ __forceinline__ void unpack8(const uint4& q, float (&f)[8]) {
+  float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y), c = unpack_bf16x2(q.z),
+         d = unpack_bf16x2(q.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
 __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
   uint4 q;
   q.x = pack_bf16x2(f[0], f[1]);
@@ -146,9 +151,37 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
     for (int j = 0; j < 8; ++j) { dg[i][j] = 0.f; db[i][j] = 0.f; g[i][j] = 0.f; }
     if (vi < nvec) load8(gamma + vi * 8, g[i]);
   }
+  // The next row's vectors are requested before the current row is reduced: with a few rows per
+  // CTA in sequence, one row's loads in flight per warp left most of the memory latency exposed.
+  uint4 cx[VPT], cdy[VPT], cr[VPT];
+  float cmean = 0.f, crstd = 0.f;
+  auto fetch = [&](int row, uint4 (&qx)[VPT], uint4 (&qdy)[VPT], uint4 (&qr)[VPT], float& mean,
+                   float& rstd) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int vi = threadIdx.x + i * blockDim.x;
+      qx[i] = qdy[i] = qr[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (vi < nvec) {
+        qx[i] = *reinterpret_cast<const uint4*>(x + (size_t)row * C + vi * 8);
+        qdy[i] = *reinterpret_cast<const uint4*>(dy + (size_t)row * C + vi * 8);
+        if (dres_in != nullptr) qr[i] = *reinterpret_cast<const uint4*>(dres_in + (size_t)row * C + vi * 8);
+      }
+    }
+    mean = (mode == 0) ? mean_in[row] : 0.f;
+    rstd = rstd_in[row];
+  };
+  if ((int)blockIdx.x < rows) fetch(blockIdx.x, cx, cdy, cr, cmean, crstd);
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const float mean = (mode == 0) ? mean_in[row] : 0.f;
-    const float rstd = rstd_in[row];
+    const int nrow = row + gridDim.x;
+    uint4 nx[VPT], ndy[VPT], nr[VPT];
+    float nmean = 0.f, nrstd = 0.f;
+    if (nrow < rows) {
+      fetch(nrow, nx, ndy, nr, nmean, nrstd);
+    } else {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) nx[i] = ndy[i] = nr[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    const float mean = cmean, rstd = crstd;
     float xh[VPT][8], gy[VPT][8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
@@ -156,8 +189,8 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
       const int vi = threadIdx.x + i * blockDim.x;
       if (vi < nvec) {
         float xv[8], dyv[8];
-        load8(x + (size_t)row * C + vi * 8, xv);
-        load8(dy + (size_t)row * C + vi * 8, dyv);
+        unpack8(cx[i], xv);
+        unpack8(cdy[i], dyv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           xh[i][j] = (xv[j] - mean) * rstd;
@@ -181,13 +214,17 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
         for (int j = 0; j < 8; ++j) o[j] = rstd * (gy[i][j] - m1 - xh[i][j] * m2);
         if (dres_in != nullptr) {
           float r[8];
-          load8(dres_in + (size_t)row * C + vi * 8, r);
+          unpack8(cr[i], r);
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] += r[j];
         }
         store8(dx + (size_t)row * C + vi * 8, o);
       }
     }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) { cx[i] = nx[i]; cdy[i] = ndy[i]; cr[i] = nr[i]; }
+    cmean = nmean;
+    crstd = nrstd;
   }
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
@@ -208,12 +245,12 @@ __global__ void norm_bwd_finalize_kernel(const float* __restrict__ partial_dg,
                                          __nv_bfloat16* __restrict__ dgamma,
                                          __nv_bfloat16* __restrict__ dbeta, int nparts, int C,
                                          int accumulate) {
-  // block (32, 8): 32 adjacent columns, the partial rows split over threadIdx.y
-  __shared__ float sa[8][33], sb[8][33];
+  // block (32, 32): 32 adjacent columns, the partial rows split over threadIdx.y
+  __shared__ float sa[32][33], sb[32][33];
   const int c = blockIdx.x * 32 + threadIdx.x;
   float a = 0.f, b = 0.f;
   if (c < C) {
-    for (int p = threadIdx.y; p < nparts; p += 8) {
+    for (int p = threadIdx.y; p < nparts; p += 32) {
       a += partial_dg[(size_t)p * C + c];
       if (partial_db != nullptr) b += partial_db[(size_t)p * C + c];
     }
@@ -225,7 +262,7 @@ __global__ void norm_bwd_finalize_kernel(const float* __restrict__ partial_dg,
   a = 0.f;
   b = 0.f;
 #pragma unroll
-  for (int y = 0; y < 8; ++y) {
+  for (int y = 0; y < 32; ++y) {
     a += sa[y][threadIdx.x];
     b += sb[y][threadIdx.x];
   }
@@ -272,7 +309,7 @@ MMJ_API int mmj_norm_fwd(const void* x, const void* res, void* res_out, const vo
 // Number of partial rows the backward writes (scratch must hold nparts * C floats, twice for
 // LayerNorm).
 MMJ_API int mmj_norm_bwd_parts(int rows) {
-  int n = 148 * 4;
+  int n = 148 * 8;
   return rows < n ? rows : n;
 }
 
@@ -295,7 +332,7 @@ MMJ_API int mmj_norm_bwd(const void* dy, const void* x, const void* gamma, const
     norm_bwd_kernel<2><<<nparts, threads, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, mean, rstd,
         (const __nv_bfloat16*)dres_in, (__nv_bfloat16*)dx, pdg, pdb, rows, C, mode);
-  norm_bwd_finalize_kernel<<<(C + 31) / 32, dim3(32, 8), 0, (cudaStream_t)stream>>>(
+  norm_bwd_finalize_kernel<<<(C + 31) / 32, dim3(32, 32), 0, (cudaStream_t)stream>>>(
       pdg, pdb, (__nv_bfloat16*)dgamma, (__nv_bfloat16*)dbeta, nparts, C, accumulate);
   return (int)cudaGetLastError();
 }
