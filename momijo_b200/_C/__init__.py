@@ -22,6 +22,7 @@ P, I, L, F = c_void_p, c_int, c_longlong, c_float
 
 # name -> (argtypes, kernels launched per call)
 _SIGS = {
+    "mmj_gemm_pair_clusters": ([], 0),
     "mmj_gemm_bf16": ([P, L, I, P, L, I, P, L, I, I, I, I, P, P, L, P, L, P, I, P, P], 1),
     "mmj_gemm_bf16_grouped": ([P, L, P, L, I, I, I, P, L, I, I, I, I, P, L, P, P, P, I, P, P], 1),
     "mmj_gemm_bf16_grouped_k": ([P, L, P, L, P, L, I, I, I, I, P, I, I, I, P, P], 1),

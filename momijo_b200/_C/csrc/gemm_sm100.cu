@@ -682,6 +682,204 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 }
 
 // ---------------------------------------------------------------------------------------------
+// CTA-pair variant (cta_group::2) for plain products: two CTAs of a cluster own one 256 x 256 tile.
+// Each CTA stages its own 128 rows of A and its own 128-column half of B (32 KiB per 64-deep K
+// block instead of 48 KiB for a 128 x 256 tile on one CTA: a third less traffic from L2 into shared
+// memory per FLOP), keeps 128 x 256 of the accumulator in its own TMEM (two accumulators, so the
+// epilogue still overlaps the next main loop) and stores its own rows. The rank-0 CTA issues the
+// MMAs for the pair; both CTAs' loads are credited to rank 0's "full" barrier, the MMA's commits
+// release the stage in both CTAs, and both CTAs' epilogue warps arrive on rank 0's "accumulator
+// free" barrier. No load uses multicast.
+// ---------------------------------------------------------------------------------------------
+constexpr int kPairBN = 256;
+constexpr int kPairStageBytes = kAStageBytes + (kPairBN / 2) * kGemmBK * 2;  // 32 KiB
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
+                      const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  __shared__ __align__(8) uint64_t full_bar[kGemmMaxStages];
+  __shared__ __align__(8) uint64_t empty_bar[kGemmMaxStages];
+  __shared__ __align__(8) uint64_t tfull_bar[2];
+  __shared__ __align__(8) uint64_t tempty_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  __shared__ __align__(16) uint8_t epi_stage[kEpiWarps][32 * 80];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = (int)blockIdx.x >> 1;
+  const int num_pairs = (int)gridDim.x >> 1;
+  const int stages = p.stages;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 2 * kEpiWarps);  // epilogue warps of both CTAs (used on rank 0)
+    }
+    abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&tmem_slot, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  const int num_m = (p.M + 2 * kGemmBM - 1) / (2 * kGemmBM);
+  const int num_n = (p.N + kPairBN - 1) / kPairBN;
+  const int num_k = (p.K + kGemmBK - 1) / kGemmBK;
+  const int num_tiles = num_m * num_n;
+
+  if (num_k > 0) {
+    if (warp == 0) {
+      // ======================= TMA producer (both CTAs) =======================
+      if (lane == 0) {
+        const uint32_t full0 = mapa_shared(smem_u32(&full_bar[0]), 0);  // rank 0's barriers
+        int s = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+          const TileCoord tc = tile_of(t, num_m, num_n, p);
+          const int m0 = tc.m_tile * 2 * kGemmBM + (int)rank * kGemmBM;
+          const int n0 = tc.n_tile * kPairBN + (int)rank * (kPairBN / 2);
+          for (int kb = 0; kb < num_k; ++kb) {
+            if (!mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, p.status, kTimeoutEmpty, kb)) {
+              ok = false;
+              break;
+            }
+            uint8_t* sA = smem + (size_t)s * kPairStageBytes;
+            uint8_t* sB = sA + kAStageBytes;
+            if (leader) mbar_expect_tx(&full_bar[s], 2u * (uint32_t)kPairStageBytes);
+            const uint32_t fb = full0 + (uint32_t)(s * sizeof(uint64_t));
+            const int k0 = kb * kGemmBK;
+            if (!p.a_mn) {
+              tma_load_2d_pair(sA, &tmA, fb, k0, m0);
+            } else {
+              tma_load_2d_pair(sA, &tmA, fb, m0, k0);
+              tma_load_2d_pair(sA + 8192, &tmA, fb, m0 + 64, k0);
+            }
+            if (!p.b_mn) {
+              tma_load_2d_pair(sB, &tmB, fb, k0, n0);
+            } else {
+              tma_load_2d_pair(sB, &tmB, fb, n0, k0);
+              tma_load_2d_pair(sB + 8192, &tmB, fb, n0 + 64, k0);
+            }
+            if (++s == stages) { s = 0; ph ^= 1; }
+          }
+        }
+      }
+    } else if (warp == 1) {
+      // ======================= MMA issuer (rank 0 only) =======================
+      if (lane == 0 && leader) {
+        const uint32_t idesc = make_idesc_bf16(2 * kGemmBM, kPairBN, p.a_mn, p.b_mn);
+        const uint32_t a_lbo = p.a_mn ? 8192u : 16u;
+        const uint32_t b_lbo = p.b_mn ? 8192u : 16u;
+        const uint32_t a_kstep = p.a_mn ? 2048u : 32u;
+        const uint32_t b_kstep = p.b_mn ? 2048u : 32u;
+        const uint32_t empty_own = smem_u32(&empty_bar[0]);
+        const uint32_t empty_peer = mapa_shared(empty_own, 1);
+        const uint32_t tfull_own = smem_u32(&tfull_bar[0]);
+        const uint32_t tfull_peer = mapa_shared(tfull_own, 1);
+        const uint32_t empty_own_c = mapa_shared(empty_own, 0);
+        const uint32_t tfull_own_c = mapa_shared(tfull_own, 0);
+        int s = 0;
+        uint32_t ph = 0;
+        int acc = 0;
+        uint32_t acc_ph = 0;
+        bool ok = true;
+        for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+          if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, &abort_flag, p.status, kTimeoutTmemEmpty,
+                         t)) {
+            break;
+          }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kAccCols);
+          for (int kb = 0; kb < num_k; ++kb) {
+            if (!mbar_wait(&full_bar[s], ph, &abort_flag, p.status, kTimeoutFull, kb)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t a_base = smem_u32(smem + (size_t)s * kPairStageBytes);
+            const uint32_t b_base = a_base + (uint32_t)kAStageBytes;
+#pragma unroll
+            for (int k = 0; k < kGemmBK / 16; ++k) {
+              const uint64_t da = make_smem_desc(a_base + k * a_kstep, a_lbo, 1024);
+              const uint64_t db = make_smem_desc(b_base + k * b_kstep, b_lbo, 1024);
+              umma_bf16_ss_pair(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            }
+            // the stage is free in both CTAs once these MMAs retire
+            umma_commit_pair(empty_own_c + (uint32_t)(s * sizeof(uint64_t)));
+            umma_commit_pair(empty_peer + (uint32_t)(s * sizeof(uint64_t)));
+            if (++s == stages) { s = 0; ph ^= 1; }
+          }
+          if (!ok) break;
+          umma_commit_pair(tfull_own_c + (uint32_t)(acc * sizeof(uint64_t)));
+          umma_commit_pair(tfull_peer + (uint32_t)(acc * sizeof(uint64_t)));
+          if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+        }
+      }
+    } else {
+      // ======================= epilogue warps (both CTAs) =======================
+      const int quad = warp & 3;
+      const int chalf = (warp - 2) >> 2;
+      const uint32_t tempty0 = mapa_shared(smem_u32(&tempty_bar[0]), 0);
+      int acc = 0;
+      uint32_t acc_ph = 0;
+      for (int t = pair; t < num_tiles; t += num_pairs) {
+        const TileCoord tc = tile_of(t, num_m, num_n, p);
+        const int m0 = tc.m_tile * 2 * kGemmBM + (int)rank * kGemmBM;
+        const int n0 = tc.n_tile * kPairBN;
+        if (!mbar_wait_warp(&tfull_bar[acc], acc_ph, &abort_flag, p.status, kTimeoutTmemFull, t)) break;
+        tc_fence_after();
+        const int row = m0 + quad * 32 + lane;
+        const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kAccCols);
+        uint8_t* st = (m0 + quad * 32 + 32 <= p.M) ? epi_stage[warp - 2] : nullptr;
+        for (int c = chalf; c < kPairBN / 32; c += 2) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + (uint32_t)(c * 32), r);
+          tmem_ld_wait();
+          const int col0 = n0 + c * 32;
+          if (row < p.M && col0 < p.N) {
+            if (p.epi & kEpiOutF32)
+              epilogue_store_chunk<true>(p, r, row, col0);
+            else
+              epilogue_store_chunk<false>(p, r, row, col0, st, lane);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(tempty0 + (uint32_t)(acc * sizeof(uint64_t)));
+        if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+      }
+    }
+  }
+
+  // ---------------- teardown: neither CTA leaves (or frees TMEM) while its peer may still signal it
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -808,9 +1006,83 @@ int launch_gemm(GemmParams& p, const void* A, long long lda, long long a_rows, c
   return (int)cudaGetLastError();
 }
 
+// Pair kernel launcher: plain products only (no flags, groups, gathered or scattered operands).
+static int g_pair_max_dyn = 0;
+static int g_pair_clusters = 0;
+
+int launch_gemm_pair(GemmParams& p, const void* A, long long lda, long long a_rows, const void* B,
+                     long long ldb, long long b_rows, cudaStream_t stream) {
+  if (p.M <= 0 || p.N <= 0) return 0;
+  if ((lda % 8) != 0 || (ldb % 8) != 0) return -2;
+  if (p.epi & kEpiScatterPeers) return -7;
+  {
+    const int out_elems = (p.epi & kEpiOutF32) ? 4 : 8;
+    bool ok = (p.ldd % out_elems == 0) && (((uintptr_t)p.D & 15) == 0);
+    if (p.epi & kEpiBias) ok = ok && (((uintptr_t)p.bias & 15) == 0);
+    if (p.epi & kEpiGelu) ok = ok && (p.ldd2 % 8 == 0) && (((uintptr_t)p.D2 & 15) == 0);
+    if (p.epi & (kEpiDGelu | kEpiAddAux | kEpiMulAux))
+      ok = ok && (p.ldaux % 8 == 0) && (((uintptr_t)p.aux & 15) == 0);
+    p.vec_ok = ok ? 1 : 0;
+  }
+  if (((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -3;
+  p.bn = kPairBN;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!p.a_mn)
+    rc = make_tmap_bf16_2d(&tmA, A, (uint64_t)p.K, (uint64_t)a_rows, (uint64_t)lda, 64, 128);
+  else
+    rc = make_tmap_bf16_2d(&tmA, A, (uint64_t)p.M, (uint64_t)a_rows, (uint64_t)lda, 64, 64);
+  if (rc) return rc;
+  if (!p.b_mn)
+    rc = make_tmap_bf16_2d(&tmB, B, (uint64_t)p.K, (uint64_t)b_rows, (uint64_t)ldb, 64, kPairBN / 2);
+  else
+    rc = make_tmap_bf16_2d(&tmB, B, (uint64_t)p.N, (uint64_t)b_rows, (uint64_t)ldb, 64, 64);
+  if (rc) return rc;
+
+  int stages = (200 * 1024) / kPairStageBytes;
+  if (stages > kGemmMaxStages) stages = kGemmMaxStages;
+  p.stages = stages;
+  const int smem_bytes = stages * kPairStageBytes + 1024;
+  if (g_pair_max_dyn == 0) {
+    cudaFuncAttributes fa;
+    cudaError_t e = cudaFuncGetAttributes(&fa, gemm_bf16_pair_kernel);
+    if (e != cudaSuccess) return (int)e;
+    const int max_dyn = 232448 - (int)fa.sharedSizeBytes;
+    e = cudaFuncSetAttribute(gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn);
+    if (e != cudaSuccess) return (int)e;
+    // how many pairs the device holds at once (a persistent grid must not exceed it)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * sm_count());
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = (size_t)smem_bytes;
+    cudaLaunchAttribute at;
+    at.id = cudaLaunchAttributeClusterDimension;
+    at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+    cfg.attrs = &at;
+    cfg.numAttrs = 1;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, gemm_bf16_pair_kernel, &cfg);
+    if (e != cudaSuccess || n <= 0) { cudaGetLastError(); n = sm_count() / 2; }
+    g_pair_clusters = n;
+    g_pair_max_dyn = max_dyn;
+  }
+  if (smem_bytes > g_pair_max_dyn) return -6;
+  const int num_m = (p.M + 2 * kGemmBM - 1) / (2 * kGemmBM);
+  const int num_n = (p.N + kPairBN - 1) / kPairBN;
+  long long tiles = (long long)num_m * num_n;
+  int pairs = g_pair_clusters;
+  if (tiles < pairs) pairs = (int)tiles;
+  p.gemm_ctas = 2 * pairs;
+  gemm_bf16_pair_kernel<<<2 * pairs, kThreads, smem_bytes, stream>>>(tmA, tmB, p);
+  return (int)cudaGetLastError();
+}
+
 }  // namespace mmj
 
 using namespace mmj;
+
+// Number of CTA pairs the device holds at once for the pair kernel (0 before its first launch).
+MMJ_API int mmj_gemm_pair_clusters() { return g_pair_clusters; }
 
 // Plain / fused-epilogue GEMM.
 //   a_mn = 0: A is [M, K] row-major (lda);  a_mn = 1: A is [K, M] row-major (lda)
@@ -832,6 +1104,8 @@ MMJ_API int mmj_gemm_bf16(const void* A, long long lda, int a_mn, const void* B,
   p.bias = bias; p.aux = aux; p.ldaux = ldaux;
   p.row_scale = row_scale;
   p.status = status;
+  if ((bn >> 13) & 1)  // bit 13 of `bn`: CTA-pair kernel, 256 x 256 tiles
+    return launch_gemm_pair(p, A, lda, a_mn ? K : M, B, ldb, b_mn ? K : N, (cudaStream_t)stream);
   return launch_gemm(p, A, lda, a_mn ? K : M, B, ldb, b_mn ? K : N, 0, (cudaStream_t)stream);
 }
 

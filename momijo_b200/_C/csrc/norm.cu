@@ -133,7 +133,10 @@ __global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
 // dx = rstd * (dy*g - mean_c(dy*g) - xhat * mean_c(dy*g*xhat))        (LayerNorm)
 // dx = rstd * (dy*g - xhat * mean_c(dy*g*xhat))                          (RMSNorm)
 // Optional dres_in is added to dx (gradient arriving through the residual branch).
-template <int VPT>
+// kPrefetch: request the next row's vectors before reducing the current one (narrow rows, where a
+// CTA is a few warps and several CTAs share an SM; for wide rows the extra registers would cost a
+// resident CTA).
+template <int VPT, bool kPrefetch>
 __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
                                 const __nv_bfloat16* __restrict__ x,
                                 const __nv_bfloat16* __restrict__ gamma,
@@ -170,12 +173,14 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
     mean = (mode == 0) ? mean_in[row] : 0.f;
     rstd = rstd_in[row];
   };
-  if ((int)blockIdx.x < rows) fetch(blockIdx.x, cx, cdy, cr, cmean, crstd);
+  if (kPrefetch && (int)blockIdx.x < rows) fetch(blockIdx.x, cx, cdy, cr, cmean, crstd);
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const int nrow = row + gridDim.x;
     uint4 nx[VPT], ndy[VPT], nr[VPT];
     float nmean = 0.f, nrstd = 0.f;
-    if (nrow < rows) {
+    if (!kPrefetch) {
+      fetch(row, cx, cdy, cr, cmean, crstd);
+    } else if (nrow < rows) {
       fetch(nrow, nx, ndy, nr, nmean, nrstd);
     } else {
 #pragma unroll
@@ -221,10 +226,12 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
         store8(dx + (size_t)row * C + vi * 8, o);
       }
     }
+    if (kPrefetch) {
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) { cx[i] = nx[i]; cdy[i] = ndy[i]; cr[i] = nr[i]; }
-    cmean = nmean;
-    crstd = nrstd;
+      for (int i = 0; i < VPT; ++i) { cx[i] = nx[i]; cdy[i] = ndy[i]; cr[i] = nr[i]; }
+      cmean = nmean;
+      crstd = nrstd;
+    }
   }
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
@@ -321,15 +328,21 @@ MMJ_API int mmj_norm_bwd(const void* dy, const void* x, const void* gamma, const
   if (rows <= 0) return 0;
   const int vpt = (C / 8 > 1024) ? 2 : 1;
   const int threads = norm_threads(C, vpt);
-  const int nparts = mmj_norm_bwd_parts(rows);
+  const bool prefetch = threads <= 256;
+  int nparts = mmj_norm_bwd_parts(rows);  // what the caller sized the scratch for
+  if (!prefetch && nparts > 148 * 4) nparts = 148 * 4;
   float* pdg = scratch;
   float* pdb = (mode == 0 && dbeta != nullptr) ? scratch + (size_t)nparts * C : nullptr;
-  if (vpt == 1)
-    norm_bwd_kernel<1><<<nparts, threads, 0, (cudaStream_t)stream>>>(
+  if (vpt == 1 && prefetch)
+    norm_bwd_kernel<1, true><<<nparts, threads, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, mean, rstd,
+        (const __nv_bfloat16*)dres_in, (__nv_bfloat16*)dx, pdg, pdb, rows, C, mode);
+  else if (vpt == 1)
+    norm_bwd_kernel<1, false><<<nparts, threads, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, mean, rstd,
         (const __nv_bfloat16*)dres_in, (__nv_bfloat16*)dx, pdg, pdb, rows, C, mode);
   else
-    norm_bwd_kernel<2><<<nparts, threads, 0, (cudaStream_t)stream>>>(
+    norm_bwd_kernel<2, false><<<nparts, threads, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, mean, rstd,
         (const __nv_bfloat16*)dres_in, (__nv_bfloat16*)dx, pdg, pdb, rows, C, mode);
   norm_bwd_finalize_kernel<<<(C + 31) / 32, dim3(32, 32), 0, (cudaStream_t)stream>>>(

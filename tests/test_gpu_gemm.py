@@ -89,3 +89,32 @@ def test_gemm_padded_vocab_view():
 def test_gemm_deterministic():
     a, b = _rand(1024, 512), _rand(768, 512)
     assert torch.equal(gemm(a, b), gemm(a, b))
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 768), (1000, 520, 328), (2048, 2304, 768),
+                                   (4096, 1024, 1536)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_cta_pair(M, N, K, a_mn, b_mn):
+    """CTA-pair kernel (two SMs per 256 x 256 tile): same products as the one-SM kernel."""
+    torch.manual_seed(3)
+    a = _rand(K, M) if a_mn else _rand(M, K)
+    b = _rand(K, N) if b_mn else _rand(N, K)
+    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, pair=True)
+    A = (a.t() if a_mn else a).float()
+    B = (b if b_mn else b.t()).float()
+    _close(out, A @ B)
+
+
+def test_gemm_cta_pair_epilogues():
+    torch.manual_seed(4)
+    M, N, K = 1024, 1024, 384
+    a, b = _rand(M, K), _rand(N, K, scale=0.05)
+    bias, aux = _rand(N), _rand(M, N)
+    ref = a.float() @ b.float().t()
+    act, pre = gemm(a, b, bias=bias, gelu=True, pair=True)
+    _close(pre, ref + bias.float())
+    _close(act, _gelu_tanh(ref + bias.float()))
+    _close(gemm(a, b, dgelu_aux=aux, pair=True), ref * _gelu_tanh_grad(aux.float()))
+    _close(gemm(a, b, add_aux=aux, pair=True), ref + aux.float())
+    o32 = gemm(a, b, out_f32=True, pair=True)
+    _close(o32, ref, tol=1e-3)
