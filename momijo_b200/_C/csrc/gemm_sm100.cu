@@ -742,9 +742,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   const int num_m = (p.M + 2 * kGemmBM - 1) / (2 * kGemmBM);
   const int num_n = (p.N + kPairBN - 1) / kPairBN;
   const int num_k = (p.K + kGemmBK - 1) / kGemmBK;
-  const int num_tiles = num_m * num_n;
+  const int per_group = num_m * num_n;
+  const int num_tiles = (p.groups_k > 0) ? p.groups_k * per_group : per_group;
 
-  if (num_k > 0) {
+  if (num_k > 0 || p.groups_k > 0) {
     if (warp == 0) {
       // ======================= TMA producer (both CTAs) =======================
       if (lane == 0) {
@@ -753,10 +754,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         uint32_t ph = 0;
         bool ok = true;
         for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-          const TileCoord tc = tile_of(t, num_m, num_n, p);
+          const KRange kr = krange_of(t, per_group, num_k, p);
+          const TileCoord tc = tile_of(kr.tt, num_m, num_n, p);
           const int m0 = tc.m_tile * 2 * kGemmBM + (int)rank * kGemmBM;
           const int n0 = tc.n_tile * kPairBN + (int)rank * (kPairBN / 2);
-          for (int kb = 0; kb < num_k; ++kb) {
+          for (int kb = 0; kb < kr.nk; ++kb) {
             if (!mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, p.status, kTimeoutEmpty, kb)) {
               ok = false;
               break;
@@ -765,7 +767,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
             uint8_t* sB = sA + kAStageBytes;
             if (leader) mbar_expect_tx(&full_bar[s], 2u * (uint32_t)kPairStageBytes);
             const uint32_t fb = full0 + (uint32_t)(s * sizeof(uint64_t));
-            const int k0 = kb * kGemmBK;
+            const int k0 = kr.k_begin + kb * kGemmBK;
             if (!p.a_mn) {
               tma_load_2d_pair(sA, &tmA, fb, k0, m0);
             } else {
@@ -802,13 +804,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         uint32_t acc_ph = 0;
         bool ok = true;
         for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+          const KRange kr = krange_of(t, per_group, num_k, p);
+          if (kr.nk == 0) continue;  // empty contraction: the epilogues write zeros on their own
           if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, &abort_flag, p.status, kTimeoutTmemEmpty,
                          t)) {
             break;
           }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kAccCols);
-          for (int kb = 0; kb < num_k; ++kb) {
+          for (int kb = 0; kb < kr.nk; ++kb) {
             if (!mbar_wait(&full_bar[s], ph, &abort_flag, p.status, kTimeoutFull, kb)) {
               ok = false;
               break;
@@ -841,9 +845,29 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       int acc = 0;
       uint32_t acc_ph = 0;
       for (int t = pair; t < num_tiles; t += num_pairs) {
-        const TileCoord tc = tile_of(t, num_m, num_n, p);
+        const KRange kr = krange_of(t, per_group, num_k, p);
+        const TileCoord tc = tile_of(kr.tt, num_m, num_n, p);
         const int m0 = tc.m_tile * 2 * kGemmBM + (int)rank * kGemmBM;
         const int n0 = tc.n_tile * kPairBN;
+        const int out_row0 = kr.g * p.M;  // grouped-K: group g writes rows [g*M, (g+1)*M)
+        if (kr.nk == 0) {
+          const int zrow = m0 + quad * 32 + lane;
+          if (zrow < p.M) {
+            uint32_t z[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) z[i] = 0u;
+            for (int c = chalf; c < kPairBN / 32; c += 2) {
+              const int col0 = n0 + c * 32;
+              if (col0 < p.N) {
+                if (p.epi & kEpiOutF32)
+                  epilogue_store_chunk<true>(p, z, zrow + out_row0, col0);
+                else
+                  epilogue_store_chunk<false>(p, z, zrow + out_row0, col0);
+              }
+            }
+          }
+          continue;
+        }
         if (!mbar_wait_warp(&tfull_bar[acc], acc_ph, &abort_flag, p.status, kTimeoutTmemFull, t)) break;
         tc_fence_after();
         const int row = m0 + quad * 32 + lane;
@@ -856,9 +880,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
           const int col0 = n0 + c * 32;
           if (row < p.M && col0 < p.N) {
             if (p.epi & kEpiOutF32)
-              epilogue_store_chunk<true>(p, r, row, col0);
+              epilogue_store_chunk<true>(p, r, row + out_row0, col0);
             else
-              epilogue_store_chunk<false>(p, r, row, col0, st, lane);
+              epilogue_store_chunk<false>(p, r, row + out_row0, col0, st, lane);
           }
         }
         tc_fence_before();
@@ -1070,6 +1094,7 @@ int launch_gemm_pair(GemmParams& p, const void* A, long long lda, long long a_ro
   const int num_m = (p.M + 2 * kGemmBM - 1) / (2 * kGemmBM);
   const int num_n = (p.N + kPairBN - 1) / kPairBN;
   long long tiles = (long long)num_m * num_n;
+  if (p.groups_k > 0) tiles *= p.groups_k;
   int pairs = g_pair_clusters;
   if (tiles < pairs) pairs = (int)tiles;
   p.gemm_ctas = 2 * pairs;
@@ -1244,5 +1269,7 @@ MMJ_API int mmj_gemm_bf16_grouped_k(const void* A, long long lda, const void* B,
   p.status = status;
   p.groups_k = groups;
   p.group_k = group_k_dev;
+  if ((bn >> 13) & 1)  // CTA-pair kernel
+    return launch_gemm_pair(p, A, lda, rows, B, ldb, rows, (cudaStream_t)stream);
   return launch_gemm(p, A, lda, rows, B, ldb, rows, 0, (cudaStream_t)stream);
 }

@@ -66,6 +66,7 @@ _SPLITK = {"ranges": {}, "scratch": None, "enabled": True, "force": None}
 # Measured cost of one 64-deep K block of a tile, in SM cycles (B200, operands streamed from L2/HBM):
 # the taller / wider the tile, the fewer operand bytes it pulls per FLOP.
 _KBLOCK_CYCLES = {(128, False): 850.0, (256, False): 1100.0, (128, True): 1230.0, (256, True): 2100.0}
+_PAIR_KBLOCK_CYCLES = 920.0   # 256 x 256 tile on a CTA pair (128 x 256 per SM, half of B staged per SM)
 
 
 def plan_wgrad(M: int, N: int, K: int):
@@ -80,21 +81,26 @@ def plan_wgrad(M: int, N: int, K: int):
     if not _SPLITK["enabled"] or K < 4096 or plain_tiles >= 2 * 148:
         return 1, 128, False
     best, best_cost = (1, 128, False), None
-    for (bn, tall), kcyc in _KBLOCK_CYCLES.items():
+    cands = list(_KBLOCK_CYCLES.items())
+    if _PAIR["mode"] != "0" and M >= 256 and N >= 256:
+        cands.append(((256, "pair"), _PAIR_KBLOCK_CYCLES))
+    for (bn, tall), kcyc in cands:
         if bn > max(128, N) or (tall and M < 256):
             continue
         tiles = -(-M // (256 if tall else 128)) * -(-N // bn)
+        units = 74 if tall == "pair" else 148        # a pair tile occupies two SMs
         for S in range(1, 17):
             if K // S < 1024:
                 break
-            waves = -(-(tiles * S) // 148)
+            waves = -(-(tiles * S) // units)
             cost = waves * (K / S / 64.0) * kcyc
             if S > 1 or tall:
                 cost += 5700.0 + S * M * N * 0.0026    # reduction pass: launch + slab traffic
             if best_cost is None or cost < best_cost - 1e-6:
                 best, best_cost = (S, bn, tall), cost
     S, bn, tall = best
-    if S == 1 and tall:      # a single range needs no slabs: fall back to the plain kernel
+    if S == 1 and tall:      # a single range needs no slabs: fall back to the plain kernel (which picks
+        # its own tile shape, the pair kernel included)
         return 1, 128, False
     return best
 
@@ -145,7 +151,8 @@ def _gemm_split_k(a, b, out, accumulate, M, N, K, S, bn, tall=False):
         sc = torch.empty(need, dtype=torch.float32, device=a.device)
         _SPLITK["scratch"] = sc
     _C.call("mmj_gemm_bf16_grouped_k", _C.ptr(a), a.stride(0), _C.ptr(b), b.stride(0), _C.ptr(sc), N, K, M, N, S,
-            _C.ptr(_split_ranges(K, S, a.device)), 1, 0, bn | (TALL if tall else 0),
+            _C.ptr(_split_ranges(K, S, a.device)), 1, 0,
+            bn | (PAIR if tall == "pair" else TALL if tall else 0),
             _C.ptr(_C.status_tensor(a.device)),
             _C.current_stream())
     _C.call("mmj_splitk_reduce", _C.ptr(sc), M * N, S, _C.ptr(out), M * N, int(accumulate), _C.current_stream())

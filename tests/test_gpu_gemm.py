@@ -118,3 +118,27 @@ def test_gemm_cta_pair_epilogues():
     _close(gemm(a, b, add_aux=aux, pair=True), ref + aux.float())
     o32 = gemm(a, b, out_f32=True, pair=True)
     _close(o32, ref, tol=1e-3)
+
+
+@pytest.mark.parametrize("force", [None, (4, 128, False), (2, 256, True), (2, 256, "pair"), (5, 256, "pair")])
+@pytest.mark.parametrize("M,N", [(768, 768), (3072, 768), (520, 1000)])
+def test_gemm_split_k_weight_gradient(force, M, N):
+    """dW = dy^T x with a long contraction: split-K slabs + reduction, on one-SM tiles and on CTA pairs."""
+    from momijo_b200.ops import gemm as gemm_mod
+    import sys
+    mod = sys.modules["momijo_b200.ops.gemm"]
+    torch.manual_seed(5)
+    K = 8192
+    dy, x = _rand(K, M, scale=0.1), _rand(K, N, scale=0.1)
+    ref = dy.float().t() @ x.float()
+    old = mod._SPLITK["force"]
+    mod._SPLITK["force"] = force
+    try:
+        out = gemm(dy, x, a_mn=True, b_mn=True)
+        _close(out, ref)
+        acc = _rand(M, N)
+        expect = ref + acc.float()
+        gemm(dy, x, a_mn=True, b_mn=True, out=acc, accumulate=True)
+        _close(acc, expect)
+    finally:
+        mod._SPLITK["force"] = old
