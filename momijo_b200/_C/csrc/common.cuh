@@ -272,8 +272,10 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t cta_addr, uint32_t rank
   return r;
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
-               : "memory");
+  // default (CTA-scope release) semantics: the arrival only has to order this warp's TMEM reads, which
+  // tcgen05.wait::ld and the tcgen05 fence already did; a cluster-scope release would also wait for
+  // every global store of the epilogue to drain
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // One warp in each CTA of the pair, same warp index, same destination offset.
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst, uint32_t ncols) {
