@@ -160,9 +160,10 @@ __device__ __forceinline__ void staged_store_bf16(uint8_t* st, int lane, const f
 template <bool kOutF32>
 __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const uint32_t (&acc)[32],
                                                      int row, int col0, uint8_t* st = nullptr,
-                                                     int lane = 0) {
+                                                     int lane = 0, const uint4* auxq = nullptr) {
   // One thread owns 32 consecutive columns [col0, col0+32) of output row `row`. With `st` set the
-  // whole warp is here (32 valid rows, lane = row offset) and full chunks leave through it.
+  // whole warp is here (32 valid rows, lane = row offset) and full chunks leave through it. `auxq`:
+  // the chunk's 32 aux values, already loaded by the caller (full chunks only).
   const int epi = p.epi;
   float v[32];
 #pragma unroll
@@ -219,7 +220,7 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const 
     if (full) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        uint4 q = reinterpret_cast<const uint4*>(a)[i];
+        uint4 q = (auxq != nullptr) ? auxq[i] : reinterpret_cast<const uint4*>(a)[i];
         float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z),
                f3 = unpack_bf16x2(q.w);
         x[8 * i + 0] = f0.x; x[8 * i + 1] = f0.y; x[8 * i + 2] = f1.x; x[8 * i + 3] = f1.y;
@@ -873,16 +874,41 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         const int row = m0 + quad * 32 + lane;
         const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kAccCols);
         uint8_t* st = (m0 + quad * 32 + 32 <= p.M) ? epi_stage[warp - 2] : nullptr;
+        // The aux operand of the GELU' / add / multiply epilogues is requested one chunk ahead, so that
+        // its latency hides behind the previous chunk instead of following every TMEM read.
+        const bool has_aux = (p.epi & (kEpiDGelu | kEpiAddAux | kEpiMulAux)) != 0 && p.vec_ok && row < p.M;
+        const __nv_bfloat16* aux_row =
+            reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)(row + out_row0) * p.ldaux;
+        uint4 aq[4], aq_next[4];
+        bool aq_ok = false, aq_next_ok = false;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) aq_next[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (has_aux && n0 + chalf * 32 + 32 <= p.N) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            aq_next[i] = reinterpret_cast<const uint4*>(aux_row + n0 + chalf * 32)[i];
+          aq_next_ok = true;
+        }
         for (int c = chalf; c < kPairBN / 32; c += 2) {
           uint32_t r[32];
           tmem_ld_32x32(t_row + (uint32_t)(c * 32), r);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) aq[i] = aq_next[i];
+          aq_ok = aq_next_ok;
+          aq_next_ok = false;
+          const int ncol0 = n0 + (c + 2) * 32;
+          if (has_aux && c + 2 < kPairBN / 32 && ncol0 + 32 <= p.N) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) aq_next[i] = reinterpret_cast<const uint4*>(aux_row + ncol0)[i];
+            aq_next_ok = true;
+          }
           tmem_ld_wait();
           const int col0 = n0 + c * 32;
           if (row < p.M && col0 < p.N) {
             if (p.epi & kEpiOutF32)
-              epilogue_store_chunk<true>(p, r, row + out_row0, col0);
+              epilogue_store_chunk<true>(p, r, row + out_row0, col0, nullptr, 0, aq_ok ? aq : nullptr);
             else
-              epilogue_store_chunk<false>(p, r, row + out_row0, col0, st, lane);
+              epilogue_store_chunk<false>(p, r, row + out_row0, col0, st, lane, aq_ok ? aq : nullptr);
           }
         }
         tc_fence_before();
