@@ -252,12 +252,14 @@ __global__ void norm_bwd_finalize_kernel(const float* __restrict__ partial_dg,
                                          __nv_bfloat16* __restrict__ dgamma,
                                          __nv_bfloat16* __restrict__ dbeta, int nparts, int C,
                                          int accumulate) {
-  // block (32, 32): 32 adjacent columns, the partial rows split over threadIdx.y
-  __shared__ float sa[32][33], sb[32][33];
-  const int c = blockIdx.x * 32 + threadIdx.x;
+  // block (16, 64): 16 adjacent columns (one 64-byte piece per partial row), the partial rows split over
+  // threadIdx.y; narrow column strips give 48 CTAs for C = 768 where 32-column strips gave 24 and left
+  // the 7 MB of partials to two dozen SMs
+  __shared__ float sa[64][17], sb[64][17];
+  const int c = blockIdx.x * 16 + threadIdx.x;
   float a = 0.f, b = 0.f;
   if (c < C) {
-    for (int p = threadIdx.y; p < nparts; p += 32) {
+    for (int p = threadIdx.y; p < nparts; p += 64) {
       a += partial_dg[(size_t)p * C + c];
       if (partial_db != nullptr) b += partial_db[(size_t)p * C + c];
     }
@@ -269,7 +271,7 @@ __global__ void norm_bwd_finalize_kernel(const float* __restrict__ partial_dg,
   a = 0.f;
   b = 0.f;
 #pragma unroll
-  for (int y = 0; y < 32; ++y) {
+  for (int y = 0; y < 64; ++y) {
     a += sa[y][threadIdx.x];
     b += sb[y][threadIdx.x];
   }
@@ -345,7 +347,7 @@ MMJ_API int mmj_norm_bwd(const void* dy, const void* x, const void* gamma, const
     norm_bwd_kernel<2, false><<<nparts, threads, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, mean, rstd,
         (const __nv_bfloat16*)dres_in, (__nv_bfloat16*)dx, pdg, pdb, rows, C, mode);
-  norm_bwd_finalize_kernel<<<(C + 31) / 32, dim3(32, 32), 0, (cudaStream_t)stream>>>(
+  norm_bwd_finalize_kernel<<<(C + 15) / 16, dim3(16, 64), 0, (cudaStream_t)stream>>>(
       pdg, pdb, (__nv_bfloat16*)dgamma, (__nv_bfloat16*)dbeta, nparts, C, accumulate);
   return (int)cudaGetLastError();
 }
