@@ -91,6 +91,17 @@ def predict(model, inputs, options: PredictOptions | None = None):
     return torch.cat([net(inputs[i:i + bs]) for i in range(0, inputs.shape[0], bs)], 0)
 
 
+def evaluate_with_options(model, loader, opts: EvalOptions | None = None):
+    """``evaluate`` limited to ``opts.steps`` batches when that is positive
+    (legacy/src/momijo/learn/api/functional.mojo:157-163)."""
+    return evaluate(model, loader, opts)
+
+
+def predict_with_options(model, inputs, opts: PredictOptions | None = None):
+    """``predict`` in chunks of ``opts.batch_size`` (legacy/src/momijo/learn/api/functional.mojo:187-203)."""
+    return predict(model, inputs, opts)
+
+
 def matmul_i8_i8_to_i32(a_q: torch.Tensor, b_q: torch.Tensor) -> torch.Tensor:
     """int8 [M,K] x int8 [N,K]^T -> int32 [M,N]."""
     return a_q.to(torch.int32) @ b_q.to(torch.int32).t()

@@ -76,6 +76,10 @@ class QConfig:
         return f"QConfig(backend={self.backend}, dtype={self.dtype})"
 
 
+def get_default_qconfig(backend: str = "fbgemm") -> QConfig:
+    return QConfig(backend)
+
+
 class MinMaxObserver:
     def __init__(self):
         self.min_val, self.max_val = float("inf"), float("-inf")

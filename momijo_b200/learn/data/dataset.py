@@ -6,15 +6,92 @@ from __future__ import annotations
 from typing import Callable, Iterable, List
 
 
+class LCG32:
+    """state <- state * 1664525 + 1013904223 (mod 2^32) (legacy/src/momijo/learn/data/dataset.mojo:570-585)."""
+
+    def __init__(self, seed: int):
+        self.state = int(seed) & 0xFFFFFFFF
+
+    def next_u32(self) -> int:
+        self.state = (self.state * 1664525 + 1013904223) & 0xFFFFFFFF
+        return self.state
+
+    def randint(self, lo: int, hi: int) -> int:
+        """Integer in [lo, hi) from the low 31 bits of the next state."""
+        span = hi - lo
+        if span <= 0:
+            return lo
+        return lo + (self.next_u32() & 0x7FFFFFFF) % span
+
+
+def shuffle_inplace(idxs: List[int], seed: int) -> List[int]:
+    """Fisher-Yates from the back with ``LCG32(seed)`` (legacy/src/momijo/learn/data/dataset.mojo:588-597)."""
+    rng = LCG32(seed)
+    for i in range(len(idxs) - 1, 0, -1):
+        j = rng.randint(0, i + 1)
+        idxs[i], idxs[j] = idxs[j], idxs[i]
+    return idxs
+
+
 def lcg_shuffle(n: int, seed: int) -> List[int]:
-    """Fisher-Yates with the reference LCG (dataset.mojo:570-597)."""
-    idx = list(range(n))
-    state = seed & 0xFFFFFFFF
-    for i in range(n - 1, 0, -1):
-        state = (state * 1664525 + 1013904223) & 0xFFFFFFFF
-        j = state % (i + 1)
-        idx[i], idx[j] = idx[j], idx[i]
-    return idx
+    """Shuffled ``range(n)``: ``shuffle_inplace(make_arange(n), seed)``."""
+    return shuffle_inplace(list(range(n)), seed)
+
+
+def make_arange(n: int) -> List[int]:
+    return list(range(max(0, n)))
+
+
+def clamp_index(i: int, n: int) -> int:
+    """i clamped into [0, n - 1]; 0 for an empty range."""
+    if n <= 0:
+        return 0
+    return min(max(i, 0), n - 1)
+
+
+def make_random_index_partition(n: int, train_ratio: float, seed: int):
+    """(train indices, validation indices): a seeded shuffle of range(n) cut at int(n * train_ratio)
+    (legacy/src/momijo/learn/data/dataset.mojo:599-617)."""
+    idxs = lcg_shuffle(n, seed)
+    k = min(max(int(float(n) * train_ratio), 0), n)
+    return idxs[:k], idxs[k:]
+
+
+class IndexIter:
+    """Cursor over ``range(n)`` (legacy/src/momijo/learn/data/dataset.mojo:307-323)."""
+
+    def __init__(self, n: int):
+        self.i, self.n = 0, n
+
+    def reset(self):
+        self.i = 0
+
+    def done(self) -> bool:
+        return self.i >= self.n
+
+
+class IndexAdapter:
+    """Uniform ``len`` / ``[]`` view of any indexable source, optionally through caller-supplied accessors
+    (legacy/src/momijo/learn/data/dataset.mojo:355-388)."""
+
+    def __init__(self, base, len_fn=None, get_fn=None):
+        self.base = base
+        self._len = len_fn or (lambda b: len(b))
+        self._get = get_fn or (lambda b, i: b[i])
+
+    def __len__(self):
+        return self._len(self.base)
+
+    def __getitem__(self, idx):
+        return self._get(self.base, idx)
+
+    @staticmethod
+    def from_dataset(base):
+        return IndexAdapter(base)
+
+    @staticmethod
+    def from_image_folder(base):
+        return IndexAdapter(base)
 
 
 class Dataset:
@@ -92,6 +169,25 @@ class IterableDataset:
     def __iter__(self):
         return iter(self.source() if callable(self.source) else self.source)
 
+    # cursor protocol of the reference (legacy/src/momijo/learn/data/dataset.mojo:334-352)
+    def with_dataset(self, data):
+        self.source = data
+        return self
+
+    def __len__(self):
+        return len(self.source)
+
+    def _make_index_iter(self):
+        return IndexIter(len(self))
+
+    def next_item(self, it):
+        """Item under the cursor (and advance), or None at the end."""
+        if it.done():
+            return None
+        idx = it.i
+        it.i += 1
+        return self.source[idx]
+
     def map(self, fn):
         src = self
         return IterableDataset(lambda: (fn(x) for x in src))
@@ -153,3 +249,22 @@ class EnumerateDataset(Dataset):
         return (self.start0 + i, self.base[i])
 
     get = __getitem__
+
+
+# ---- factories of the reference (legacy/src/momijo/learn/data/dataset.mojo:517-548) ------------------------
+def make_index_slice(base, start: int, length: int, mk_empty=None):
+    """View of ``length`` items of ``base`` from ``start``. ``mk_empty`` (the reference's filler for
+    out-of-range reads) is accepted and unused: out-of-range reads raise IndexError here."""
+    return IndexSliceDataset(IndexAdapter(base), start, start + length)
+
+
+def make_index_list(base, indices, mk_empty=None):
+    return IndexListDataset(IndexAdapter(base), indices)
+
+
+def make_zip(left, right):
+    return ZipDataset(IndexAdapter(left), IndexAdapter(right))
+
+
+def make_enumerate(base):
+    return EnumerateDataset(IndexAdapter(base))

@@ -23,6 +23,9 @@ class ImageFolderDataset:
     def __len__(self):
         return len(self.samples)
 
+    def num_classes(self) -> int:
+        return len(self.classes)
+
     def __getitem__(self, i):
         from ...vision import imread
 
@@ -36,3 +39,24 @@ class ImageFolderDataset:
         return t, label
 
     get = __getitem__
+
+
+def list_dirs_sorted(root: str):
+    """Names of the sub-directories of ``root`` in lexicographic order; [] if ``root`` cannot be listed
+    (legacy/src/momijo/learn/data/image.mojo:70-91)."""
+    try:
+        return sorted(d for d in os.listdir(root) if os.path.isdir(os.path.join(root, d)))
+    except OSError:
+        return []
+
+
+def list_dirs_sorted_paths(root: str):
+    return [os.path.join(root, d) for d in list_dirs_sorted(root)]
+
+
+def list_pngs_sorted(root: str):
+    """Full paths of the ``.png`` files (any case) of ``root``, sorted by file name."""
+    try:
+        return [os.path.join(root, f) for f in sorted(os.listdir(root)) if f.lower().endswith(".png")]
+    except OSError:
+        return []

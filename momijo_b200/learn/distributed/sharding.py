@@ -103,3 +103,27 @@ class ZeroStage1:
         r = self.shard_range(total_len)
         buf[r.start:r.end] = shard
         return C.allreduce(buf) if C.is_distributed() else buf
+
+    def reduce_scatter_tensor(self, grads_full: torch.Tensor) -> torch.Tensor:
+        """Sum ``grads_full`` over ranks and keep this rank's shard."""
+        flat = grads_full.reshape(-1)
+        total = C.allreduce(flat.clone()) if C.is_distributed() else flat
+        r = self.shard_range(flat.numel())
+        return total[r.start:r.end]
+
+    # names of the reference's 1-D adapters (legacy/src/momijo/learn/distributed/sharding.mojo:225-240)
+    shard_tensor_f64 = shard_tensor
+    allgather_tensor_f64 = allgather_tensor
+    reduce_scatter_tensor_f64 = reduce_scatter_tensor
+
+
+def shard_tensor_f64(zero: ZeroStage1, t: torch.Tensor) -> torch.Tensor:
+    return zero.shard_tensor(t)
+
+
+def allgather_tensor_f64(zero: ZeroStage1, shard: torch.Tensor, total_len: int) -> torch.Tensor:
+    return zero.allgather_tensor(shard, total_len)
+
+
+def reduce_scatter_tensor_f64(zero: ZeroStage1, grads_full: torch.Tensor) -> torch.Tensor:
+    return zero.reduce_scatter_tensor(grads_full)

@@ -67,3 +67,36 @@ def dry_trace(model, example):
     with torch.no_grad():
         out = model(example)
     return {"shape": list(out.shape), "dtype": str(out.dtype)} if isinstance(out, torch.Tensor) else {}
+
+
+@dataclass
+class JITReport:
+    """What a compile call did (legacy/src/momijo/learn/engine/jit_compile.mojo:79-108)."""
+    graph_enabled: bool = False
+    passes_applied: int = 0
+    lowered_ops: int = 0
+    fallback_ops: int = 0
+    notes: str = ""
+
+    def __str__(self):
+        return (f"JITReport(graph={'true' if self.graph_enabled else 'false'}, passes={self.passes_applied}, "
+                f"lowered_ops={self.lowered_ops}, fallback_ops={self.fallback_ops}, notes='{self.notes}')")
+
+
+def compile_report(model, options: JITOptions) -> JITReport:
+    """The report the reference's ``compile_with`` fills in: nothing is lowered ahead of time; with
+    ``options.graph`` the executor captures a CUDA graph on its first call."""
+    return JITReport(graph_enabled=options.graph, notes="CUDA-graph capture on first call" if options.graph
+                     else "eager execution")
+
+
+def prefer_graph(opts: JITOptions) -> bool:
+    return bool(opts.graph)
+
+
+def build_executor(opts: JITOptions, fn=None) -> GraphExecutor:
+    """Executor for ``fn`` (identity when omitted) under ``opts``; ``is_valid`` tells whether graph
+    capture was asked for (legacy/src/momijo/learn/engine/jit_compile.mojo:181-184)."""
+    ex = GraphExecutor(fn, opts)
+    ex.is_valid = bool(opts.graph)
+    return ex

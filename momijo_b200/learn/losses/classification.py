@@ -57,3 +57,34 @@ def label_smoothing_cross_entropy(logits, target, smoothing=0.1):
     nll = -logp.gather(-1, tg.unsqueeze(-1)).squeeze(-1)
     r = ((1 - smoothing) * nll + smoothing * (-logp.mean(-1))).mean()
     return r if isinstance(logits, torch.Tensor) else float(r)
+
+
+def focal_loss_binary_with_logits(logits, targets, gamma=2.0, alpha=0.25):
+    """Binary focal loss on logits: w * (1 - p_t)^gamma * BCE, w = alpha for targets equal to 1 and
+    1 - alpha otherwise, averaged (legacy/src/momijo/learn/losses/classification.mojo:193-214, 339-345)."""
+    x, y = _t(logits).double(), _t(targets).double().clamp(0, 1)
+    if x.numel() == 0:
+        return 0.0
+    p = torch.sigmoid(x)
+    pos = y == 1.0
+    pt = torch.where(pos, p, 1 - p)
+    w = torch.where(pos, torch.full_like(p, alpha), torch.full_like(p, 1 - alpha))
+    ce = torch.nn.functional.binary_cross_entropy_with_logits(x, y, reduction="none")
+    return float((w * (1 - pt) ** gamma * ce).mean())
+
+
+def focal_loss_multiclass_with_logits(logits, target, gamma=2.0, alpha=0.25):
+    """Multi-class focal loss on [N, C] logits; ``target`` is either N class indices or an [N, C] one-hot
+    matrix (every non-zero entry contributes). One alpha for all classes, sum divided by N
+    (legacy/src/momijo/learn/losses/classification.mojo:216-260, 348-363)."""
+    lg = _t(logits).double()
+    if lg.numel() == 0:
+        return 0.0
+    probs = torch.softmax(lg, -1)
+    tg = _t(target)
+    eps = 1e-12
+    term = alpha * (1 - probs) ** gamma * (-(probs.clamp(eps, 1.0)).log())
+    if tg.dim() == 1:
+        picked = term.gather(-1, tg.long().unsqueeze(-1)).squeeze(-1)
+        return float(picked.sum() / lg.shape[0])
+    return float((term * (tg != 0)).sum() / lg.shape[0])

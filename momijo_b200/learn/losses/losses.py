@@ -111,3 +111,22 @@ def triplet(anchor, positive, negative, margin=1.0, reduction="mean"):
 def cosine_embedding(a, b, y, margin=0.0, reduction="mean"):
     cos = tF.cosine_similarity(a, b, dim=-1)
     return _reduce(torch.where(y > 0, 1 - cos, (cos - margin).clamp_min(0)), reduction)
+
+
+def triplet_loss(anchor, positive, negative, margin: float = 1.0):
+    """max(0, sum((a-p)^2) - sum((a-n)^2) + margin) with both sums taken over every element, as the
+    reference's tensor overload does (legacy/src/momijo/learn/losses/losses.mojo:257-270). The per-row
+    L2 form is ``losses.ranking.triplet_loss``."""
+    dap = (anchor - positive).pow(2).sum()
+    dan = (anchor - negative).pow(2).sum()
+    return (dap - dan + margin).clamp_min(0)
+
+
+def cosine_embedding_loss(x1, x2, target, margin: float = 0.0, eps: float = 1e-12):
+    """Whole-tensor cosine between x1 and x2; 1 - cos where target > 0, max(0, cos - margin) elsewhere,
+    averaged over target (legacy/src/momijo/learn/losses/losses.mojo:273-290)."""
+    dot = (x1 * x2).sum()
+    n1 = ((x1 * x1).sum() + eps).sqrt()
+    n2 = ((x2 * x2).sum() + eps).sqrt()
+    cos = dot / (n1 * n2)
+    return torch.where(target > 0, 1.0 - cos, (cos - margin).clamp_min(0)).mean()

@@ -39,3 +39,32 @@ def bce_dice_loss(probs, target, eps=1e-12):
     p, t = _t(probs).clamp(eps, 1 - eps), _t(target)
     bce = -(t * p.log() + (1 - t) * (1 - p).log()).mean()
     return _out(bce + _t(dice_loss(p, t)), probs)
+
+
+def dice_loss_mc_vec(preds_per_class, targets_per_class, eps=1e-6):
+    """Per-class binary Dice losses (legacy/src/momijo/learn/losses/segmentation.mojo:112-121, 223-232)."""
+    assert len(preds_per_class) == len(targets_per_class)
+    return [float(dice_loss(_t(p).clamp(0, 1), _t(t).clamp(0, 1), eps))
+            for p, t in zip(preds_per_class, targets_per_class)]
+
+
+def iou_loss_mc_vec(preds_per_class, targets_per_class, eps=1e-6):
+    assert len(preds_per_class) == len(targets_per_class)
+    return [float(iou_loss(_t(p).clamp(0, 1), _t(t).clamp(0, 1), eps))
+            for p, t in zip(preds_per_class, targets_per_class)]
+
+
+def _mc_reduce(vec, reduction):
+    if not vec:
+        return 0.0
+    return float(sum(vec)) if reduction == "sum" else float(sum(vec) / len(vec))   # "none" also averages
+
+
+def dice_loss_mc(preds_per_class, targets_per_class, eps=1e-6, reduction="mean"):
+    """Mean (or sum) of the per-class Dice losses; ``reduction="none"`` averages too, as in the reference
+    (legacy/src/momijo/learn/losses/segmentation.mojo:134-144)."""
+    return _mc_reduce(dice_loss_mc_vec(preds_per_class, targets_per_class, eps), reduction)
+
+
+def iou_loss_mc(preds_per_class, targets_per_class, eps=1e-6, reduction="mean"):
+    return _mc_reduce(iou_loss_mc_vec(preds_per_class, targets_per_class, eps), reduction)

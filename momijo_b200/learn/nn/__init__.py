@@ -3,7 +3,7 @@ from .module import Module, TAGS  # noqa: F401
 from .layers import (  # noqa: F401
     Linear, ReLU, LeakyReLU, Sigmoid, Tanh, GELU, SiLU, BatchNorm1d, BatchNorm2d, Dropout, Flatten,
     QuantLinear, Embedding, LayerNorm, RMSNorm, RotaryEmbedding, SwiGLU, quantize_symmetric_int8,
-    dropout_mask,
+    dropout_mask, Seq512,
 )
 from .conv import Conv2d, MaxPool2d  # noqa: F401
 from .avgpool import AvgPool2d  # noqa: F401

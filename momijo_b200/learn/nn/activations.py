@@ -137,3 +137,8 @@ def log_softmax(x, axis=-1):
     legacy/src/momijo/tensor/math.mojo:463-478)."""
     t, kind = _t(x)
     return _back(torch.log_softmax(t, dim=axis), kind)
+
+
+# the reference spells these two both ways (legacy/src/momijo/learn/nn/activations.mojo:533-560)
+hardsigmoid = hard_sigmoid
+swish = silu

@@ -63,3 +63,9 @@ class MultiHeadAttention(Module):
             o = (p @ vh).transpose(1, 2).reshape(B * T, C).to(x.dtype)
         out = self.Wo(o)
         return out.reshape(B, T, C).transpose(0, 1)
+
+
+def sqrt64(x: float) -> float:
+    """Square root that returns 0.0 for non-positive input (legacy/src/momijo/learn/nn/attention.mojo:25-36)."""
+    import math
+    return math.sqrt(x) if x > 0.0 else 0.0

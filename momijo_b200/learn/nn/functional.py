@@ -118,3 +118,41 @@ def rowwise_relu_normalize(s):
     (legacy/src/momijo/learn/nn/functional.mojo:674-694)."""
     r = torch.relu(s)
     return r / r.sum(-1, keepdim=True).clamp_min(1e-12)
+
+
+# ---- names and layouts of the reference's index-based helpers ------------------------------------------
+def im2col_indices(x, kH: int, kW: int, stride: int = 1, padding: int = 0):
+    """Linear source index ((n*C + c)*H + ih)*W + iw of every im2col entry, 0 where the window hangs over
+    the border; shape [N, C*kH*kW, OH*OW] (legacy/src/momijo/learn/nn/functional.mojo:321-365). Only the
+    shape of ``x`` is used."""
+    N, C, H, W = (int(s) for s in x.shape)
+    lin = torch.arange(N * C * H * W, dtype=torch.float64).reshape(N, C, H, W)
+    # unfold pads with zeros, which is exactly the "outside" marker of the reference
+    cols = tF.unfold(lin, (kH, kW), padding=padding, stride=stride)
+    return cols.to(torch.int64)
+
+
+def col2im_indices(cols, idxs, x_shape):
+    """Scatter-add ``cols`` [N, K, L] back into an [N, C, H, W] tensor at the linear indices ``idxs``;
+    entries whose index is 0 are skipped, as in the reference, which uses 0 as the padding marker
+    (legacy/src/momijo/learn/nn/functional.mojo:398-424)."""
+    N, C, H, W = (int(s) for s in x_shape)
+    out = torch.zeros(N * C * H * W, dtype=cols.dtype, device=cols.device)
+    idx = idxs.reshape(-1).to(cols.device)
+    vals = cols.reshape(-1)
+    keep = idx > 0
+    out.index_add_(0, idx[keep], vals[keep])
+    return out.reshape(N, C, H, W)
+
+
+def conv2d_depthwise(x, k, stride: int = 1, padding: int = 0):
+    """One kernel per channel; ``k`` is [C, kH, kW] or [C, 1, kH, kW]
+    (legacy/src/momijo/learn/nn/functional.mojo:573-617)."""
+    if k.dim() == 3:
+        k = k[:, None]
+    return depthwise_conv2d(x, k, None, stride, padding)
+
+
+def conv2d_pointwise(x, w):
+    """1x1 convolution with ``w`` [F, C] (legacy/src/momijo/learn/nn/functional.mojo:620-647)."""
+    return pointwise_conv2d(x, w)

@@ -331,3 +331,17 @@ class SwiGLU(Module):
 
     def forward(self, x):
         return ops.linear(ops.swiglu(ops.linear(x, self.w_gu)), self.w_down)
+
+
+class Seq512(Module):
+    """Linear(512, 512) -> ReLU -> Linear(512, 512), the fixed demo stack of the reference
+    (legacy/src/momijo/learn/nn/module.mojo:459-477)."""
+
+    def __init__(self):
+        super().__init__()
+        self.l1 = Linear(512, 512)
+        self.a = ReLU()
+        self.l2 = Linear(512, 512)
+
+    def forward(self, x):
+        return self.l2(self.a(self.l1(x)))

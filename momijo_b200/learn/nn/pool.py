@@ -44,3 +44,12 @@ def avg_unpool2d(y, kernel, stride=None):
     s = _pair(stride) if stride is not None else k
     up = y.repeat_interleave(s[0], 2).repeat_interleave(s[1], 3)
     return up / float(k[0] * k[1])
+
+
+def pool2d_core(x, k: int, stride: int = 0, padding: int = 0, mode: int = 0):
+    """Square-window pooling over NCHW: ``mode`` 0 = max, otherwise mean over the in-range taps; a stride
+    of 0 (or less) means the window size (legacy/src/momijo/learn/nn/pool.mojo:74-137)."""
+    st = stride if stride > 0 else k
+    if mode == 0:
+        return tF.max_pool2d(x, k, st, padding)
+    return tF.avg_pool2d(x, k, st, padding, count_include_pad=False)

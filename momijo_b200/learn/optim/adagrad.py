@@ -22,3 +22,15 @@ class Adagrad(_PerLayerOptimizer):
             self.state[key] = acc
         acc.addcmul_(g, g)
         p.sub_(self.lr * g / (acc.sqrt() + self.eps))
+
+
+def adagrad_update_scalar(param: float, grad: float, acc: float, lr: float, eps: float, weight_decay: float):
+    """One Adagrad step on a scalar: returns (new parameter, new accumulator)
+    (legacy/src/momijo/learn/optim/adagrad.mojo:59-77)."""
+    import math
+    g = grad + weight_decay * param if weight_decay != 0.0 else grad
+    acc_new = acc + g * g
+    denom = math.sqrt(acc_new) + eps
+    if denom <= 0.0:
+        denom = eps
+    return param - lr * g / denom, acc_new

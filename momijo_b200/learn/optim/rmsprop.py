@@ -36,3 +36,16 @@ class RMSprop(_PerLayerOptimizer):
             p.sub_(self.lr * g / denom)
         if self.weight_decay and self.decoupled:
             p.mul_(1 - self.lr * self.weight_decay)
+
+
+class OptParam:
+    """Scalar parameter with its gradient (legacy/src/momijo/learn/optim/rmsprop.mojo:95-101)."""
+
+    def __init__(self, value: float, grad: float = 0.0):
+        self.value, self.grad = value, grad
+
+
+def step_conv2d(opt: RMSprop, layer, dW, db):
+    """RMSprop update of a ``Conv2d`` layer's weight and bias from explicit gradients
+    (legacy/src/momijo/learn/optim/rmsprop.mojo:48-54)."""
+    return opt.step_conv2d(layer, dW, db)

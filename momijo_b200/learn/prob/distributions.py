@@ -140,3 +140,13 @@ class Normal(_Dist):
 
     def entropy(self):
         return 0.5 * math.log(2 * math.pi * math.e * self.std ** 2)
+
+
+def ln(x: float) -> float:
+    """Natural log; -inf for non-positive input (legacy/src/momijo/learn/prob/distributions.mojo:54-65)."""
+    return math.log(x) if x > 0.0 else float("-inf")
+
+
+def sqrt(x: float) -> float:
+    """Square root; 0.0 for non-positive input (legacy/src/momijo/learn/prob/distributions.mojo:67-75)."""
+    return math.sqrt(x) if x > 0.0 else 0.0

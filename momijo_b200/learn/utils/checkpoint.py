@@ -234,6 +234,14 @@ def exists_checkpoint(path: str, stem: Optional[str] = None) -> bool:
     return os.path.exists(_header_path(base)) or os.path.exists(_state_path(base))
 
 
+def exists_checkpoint_at(dir_: str, stem: str) -> bool:
+    """``exists_checkpoint(dir_ + "/" + stem)`` (legacy/src/momijo/learn/utils/checkpoint.mojo:366-373)."""
+    base = dir_
+    if base and not base.endswith("/"):
+        base += "/"
+    return exists_checkpoint(base + stem)
+
+
 def read_model_class_from_header(path: str, stem: Optional[str] = None) -> str:
     base = os.path.join(path, stem) if stem is not None else path
     return _extract_model_class_from_header(_read_text(_header_path(base)))

@@ -143,3 +143,18 @@ class TrainingLoopProfiler(LabelProfiler):
 
     def summary(self) -> dict:
         return {k: self.get(k).mean() / 1e6 for k in self.LABELS}
+
+
+# unit conversions of the reference (legacy/src/momijo/learn/utils/profiling.mojo:31-46)
+def ns_to_s(ns: int) -> float:
+    return float(ns) / 1_000_000_000.0
+
+
+def ns_to_ms(ns: int) -> float:
+    return float(ns) / 1_000_000.0
+
+
+def s_to_ns(seconds: float) -> int:
+    """Negative durations clamp to 0; the result saturates at 2**64 - 1."""
+    s = max(float(seconds), 0.0)
+    return min(int(s * 1_000_000_000.0), (1 << 64) - 1)

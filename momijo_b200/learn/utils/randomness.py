@@ -128,3 +128,34 @@ def seed_all(seed: int) -> SeedBundle:
 def derived_rngs(seed: int, n: int) -> list:
     sm = SplitMix64(seed)
     return [RNG(sm.next_u64()) for _ in range(n)]
+
+
+# ---- seed-in, value-out helpers (legacy/src/momijo/learn/utils/randomness.mojo:404-452): each builds a
+# fresh generator from ``seed`` (negative seeds use their magnitude), so the same call always returns the
+# same value and no global state is touched.
+def rng_from_seed(seed: int) -> RNG:
+    return RNG(-seed if seed < 0 else seed)
+
+
+def randint(seed: int, low: int, high: int) -> int:
+    return rng_from_seed(seed).randint(low, high)
+
+
+def uniform(seed: int, low: float = 0.0, high: float = 1.0) -> float:
+    return rng_from_seed(seed).uniform(low, high)
+
+
+def normal(seed: int, mean: float = 0.0, std: float = 1.0) -> float:
+    return rng_from_seed(seed).normal(mean, std)
+
+
+def bernoulli(seed: int, p: float) -> int:
+    return int(rng_from_seed(seed).bernoulli(p))
+
+
+def permutation(seed: int, n: int) -> list:
+    return rng_from_seed(seed).permutation(n)
+
+
+def choice_k(seed: int, n: int, k: int) -> list:
+    return rng_from_seed(seed).choice_k(n, k)
