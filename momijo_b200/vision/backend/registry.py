@@ -18,6 +18,9 @@ class BackendKind(IntEnum):
     CUDA = 2
 
 
+Backend = BackendKind   # the reference's name for the enumeration (registry.mojo:25-27)
+
+
 class KernelRegistry:
     def __init__(self, kind: BackendKind = None, schedule: Schedule = None):
         if kind is None:

@@ -27,3 +27,11 @@ class Schedule:
 
 def default_schedule() -> Schedule:
     return Schedule()
+
+
+def auto_schedule(img_h: int, img_w: int) -> Schedule:
+    """The reference's heuristic is a constant 64 x 64 tile with 16-wide vectors
+    (legacy/src/momijo/vision/backend/schedule.mojo:28-33); the CUDA fields keep their defaults, except that
+    the grid cap shrinks for images with fewer pixels than a full grid would cover."""
+    px = max(1, int(img_h) * int(img_w))
+    return Schedule(64, 64, 16, 256, max(1, min(148 * 16, (px + 255) // 256)))

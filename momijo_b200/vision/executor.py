@@ -5,7 +5,7 @@ from __future__ import annotations
 
 from .backend.registry import KernelRegistry, default_registry
 from .image import ColorSpace, Image
-from .ir import Graph, OpKind, optimize
+from .ir import Graph, OpKind, OpNode, optimize
 
 
 def run_graph(g: Graph, img: Image, registry: KernelRegistry = None, do_optimize: bool = True) -> Image:
@@ -35,3 +35,22 @@ def run_graph(g: Graph, img: Image, registry: KernelRegistry = None, do_optimize
         else:
             raise ValueError(f"unknown op kind {k}")
     return Image(t, meta)
+
+
+def run_graph_no_fuse(g: Graph, img: Image, registry: KernelRegistry = None) -> Image:
+    """Every node as written, no fusion or simplification pass first
+    (legacy/src/momijo/vision/executor.mojo:91-99)."""
+    return run_graph(g, img, registry, do_optimize=False)
+
+
+def run_single_op(kind, img: Image, oh: int = 0, ow: int = 0, registry: KernelRegistry = None) -> Image:
+    """One op by kind; kinds that need no size ignore ``oh`` / ``ow``, unknown kinds pass the image through
+    (legacy/src/momijo/vision/executor.mojo:103-113)."""
+    try:
+        kind = OpKind(kind)
+    except ValueError:
+        return img.clone()
+    if kind == OpKind.ConvertRGBToGray and img.channels() != 3:
+        return img.clone()
+    g = Graph([OpNode(kind, oh, ow)])
+    return run_graph(g, img, registry, do_optimize=False)

@@ -17,7 +17,7 @@ import torch
 
 class ColorSpace:
     """Enumeration by name (legacy/src/momijo/vision/dtypes.mojo ``ColorSpace``)."""
-    _names = ("SRGB", "LINEAR", "GRAY", "BGR", "RGB", "HSV", "YCBCR")
+    _names = ("SRGB", "LINEAR", "GRAY", "BGR", "RGB", "HSV", "YCBCR", "UNKNOWN")
 
     def __init__(self, name: str = "SRGB"):
         name = name.upper()
@@ -40,7 +40,7 @@ for _n in ColorSpace._names:
 
 
 class Layout:
-    _names = ("HWC", "CHW")
+    _names = ("HWC", "CHW", "PLANAR")
 
     def __init__(self, name: str = "HWC"):
         name = name.upper()
@@ -60,6 +60,7 @@ class Layout:
 
 Layout.HWC = staticmethod(lambda: Layout("HWC"))
 Layout.CHW = staticmethod(lambda: Layout("CHW"))
+Layout.PLANAR = staticmethod(lambda: Layout("PLANAR"))
 
 
 @dataclass
@@ -295,6 +296,17 @@ def zeros_hwc_u8(h, w, c):
 
 def make_zero_u8_hwc(h, w, c, cs=None):
     return Image.new_hwc_u8(h, w, c, 0, cs)
+
+
+def make_u8_hwc(data, h: int, w: int, c: int, cs: ColorSpace = None) -> Image:
+    """Image over an existing packed HWC uint8 buffer (tensor, bytes, bytearray or numpy array) without
+    copying where possible; an invalid shape gives an empty image
+    (legacy/src/momijo/vision/image.mojo:613-626)."""
+    if h <= 0 or w <= 0 or c <= 0:
+        return Image(torch.zeros(0, 0, 0, dtype=torch.uint8), ImageMeta(None, cs))
+    from .tensor import tensor_from_u8_array_hwc
+    t = data.reshape(h, w, c) if isinstance(data, torch.Tensor) else tensor_from_u8_array_hwc(data, h * w * c, h, w, c)
+    return Image(t, ImageMeta(None, cs))
 
 
 def validate_image(img: Image) -> bool:

@@ -15,3 +15,6 @@ from .hough import hough_circles, hough_lines, hough_lines_p  # noqa: F401
 from .morph import MORPH_DILATE, MORPH_ERODE, dilate, erode, morphology  # noqa: F401
 from .segmentation import connected_components  # noqa: F401
 from .threshold import adaptive_threshold, otsu_level, threshold_binary, threshold_otsu  # noqa: F401
+from .random_ops import (ColorJitter, Keypoint, RandomHorizontalFlip, RandomResizedCrop, RandomRotation,  # noqa: F401,E402
+                         ToTensor, abs_f64, maybe_resize_placeholder, random_affine_placeholder,
+                         random_resized_crop, resize_nearest_u8_hwc)

@@ -141,13 +141,8 @@ def clahe_color_bgr(img, clip_limit: float = 2.0, tile: int = 8):
 
 
 def color_jitter(img: Image, brightness: float, contrast: float, saturation: float, hue: float) -> Image:
-    f = img.numpy().astype(np.float32)
-    f = f * (1.0 + brightness)
-    mean = f.mean()
-    f = (f - mean) * (1.0 + contrast) + mean
-    if f.shape[2] >= 3:
-        g = f[..., :3].mean(-1, keepdims=True)
-        f[..., :3] = (f[..., :3] - g) * (1.0 + saturation) + g
-        if hue:
-            f[..., :3] = np.roll(f[..., :3], 1, -1) * abs(hue) + f[..., :3] * (1 - abs(hue))
-    return Image(torch.from_numpy(np.clip(f + 0.5, 0, 255).astype(np.uint8)).to(img.device), img.meta().copy())
+    """``ColorJitter(brightness, contrast, saturation, hue)(img)``: multiplicative brightness and contrast
+    factors (1.0 = unchanged), saturation factor, hue shift in degrees
+    (legacy/src/momijo/vision/transforms/color.mojo:622-625)."""
+    from .random_ops import ColorJitter
+    return ColorJitter(brightness, contrast, saturation, hue)(img)
