@@ -17,7 +17,7 @@ from .ir import Graph, OpKind, OpNode, fuse_resizes, simplify_convert_color  # n
 from .tensor import (Tensor, array_from_tensor_u8_hwc, empty_1d, empty_hwc, packed_chw_strides, packed_hwc_strides,  # noqa: F401
                      tensor_from_raw_chw, tensor_from_raw_strided, tensor_from_u8_array_hwc, to_tensor_chw,
                      to_tensor_float32, to_tensor_float64, to_tensor_hwc, unsafe_view_from_raw_u8)
-from . import dtypes  # noqa: F401
+from . import dtypes, memory  # noqa: F401
 from .dtypes import (DType, colorspace_from_name, colorspace_name, dtype_bytes, dtype_from_name, dtype_is_float,  # noqa: F401
                      dtype_is_integer, dtype_name, layout_from_name, layout_name)
 from .image import make_u8_hwc  # noqa: F401

@@ -127,3 +127,82 @@ def read_ppm(path: str) -> Image:
 
 def write_ppm(path: str, img: Image) -> bool:
     return write_image_any(path, img)
+
+
+# ---- readers with a synthetic fallback (legacy/src/momijo/vision/io/registry.mojo:18-190,
+# legacy/src/momijo/vision/io/image.mojo:26-46, legacy/src/momijo/vision/io/jpeg.mojo:60-121, 246-270).
+# They return (ok, uint8 HWC tensor); when nothing decodes, ``ok`` is False and the tensor is the
+# reference's test pattern (y*7 + x*11 + ch*29) mod 256, so downstream code still has pixels to work on.
+def make_dummy_u8_hwc_tensor(h: int = 32, w: int = 32, c: int = 3, default: int = 32) -> torch.Tensor:
+    h = h if h > 0 else default
+    w = w if w > 0 else default
+    c = c if c in (1, 3) else 3
+    y = torch.arange(h)[:, None, None]
+    x = torch.arange(w)[None, :, None]
+    ch = torch.arange(c)[None, None, :]
+    return ((y * 7 + x * 11 + ch * 29) % 256).to(torch.uint8)
+
+
+def unsafe_char_from_code(code: int) -> str:
+    return chr(code) if 0 <= code < 0x110000 else "?"
+
+
+def _try_decode(path: str, fmts) -> Tuple[bool, torch.Tensor]:
+    try:
+        with open(path, "rb") as f:
+            buf = f.read()
+    except OSError:
+        return False, None
+    for fmt in fmts:
+        try:
+            return True, torch.from_numpy(np.ascontiguousarray(_DECODERS[fmt](buf)))
+        except Exception:       # a decoder rejecting foreign bytes is the expected case here
+            continue
+    return False, None
+
+
+def _order_for(path: str):
+    p = path.lower()
+    if p.endswith((".jpg", ".jpeg", ".jpe")):
+        return ("jpeg", "png")
+    if p.endswith(".png"):
+        return ("png", "jpeg")
+    if p.endswith((".ppm", ".pgm")):
+        return ("ppm", "jpeg", "png")
+    return ("jpeg", "png")
+
+
+def read_image_auto(path: str) -> Tuple[bool, torch.Tensor]:
+    """Decoder chosen by extension, the other formats tried next; a 32 x 32 x 3 pattern on failure."""
+    ok, t = _try_decode(path, _order_for(path))
+    return (True, t) if ok else (False, make_dummy_u8_hwc_tensor(32, 32, 3))
+
+
+def read_image_auto_with_fallback(path: str, fallback_h: int = 64, fallback_w: int = 64, fallback_c: int = 3):
+    ok, t = _try_decode(path, _order_for(path))
+    return (True, t) if ok else (False, make_dummy_u8_hwc_tensor(fallback_h, fallback_w, fallback_c, 64))
+
+
+def read_image_with_fallback(path: str, fallback_h: int = 64, fallback_w: int = 64, fallback_c: int = 3):
+    ok, t = _try_decode(path, ("png", "jpeg", "ppm"))
+    return (True, t) if ok else (False, make_dummy_u8_hwc_tensor(fallback_h, fallback_w, fallback_c, 64))
+
+
+def has_jpeg_codec() -> bool:
+    return "jpeg" in _DECODERS
+
+
+def read_jpeg_with_fallback(path: str, fallback_h: int = 64, fallback_w: int = 64, fallback_c: int = 3):
+    ok, t = _try_decode(path, ("jpeg",))
+    return (True, t) if ok else (False, make_dummy_u8_hwc_tensor(fallback_h, fallback_w, fallback_c, 64))
+
+
+def read_jpeg_image(path: str) -> Image:
+    """Decoded image, or the 64 x 64 x 3 pattern as an Image when the file cannot be decoded."""
+    ok, t = read_jpeg_with_fallback(path)
+    cs = ColorSpace("GRAY") if t.shape[2] == 1 else ColorSpace("RGB")
+    return Image(t, ImageMeta(None, cs))
+
+
+def write_jpeg_image(path: str, img: Image, quality: int = 90) -> bool:
+    return write_jpeg(path, img, quality)

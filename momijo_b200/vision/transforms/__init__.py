@@ -17,4 +17,5 @@ from .segmentation import connected_components  # noqa: F401
 from .threshold import adaptive_threshold, otsu_level, threshold_binary, threshold_otsu  # noqa: F401
 from .random_ops import (ColorJitter, Keypoint, RandomHorizontalFlip, RandomResizedCrop, RandomRotation,  # noqa: F401,E402
                          ToTensor, abs_f64, maybe_resize_placeholder, random_affine_placeholder,
-                         random_resized_crop, resize_nearest_u8_hwc)
+                         random_resized_crop, resize_nearest_u8_hwc, resize_nearest_u8_hwc_tiled,
+                         resize_nearest_u8_hwc_tiled_scheduled)

@@ -241,3 +241,14 @@ def maybe_resize_placeholder(x, img_size: int):
 
 def abs_f64(v: float) -> float:
     return -v if v < 0 else v
+
+
+def resize_nearest_u8_hwc_tiled_scheduled(x, out_h: int, out_w: int, sched=None):
+    """Same pixels as ``resize_nearest_u8_hwc``; the schedule only sets the tile walk of the host loop in the
+    reference (legacy/src/momijo/vision/transforms/tile.mojo:24-90) and the launch shape of the CUDA kernel
+    here, so it cannot change the result."""
+    return resize_nearest_u8_hwc(x, out_h, out_w)
+
+
+def resize_nearest_u8_hwc_tiled(x, out_h: int, out_w: int):
+    return resize_nearest_u8_hwc(x, out_h, out_w)
