@@ -6,8 +6,10 @@ from .frame import (  # noqa: F401
 from .frame import bool_ as bool  # noqa: F401
 from .ops import *  # noqa: F401,F403
 from .ops import range, filter, where, copy, rename  # noqa: F401
-from . import window, extras  # noqa: F401,E402
+from . import window, extras, relational  # noqa: F401,E402
 from .window import *  # noqa: F401,F403,E402
 from .extras import *  # noqa: F401,F403,E402
+from .relational import *  # noqa: F401,F403,E402
+from .relational import eval, get  # noqa: F401,E402
 from .ops import range, filter, where, copy, rename  # noqa: F401,E402,F811
 from .frame import bool_ as bool  # noqa: F401,E402,F811
