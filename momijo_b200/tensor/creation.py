@@ -223,3 +223,164 @@ for _name, _dt in {"float64": _F64, "float32": _F32, "int": _I64, "int32": _I32,
 def from_list(xs, dtype=None, shape=None):
     t = torch.tensor(xs, dtype=dtype)
     return _wrap(t.reshape(list(shape)) if shape is not None else t)
+
+
+# ---- the remaining typed names of the reference (legacy/src/momijo/tensor/creation.mojo:39-1500) -------------------
+# One family per dtype suffix, generated from the generic factory; the ``*_with`` forms take the reference's
+# element converter (``f``) and apply it to every generated value, so any Python callable works.
+_ALL_DT = {"f16": torch.float16, "f32": _F32, "f64": _F64, "i8": _I8, "i16": _I16, "i32": _I32, "i64": _I64,
+           "u8": _U8, "u16": torch.uint16, "u32": torch.uint32, "u64": torch.uint64, "int": _I64}
+
+
+def _cast(t, dt):
+    """Cast with wrap-around for the unsigned types that torch cannot reach directly from every source."""
+    if dt in (torch.uint16, torch.uint32, torch.uint64):
+        return t.to(torch.int64).to(dt)
+    return t.to(dt)
+
+
+def clamp01(x: float) -> float:
+    return 0.0 if x < 0.0 else (1.0 if x > 1.0 else x)
+
+
+def rotl64(x: int, k: int) -> int:
+    k &= 63
+    x &= (1 << 64) - 1
+    return x if k == 0 else ((x << k) | (x >> (64 - k))) & ((1 << 64) - 1)
+
+
+def init_rng(seed=None) -> RNG64:
+    return RNG64(0xD1B54A32D192ED03 if seed is None else int(seed))
+
+
+def zero_scalar_of(from_f64):
+    return from_f64(0.0)
+
+
+def scalar_zero_tensor(dtype=_F64):
+    return _wrap(torch.zeros((), dtype=dtype))
+
+
+def _apply(t, f):
+    if f is None:
+        return _wrap(t)
+    flat = [f(v) for v in t.reshape(-1).tolist()]
+    return _wrap(torch.tensor(flat).reshape(t.shape))
+
+
+def empty_tensor(dtype=_F64):
+    return _wrap(torch.zeros(0, dtype=dtype))
+
+
+def empty_tensor_with(from_f64=None, shape=None):
+    return _apply(torch.zeros(_shape(shape) if shape is not None else [0], dtype=_F64), from_f64)
+
+
+def empty_like(x):
+    from .tensor import _raw
+    return _wrap(torch.empty_like(_raw(x)))
+
+
+def zeros_with_shape(shape, from_f64=None): return _apply(torch.zeros(_shape(shape), dtype=_F64), from_f64)    # noqa: E704
+def ones_with_shape(shape, from_f64=None): return _apply(torch.ones(_shape(shape), dtype=_F64), from_f64)      # noqa: E704
+def eye_with_shape(rows, cols, from_f64=None): return _apply(torch.eye(rows, cols, dtype=_F64), from_f64)      # noqa: E704
+
+
+def arange_with(start, f=None, stop=-1, step=1):
+    """``arange(start, stop, step)``; with ``stop`` left at -1 the range is ``[0, start)``."""
+    if stop == -1:
+        start, stop = 0, start
+    return _apply(torch.arange(start, stop, step), f)
+
+
+def linspace_list_f64(a: float, b: float, n: int, endpoint: bool = True):
+    if n <= 0:
+        return []
+    if n == 1:
+        return [float(a)]
+    step = (b - a) / (n - 1 if endpoint else n)
+    return [a + i * step for i in range(n)]
+
+
+def linspace_with(a, b, n, f=None, endpoint=True):
+    return _apply(torch.tensor(linspace_list_f64(a, b, n, endpoint), dtype=_F64), f)
+
+
+def linspace_Int(a, b, n, endpoint=True):
+    return _wrap(torch.tensor([int(v) for v in linspace_list_f64(a, b, n, endpoint)], dtype=_I64))
+
+
+def randu_with(shape, f=None, low=0.0, high=1.0, seed=None):
+    t = torch.rand(_shape(shape), generator=_gen(0 if seed is None else seed), dtype=_F64) * (high - low) + low
+    return _apply(t, f)
+
+
+rand_with_shape = randu_with
+
+
+def rand_like_with(x, f=None, low=0.0, high=1.0, seed=None):
+    return randu_with(list(x.shape), f, low, high, seed)
+
+
+def bernoulli_with(shape, p, f=None, seed=None):
+    t = (torch.rand(_shape(shape), generator=_gen(0 if seed is None else seed), dtype=_F64) < p).to(_I64)
+    return _apply(t, f)
+
+
+def randperm_with(n, f=None, seed=None):
+    return _apply(torch.randperm(n, generator=_gen(0 if seed is None else seed)), f)
+
+
+def normal_f32(shape, mean=0.0, std=1.0, seed: int = 0):
+    return normal(shape, mean, std, seed, _F32)
+
+
+def from_2d_list(xs, dtype=None):
+    return from_list(xs, dtype)
+
+
+def from_3d_list(xs, dtype=None):
+    return from_list(xs, dtype)
+
+
+def _u01(shape, seed):
+    return torch.rand(_shape(shape), generator=_gen(0 if seed is None else seed), dtype=_F64)
+
+
+def _mk_typed():
+    g = globals()
+
+    def family(dt):
+        wide = _F64 if dt.is_floating_point else _I64
+
+        def arange_(start, stop=None, step=1):
+            lo, hi = (0, start) if stop is None else (start, stop)
+            return _wrap(_cast(torch.arange(lo, hi, step, dtype=wide), dt))
+
+        def bernoulli_(shape, p=0.5, seed=0):
+            return _wrap(_cast((_u01(shape, seed) < p).to(_I64), dt))
+
+        def randperm_(n, seed=0):
+            return _wrap(_cast(torch.randperm(n, generator=_gen(seed)), dt))
+
+        def randu_(shape, low=0.0, high=1.0, seed=None):
+            return _wrap(_cast(_u01(shape, seed) * (high - low) + low, dt))
+
+        def rand_like_(x, low=0.0, high=1.0, seed=None):
+            return randu_(list(x.shape), low, high, seed)
+
+        def randn_like_(x, seed=0):
+            return _wrap(_cast(torch.randn(list(x.shape), generator=_gen(seed), dtype=_F64), dt))
+
+        return {"arange": arange_, "bernoulli": bernoulli_, "randperm": randperm_, "randu": randu_,
+                "rand_like": rand_like_, "randn_like": randn_like_}
+
+    for sfx, dt in _ALL_DT.items():
+        for base, fn in family(dt).items():
+            g.setdefault(f"{base}_{sfx}", fn)
+    for base in ("arange", "bernoulli", "rand_like", "randn_like"):
+        for sfx in ("f32", "f64", "int"):
+            g.setdefault(f"{base}_{sfx}_alias", g[f"{base}_{sfx}"])
+
+
+_mk_typed()

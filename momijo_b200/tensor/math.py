@@ -198,3 +198,9 @@ def complex(re, im):
 def complex_abs(z): return _wrap(_t(z).abs())
 def complex_real(z): return _wrap(_t(z).real)
 def complex_imag(z): return _wrap(_t(z).imag)
+
+
+# scalar shims, op-id dispatchers, logical and in-place ops (see math_compat for the op-id tables)
+from .math_compat import *  # noqa: F401,F403,E402
+from .math_compat import (expm1_32, log1p32, pow32, abs32, sqrt32, exp32, log32, sin32, cos32, tan32, tanh32,  # noqa: F401,E402
+                          floor32, ceil32, round32, sign32, sigmoid32, silu32, gelu32, elu32, selu32)
