@@ -225,3 +225,88 @@ def binary_cross_entropy(ctx, probs: GradTensor, target, eps=1e-12, weight=None,
             loss = loss * w
         return _reduce(loss, reduction)
     return probs._op(ctx, f)
+
+
+# ---- op tags, the struct-of-lists tape record and small helpers of the reference
+# (legacy/src/momijo/tensor/autograd.mojo:18-300, 2179-2200). Differentiation itself runs on torch autograd
+# (``GradTensor`` above); ``Tape`` keeps the reference's bookkeeping layout for code that inspects or builds
+# tapes directly, and the tag functions return the same numbers.
+_TAGS = {
+    "LEAF": 0, "ADD": 1, "MUL": 2, "ADDS": 3, "MULS": 4, "SUM_ALL": 5, "MEAN_ALL": 6, "RESHAPE": 7, "PERMUTE": 8,
+    "SUM_AX": 9, "MEAN_AX": 10, "NEG": 11, "SUB": 12, "DIVS": 13, "SQUARE": 14, "POWS": 15, "TRANSPOSE2D": 16,
+    "FLATTEN": 17, "MATMUL2D": 18, "MAXS": 19, "MINS": 20, "RELU": 21, "LRELU": 22, "REPEAT": 23, "GATHER": 24,
+    "INDEX_AXIS": 25, "TAKE": 26, "SCATTER": 27, "MASKED_SELECT": 28, "MASKED_SELECT_ELEM": 29, "DIV": 30,
+    "CLIP": 31, "CLAMP_DISABLED": 32, "CLAMP_DISA": 31, "TENSORDOT": 51, "SQRT": 60, "EXP": 61, "LOG": 62,
+    "TANH": 63, "SIGMOID": 64, "ABS": 65, "SIGN": 66, "FLOOR": 67, "CEIL": 68, "ROUND": 69, "LOG1P": 70,
+    "EXPM1": 71, "CLAMP": 72, "STD": 80, "WHERE": 90,
+}
+for _tag_name, _tag_id in _TAGS.items():
+    globals()[f"TAG_{_tag_name}"] = (lambda v: (lambda: v))(_tag_id)
+
+
+class Tape:
+    """values / grads / op_tags / parents / scalars / shapes / orders / axes / keep, one entry per node."""
+
+    def __init__(self):
+        self.values, self.grads, self.op_tags, self.parents = [], [], [], []
+        self.scalars, self.shapes, self.orders, self.axes, self.keep = [], [], [], [], []
+
+    def _push_common(self, val, op: int, p0: int = -1, p1: int = -1, s: float = 0.0, shp=(), ord=(), ax: int = -1,
+                     kd: bool = False) -> int:
+        v = _v(val)
+        self.values.append(v.clone())
+        self.grads.append(torch.zeros_like(v))
+        self.op_tags.append(op)
+        self.parents.append([p0, p1])
+        self.scalars.append(s)
+        self.shapes.append(list(shp))
+        self.orders.append(list(ord))
+        self.axes.append(ax)
+        self.keep.append(kd)
+        return len(self.values) - 1
+
+    def add_leaf(self, x) -> int:
+        return self._push_common(x, 0)
+
+    def add_node(self, val, op: int, p0: int = -1, p1: int = -1, **kw) -> int:
+        return self._push_common(val, op, p0, p1, **kw)
+
+    def __len__(self):
+        return len(self.values)
+
+    def zero_grads(self):
+        for g in self.grads:
+            g.zero_()
+
+
+def needs_grad(flag_a: bool, flag_b: bool = False) -> bool:
+    return bool(flag_a or flag_b)
+
+
+def shape_like(x):
+    return list(_v(x).shape)
+
+
+def broadcast_to_shape(x, shape):
+    from .tensor import _wrap
+    t = _v(x)
+    return _wrap(t.clone() if list(t.shape) == list(shape) else t.expand(list(shape)).clone())
+
+
+def no_grad_do(ctx: GradContext, f) -> None:
+    """Run ``f()`` with gradient tracking off, restoring it afterwards even if ``f`` raises."""
+    no_grad_begin(ctx)
+    try:
+        f()
+    finally:
+        no_grad_end(ctx)
+
+
+def _mask_out(t):
+    from .tensor import _wrap
+    return _wrap(t.to(torch.int64))
+
+
+def mask_not(mask): return _mask_out(_v(mask) == 0)                                   # noqa: E704
+def mask_and(a, b): return _mask_out((_v(a) != 0) & (_v(b) != 0))                     # noqa: E704
+def mask_or(a, b): return _mask_out((_v(a) != 0) | (_v(b) != 0))                      # noqa: E704

@@ -118,3 +118,27 @@ def dispatch_binary_f32(ctx, cpu_impl, gpu_impl, a, b):
 
 dispatch_unary_f64 = dispatch_unary_i = dispatch_unary_f32
 dispatch_binary_f64 = dispatch_binary_i = dispatch_binary_f32
+
+
+# ---- context helpers of the reference (legacy/src/momijo/tensor/device.mojo:104-350) ----------------------------------
+def resolve_device(ctx=None) -> Device:
+    return Device.cpu() if ctx is None else ctx.current()
+
+
+def get_device_name(ctx=None) -> str:
+    return str(resolve_effective_device(resolve_device(ctx)))
+
+
+def set_device_cpu(ctx: RuntimeDeviceContext) -> RuntimeDeviceContext:
+    ctx.set_device(Device.cpu())
+    return ctx
+
+
+def set_device_gpu(ctx: RuntimeDeviceContext) -> RuntimeDeviceContext:
+    """Falls back to the CPU when no GPU is present, like every device request."""
+    ctx.set_device(Device.gpu())
+    return ctx
+
+
+def zeros_i(shape, ctx=None): return _fill(shape, 0, torch.int64, ctx)      # noqa: E704
+def ones_i(shape, ctx=None): return _fill(shape, 1, torch.int64, ctx)       # noqa: E704

@@ -109,3 +109,94 @@ def raise_or(status: Status, fallback):
     if _LENIENT["on"]:
         return fallback
     raise TensorError(status.kind, status.msg)
+
+
+# ---- assert-free checks and constructors of the reference (legacy/src/momijo/tensor/errors.mojo:96-295) ---------------
+# The boolean checks print ``ERROR: ...`` and return False instead of raising; the ``*_status`` forms return a
+# ``Status``.
+def OkStatus() -> Status:
+    return Status.success()
+
+
+def ErrStatus(kind, message: str = "", where_: str = "") -> Status:
+    return Status.fail(kind, f"{message} ({where_})" if where_ else message)
+
+
+def _err(kind, msg, where_):
+    return TensorError(kind, f"{msg} ({where_})" if where_ else msg)
+
+
+def err_invalid_arg(msg: str, where_: str = ""): return _err(ErrorKind.VALUE, msg, where_)          # noqa: E704
+def err_shape_mismatch(msg: str, where_: str = ""): return _err(ErrorKind.SHAPE, msg, where_)       # noqa: E704
+def err_dtype_mismatch(msg: str, where_: str = ""): return _err(ErrorKind.DTYPE, msg, where_)       # noqa: E704
+def err_not_contiguous(msg: str, where_: str = ""): return _err(ErrorKind.VALUE, msg, where_)       # noqa: E704
+def err_out_of_bounds(msg: str, where_: str = ""): return _err(ErrorKind.INDEX, msg, where_)        # noqa: E704
+def err_not_implemented(msg: str, where_: str = ""): return _err(ErrorKind.VALUE, msg, where_)      # noqa: E704
+
+
+def fail(msg: str) -> None:
+    print("ERROR: " + msg)
+
+
+def require(cond: bool, msg: str) -> bool:
+    if not cond:
+        fail(msg)
+        return False
+    return True
+
+
+class ErrorList:
+    def __init__(self):
+        self.items = []
+
+    def push(self, e) -> None:
+        self.items.append(e)
+
+    def any(self) -> bool:
+        return len(self.items) > 0
+
+    def clear(self) -> None:
+        self.items = []
+
+    def __len__(self):
+        return len(self.items)
+
+    def join_messages(self) -> str:
+        return "; ".join(str(e) for e in self.items)
+
+
+def check_equal_len(a: int, b: int, what: str) -> bool:
+    return require(a == b, f"{what}: length mismatch {a} vs {b}")
+
+
+def check_product(shape, expected: int, what: str = "shape product") -> bool:
+    n = 1
+    for d in shape:
+        n *= d
+    return require(n == expected, f"{what}: {n} != {expected}")
+
+
+def check_non_empty(n: int, what: str = "length") -> bool:
+    return require(n > 0, f"{what} must be non-empty")
+
+
+def check_positive(x: int, what: str) -> bool:
+    return require(x > 0, f"{what} must be positive")
+
+
+def check_broadcastable_like(a, b, ctx: str = "broadcast") -> bool:
+    return require(check_broadcastable(list(a), list(b)).ok, f"{ctx}: shapes {list(a)} and {list(b)} do not broadcast")
+
+
+def check_axis_status(axis: int, ndim: int, ctx: str = "axis") -> Status:
+    ok = -ndim <= axis < ndim
+    return OkStatus() if ok else ErrStatus(ErrorKind.AXIS, ctx, "check_axis")
+
+
+def check_same_shape_status(a, b, what: str = "shape") -> Status:
+    return OkStatus() if list(a) == list(b) else ErrStatus(ErrorKind.SHAPE, what, "check_same_shape")
+
+
+def check_broadcastable_status(a, b, ctx: str = "broadcast") -> Status:
+    return OkStatus() if check_broadcastable(list(a), list(b)).ok else ErrStatus(ErrorKind.BROADCAST, ctx,
+                                                                                  "check_broadcastable")

@@ -118,3 +118,85 @@ def atomic_add_f32(buf, index, value):
     """A real atomic accumulate (the reference's helper is a plain add, runtime.mojo:209-211)."""
     buf.index_put_((torch.as_tensor([index], device=buf.device),), torch.as_tensor([value], dtype=buf.dtype, device=buf.device), accumulate=True)
     return buf
+
+
+# ---- host forms of the reference's remaining kernels (legacy/src/momijo/tensor/gpu/runtime.mojo:202, 328, 1124-1330,
+# 1328-1930). They take Python lists (the reference's CPU fallbacks do as well) or tensors and are the
+# oracles of the CUDA kernels above: ``launch_adam_1d_gpu`` and ``launch_pack_nchw`` do the same work on device.
+def memset_f32(buf, value: float) -> None:
+    if hasattr(buf, "fill_"):
+        buf.fill_(value)
+    else:
+        for i in range(len(buf)):
+            buf[i] = value
+
+
+def sqrt32(x: float) -> float:
+    """sqrtf: exact square root rounded to float32 (the reference iterates Newton steps; the fused AdamW
+    kernel uses the exact instruction)."""
+    import math
+    import struct
+    return 0.0 if x <= 0.0 else struct.unpack("<f", struct.pack("<f", math.sqrt(x)))[0]
+
+
+def adam_update_kernel(w, g, m, v, n: int, lr, beta1, beta2, eps, weight_decay, bc1, bc2) -> None:
+    """One Adam step over the first ``n`` elements, in place: m and v are exponential averages of g and g^2,
+    the bias-corrected ratio m/bc1 / (sqrt(v/bc2) + eps) is scaled by lr, and a non-zero weight decay is applied
+    to the weight first (decoupled)."""
+    for i in range(n):
+        wi, gi = w[i], g[i]
+        mi = beta1 * m[i] + (1.0 - beta1) * gi
+        vi = beta2 * v[i] + (1.0 - beta2) * gi * gi
+        step = (mi / bc1) / (sqrt32(vi / bc2) + eps)
+        if weight_decay != 0.0:
+            wi = wi - lr * weight_decay * wi
+        w[i], m[i], v[i] = wi - lr * step, mi, vi
+
+
+def launch_adam_1d_cpu(w, g, m, v, lr, beta1, beta2, eps, weight_decay, bc1, bc2, block_size_hint: int = 256) -> None:
+    adam_update_kernel(w, g, m, v, len(w), lr, beta1, beta2, eps, weight_decay, bc1, bc2)
+
+
+def k_hw_to_chw1(tid: int, src, dst, H: int, W: int) -> None:
+    if tid < H * W:
+        dst[tid] = src[tid]
+
+
+k_hwc1_to_chw1 = k_hw_to_chw1
+
+
+def k_hw_to_nchw0(tid: int, src, dst, H: int, W: int, dst_base: int) -> None:
+    if tid < H * W:
+        dst[dst_base + tid] = src[tid]
+
+
+k_hwc1_to_nchw0 = k_hw_to_nchw0
+
+
+def k_chw_copy(tid: int, src, dst, C: int, H: int, W: int, dst_base: int) -> None:
+    if tid < C * H * W:
+        dst[dst_base + tid] = src[tid]
+
+
+def launch_1d_maxpool_bw(total_threads, block_size, kernel, x, gy, dx, N, C, H, W, OH, OW, kH, kW, sH, sW, pH, pW):
+    """Max-pool backward over flat NCHW lists: every output gradient goes to the first maximum of its window.
+    ``kernel`` (the reference's per-thread function) may be None; when given it is called per output element
+    as ``kernel(tid, x, gy, dx, N, C, H, W, OH, OW, kH, kW, sH, sW, pH, pW)``."""
+    if total_threads <= 0:
+        return
+    for tid in range(min(total_threads, N * C * OH * OW)):
+        if kernel is not None:
+            kernel(tid, x, gy, dx, N, C, H, W, OH, OW, kH, kW, sH, sW, pH, pW)
+            continue
+        ow, oh = tid % OW, (tid // OW) % OH
+        nc = tid // (OW * OH)
+        best, arg = None, -1
+        for kh in range(kH):
+            for kw in range(kW):
+                ih, iw = oh * sH - pH + kh, ow * sW - pW + kw
+                if 0 <= ih < H and 0 <= iw < W:
+                    idx = (nc * H + ih) * W + iw
+                    if best is None or x[idx] > best:
+                        best, arg = x[idx], idx
+        if arg >= 0:
+            dx[arg] += gy[tid]

@@ -127,3 +127,102 @@ def save_npy(path, x):
 
 def load_npy(path):
     return _wrap(torch.from_numpy(np.load(path)))
+
+
+# ---- converter-parameterised text forms (legacy/src/momijo/tensor/io.mojo:247-680). ``from_f64`` / ``to_f64`` are
+# the element converters of the reference's generic functions; any callable (or None) works here.
+def _conv_in(vals, from_f64):
+    return [from_f64(float(v)) for v in vals] if from_f64 is not None else [float(v) for v in vals]
+
+
+def _conv_out(x, to_f64):
+    r = _raw(x).cpu()
+    flat = r.reshape(-1).tolist()
+    return r, ([to_f64(v) for v in flat] if to_f64 is not None else [float(v) for v in flat])
+
+
+def csv_to_tensor_with(text: str, from_f64=None, opts: CsvOptions = None):
+    """Rows of delimiter-separated numbers -> 2-D tensor (ragged rows are padded with zeros)."""
+    opts = opts or CsvOptions()
+    lines = [l.strip() for l in text.splitlines() if l.strip()]
+    if opts.has_header and lines:
+        lines = lines[1:]
+    rows = [_conv_in([c for c in l.split(opts.delimiter) if c.strip() != ""], from_f64) for l in lines]
+    width = max((len(r) for r in rows), default=0)
+    rows = [r + [0] * (width - len(r)) for r in rows]
+    return _wrap(torch.tensor(rows) if rows else torch.zeros(0, 0))
+
+
+def tensor_to_csv(x, to_f64=None, delim: str = ",", header=None) -> str:
+    r, flat = _conv_out(x, to_f64)
+    cols = r.shape[-1] if r.dim() >= 1 else 1
+    rows = [flat[i:i + cols] for i in range(0, len(flat), max(cols, 1))]
+    out = [delim.join(header)] if header else []
+    out += [delim.join(repr(v) for v in row) for row in rows]
+    return "\n".join(out) + ("\n" if out else "")
+
+
+def json_numbers_to_tensor_with(text: str, from_f64=None):
+    """A JSON array of numbers (nested arrays give the shape)."""
+    try:
+        data = json.loads(text)
+    except ValueError:
+        return _wrap(torch.zeros(0))
+    t = torch.tensor(data, dtype=torch.float64)
+    return _wrap(torch.tensor(_conv_in(t.reshape(-1).tolist(), from_f64)).reshape(t.shape))
+
+
+def tensor_to_json_array(x, to_f64=None, pretty: bool = True) -> str:
+    r, flat = _conv_out(x, to_f64)
+    nested = torch.tensor(flat, dtype=torch.float64).reshape(r.shape).tolist() if flat else []
+    return json.dumps(nested, indent=2 if pretty else None)
+
+
+def xml_numbers_to_tensor_with(text: str, from_f64=None, row_tag: str = "row", item_tag: str = "v"):
+    rows = re.findall(rf"<{row_tag}[^>]*>(.*?)</{row_tag}>", text, re.S)
+    if not rows:
+        rows = [text]
+    data = [_conv_in(re.findall(rf"<{item_tag}[^>]*>\s*([^<\s]+)\s*</{item_tag}>", r), from_f64) for r in rows]
+    width = max((len(r) for r in data), default=0)
+    data = [r + [0] * (width - len(r)) for r in data]
+    return _wrap(torch.tensor(data) if data and width else torch.zeros(0, 0))
+
+
+def tensor_to_xml_numbers(x, to_f64=None, root_tag: str = "tensor", row_tag: str = "row", item_tag: str = "v") -> str:
+    r, flat = _conv_out(x, to_f64)
+    cols = r.shape[-1] if r.dim() >= 1 else 1
+    rows = [flat[i:i + cols] for i in range(0, len(flat), max(cols, 1))]
+    body = "".join(f"<{row_tag}>" + "".join(f"<{item_tag}>{v!r}</{item_tag}>" for v in row) + f"</{row_tag}>"
+                   for row in rows)
+    return f"<{root_tag}>{body}</{root_tag}>"
+
+
+def _read(path: str) -> str:
+    try:
+        with open(path) as f:
+            return f.read()
+    except OSError:
+        return ""
+
+
+def _write(path: str, text: str) -> bool:
+    try:
+        with open(path, "w") as f:
+            f.write(text)
+        return True
+    except OSError:
+        return False
+
+
+def read_csv_with(path, from_f64=None, opts: CsvOptions = None): return csv_to_tensor_with(_read(path), from_f64, opts)   # noqa: E704,E501
+def write_csv(x, to_f64, path, delim=",", header=None): return _write(path, tensor_to_csv(x, to_f64, delim, header))     # noqa: E704,E501
+def read_json_numbers_with(path, from_f64=None): return json_numbers_to_tensor_with(_read(path), from_f64)              # noqa: E704,E501
+def write_json_numbers(x, to_f64, path, pretty=True): return _write(path, tensor_to_json_array(x, to_f64, pretty))      # noqa: E704,E501
+
+
+def read_xml_numbers_with(path, from_f64=None, row_tag="row", item_tag="v"):
+    return xml_numbers_to_tensor_with(_read(path), from_f64, row_tag, item_tag)
+
+
+def write_xml_numbers(x, to_f64, path, root_tag="tensor", row_tag="row", item_tag="v"):
+    return _write(path, tensor_to_xml_numbers(x, to_f64, root_tag, row_tag, item_tag))

@@ -52,3 +52,40 @@ def safe_log(x, eps=1e-12):
 
 def safe_sqrt(x):
     return _wrap(torch.sqrt(_raw(x).double().clamp_min(0.0)))
+
+
+# ---- scalar and float64-specialised names (legacy/src/momijo/tensor/nanops.mojo:111-655) -----------------------------
+import math as _math  # noqa: E402
+
+
+def isnan_f64(v: float) -> bool: return v != v                          # noqa: E704
+def isinf_f64(v: float) -> bool: return v in (_math.inf, -_math.inf)    # noqa: E704
+def isfinite_f64(v: float) -> bool: return v == v and not isinf_f64(v)  # noqa: E704
+
+
+def nan_to_num_f64(v: float, nan: float = 0.0, posinf: float = 1.7976931348623157e308,
+                   neginf: float = -1.7976931348623157e308) -> float:
+    return nan if v != v else (posinf if v == _math.inf else (neginf if v == -_math.inf else v))
+
+
+def safe_log_scalar(x: float, eps: float = 1e-12) -> float:
+    return _math.log(x if x > eps else eps)
+
+
+def safe_sqrt_scalar(x: float) -> float:
+    return _math.sqrt(x) if x > 0 else 0.0
+
+
+def nansum_all_f64(x) -> float: return float(torch.nansum(_raw(x).double()))            # noqa: E704
+def nanmean_all_f64(x) -> float: return float(torch.nanmean(_raw(x).double()))          # noqa: E704
+
+
+def nanmin_all_f64(x) -> float:
+    r = _raw(x).double().reshape(-1)
+    r = r[~torch.isnan(r)]
+    return float(r.min()) if r.numel() else float("nan")
+
+
+def nansum_axis_contig_f64(x, axis: int = -1): return nansum(x, axis)       # noqa: E704
+def nanmean_axis_contig_f64(x, axis: int = -1): return nanmean(x, axis)     # noqa: E704
+def nanmin_axis_contig_f64(x, axis: int = -1): return nanmin(x, axis)       # noqa: E704

@@ -34,3 +34,18 @@ def tensor_to_string(t) -> str:
     dt = str(r.dtype).replace("torch.", "")
     body = _nd(r.detach().cpu().tolist() if r.dtype != torch.bfloat16 else r.detach().float().cpu().tolist())
     return f"Tensor(shape={list(r.shape)}, dtype={dt}, data={body})"
+
+
+# names of the reference (legacy/src/momijo/tensor/printing.mojo:13-61)
+def to_string_list(xs) -> str: return list_to_string(xs)          # noqa: E704
+def to_string_dict(d) -> str: return dict_to_string(d)            # noqa: E704
+def to_string_tensor(t) -> str: return tensor_to_string(t)        # noqa: E704
+
+
+to_string_inttensor = to_string_tensor
+
+
+def ravel(x) -> list:
+    """Flat Python list of a tensor's elements (row-major)."""
+    from .tensor import _raw
+    return _raw(x).reshape(-1).tolist()

@@ -561,3 +561,37 @@ def __getattr__(name):
         free.__name__ = name
         return free
     raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+
+
+# ---- selector records and storage sharing (legacy/src/momijo/tensor/tensor.mojo:635-790) -----------------------------
+class StrIndex:
+    """A textual index such as ``"1:3, ::2"``; ``S(spec)`` turns the same text into slice keys."""
+
+    def __init__(self, spec: str):
+        self.spec = spec
+
+    def keys(self):
+        return S(self.spec)
+
+
+class EllipsisSpec:
+    """Stands for ``...`` in a list of selectors."""
+
+
+def make_fancy_sel(js):
+    from .helpers import IndexSel
+    return IndexSel(fancy=list(js))
+
+
+def clone_sel(x):
+    """Independent copy of a selector (its index list is copied, not aliased)."""
+    from .helpers import IndexSel, SliceSpec
+    sl = SliceSpec(x.slice.start, x.slice.stop, x.slice.step) if x.slice is not None else None
+    return IndexSel(x.index, sl, list(x.fancy) if x.fancy is not None else None)
+
+
+def share(data, shape, strides, offset: int = 0):
+    """Tensor over existing storage (a torch tensor, or a list that is copied once) with explicit shape, element
+    strides and offset; no element is copied when ``data`` is a tensor."""
+    base = _raw(data) if isinstance(data, (torch.Tensor, Tensor)) else torch.tensor(list(data))
+    return _wrap(torch.as_strided(base.reshape(-1), list(shape), list(strides), offset))

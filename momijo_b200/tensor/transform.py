@@ -189,3 +189,182 @@ def chunk(x, n: int, axis: int = 0):
 
 def unbind(x, axis: int = 0):
     return [_wrap(v) for v in torch.unbind(_raw(x), axis)]
+
+
+# ---- further transform names of the reference (legacy/src/momijo/tensor/transform.mojo:49-2850) ---------------------
+def reflect_index(i: int, n: int) -> int:
+    """Mirror without repeating the edge sample: ... 2 1 | 0 1 2 ... n-1 | n-2 ..."""
+    if n <= 1:
+        return 0
+    period = 2 * n - 2
+    ii = i % period
+    return ii if ii < n else period - ii
+
+
+def symmetric_index(i: int, n: int) -> int:
+    """Mirror repeating the edge sample: ... 1 0 | 0 1 ... n-1 | n-1 n-2 ..."""
+    if n <= 1:
+        return 0
+    ii = (-i - 1 if i < 0 else i) % (2 * n)
+    return ii if ii < n else 2 * n - 1 - ii
+
+
+def replicate_index(i: int, n: int) -> int:
+    return 0 if n <= 0 else min(max(i, 0), n - 1)
+
+
+def circular_index(i: int, n: int) -> int:
+    return 0 if n <= 0 else i % n
+
+
+def pad_map_index(i: int, n: int, mode: int) -> int:
+    """mode: 0 replicate, 1 reflect, 2 symmetric, 3 circular."""
+    return [replicate_index, reflect_index, symmetric_index, circular_index][mode if 0 <= mode <= 3 else 0](i, n)
+
+
+def pad_nd(x, pad_pairs, constant=0):
+    """Constant padding with one (before, after) pair per axis, first axis first."""
+    return pad(x, [tuple(p) for p in pad_pairs], "constant", constant)
+
+
+pad_nd_flat = pad_nd
+
+
+def pad_nd_map(x, pad_pairs, mode: int):
+    """Index-mapped padding (``pad_map_index`` modes) with one (before, after) pair per axis."""
+    return pad(x, [tuple(p) for p in pad_pairs], ["replicate", "reflect", "symmetric", "circular"][mode])
+
+
+def pad1d(x, left: int, right: int, constant=0):
+    return pad_nd(x, [(max(left, 0), max(right, 0))], constant)
+
+
+def pad2d(x, top: int, bottom: int, left: int, right: int, constant=0):
+    return pad_nd(x, [(max(top, 0), max(bottom, 0)), (max(left, 0), max(right, 0))], constant)
+
+
+def pad_constant(x, pads, constant=0):
+    """``pads`` = [before_0, after_0, before_1, after_1, ...]; a list of the wrong length returns a copy."""
+    r = _raw(x)
+    if len(pads) != 2 * r.dim():
+        return _wrap(r.clone())
+    return pad_nd(x, [(pads[2 * i], pads[2 * i + 1]) for i in range(r.dim())], constant)
+
+
+def pad_dispatch(x, pads, mode: str = "constant", value=0):
+    r = _raw(x)
+    if len(pads) != 2 * r.dim():
+        return _wrap(r.clone())
+    pairs = [(pads[2 * i], pads[2 * i + 1]) for i in range(r.dim())]
+    return pad(x, pairs, mode, value)
+
+
+def expand_as(x, other):
+    return expand(x, list(_raw(other).shape))
+
+
+tensor_expand = expand
+
+
+def flip2d_axis(x, axis: int):
+    r = _raw(x)
+    return _wrap(r.clone() if r.dim() != 2 else torch.flip(r, [axis]))
+
+
+def sliding_window_core(x, win: int, step: int = 1):
+    """[n_windows, win] windows of a 1-D tensor; other ranks come back as a copy."""
+    r = _raw(x)
+    if r.dim() != 1 or win <= 0 or step <= 0 or r.shape[0] < win:
+        return _wrap(r.clone())
+    return _wrap(r.unfold(0, win, step).clone())
+
+
+def ravel(x):
+    return flatten(x)
+
+
+def size(x) -> int:
+    return _raw(x).numel()
+
+
+def squeeze_all(x):
+    return _wrap(_raw(x).squeeze())
+
+
+tensor_squeeze = squeeze_all
+
+
+def squeeze_axis(x, axis: int):
+    r = _raw(x)
+    a = axis + r.dim() if axis < 0 else axis
+    return _wrap(r.squeeze(a) if 0 <= a < r.dim() and r.shape[a] == 1 else r)
+
+
+def tensor_expand_dims(t, axis: int):
+    r = _raw(t)
+    a = axis + r.dim() + 1 if axis < 0 else axis
+    return _wrap(r.unsqueeze(min(max(a, 0), r.dim())))
+
+
+def tensor_flatten_view(x):
+    r = _raw(x)
+    return _wrap(r.view(-1) if r.is_contiguous() else r.reshape(-1))
+
+
+def tensor_as_strided(x, size_, stride, storage_offset: int = 0):
+    return as_strided(x, size_, stride, storage_offset)
+
+
+def tensor_permute(x, axes):
+    return permute(x, axes)
+
+
+def is_identity_perm(perm) -> bool:
+    return list(perm) == list(range(len(perm)))
+
+
+def is_row_major(shape, strides) -> bool:
+    acc, exp = 1, []
+    for d in reversed(list(shape)):
+        exp.append(acc)
+        acc *= d
+    return list(reversed(exp)) == list(strides)
+
+
+is_row_major_full = is_row_major
+
+
+def is_contig2d_rowmajor(shape, strides) -> bool:
+    return len(shape) == 2 and is_row_major(shape, strides)
+
+
+def is_contig3d_lastdim(shape, strides) -> bool:
+    """Rank >= 3 with a unit stride on the last axis and a full row pitch on the one before it."""
+    return len(shape) >= 3 and len(strides) >= 3 and strides[-1] == 1 and strides[-2] == shape[-1]
+
+
+def is_contig4d_spatial_last(shape, strides) -> bool:
+    return len(shape) == 4 and is_contig3d_lastdim(shape, strides)
+
+
+def view_reshape_strides_if_contiguous(old_shape, new_shape):
+    """(ok, row-major strides of ``new_shape``) when the element counts agree."""
+    n_old = n_new = 1
+    for d in old_shape:
+        n_old *= d
+    for d in new_shape:
+        n_new *= d
+    if n_old != n_new:
+        return False, []
+    acc, st = 1, []
+    for d in reversed(list(new_shape)):
+        st.append(acc)
+        acc *= d
+    return True, list(reversed(st))
+
+
+def transpose2d_auto(x):
+    return transpose2d(x)
+
+
+transpose2d_cpu_parallel = transpose2d_gpu = transpose2d_auto
