@@ -36,4 +36,5 @@ from .broadcast import broadcast_to, matmul, broadcast_shapes, tensordot, clip, 
 from .autograd import GradContext, GradTensor, no_grad_begin, no_grad_end, stop_gradient  # noqa: F401
 from .device import Device, RuntimeDeviceContext, ScopedDevice, to_device, device_of, gpu_available  # noqa: F401
 from .tensor_dyn import AnyTensor, AnyBuffer, TensorView  # noqa: F401
+from . import tensor_methods  # noqa: F401  (binds the method spellings onto Tensor)
 from . import nanops, printing, helpers, math, indexing, transform, axis, io, cast, creation, broadcast, autograd, device, errors, dtype  # noqa: F401

@@ -39,11 +39,11 @@ def no_grad_end(ctx: GradContext):
 
 
 def stop_gradient(ctx: GradContext, x: "GradTensor") -> "GradTensor":
-    return ctx._track(x.value.detach(), False)
+    return ctx._track(x._val.detach(), False)
 
 
 def _v(x):
-    return x.value if isinstance(x, GradTensor) else (_raw(x) if isinstance(x, torch.Tensor) else x)
+    return x._val if isinstance(x, GradTensor) else (_raw(x) if isinstance(x, torch.Tensor) else x)
 
 
 def _rg(*xs):
@@ -54,7 +54,7 @@ class GradTensor:
     """``(id, requires_grad)`` handle; the value lives on the context's tape."""
 
     def __init__(self, id: int, requires_grad: bool, value: torch.Tensor):
-        self.id, self.requires_grad, self.value = id, requires_grad, value
+        self.id, self.requires_grad, self._val = id, requires_grad, value
 
     @staticmethod
     def from_tensor(ctx: GradContext, t, requires_grad: bool = False) -> "GradTensor":
@@ -65,27 +65,85 @@ class GradTensor:
         return ctx._track(v, rg)
 
     def tensor(self, ctx: GradContext = None):
-        return _wrap(self.value.detach())
+        return _wrap(self._val.detach())
 
     def grad(self, ctx: GradContext = None):
-        g = self.value.grad
-        return _wrap(g if g is not None else torch.zeros_like(self.value))
+        g = self._val.grad
+        return _wrap(g if g is not None else torch.zeros_like(self._val))
+
+    # ---- read-only accessors (legacy/src/momijo/tensor/autograd.mojo:320-365, 1079-1105) -------------------
+    @staticmethod
+    def from_randn(ctx: GradContext, shape, requires_grad: bool = False) -> "GradTensor":
+        return GradTensor.from_tensor(ctx, torch.randn(list(shape)), requires_grad)
+
+    @staticmethod
+    def has_matmul2d() -> bool:
+        return True
+
+    def value(self, ctx: GradContext = None):
+        return _wrap(self._val.detach().clone())
+
+    def shape(self, ctx: GradContext = None):
+        return list(self._val.shape)
+
+    def numel(self, ctx: GradContext = None) -> int:
+        return self._val.numel()
+
+    def item(self, ctx: GradContext = None) -> float:
+        return float(self._val.detach().reshape(-1)[0])
+
+    def at_flat(self, ctx: GradContext, i: int) -> float:
+        return float(self._val.detach().reshape(-1)[i])
+
+    def to_list(self, ctx: GradContext = None):
+        return self._val.detach().reshape(-1).tolist()
+
+    def to_string(self, ctx: GradContext = None) -> str:
+        return str(_wrap(self._val.detach()))
+
+    def to_Float32(self, ctx: GradContext = None) -> "GradTensor":
+        return self
+
+    def to_int_value(self, ctx: GradContext = None):
+        return _wrap(self._val.detach().to(torch.int64))
+
+    def to_float32_value(self, ctx: GradContext = None):
+        return _wrap(self._val.detach().to(torch.float32))
+
+    def _cmp_scalar(self, ctx, fn, s):
+        """Comparison masks are 0/1 floats on a fresh untracked node (autograd.mojo:1291-1340)."""
+        return ctx._track(fn(self._val.detach(), s).to(torch.float32), False)
+
+    def eq_scalar(self, ctx, s): return self._cmp_scalar(ctx, torch.eq, s)
+    def ne_scalar(self, ctx, s): return self._cmp_scalar(ctx, torch.ne, s)
+    def lt_scalar(self, ctx, s): return self._cmp_scalar(ctx, torch.lt, s)
+    def le_scalar(self, ctx, s): return self._cmp_scalar(ctx, torch.le, s)
+    def gt_scalar(self, ctx, s): return self._cmp_scalar(ctx, torch.gt, s)
+    def ge_scalar(self, ctx, s): return self._cmp_scalar(ctx, torch.ge, s)
+
+    def sum_axis(self, ctx, axis: int, keepdims: bool = False): return self.sum(ctx, axis, keepdims)
+    def mean_axis(self, ctx, axis: int, keepdims: bool = False): return self.mean(ctx, axis, keepdims)
+
+    def select(self, ctx, mask, other):
+        """``where(mask, self, other)`` (autograd.mojo:816-817)."""
+        m = _raw(mask).bool() if isinstance(mask, torch.Tensor) else torch.as_tensor(mask).bool()
+        return self._op(ctx, lambda a, b: torch.where(m, a, b), other)
 
     def backward(self, ctx: GradContext = None, grad=None):
         """Seeds ones (like the reference) and back-propagates once through every node."""
-        seed = torch.ones_like(self.value) if grad is None else _raw(grad)
+        seed = torch.ones_like(self._val) if grad is None else _raw(grad)
         for n in (ctx.nodes if ctx is not None else []):
-            if n.value.is_leaf and n.value.grad is not None:
-                n.value.grad = None
-        self.value.backward(seed)
+            if n._val.is_leaf and n._val.grad is not None:
+                n._val.grad = None
+        self._val.backward(seed)
 
     def _op(self, ctx, fn, *others):
         rg = _rg(self, *others) and ctx.grad_enabled()
         if rg:
-            out = fn(self.value, *[_v(o) for o in others])
+            out = fn(self._val, *[_v(o) for o in others])
         else:
             with torch.no_grad():
-                out = fn(self.value, *[_v(o) for o in others])
+                out = fn(self._val, *[_v(o) for o in others])
         return ctx._track(out, rg)
 
     # binary (tensor / GradTensor / scalar operands)
@@ -171,12 +229,12 @@ class GradTensor:
     clamp = clip
 
     # comparisons (no gradient)
-    def eq(self, ctx, o): return ctx._track((self.value == _v(o)).float(), False)
-    def ne(self, ctx, o): return ctx._track((self.value != _v(o)).float(), False)
-    def lt(self, ctx, o): return ctx._track((self.value < _v(o)).float(), False)
-    def le(self, ctx, o): return ctx._track((self.value <= _v(o)).float(), False)
-    def gt(self, ctx, o): return ctx._track((self.value > _v(o)).float(), False)
-    def ge(self, ctx, o): return ctx._track((self.value >= _v(o)).float(), False)
+    def eq(self, ctx, o): return ctx._track((self._val == _v(o)).float(), False)
+    def ne(self, ctx, o): return ctx._track((self._val != _v(o)).float(), False)
+    def lt(self, ctx, o): return ctx._track((self._val < _v(o)).float(), False)
+    def le(self, ctx, o): return ctx._track((self._val <= _v(o)).float(), False)
+    def gt(self, ctx, o): return ctx._track((self._val > _v(o)).float(), False)
+    def ge(self, ctx, o): return ctx._track((self._val >= _v(o)).float(), False)
 
 
 def _reduce(x, reduction):
@@ -270,6 +328,12 @@ class Tape:
 
     def add_node(self, val, op: int, p0: int = -1, p1: int = -1, **kw) -> int:
         return self._push_common(val, op, p0, p1, **kw)
+
+    def add_unary(self, val, op: int, p: int, s: float = 0.0, shp=(), ord=(), ax: int = -1, kd: bool = False) -> int:
+        return self._push_common(val, op, p, -1, s, shp, ord, ax, kd)
+
+    def add_binary(self, val, op: int, p0: int, p1: int) -> int:
+        return self._push_common(val, op, p0, p1)
 
     def __len__(self):
         return len(self.values)

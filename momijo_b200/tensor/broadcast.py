@@ -84,7 +84,11 @@ def same_shape(a, b) -> bool:
     return list(a) == list(b)
 
 
-def can_broadcast_shapes(a, b) -> bool:
+def can_broadcast_shapes(a, b, strict: bool = False) -> bool:
+    """NumPy rule (right-aligned, missing axes count as 1); ``strict`` also wants equal rank
+    (legacy/src/momijo/tensor/broadcast.mojo:2012-2080)."""
+    if strict and len(a) != len(b):
+        return False
     pa, pb = align_right(a, b)
     return all(x == y or x == 1 or y == 1 for x, y in zip(pa, pb))
 

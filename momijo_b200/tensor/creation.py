@@ -26,10 +26,31 @@ class SplitMix64:
         z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & M
         return z ^ (z >> 31)
 
+    next = next_u64
+
 
 class RNG64(SplitMix64):
+    """SplitMix64 stream with float and bounded-integer draws (legacy/src/momijo/tensor/creation.mojo:78-126)."""
+
     def uniform(self) -> float:
         return (self.next_u64() >> 11) * (1.0 / 9007199254740992.0)
+
+    next_f64 = uniform
+
+    def next_f32(self) -> float:
+        return float(torch.tensor(self.uniform(), dtype=torch.float32))
+
+    def next_i32(self, low: int, high: int) -> int:
+        """Unbiased integer in [low, high): draws above the largest multiple of the span are rejected."""
+        span = high - low
+        if span <= 0:
+            return low
+        full = 0xFFFFFFFFFFFFFFFF
+        limit = full - (full % span)
+        u = self.next_u64()
+        while u >= limit:
+            u = self.next_u64()
+        return low + u % span
 
 
 def _shape(shape):

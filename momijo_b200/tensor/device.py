@@ -26,6 +26,9 @@ class Device:
     def is_gpu(self):
         return self.tag == 1
 
+    def is_cpu(self):
+        return self.tag == 0
+
     def torch_device(self):
         return torch.device("cuda", self.index) if self.tag == 1 else torch.device("cpu")
 
@@ -47,6 +50,27 @@ def resolve_effective_device(requested: Device) -> Device:
 class RuntimeDeviceContext:
     def __init__(self, device: Device | None = None):
         self.device = resolve_effective_device(device or Device.cpu())
+
+    # the reference's spellings (legacy/src/momijo/tensor/device.mojo:47-75)
+    @staticmethod
+    def cpu() -> "RuntimeDeviceContext":
+        return RuntimeDeviceContext(Device.cpu())
+
+    @staticmethod
+    def gpu() -> "RuntimeDeviceContext":
+        return RuntimeDeviceContext(Device.gpu())
+
+    def set_cpu(self) -> None:
+        self.device = Device.cpu()
+
+    def set_gpu(self) -> None:
+        self.device = resolve_effective_device(Device.gpu())
+
+    def get(self) -> Device:
+        return self.device
+
+    def __str__(self):
+        return f"RuntimeDeviceContext({self.device})"
 
     def set_device(self, d: Device):
         self.device = resolve_effective_device(d)

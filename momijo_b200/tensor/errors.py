@@ -7,19 +7,51 @@ from dataclasses import dataclass
 from typing import Any, Generic, TypeVar
 
 
-class ErrorKind:
-    OK, SHAPE, AXIS, BROADCAST, DTYPE, INDEX, VALUE, IO, DEVICE = range(9)
-    _names = ["ok", "shape", "axis", "broadcast", "dtype", "index", "value", "io", "device"]
+class ErrorKind(int):
+    """Error category with the reference's codes (legacy/src/momijo/tensor/errors.mojo:18-52). Instances are ints, so
+    they compare with plain codes; the upper-case aliases are the categories this package's own checks raise."""
+    _names = ["OK", "InvalidArgument", "ShapeMismatch", "DTypeMismatch", "DeviceUnavailable", "NotContiguous",
+              "OutOfBounds", "MemoryAllocation", "ArithmeticOverflow", "DivideByZero", "NotImplemented"]
+
+    @property
+    def code(self) -> int:
+        return int(self)
+
+    def ravel(self) -> str:
+        return self._names[int(self)] if 0 <= int(self) < len(self._names) else "Unknown"
+
+    __str__ = ravel
 
     @staticmethod
     def name(k: int) -> str:
-        return ErrorKind._names[k]
+        return ErrorKind(k).ravel()
+
+
+for _code, _name in enumerate(ErrorKind._names):
+    # Constants answer both as values (``ErrorKind.OK``) and, like the reference's static constructors, when called.
+    setattr(ErrorKind, _name, type("_Kind", (ErrorKind,), {"__call__": lambda self: ErrorKind(int(self))})(_code))
+ErrorKind.VALUE, ErrorKind.SHAPE, ErrorKind.DTYPE = ErrorKind.InvalidArgument, ErrorKind.ShapeMismatch, ErrorKind.DTypeMismatch
+ErrorKind.AXIS, ErrorKind.INDEX, ErrorKind.BROADCAST = ErrorKind.OutOfBounds, ErrorKind.OutOfBounds, ErrorKind.ShapeMismatch
+ErrorKind.IO, ErrorKind.DEVICE = ErrorKind.InvalidArgument, ErrorKind.DeviceUnavailable
 
 
 class TensorError(Exception):
-    def __init__(self, kind: int = ErrorKind.VALUE, msg: str = ""):
-        super().__init__(f"[{ErrorKind.name(kind)}] {msg}")
-        self.kind, self.msg = kind, msg
+    """kind / message / where (errors.mojo:56-74)."""
+
+    def __init__(self, kind: int = ErrorKind.VALUE, msg: str = "", where_: str = ""):
+        self.kind, self.msg, self.message, self.where_ = ErrorKind(int(kind)), msg, msg, where_
+        super().__init__(self.ravel())
+
+    def ok(self) -> bool:
+        return int(self.kind) == 0
+
+    def ravel(self) -> str:
+        s = "[" + self.kind.ravel() + "]"
+        if self.msg:
+            s += " " + self.msg
+        if self.where_:
+            s += " (at " + self.where_ + ")"
+        return s
 
 
 @dataclass
@@ -27,14 +59,33 @@ class Status:
     ok: bool = True
     kind: int = ErrorKind.OK
     msg: str = ""
+    where_: str = ""
 
     @staticmethod
     def success():
         return Status()
 
     @staticmethod
-    def fail(kind, msg=""):
-        return Status(False, kind, msg)
+    def fail(kind, msg="", where_=""):
+        return Status(False, kind, msg, where_)
+
+    def is_ok(self) -> bool:
+        return self.ok
+
+    def is_err(self) -> bool:
+        return not self.ok
+
+    def error(self) -> TensorError:
+        return TensorError(self.kind, self.msg, self.where_)
+
+    @property
+    def err(self) -> TensorError:
+        return self.error()
+
+    def ravel(self) -> str:
+        return "OK" if self.ok else self.error().ravel()
+
+    __str__ = ravel
 
 
 T = TypeVar("T")
@@ -48,18 +99,27 @@ class Result(Generic[T]):
     def is_ok(self):
         return self.status is None or self.status.ok
 
+    def is_err(self):
+        return not self.is_ok()
+
+    def error(self) -> TensorError:
+        return (self.status or Status()).error()
+
     def unwrap(self):
         if not self.is_ok():
-            raise TensorError(self.status.kind, self.status.msg)
+            raise self.status.error()
         return self.value
+
+    def unwrap_or(self, default_value):
+        return self.value if self.is_ok() else default_value
 
 
 def Ok(v):
     return Result(v, Status.success())
 
 
-def Err(kind, msg=""):
-    return Result(None, Status.fail(kind, msg))
+def Err(kind, msg="", where_=""):
+    return Result(None, Status.fail(kind, msg, where_))
 
 
 _LENIENT = {"on": False}
@@ -108,7 +168,7 @@ def raise_or(status: Status, fallback):
         return None
     if _LENIENT["on"]:
         return fallback
-    raise TensorError(status.kind, status.msg)
+    raise status.error()
 
 
 # ---- assert-free checks and constructors of the reference (legacy/src/momijo/tensor/errors.mojo:96-295) ---------------
@@ -119,19 +179,19 @@ def OkStatus() -> Status:
 
 
 def ErrStatus(kind, message: str = "", where_: str = "") -> Status:
-    return Status.fail(kind, f"{message} ({where_})" if where_ else message)
+    return Status.fail(kind, message, where_)
 
 
 def _err(kind, msg, where_):
-    return TensorError(kind, f"{msg} ({where_})" if where_ else msg)
+    return TensorError(kind, msg, where_)
 
 
 def err_invalid_arg(msg: str, where_: str = ""): return _err(ErrorKind.VALUE, msg, where_)          # noqa: E704
 def err_shape_mismatch(msg: str, where_: str = ""): return _err(ErrorKind.SHAPE, msg, where_)       # noqa: E704
 def err_dtype_mismatch(msg: str, where_: str = ""): return _err(ErrorKind.DTYPE, msg, where_)       # noqa: E704
-def err_not_contiguous(msg: str, where_: str = ""): return _err(ErrorKind.VALUE, msg, where_)       # noqa: E704
+def err_not_contiguous(msg: str, where_: str = ""): return _err(ErrorKind.NotContiguous, msg, where_)       # noqa: E704
 def err_out_of_bounds(msg: str, where_: str = ""): return _err(ErrorKind.INDEX, msg, where_)        # noqa: E704
-def err_not_implemented(msg: str, where_: str = ""): return _err(ErrorKind.VALUE, msg, where_)      # noqa: E704
+def err_not_implemented(msg: str, where_: str = ""): return _err(ErrorKind.NotImplemented, msg, where_)      # noqa: E704
 
 
 def fail(msg: str) -> None:

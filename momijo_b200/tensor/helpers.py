@@ -86,6 +86,8 @@ class XorShift64:
     def uniform(self) -> float:
         return (self.next_u64() >> 11) * (1.0 / 9007199254740992.0)
 
+    next_unit_f64 = uniform
+
 
 def sort_values(x, descending=False):
     return _wrap(torch.sort(_raw(x).reshape(-1), descending=descending, stable=True).values)

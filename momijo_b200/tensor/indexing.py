@@ -426,23 +426,84 @@ class Shape(list):
     def rank(self) -> int:
         return len(self)
 
+    ndim = rank
+
+    @property
+    def dims(self):
+        return list(self)
+
 
 class NDIter:
-    """Row-major iterator over the coordinates of a shape."""
+    """Row-major walk over the coordinates of a shape. Works as a Python iterable and through the reference's cursor
+    calls ``next`` / ``next_inplace`` / ``reset`` (legacy/src/momijo/tensor/indexing.mojo:123-196); a rank-0 shape
+    yields one empty coordinate."""
 
     def __init__(self, shape):
-        self.shape = list(shape)
+        self.shape = Shape(shape)
+        self.reset()
+
+    def reset(self) -> None:
+        self.idx = [0] * len(self.shape)
+        self.started = False
+        self.finished = any(d <= 0 for d in self.shape)
+
+    def next_inplace(self, out_idx: list) -> bool:
+        if self.finished:
+            return False
+        if not self.started:
+            self.started = True
+            if len(self.shape) == 0:
+                self.finished = True
+            out_idx[:] = self.idx
+            return True
+        for ax in range(len(self.shape) - 1, -1, -1):
+            self.idx[ax] += 1
+            if self.idx[ax] < self.shape[ax]:
+                out_idx[:] = self.idx
+                return True
+            self.idx[ax] = 0
+        self.finished = True
+        return False
+
+    def next(self):
+        out: list = []
+        ok = self.next_inplace(out)
+        return ok, out
 
     def __iter__(self):
-        import itertools
-        return (list(c) for c in itertools.product(*(range(d) for d in self.shape)))
+        it = NDIter(self.shape)
+        while True:
+            ok, c = it.next()
+            if not ok:
+                return
+            yield c
 
 
 class NDLinearIter:
-    """Row-major iterator yielding the linear offsets of a strided layout."""
+    """The same walk, also giving the linear offset of each coordinate in a strided layout
+    (indexing.mojo:198-270). Iterating yields the offsets."""
 
-    def __init__(self, shape, strides, offset: int = 0):
-        self.shape, self.strides, self.offset = list(shape), list(strides), offset
+    def __init__(self, shape, strides=None, offset: int = 0):
+        if strides is None or isinstance(strides, LayoutView):
+            view = strides
+            self.strides = list(view.strides) if view is not None else []
+            offset = view.offset if view is not None else 0
+        else:
+            self.strides = list(strides)
+        self.shape, self.offset = Shape(shape), offset
+        self._it = NDIter(self.shape)
+
+    def reset(self) -> None:
+        self._it.reset()
+
+    def next_inplace(self, out_idx: list):
+        ok = self._it.next_inplace(out_idx)
+        return ok, (ravel_index_with_offset(out_idx, self.strides, self.offset) if ok else 0)
+
+    def next(self):
+        out: list = []
+        ok, lin = self.next_inplace(out)
+        return ok, out, lin
 
     def __iter__(self):
         return (ravel_index_with_offset(c, self.strides, self.offset) for c in NDIter(self.shape))

@@ -187,6 +187,8 @@ class Complex128:
     def __sub__(self, o): return Complex128(self.re - o.re, self.im - o.im)
     def __mul__(self, o): return Complex128(self.re * o.re - self.im * o.im, self.re * o.im + self.im * o.re)
     def abs(self): return (self.re ** 2 + self.im ** 2) ** 0.5
+    def real(self): return self.re
+    def imag(self): return self.im
     def conj(self): return Complex128(self.re, -self.im)
     def __repr__(self): return f"({self.re}+{self.im}j)"
 

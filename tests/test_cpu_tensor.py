@@ -67,9 +67,9 @@ def test_autograd_compat_and_single_visit():
     lg = T.GradTensor.from_tensor(ctx2, T.from_2d_list_float32([[1.0, 2.0, 0.5], [0.1, 0.2, 3.0]]), True)
     loss = T.autograd.cross_entropy(ctx2, lg, T.from_list_int([1, 2]))
     ref = torch.nn.functional.cross_entropy(torch.tensor([[1.0, 2.0, 0.5], [0.1, 0.2, 3.0]]), torch.tensor([1, 2]))
-    assert abs(float(loss.value) - float(ref)) < 1e-6
+    assert abs(float(loss.value()) - float(ref)) < 1e-6
     b = T.autograd.bce_with_logits(ctx2, lg, T.zeros([2, 3]))
-    assert abs(float(b.value) - float(torch.nn.functional.binary_cross_entropy_with_logits(lg.value, torch.zeros(2, 3)))) < 1e-6
+    assert abs(float(b.value()) - float(torch.nn.functional.binary_cross_entropy_with_logits(lg.value(), torch.zeros(2, 3)))) < 1e-6
 
 
 def test_dtype_lattice():

@@ -92,3 +92,39 @@ def test_reductions_padding_io_tape(tmp_path):
     w, mm, vv = [1.0], [0.0], [0.0]
     R.launch_adam_1d_cpu(w, [0.1], mm, vv, 0.1, 0.9, 0.999, 1e-8, 0.0, 0.1, 0.001)
     assert abs(w[0] - 0.9) < 1e-6
+
+
+def test_tensor_method_spellings_and_cursors():
+    from momijo_b200.tensor import Tensor
+    from momijo_b200.tensor import device as D, dtype as DT
+    from momijo_b200.tensor.tensor_dyn import AnyBuffer, AnyTensor
+    x = from_list([[1, 2, 3], [4, 5, 6]])
+    assert x.select_copy([x.idx(1)]).tolist() == [4, 5, 6] and x.select_view([x.all_axis(), x.slc(0, 3, 2)]).tolist() == [[1, 3], [4, 6]]
+    x.select_set_scalar([x.idx(0), x.rng(1, 3)], 9)
+    assert x.tolist() == [[1, 9, 9], [4, 5, 6]] and x.slice([(0, 2, 1), (1, 3, 1)]).tolist() == [[9, 9], [5, 6]]
+    assert x.get2(1, 2) == 6 and x.len() == 2 and x.slice_inplace(1, 2, None, -1).tolist() == [[9, 9, 1], [6, 5, 4]]
+    b = Tensor([0.0])
+    b.append(1.0); b.append_list([2.0, 3.0]); b.append_repeat(7.0, 2); b.set_shape_row_major([2, 3])
+    assert b.tolist() == [[0.0, 1.0, 2.0], [3.0, 7.0, 7.0]]
+    assert x.not_bitwise().sum().item() == 0 and x.lshift_scalar(1).tolist()[1] == [8, 10, 12] and x.mod_scalar(4).tolist()[1] == [0, 1, 2]
+    assert x.set_xor(from_list([9, 100])).tolist() == [1, 4, 5, 6, 100] and x.can_broadcast_with(from_list([1, 2, 3])) and not x.can_broadcast_with(from_list([1, 2, 3]), True)
+    it = I.NDIter([2, 2])
+    assert it.next() == (True, [0, 0]) and it.next() == (True, [0, 1]) and list(I.NDIter([])) == [[]]
+    lin = I.NDLinearIter([2, 2], [2, 1], 1)
+    assert lin.next() == (True, [0, 0], 1) and lin.next() == (True, [0, 1], 2)
+    st = E.ErrStatus(E.ErrorKind.OutOfBounds(), "axis 3", "check_axis")
+    assert st.ravel() == "[OutOfBounds] axis 3 (at check_axis)" and st.is_err() and E.ErrorKind.SHAPE == 2
+    assert E.Err(E.ErrorKind.DivideByZero, "x").unwrap_or(5) == 5 and E.Ok(3).unwrap_or(5) == 3
+    ctx = A.GradContext()
+    g = A.GradTensor.from_tensor(ctx, from_list([1.0, -2.0]), True)
+    assert g.shape(ctx) == [2] and g.at_flat(ctx, 1) == -2.0 and g.gt_scalar(ctx, 0.0).to_list(ctx) == [1.0, 0.0]
+    assert g.select(ctx, from_list([1, 0]), g.mul(ctx, 2.0)).to_list(ctx) == [1.0, -4.0] and g.value(ctx).tolist() == [1.0, -2.0]
+    a = AnyTensor(from_list([1.5, 2.5]))
+    assert a.to_tensor_i32().tolist() == [1, 2]
+    a.full_like_dtype_shape(DT.from_name("int32"), [2], 3.9)
+    assert a.unwrap().tolist() == [3, 3]
+    buf = AnyBuffer()
+    buf.append_cast_from_f64(3.7, DT.from_name("int32").tag)
+    assert buf.length() == 1 and buf.get_f64(0) == 3.0
+    c = D.RuntimeDeviceContext.cpu()
+    assert c.get().is_cpu() and CR.RNG64(1).next_i32(3, 4) == 3
