@@ -14,7 +14,7 @@ class EarlyStopping:
 
     def reset(self):
         self.best = self.baseline if self.baseline is not None else (math.inf if self.mode == "min" else -math.inf)
-        self.best_epoch, self.wait, self.stopped, self.best_state = -1, 0, False, None
+        self.best_epoch, self.wait, self.stopped, self.best_state, self.stopped_epoch = -1, 0, False, None, -1
 
     def _improved(self, cur):
         return cur < self.best - self.min_delta if self.mode == "min" else cur > self.best + self.min_delta
@@ -28,7 +28,7 @@ class EarlyStopping:
         else:
             self.wait += 1
             if self.wait >= self.patience:
-                self.stopped = True
+                self.stopped, self.stopped_epoch = True, epoch
                 if self.verbose:
                     print(f"[EarlyStopping] stop at epoch {epoch}, best {self.best} @ {self.best_epoch}")
         return self.stopped
@@ -41,6 +41,47 @@ class EarlyStopping:
         if stop and self.restore_best_weights and self.best_state is not None:
             model.load_state_dict(self.best_state)
         return stop
+
+    # ---- configuration setters and weight capture (early_stopping.mojo:90-157, 230-237) ------------------
+    def set_mode(self, mode: str):
+        if mode in ("min", "max"):
+            self.mode = mode
+
+    def set_monitor(self, monitor: str):
+        self.monitor = monitor
+
+    def set_min_delta(self, v: float):
+        self.min_delta = v
+
+    def set_patience(self, v: int):
+        self.patience = v
+
+    def set_baseline(self, v=None):
+        self.baseline = v
+        self.best = v if v is not None else (math.inf if self.mode == "min" else -math.inf)
+
+    def set_restore_best_weights(self, flag: bool):
+        self.restore_best_weights = flag
+
+    def set_verbose(self, flag: bool):
+        self.verbose = flag
+
+    def capture_best(self, model):
+        if self.restore_best_weights:
+            self.best_state = copy.deepcopy(model.state_dict())
+
+    def restore_best(self, model):
+        if self.restore_best_weights and self.best_state is not None:
+            model.load_state_dict(self.best_state)
+
+    @property
+    def best_score(self):
+        return self.best
+
+    def summary(self) -> str:
+        return ("{ 'monitor': '%s', 'mode': '%s', 'patience': %d, 'min_delta': %s, 'best_score': %s, 'best_epoch': %d, "
+                "'stopped_epoch': %d }" % (self.monitor, self.mode, self.patience, self.min_delta, self.best,
+                                           self.best_epoch, self.stopped_epoch))
 
     def should_stop(self) -> bool:
         return self.stopped

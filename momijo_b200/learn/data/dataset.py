@@ -104,12 +104,57 @@ class Dataset:
     def __getitem__(self, i):
         return self.items[i]
 
-    def get(self, i):
+    _MISSING = object()
+
+    def get(self, i, default=_MISSING):
+        """``get(i)`` indexes; ``get(i, default)`` gives the default outside the range
+        (legacy/src/momijo/learn/data/dataset.mojo:94-100)."""
+        if default is not Dataset._MISSING and not 0 <= i < len(self.items):
+            return default
         return self.items[i]
 
     def append(self, x):
         self.items.append(x)
         return self
+
+    # ---- list surface of the reference (dataset.mojo:58-175) -------------------------------------------------
+    @staticmethod
+    def from_list(items) -> "Dataset":
+        return Dataset(items)
+
+    def with_items(self, items):
+        self.items = list(items)
+        return self
+
+    def is_empty(self) -> bool:
+        return len(self.items) == 0
+
+    def front(self):
+        return self.items[0] if len(self.items) else None
+
+    def back(self):
+        return self.items[-1] if len(self.items) else None
+
+    def set(self, idx: int, value) -> None:
+        if 0 <= idx < len(self.items):
+            self.items[idx] = value
+
+    def extend(self, values) -> None:
+        self.items.extend(values)
+
+    def insert(self, idx: int, value) -> None:
+        self.items.insert(min(max(idx, 0), len(self.items)), value)
+
+    def pop(self):
+        return self.items.pop() if len(self.items) else None
+
+    def clear(self) -> None:
+        self.items = []
+
+    def slice(self, start: int, stop: int) -> "Dataset":
+        s = max(start, 0)
+        e = min(max(stop, s), len(self.items))
+        return Dataset(self.items[s:e])
 
     def map(self, fn: Callable):
         return Dataset([fn(x) for x in self.items])
@@ -140,10 +185,36 @@ class Dataset:
 class TupleDataset(Dataset):
     """Pairs ``(x, y)`` built from two parallel sequences."""
 
-    def __init__(self, xs, ys):
+    def __init__(self, xs=(), ys=()):
         if len(xs) != len(ys):
             raise ValueError("length mismatch")
         super().__init__(list(zip(xs, ys)))
+
+    # The factory forms truncate to the shorter list instead of raising (dataset.mojo:227-253).
+    @staticmethod
+    def from_lists(x, y) -> "TupleDataset":
+        m = min(len(x), len(y))
+        return TupleDataset(list(x)[:m], list(y)[:m])
+
+    def with_lists(self, x, y):
+        m = min(len(x), len(y))
+        self.items = list(zip(list(x)[:m], list(y)[:m]))
+        return self
+
+    def get(self, idx, default_a=Dataset._MISSING, default_b=None):
+        if default_a is not Dataset._MISSING and not 0 <= idx < len(self.items):
+            return (default_a, default_b)
+        return self.items[idx]
+
+    def append(self, a, b=Dataset._MISSING):
+        self.items.append(a if b is Dataset._MISSING else (a, b))
+        return self
+
+    def to_lists(self):
+        return [a for a, _ in self.items], [b for _, b in self.items]
+
+    def to_dataset(self) -> Dataset:
+        return Dataset(self.items)
 
 
 class TensorDataset(Dataset):

@@ -25,6 +25,12 @@ class RandomSampler:
     def __iter__(self):
         return iter(self.epoch_indices(0))
 
+    def set_seed(self, seed: int) -> None:
+        self.seed = seed
+
+    def set_shuffle(self, flag: bool) -> None:
+        self.shuffle = flag
+
 
 class SequentialSampler(RandomSampler):
     def __init__(self, size: int):
@@ -42,6 +48,20 @@ class DistributedSampler:
 
     def set_epoch(self, epoch: int):
         self.epoch = epoch
+
+    def set_seed(self, seed: int) -> None:
+        self.seed = seed
+
+    def set_shuffle(self, flag: bool) -> None:
+        self.shuffle = flag
+
+    def set_rank(self, rank: int) -> None:
+        """Out-of-range ranks are clamped into [0, world_size)."""
+        self.rank = min(max(rank, 0), self.world_size - 1)
+
+    def set_world_size(self, world_size: int) -> None:
+        self.world_size = max(world_size, 1)
+        self.rank = min(self.rank, self.world_size - 1)
 
     def num_samples(self) -> int:
         if self.drop_last:

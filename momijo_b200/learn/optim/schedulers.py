@@ -227,3 +227,57 @@ class ReduceLROnPlateau:
             if k != "type" and hasattr(self, k):
                 setattr(self, k, v)
         return True
+
+
+# ---- setters of the reference (legacy/src/momijo/learn/optim/schedulers.mojo:126-131, 213-222, 388-404, 535-550,
+# 657-669, 781-795, 1111-1150). They clamp like the reference and do not recompute the current rate: the next
+# ``step`` / ``step_to`` does. --------------------------------------------------------------------------------------
+def _set_base_lr(self, lr: float) -> None:
+    self.base_lr = max(float(lr), 0.0, getattr(self, "min_lr", 0.0))
+
+
+def _set_min_lr(self, lr: float) -> None:
+    v = max(float(lr), 0.0)
+    if hasattr(self, "base_lr") and self.base_lr < v:
+        self.base_lr = v
+    self.min_lr = v
+    if hasattr(self, "lr") and self.lr < v:
+        self.lr = v
+
+
+def _set_gamma(self, g: float) -> None:
+    self.gamma = g if g > 0.0 else 0.99
+
+
+def _set_power(self, p: float) -> None:
+    self.power = max(float(p), 0.0)
+
+
+def _set_start_lr(self, lr: float) -> None:
+    self.start_lr = max(float(lr), 0.0)
+
+
+def _set_warmup_steps(self, steps: int) -> None:
+    self.warmup_steps = steps if steps > 0 else 1
+
+
+for _cls in (StepLR, ExponentialLR, MultiStepLR, PolynomialLR, CosineAnnealingLR, CosineAnnealingWarmRestarts, LinearWarmup):
+    _cls.set_base_lr = _set_base_lr
+for _cls in (PolynomialLR, CosineAnnealingLR, CosineAnnealingWarmRestarts, ReduceLROnPlateau):
+    _cls.set_min_lr = _set_min_lr
+ExponentialLR.set_gamma = StepLR.set_gamma = MultiStepLR.set_gamma = _set_gamma
+PolynomialLR.set_power = _set_power
+LinearWarmup.set_start_lr, LinearWarmup.set_warmup_steps = _set_start_lr, _set_warmup_steps
+
+
+def _plateau_set_mode(self, mode: str) -> None:
+    """Anything but "max" means "min"; the best value restarts for the new direction."""
+    self.mode = "max" if mode == "max" else "min"
+    self.best = -math.inf if self.mode == "max" else math.inf
+
+
+ReduceLROnPlateau.set_mode = _plateau_set_mode
+ReduceLROnPlateau.set_factor = lambda self, v: setattr(self, "factor", v if v > 0.0 else 0.1)
+ReduceLROnPlateau.set_patience = lambda self, k: setattr(self, "patience", max(int(k), 0))
+ReduceLROnPlateau.set_threshold = lambda self, v: setattr(self, "threshold", max(float(v), 0.0))
+ReduceLROnPlateau.set_cooldown = lambda self, v: setattr(self, "cooldown", max(int(v), 0))

@@ -164,8 +164,13 @@ def test_streaming_metric_merge_matches_single_pass():
     b.update_many(xs[13:])
     full.update_many(xs)
     a.merge(b)
-    assert a.count == full.count and abs(a.mean - full.mean) < 1e-12 and abs(a.variance() - full.variance()) < 1e-9
-    assert (a.min, a.max) == (full.min, full.max)
+    assert a.count() == full.count() and abs(a.mean() - full.mean()) < 1e-12 and abs(a.variance() - full.variance()) < 1e-9
+    assert (a.min(), a.max()) == (full.min(), full.max()) and abs(a.sum() - sum(xs)) < 1e-9
+    cm = L.metrics.ConfusionMatrixBinary()
+    assert cm.update_batch_scores([0.9, 0.2, 0.7, 0.1], [1, 0, 0, 1]) == 4
+    assert (cm.tp(), cm.fp(), cm.tn(), cm.fn()) == (1, 1, 1, 1) and cm.balanced_accuracy() == 0.5 and cm.compute() == 0.5
+    w = L.metrics.WeightedStreamingMetric()
+    assert w.update_batch([1.0, 3.0, 9.0], [1.0, 1.0, 0.0]) == 3 and w.mean() == 2.0 and w.max() == 3.0 and w.weight_sum() == 2.0
 
 
 def test_early_stopping_and_hooks_order():
