@@ -63,9 +63,35 @@ class autocast:
         _STATE.update(self._prev)
         return False
 
-    @staticmethod
-    def is_enabled() -> bool:
-        return _STATE["enabled"]
+    class _EnabledQuery:
+        """``autocast.is_enabled()`` on the class reads the active (context-manager) state; on an instance it
+        reads that instance's flag, like the reference's method (legacy/src/momijo/learn/amp/autocast.mojo:88-89)."""
+
+        def __get__(self, obj, owner):
+            if obj is None:
+                return lambda: _STATE["enabled"]
+            return lambda: obj.enabled
+
+    is_enabled = _EnabledQuery()
+
+    # chainable configuration (autocast.mojo:76-92)
+    def enable(self) -> "autocast":
+        self.enabled = True
+        return self
+
+    def disable(self) -> "autocast":
+        self.enabled = False
+        return self
+
+    def set_precision(self, p: AMPPrecision) -> "autocast":
+        self.precision = p
+        return self
+
+    def get_precision(self) -> AMPPrecision:
+        return self.precision
+
+    def __str__(self):
+        return f"autocast(enabled={'true' if self.enabled else 'false'}, precision={self.precision})"
 
     @staticmethod
     def dtype():
@@ -87,6 +113,9 @@ class GradScaler:
 
     def get_scale(self) -> float:
         return self.scale_value
+
+    def is_enabled(self) -> bool:
+        return self.enabled
 
     def scale(self, x):
         return x * self.scale_value if self.enabled else x

@@ -88,9 +88,12 @@ class MinMaxObserver:
         self.min_val = min(self.min_val, float(x.min()))
         self.max_val = max(self.max_val, float(x.max()))
 
-    def scale(self) -> float:
+    def scale_symmetric(self, qmax: float = 127.0) -> float:
         m = max(abs(self.min_val), abs(self.max_val))
-        return m / 127.0 if m > 0 and m != float("inf") else 1.0
+        return m / qmax if m > 0 and m != float("inf") else 1.0
+
+    def scale(self) -> float:
+        return self.scale_symmetric(127.0)
 
 
 class NNSequential(Module):
@@ -98,15 +101,19 @@ class NNSequential(Module):
         super().__init__()
         self.seq = Sequential(*modules)
         self.qconfig = qconfig or QConfig()
-        self.is_training = True
 
     def add(self, m):
         self.seq.add(m)
         return self
 
-    def train(self, mode: bool = True):
-        self.is_training = mode
-        return super().train(mode)
+    def to_sequential(self):
+        return self.seq
+
+    def set_qconfig(self, qcfg) -> None:
+        self.qconfig = qcfg
+
+    def get_qconfig(self):
+        return self.qconfig
 
     def forward(self, x, ctx=None):
         return self.seq(x)
@@ -118,7 +125,7 @@ class NNSequential(Module):
 
     def state_json(self, prefix: str = "") -> str:
         return '{"type":"NNSequential","training":%s,"qconfig":"%s","seq":%s}' % (
-            "True" if self.is_training else "False", str(self.qconfig), self.seq.state_json())
+            "True" if self.training else "False", str(self.qconfig), self.seq.state_json())
 
 
 class Prepared:
@@ -142,6 +149,8 @@ class Prepared:
 
     def __call__(self, x):
         return self.model(x)
+
+    forward = __call__
 
 
 class Converted:

@@ -26,6 +26,10 @@ class ImageFolderDataset:
     def num_classes(self) -> int:
         return len(self.classes)
 
+    def class_name(self, idx: int) -> str:
+        """Name of class ``idx``; empty for an index outside the class list."""
+        return self.classes[idx] if 0 <= idx < len(self.classes) else ""
+
     def __getitem__(self, i):
         from ...vision import imread
 

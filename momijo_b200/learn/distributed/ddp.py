@@ -48,6 +48,20 @@ class DDPLinear(Module):
     def forward(self, x):
         return self.linear(x)
 
+    @staticmethod
+    def from_module(module: Linear, pg: ProcessGroup | None = None) -> "DDPLinear":
+        """Wrap an existing ``Linear`` (shares its parameters)."""
+        d = DDPLinear(module.in_features, module.out_features, module.bias, pg)
+        d.linear = module
+        return d
+
+    def replace_module(self, module: Linear) -> None:
+        self.linear = module
+
+    @property
+    def module(self) -> Linear:
+        return self.linear
+
     def sync_gradients(self):
         for p in self.linear.parameters():
             if p.grad is not None:

@@ -27,6 +27,13 @@ class ShardRange:
     def contains(self, i: int) -> bool:
         return self.start <= i < self.end
 
+    def length(self) -> int:
+        return self.end - self.start
+
+    def clamp_index(self, idx: int) -> int:
+        """``idx`` moved into [start, end] (the end itself is allowed)."""
+        return min(max(idx, self.start), self.end)
+
     def __str__(self):
         return f"[{self.start},{self.end})"
 
@@ -49,6 +56,13 @@ class ZeroStage1:
 
     def shard_range(self, total: int) -> ShardRange:
         return partition_1d(total, self.world_size, self.rank)
+
+    def shard_index(self, length: int) -> ShardRange:
+        return partition_1d(length, self.world_size, self.rank)
+
+    def shard_list_i32(self, xs: List[int]) -> List[int]:
+        r = self.shard_index(len(xs))
+        return [int(v) for v in xs[r.start:r.end]]
 
     def shard_list(self, xs: List):
         r = self.shard_range(len(xs))

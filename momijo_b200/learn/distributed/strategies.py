@@ -21,12 +21,28 @@ class DataParallel:
     the remainder), run, concatenate (strategies.mojo:97-143)."""
 
     def __init__(self, model, devices: Optional[List[int]] = None, chunks: Optional[int] = None):
-        self.model = model
-        self.devices = list(devices) if devices else [0]
-        self.chunks = chunks or len(self.devices)
+        self._model = model
+        self._devices = list(devices) if devices else [0]
+        self._chunks = chunks or len(self._devices)
+
+    # accessors in the reference's call form (strategies.mojo:61-78)
+    def world_size(self) -> int:
+        return max(1, len(self._devices))
+
+    def devices(self) -> List[int]:
+        return list(self._devices)
+
+    def chunks(self) -> int:
+        return self._chunks
+
+    def set_chunks(self, chunks: int) -> None:
+        self._chunks = max(1, int(chunks))
+
+    def model(self):
+        return self._model
 
     def scatter_tensor(self, x: torch.Tensor):
-        k = max(1, min(self.chunks, len(self.devices)))
+        k = max(1, min(self._chunks, len(self._devices)))
         n = x.shape[0]
         base = n // k
         out, s = [], 0
@@ -46,7 +62,7 @@ class DataParallel:
         return x
 
     def forward(self, x):
-        return self.gather_tensor([self.model(c) for c in self.scatter_tensor(x) if c.shape[0]])
+        return self.gather_tensor([self._model(c) for c in self.scatter_tensor(x) if c.shape[0]])
 
     __call__ = forward
 
@@ -55,24 +71,34 @@ class DistributedDataParallel(nn.Module):
     def __init__(self, model: nn.Module, world_size: Optional[int] = None, rank: Optional[int] = None,
                  bucket_mb: float = 64.0, comm=None):
         super().__init__()
-        self.model = model
-        self.world_size = C.get_world_size() if world_size is None else world_size
-        self.rank = C.get_rank() if rank is None else rank
+        self.module = model
+        self._world_size = C.get_world_size() if world_size is None else world_size
+        self._rank = C.get_rank() if rank is None else rank
         self.bucket_elems = int(bucket_mb * (1 << 20) / 4)
         self.comm = comm
 
+    # accessors in the reference's call form (strategies.mojo:165-173)
+    def model(self):
+        return self.module
+
+    def world_size(self) -> int:
+        return self._world_size
+
+    def rank(self) -> int:
+        return self._rank
+
     def forward(self, *a, **k):
-        return self.model(*a, **k)
+        return self.module(*a, **k)
 
     def broadcast_parameters(self, src: int = 0):
         if C.is_distributed():
-            for t in list(self.model.parameters()) + list(self.model.buffers()):
+            for t in list(self.module.parameters()) + list(self.module.buffers()):
                 C.broadcast(t.data, src)
         C.barrier()
 
     def _buckets(self):
         cur, n = [], 0
-        for p in self.model.parameters():
+        for p in self.module.parameters():
             if p.grad is None:
                 continue
             cur.append(p)
@@ -117,7 +143,7 @@ class DistributedDataParallel(nn.Module):
 
     def allreduce_tensor_keep(self, t: torch.Tensor, average: bool = True):
         out = C.allreduce(t.clone(), C.ReduceOp.SUM)
-        return out / self.world_size if average else out
+        return out / self._world_size if average else out
 
     def step_and_sync(self, optimizer, grad_blob=None, found_inf: bool = False, average: bool = True):
         """all-reduce -> skip the step on ``found_inf`` -> ``zero_grad`` (strategies.mojo:218-229)."""

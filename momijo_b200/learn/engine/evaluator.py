@@ -22,6 +22,23 @@ class EvalResult:
 class Evaluator:
     def __init__(self, loss_fn=None, metrics: dict | None = None, device=None):
         self.loss_fn, self.metrics, self.device = loss_fn, metrics or {}, device
+        self.loss_name, self.metric_names = "", list(self.metrics)
+
+    # Naming builders (legacy/src/momijo/learn/engine/evaluator.mojo:114-121): a known loss name also selects that loss;
+    # metric names set the report order.
+    def with_loss(self, loss_name: str) -> "Evaluator":
+        self.loss_name = loss_name
+        if self.loss_fn is None:
+            from .. import losses
+            self.loss_fn = getattr(losses, loss_name, None)
+        return self
+
+    def with_metrics(self, names) -> "Evaluator":
+        self.metric_names = list(names)
+        if self.metrics:
+            self.metrics = {k: self.metrics[k] for k in self.metric_names if k in self.metrics} | \
+                           {k: v for k, v in self.metrics.items() if k not in self.metric_names}
+        return self
 
     @torch.no_grad()
     def evaluate(self, model, loader, steps: int = 0) -> EvalResult:

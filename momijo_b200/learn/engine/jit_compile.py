@@ -4,6 +4,7 @@ CUDA graph (static shapes), which removes launch overhead without a tracing comp
 ``check_numerics`` adds a finite check on the outputs."""
 from __future__ import annotations
 
+import dataclasses
 from dataclasses import dataclass
 
 import torch
@@ -15,6 +16,19 @@ class JITOptions:
     optimize: bool = True
     check_numerics: bool = False
     allow_mixed_precision: bool = True
+
+    # Copy-and-set builders (legacy/src/momijo/learn/engine/jit_compile.mojo:49-67): the receiver is left alone.
+    def with_graph(self, on: bool) -> "JITOptions":
+        return dataclasses.replace(self, graph=on)
+
+    def with_optimize(self, on: bool) -> "JITOptions":
+        return dataclasses.replace(self, optimize=on)
+
+    def with_check_numerics(self, on: bool) -> "JITOptions":
+        return dataclasses.replace(self, check_numerics=on)
+
+    def with_mixed_precision(self, on: bool) -> "JITOptions":
+        return dataclasses.replace(self, allow_mixed_precision=on)
 
 
 class GraphExecutor:

@@ -16,3 +16,12 @@ class AvgPool2d(Module):
 
     def forward(self, x, ctx=None):
         return tF.avg_pool2d(x, self.kernel_size, self.stride, self.padding, count_include_pad=False)
+
+    def backward(self, x, grad_y):
+        """``dx``: each output gradient is shared equally among the in-bounds inputs of its window
+        (avgpool.mojo:60-95)."""
+        import torch
+
+        xr = x.detach().requires_grad_(True)
+        y = tF.avg_pool2d(xr, self.kernel_size, self.stride, self.padding, count_include_pad=False)
+        return torch.autograd.grad(y, xr, grad_y)[0]

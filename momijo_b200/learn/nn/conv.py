@@ -31,8 +31,6 @@ class Conv2d(Module):
     def forward(self, x, ctx=None):
         return F.conv2d(x, self.weight, self.bias_t if self.bias else None, self.stride, self.pad)
 
-    forward_gpu = forward
-
     def backward(self, x, dy):
         """Explicit ``(dW, db, dx)`` like the reference's CPU backward (conv.mojo:722-853)."""
         xr = x.detach().requires_grad_(True)
@@ -54,9 +52,13 @@ class MaxPool2d(Module):
     def forward(self, x, ctx=None):
         return tF.max_pool2d(x, self.kernel, self.stride, self.pad)
 
-    forward_gpu = forward
-
     def backward(self, x, dy):
         xr = x.detach().requires_grad_(True)
         y = tF.max_pool2d(xr, self.kernel, self.stride, self.pad)
         return torch.autograd.grad(y, xr, dy)[0]
+
+
+from .module import bind_device_paths  # noqa: E402
+
+bind_device_paths(Conv2d)
+bind_device_paths(MaxPool2d)

@@ -21,3 +21,16 @@ class ConvTranspose2d(Module):
 
     def forward(self, x, ctx=None):
         return tF.conv_transpose2d(x, self.weight, self.bias, self.stride, self.padding)
+
+    def out_shape(self, H: int, W: int):
+        """``(OH, OW) = ((H - 1) * stride - 2 * pad + kernel)`` per axis (conv_transpose.mojo:40-43)."""
+        return ((H - 1) * self.stride[0] - 2 * self.padding[0] + self.kernel_size[0],
+                (W - 1) * self.stride[1] - 2 * self.padding[1] + self.kernel_size[1])
+
+    def backward(self, x, grad_y):
+        """Explicit ``(dW, db, dx)`` (conv_transpose.mojo:91-140)."""
+        xr = x.detach().requires_grad_(True)
+        w = self.weight.detach().requires_grad_(True)
+        y = tF.conv_transpose2d(xr, w, None, self.stride, self.padding)
+        dx, dw = torch.autograd.grad(y, (xr, w), grad_y)
+        return dw, grad_y.sum((0, 2, 3)), dx

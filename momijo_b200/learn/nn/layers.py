@@ -59,9 +59,15 @@ class Linear(Module):
         b = self.bias_t if self.bias else None
         return ops.linear(x, self.weight, b)
 
-    forward_auto = forward
-    forward_gpu = forward
-    forward_cpu_parallel = forward
+    def reset_parameters(self) -> None:
+        """The reference's refill: every weight ``0.01 / in_features``, bias zero (layers.mojo:361-377)."""
+        with torch.no_grad():
+            self.weight.fill_(0.01 / self.in_features)
+            self.bias_t.zero_()
+
+    def summarize(self, s) -> None:
+        s.add_params_generic("Linear", [-1, self.in_features], [-1, self.out_features],
+                             [self.weight] + ([self.bias_t] if self.bias else []), [], True)
 
     def backward(self, x, dy):
         """Explicit gradients ``(dW, db, dx)`` like the reference (layers.mojo:519-787)."""
@@ -158,6 +164,19 @@ class BatchNorm2d(Module):
         self.register_buffer("running_mean", torch.zeros(num_features, dtype=dtype))
         self.register_buffer("running_var", torch.ones(num_features, dtype=dtype))
 
+    def reset_parameters(self) -> None:
+        """Scale 1, shift 0, running mean 0 and running variance 1 (layers.mojo:1103-1120)."""
+        with torch.no_grad():
+            self.gamma.fill_(1.0)
+            self.beta.zero_()
+            self.running_mean.zero_()
+            self.running_var.fill_(1.0)
+
+    def summarize(self, s) -> None:
+        c = self.num_features
+        s.add_params_generic("BatchNorm2d", [-1, c, -1, -1], [-1, c, -1, -1], [self.gamma, self.beta],
+                             [self.running_mean, self.running_var], True)
+
     def forward(self, x, training=None):
         training = self.training if training is None else training
         if training:
@@ -236,6 +255,9 @@ class Dropout(Module):
         scale = 1.0 / (1.0 - self.p) if self.p < 1.0 else 0.0
         return x * keep.to(x.dtype) * scale
 
+    def summarize(self, s) -> None:
+        s.add_leaf("Dropout", [-1], [-1])
+
 
 class Flatten(Module):
     def __init__(self, start_dim: int = 1, end_dim: int = -1):
@@ -244,6 +266,12 @@ class Flatten(Module):
 
     def forward(self, x, ctx=None):
         return torch.flatten(x, self.start_dim, self.end_dim)
+
+    # A reshape costs the same everywhere, so every device path is the same call (layers.mojo:1608-1648).
+    forward_cpu = forward_gpu = forward_auto = forward
+
+    def summarize(self, s) -> None:
+        s.add_leaf("Flatten", [-1], [-1])
 
 
 def quantize_symmetric_int8(x: torch.Tensor, scale: float) -> torch.Tensor:
@@ -345,3 +373,9 @@ class Seq512(Module):
 
     def forward(self, x):
         return self.l2(self.a(self.l1(x)))
+
+
+from .module import bind_device_paths  # noqa: E402
+
+bind_device_paths(Linear)
+bind_device_paths(Dropout, forward=("forward_auto", "forward_gpu", "forward_cpu_fast"), backward=())

@@ -81,10 +81,24 @@ class Module(nn.Module):
         return Module._wrap(l, name)
 
     # ---- registry ---------------------------------------------------------------------------
-    def register_parameter(self, name, param):
+    def register_parameter(self, name, param, requires_grad: bool = True):
         if param is not None and not isinstance(param, nn.Parameter):
-            param = nn.Parameter(param)
+            param = nn.Parameter(param, requires_grad=requires_grad)
         super().register_parameter(name, param)
+
+    def add_parameter(self, name, value, requires_grad: bool = True):
+        self.register_parameter(name, value, requires_grad)
+
+    def add_buffer(self, name, value):
+        self.register_buffer(name, value)
+
+    def is_training(self) -> bool:
+        return self.training
+
+    def summarize(self, s) -> None:
+        """Add this layer (and its children) to a ``Summarizer``."""
+        from ..utils.summary import summarize_module
+        summarize_module(self, s)
 
     def named_parameters(self, prefix: str = "", recurse: bool = True, remove_duplicate: bool = True):
         return super().named_parameters(prefix=prefix, recurse=recurse,
@@ -110,3 +124,30 @@ class Module(nn.Module):
         for child in self.children():
             x = child(x)
         return x
+
+
+def bind_device_paths(cls, forward=("forward_auto", "forward_gpu", "forward_cpu_parallel"),
+                      backward=("backward_auto", "backward_gpu", "backward_cpu_parallel")):
+    """Give a layer the reference's per-device entry points (legacy/src/momijo/learn/nn/layers.mojo:383-787,
+    conv.mojo:78-437). Here one ``forward`` / ``backward`` serves every device, chosen by where the tensors live, so
+    ``*_auto`` is that method; ``*_gpu`` first places the layer and its inputs on the CUDA device (an error without
+    one) and the ``*_cpu*`` forms place them on the host."""
+    def make(base: str, where: str):
+        def path(self, *args, **kw):
+            if where == "auto":
+                return getattr(self, base)(*args, **kw)
+            if where == "cuda" and not torch.cuda.is_available():
+                raise RuntimeError(f"{cls.__name__}.{base}_gpu needs a CUDA device")
+            self.to(where)
+            args = [a.to(where) if isinstance(a, torch.Tensor) else a for a in args]
+            return getattr(self, base)(*args, **kw)
+        return path
+
+    for names, base in ((forward, "forward"), (backward, "backward")):
+        if not hasattr(cls, base):
+            continue
+        for n in names:
+            where = "auto" if n.endswith("_auto") else ("cuda" if n.endswith("_gpu") else "cpu")
+            if n not in cls.__dict__ or getattr(cls, n) is getattr(cls, base):
+                setattr(cls, n, make(base, where))
+    return cls

@@ -30,3 +30,17 @@ class Adam(_PerLayerOptimizer):
         vhat = st["v"] / (1 - self.beta2 ** st["t"])
         upd = mhat / (vhat.sqrt() + self.eps) + self.weight_decay * p.float()
         p.sub_((self.lr * upd).to(p.dtype))
+
+
+def _set_hyperparams(self, lr: float, beta1: float, beta2: float, eps: float, weight_decay: float) -> None:
+    self.lr, self.beta1, self.beta2, self.eps, self.weight_decay = lr, beta1, beta2, eps, weight_decay
+
+
+def _zero_state(self) -> None:
+    """Drop the moments and the step count, keep the hyper-parameters (legacy/src/momijo/learn/optim/adam.mojo:246-251)."""
+    self.state.clear()
+    if hasattr(self, "t"):
+        self.t = 0
+
+
+Adam.set_hyperparams, Adam.zero_state = _set_hyperparams, _zero_state

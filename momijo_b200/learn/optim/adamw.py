@@ -41,3 +41,17 @@ class AdamW(_PerLayerOptimizer):
         w.sub_(self.lr * (mhat / (vhat.sqrt() + self.eps) + self.weight_decay * w))
         if "master" in st or p.dtype != torch.float32:
             p.data.copy_(w.view(p.shape).to(p.dtype))
+
+
+def _set_hyperparams(self, lr: float, beta1: float, beta2: float, eps: float, weight_decay: float) -> None:
+    self.lr, self.beta1, self.beta2, self.eps, self.weight_decay = lr, beta1, beta2, eps, weight_decay
+
+
+def _zero_state(self) -> None:
+    """Drop the moments and the step count, keep the hyper-parameters (legacy/src/momijo/learn/optim/adamw.mojo:246-251)."""
+    self.state.clear()
+    if hasattr(self, "t"):
+        self.t = 0
+
+
+AdamW.set_hyperparams, AdamW.zero_state = _set_hyperparams, _zero_state

@@ -38,6 +38,52 @@ class RMSprop(_PerLayerOptimizer):
             p.mul_(1 - self.lr * self.weight_decay)
 
 
+def _rms_set_params(self, ps) -> None:
+    """Scalar mode: a list of ``OptParam`` (value, grad) pairs with fresh state (rmsprop.mojo:165-183)."""
+    self._scalars, self._tensor_pair = list(ps), None
+    self.params = []
+    self.state = {}
+
+
+def _rms_set_params_tensor(self, params, grads) -> None:
+    """Tensor mode: one parameter tensor and the gradient tensor the caller fills before each ``step``
+    (rmsprop.mojo:185-204)."""
+    if tuple(params.shape) != tuple(grads.shape):
+        raise ValueError("RMSprop.set_params_tensor: parameter and gradient shapes differ")
+    self._scalars, self._tensor_pair = None, (params, grads)
+    self.params = []
+    self.state = {}
+
+
+def _rms_step(self):
+    pair, scalars = getattr(self, "_tensor_pair", None), getattr(self, "_scalars", None)
+    with torch.no_grad():
+        if pair is not None:
+            self._update("tensor", pair[0], pair[1])
+        elif scalars is not None:
+            for i, sp in enumerate(scalars):
+                t = torch.tensor([float(sp.value)], dtype=torch.float64)
+                self._update(("s", i), t, torch.tensor([float(sp.grad)], dtype=torch.float64))
+                sp.value = float(t[0])
+        else:
+            _PerLayerOptimizer.step(self)
+
+
+def _rms_zero_grad(self, set_to_none: bool = True):
+    pair, scalars = getattr(self, "_tensor_pair", None), getattr(self, "_scalars", None)
+    if pair is not None:
+        pair[1].zero_()
+    elif scalars is not None:
+        for sp in scalars:
+            sp.grad = 0.0
+    else:
+        _PerLayerOptimizer.zero_grad(self, set_to_none)
+
+
+RMSprop.set_params, RMSprop.set_params_tensor = _rms_set_params, _rms_set_params_tensor
+RMSprop.step, RMSprop.zero_grad = _rms_step, _rms_zero_grad
+
+
 class OptParam:
     """Scalar parameter with its gradient (legacy/src/momijo/learn/optim/rmsprop.mojo:95-101)."""
 

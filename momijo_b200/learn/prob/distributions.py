@@ -26,6 +26,10 @@ class _Dist:
     def log_prob_tensor(self, x: torch.Tensor) -> torch.Tensor:
         return torch.tensor([self.log_prob(float(v)) for v in x.reshape(-1)], dtype=torch.float32).reshape(x.shape)
 
+    def mean_value(self) -> float:
+        """The reference's name for the mean (distributions.mojo:161, 225, 323, 428, 537)."""
+        return self.mean()
+
 
 class Uniform(_Dist):
     def __init__(self, low=0.0, high=1.0, seed=0):
@@ -114,6 +118,22 @@ class Categorical(_Dist):
 
     def entropy(self):
         return -sum(p * math.log(p) for p in self.probs if p > 0)
+
+    # Mean and variance of a class index mean nothing: NaN, as in the reference (distributions.mojo:428-434).
+    def mean(self):
+        return math.nan
+
+    def variance(self):
+        return math.nan
+
+    @staticmethod
+    def from_probs_tensor(probs_t, seed=0) -> "Categorical":
+        """From a 1-D tensor of weights: negatives count as 0, the rest is normalised; all-zero weights give the
+        uniform distribution (distributions.mojo:445-470)."""
+        ps = [max(float(v), 0.0) for v in probs_t.reshape(-1)]
+        if sum(ps) <= 0.0:
+            ps = [1.0] * len(ps)
+        return Categorical(ps, seed)
 
 
 class Normal(_Dist):

@@ -20,6 +20,8 @@ class SplitMix64:
         z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & M64
         return z ^ (z >> 31)
 
+    next = next_u64
+
 
 def _rotl(x, k):
     return ((x << k) | (x >> (64 - k))) & M64
@@ -29,6 +31,15 @@ class Xoshiro256ss:
     def __init__(self, seed: int = 0):
         sm = SplitMix64(seed)
         self.s = [sm.next_u64() for _ in range(4)]
+
+    @staticmethod
+    def from_seed(seed: int) -> "Xoshiro256ss":
+        """State from four SplitMix64 draws; an all-zero state gets its last word set to 1
+        (legacy/src/momijo/learn/utils/randomness.mojo:92-101)."""
+        g = Xoshiro256ss(seed)
+        if not any(g.s):
+            g.s[3] = 1
+        return g
 
     def next_u64(self) -> int:
         s = self.s
@@ -62,6 +73,17 @@ class RNG:
 
     def next_u64(self):
         return self.gen.next_u64()
+
+    @staticmethod
+    def from_int_seed(seed: int) -> "RNG":
+        return RNG(int(seed) & M64)
+
+    def next_f64_open01(self) -> float:
+        """Uniform in the open interval (0, 1): the end points map to the nearest value inside."""
+        y = (self.next_u64() >> 11) * (1.0 / 9007199254740992.0)
+        return 5e-324 if y <= 0.0 else (1.0 - 2.0 ** -53 if y >= 1.0 else y)
+
+    next_f64 = next_f64_open01
 
     def uniform(self, lo: float = 0.0, hi: float = 1.0) -> float:
         return lo + (hi - lo) * ((self.gen.next_u64() >> 11) * (1.0 / 9007199254740992.0))
@@ -111,6 +133,9 @@ class SeedBundle:
     init: int = 0
     dropout: int = 0
     aug: int = 0
+
+    def to_list(self):
+        return [self.base, self.data, self.init, self.dropout, self.aug]
 
 
 def seed_all(seed: int) -> SeedBundle:
