@@ -40,6 +40,12 @@ class KernelRegistry:
     def kind(self) -> BackendKind:
         return self._kind
 
+    def with_auto(self) -> "KernelRegistry":
+        """The same backend with the automatic schedule for an unknown image size
+        (legacy/src/momijo/vision/backend/registry.mojo:37-39)."""
+        from .schedule import auto_schedule
+        return KernelRegistry(self._kind, auto_schedule(0, 0))
+
     def schedule(self) -> Schedule:
         return self._schedule
 

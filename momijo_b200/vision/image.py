@@ -15,6 +15,15 @@ import numpy as np
 import torch
 
 
+class _Name(str):
+    """An upper-case tag that compares as a string and, when called, gives the reference's spelling:
+    ``cs.name == "GRAY"`` and ``cs.name() == "Gray"`` (legacy/src/momijo/vision/dtypes.mojo:142-148, 201-209)."""
+    _ref = {"LINEAR": "Linear", "GRAY": "Gray", "YCBCR": "YCbCr", "UNKNOWN": "Unknown"}
+
+    def __call__(self) -> str:
+        return self._ref.get(str(self), str(self))
+
+
 class ColorSpace:
     """Enumeration by name (legacy/src/momijo/vision/dtypes.mojo ``ColorSpace``)."""
     _names = ("SRGB", "LINEAR", "GRAY", "BGR", "RGB", "HSV", "YCBCR", "UNKNOWN")
@@ -23,7 +32,19 @@ class ColorSpace:
         name = name.upper()
         if name not in self._names:
             raise ValueError(f"unknown colour space {name!r}")
-        self.name = name
+        self.name = _Name(name)
+
+    def copy(self) -> "ColorSpace":
+        return ColorSpace(self.name)
+
+    @staticmethod
+    def from_name(name: str):
+        """``(found, value)``: the reference's spellings and the upper-case tags; unknown names give
+        ``(False, Unknown)`` (dtypes.mojo:211-218)."""
+        up = name.upper()
+        if up in ColorSpace._names:
+            return True, ColorSpace(up)
+        return False, ColorSpace("UNKNOWN")
 
     def __eq__(self, other):
         return isinstance(other, ColorSpace) and other.name == self.name
@@ -37,6 +58,8 @@ class ColorSpace:
 
 for _n in ColorSpace._names:
     setattr(ColorSpace, _n, staticmethod(lambda _n=_n: ColorSpace(_n)))
+for _alias, _n in (("Linear", "LINEAR"), ("Gray", "GRAY"), ("YCbCr", "YCBCR"), ("Unknown", "UNKNOWN")):
+    setattr(ColorSpace, _alias, staticmethod(lambda _n=_n: ColorSpace(_n)))
 
 
 class Layout:
@@ -46,7 +69,17 @@ class Layout:
         name = name.upper()
         if name not in self._names:
             raise ValueError(f"unknown layout {name!r}")
-        self.name = name
+        self.name = _Name(name)
+
+    def copy(self) -> "Layout":
+        return Layout(self.name)
+
+    @staticmethod
+    def from_name(name: str):
+        """``(found, value)``; unknown names give ``(False, HWC)`` (dtypes.mojo:150-155)."""
+        if name in Layout._names:
+            return True, Layout(name)
+        return False, Layout("HWC")
 
     def __eq__(self, other):
         return isinstance(other, Layout) and other.name == self.name
@@ -222,6 +255,10 @@ class Image:
         y0, x0 = max(int(y), 0), max(int(x), 0)
         y1, x1 = min(int(y) + int(h), self.height()), min(int(x) + int(w), self.width())
         return Image(self.data[y0:max(y1, y0), x0:max(x1, x0)], self._meta.copy())
+
+    def as_hwc_view(self, h: int = 0, w: int = 0, c: int = 0, s0: int = 0, s1: int = 0, s2: int = 0) -> "Image":
+        """The reference returns a copy whatever the arguments (legacy/src/momijo/vision/image.mojo:262-263)."""
+        return self.clone()
 
     def with_meta(self, meta):
         return Image(self.data, meta)

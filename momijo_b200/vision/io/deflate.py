@@ -77,6 +77,8 @@ class BitReader:
         self.cur >>= drop
         self.nbits -= drop
 
+    align_to_byte = align_byte
+
 
 class Huff:
     """Canonical Huffman table: per code length the first code, the index of its first symbol in ``values``

@@ -377,6 +377,53 @@ class BitReader:
         self.bit_buf &= (1 << self.bit_count) - 1
         return v
 
+    # ---- the rest of the reference's reader (legacy/src/momijo/vision/io/bitreader.mojo:112-185) ------------------
+    def read_bit(self) -> int:
+        return self.read_bits(1)
+
+    def peek_bits(self, n: int) -> int:
+        """Next ``n`` bits without consuming them; 0 when fewer are left."""
+        if n <= 0:
+            return 0
+        self._fill(min(n, 24))
+        if self.bit_count < n:
+            return 0
+        return (self.bit_buf >> (self.bit_count - n)) & ((1 << n) - 1)
+
+    def skip_bits(self, n: int) -> None:
+        if n <= 0:
+            return
+        self._fill(n)
+        if self.bit_count < n:
+            self.bit_buf, self.bit_count, self.eof_flag = 0, 0, True
+            return
+        self.bit_count -= n
+        self.bit_buf &= (1 << self.bit_count) - 1
+
+    def align_byte(self) -> None:
+        rem = self.bit_count % 8
+        if rem:
+            self.read_bits(rem)
+
+    def read_data_byte(self):
+        """``(ok, byte)`` straight from the stream after aligning: a stuffed ``FF 00`` gives ``FF``; a marker or the end
+        gives ``(False, 0)`` and sets the end flag."""
+        self.align_byte()
+        if self.bit_count >= 8:                      # whole bytes already buffered come first
+            return True, self.read_bits(8)
+        if self.eof_flag or self.pos >= self.length:
+            self.eof_flag = True
+            return False, 0
+        b = self.data[self.pos]
+        self.pos += 1
+        if b == 0xFF:
+            if self.pos < self.length and self.data[self.pos] == 0:
+                self.pos += 1
+                return True, 0xFF
+            self.eof_flag = True
+            return False, 0
+        return True, b
+
 
 class HuffmanTable:
     """Decoder-side table: codes ordered by length then value, with sizes and symbols alongside."""

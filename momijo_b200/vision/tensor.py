@@ -5,7 +5,68 @@ from __future__ import annotations
 
 import torch
 
-Tensor = torch.Tensor
+class Tensor(torch.Tensor):
+    """An image buffer read through the reference's accessors (legacy/src/momijo/vision/tensor.mojo:28-290): height /
+    width / channels (``shape0..2``), element strides, byte-level loads and stores, packed copies and region copies.
+    It is a ``torch.Tensor`` subclass, so every function of this package takes it as it takes a plain tensor; wrap
+    one with ``Tensor.wrap(t)``."""
+
+    @staticmethod
+    def wrap(t: torch.Tensor) -> "Tensor":
+        return t.as_subclass(Tensor)
+
+    def _dim(self, k: int) -> int:
+        return int(self.shape[k]) if self.dim() > k else 0
+
+    def height(self) -> int: return self._dim(0)
+    def width(self) -> int: return self._dim(1)
+    def channels(self) -> int: return self._dim(2)
+    shape0, shape1, shape2 = height, width, channels
+
+    def _stride(self, k: int) -> int:
+        return int(self.stride(k)) if self.dim() > k else 0
+
+    def stride0(self) -> int: return self._stride(0)
+    def stride1(self) -> int: return self._stride(1)
+    def stride2(self) -> int: return self._stride(2)
+
+    def is_empty(self) -> bool:
+        return self.numel() == 0
+
+    def is_contiguous_hwc_u8(self) -> bool:
+        return (self.dtype == torch.uint8 and self.dim() == 3
+                and (self.stride2(), self.stride1(), self.stride0()) == (1, self.shape2(), self.shape1() * self.shape2()))
+
+    def clone_deep(self) -> "Tensor":
+        """Same bytes, same strides, own storage."""
+        out = torch.empty_strided(tuple(self.shape), self.stride(), dtype=self.dtype, device=self.device)
+        out.copy_(self)
+        return Tensor.wrap(out)
+
+    clone_bytes = clone_deep
+
+    def copy_to_packed_hwc(self) -> "Tensor":
+        return Tensor.wrap(self.contiguous().clone()) if self.numel() else Tensor.wrap(torch.empty(0, dtype=self.dtype))
+
+    def ptr_u8(self) -> torch.Tensor:
+        """The bytes of a dense buffer as a flat uint8 view (stands in for the raw pointer)."""
+        return self.as_subclass(torch.Tensor).contiguous().view(-1).view(torch.uint8) if not self.is_contiguous() \
+            else self.as_subclass(torch.Tensor).view(-1).view(torch.uint8)
+
+    def store_u8_at(self, idx: int, v: int) -> None:
+        self.ptr_u8()[idx] = int(v) & 0xFF
+
+    def load_u8_at(self, idx: int) -> int:
+        return int(self.ptr_u8()[idx])
+
+    def copy_roi(self, y: int, x: int, h: int, w: int) -> "Tensor":
+        """Packed copy of the ``h x w`` window at ``(y, x)``: the origin is clamped to 0, the size to what is left of
+        the image, and an empty window gives an empty tensor (tensor.mojo:222-278)."""
+        y, x = max(y, 0), max(x, 0)
+        h, w = min(h, self.height() - y), min(w, self.width() - x)
+        if h <= 0 or w <= 0:
+            return Tensor.wrap(torch.empty(0, dtype=self.dtype))
+        return Tensor.wrap(self.as_subclass(torch.Tensor)[y:y + h, x:x + w].contiguous().clone())
 
 
 def packed_hwc_strides(h: int, w: int, c: int):

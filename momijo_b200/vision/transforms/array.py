@@ -10,7 +10,17 @@ import torch
 from ..image import Image
 from .. import kernels as K
 
-Descriptor = list  # a list of 32-byte rows (lists of ints 0..255)
+class Descriptor(list):
+    """A list of binary rows (ORB-like), each a list of 32 ints 0..255
+    (legacy/src/momijo/vision/transforms/features.mojo:43-54)."""
+
+    @property
+    def rows(self):
+        return self
+
+    @staticmethod
+    def null() -> "Descriptor":
+        return Descriptor()
 
 
 def zeros(*args, dtype=None) -> Image:

@@ -20,6 +20,9 @@ class BorderSpec:
     mode: int = 0
     value: int = 0
 
+    def cval(self) -> int:
+        return self.value
+
     @staticmethod
     def CONSTANT(val: int = 0):
         return BorderSpec(0, int(val))
