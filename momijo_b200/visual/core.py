@@ -37,8 +37,42 @@ def dumps(obj) -> str:
     return json.dumps(clean(obj), separators=(",", ":"), ensure_ascii=False)
 
 
+def _single_to_double_quoted(s: str) -> str:
+    """Rewrite a JavaScript-style fragment with single-quoted strings as JSON: quotes are swapped, embedded double
+    quotes escaped, ``\\'`` unescaped."""
+    out, i, n = [], 0, len(s)
+    while i < n:
+        ch = s[i]
+        if ch == '"':                                   # already a JSON string: copy through
+            j = i + 1
+            while j < n and s[j] != '"':
+                j += 2 if s[j] == "\\" else 1
+            out.append(s[i:j + 1])
+            i = j + 1
+        elif ch == "'":
+            j, buf = i + 1, []
+            while j < n and s[j] != "'":
+                if s[j] == "\\" and j + 1 < n:
+                    buf.append("'" if s[j + 1] == "'" else s[j:j + 2])
+                    j += 2
+                else:
+                    buf.append('\\"' if s[j] == '"' else s[j])
+                    j += 1
+            out.append('"' + "".join(buf) + '"')
+            i = j + 1
+        else:
+            out.append(ch)
+            i += 1
+    return "".join(out)
+
+
 def loads(s: str):
-    return json.loads(s)
+    """Parse a JSON fragment. The reference writes its fragments with single quotes (``{ 'type':'value' }``), so when
+    strict JSON fails the single-quoted form is accepted too."""
+    try:
+        return json.loads(s)
+    except json.JSONDecodeError:
+        return json.loads(_single_to_double_quoted(s))
 
 
 def json_string(s: str) -> str:

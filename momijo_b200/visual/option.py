@@ -37,16 +37,6 @@ class Option:
         self._parallel_axis: List[object] = []
         self._colors: List[str] = []
 
-    def __getattr__(self, attr):
-        if attr.startswith("set_") and attr[4:] in Option._single:
-            key = Option._single[attr[4:]]
-
-            def setter(fragment):
-                self._d[key] = _frag(fragment)
-                return self
-            return setter
-        raise AttributeError(attr)
-
     def set_subtitle(self, text: str, subtext: str):
         self._d["title"] = {"text": text, "subtext": subtext}
         return self
@@ -102,6 +92,18 @@ class Option:
     def to_json(self) -> str:
         return dumps(self.to_dict())
 
+
+
+def _make_fragment_setter(key: str):
+    def setter(self, fragment):
+        self._d[key] = _frag(fragment)
+        return self
+    setter.__doc__ = f"Set the ``{key}`` component from a JSON fragment (string or object)."
+    return setter
+
+
+for _short, _key in Option._single.items():
+    setattr(Option, "set_" + _short, _make_fragment_setter(_key))
 
 class EasyOption:
     """Fluent builder; every ``add_*`` appends a series, every ``set_*`` fills a top-level component."""
@@ -183,6 +185,44 @@ class EasyOption:
     def set_xaxis_value(self, name=""):
         self.o["xAxis"] = {"type": "value", "name": name}; return self
 
+    # ---- axis builders of the reference (legacy/src/momijo/visual/charts/ez_option.mojo:2237-2302); ``minv`` / ``maxv``
+    # are JSON fragments ("0", "'dataMax'") or numbers ---------------------------------------------------------------
+    @staticmethod
+    def _value_axis(name, name_location, name_gap, labels_color, minv, maxv):
+        ax = {"type": "value", "name": name, "nameLocation": name_location, "nameGap": name_gap,
+              "axisLabel": {"color": labels_color}}
+        for key, v in (("min", minv), ("max", maxv)):
+            if v not in ("", None):
+                ax[key] = _frag(v) if isinstance(v, str) else v
+        return ax
+
+    def set_xaxis_value_json(self, name, name_location, name_gap, labels_color="#333", minv="", maxv=""):
+        self.o["xAxis"] = self._value_axis(name, name_location, name_gap, labels_color, minv, maxv); return self
+
+    def set_yaxis_value_json2(self, name, name_location, name_gap, labels_color="#333", minv="", maxv=""):
+        self.o["yAxis"] = self._value_axis(name, name_location, name_gap, labels_color, minv, maxv); return self
+
+    def set_yaxis_category_json(self, name, name_location, name_gap, labels_color, data):
+        self.o["yAxis"] = {"type": "category", "name": name, "nameLocation": name_location, "nameGap": name_gap,
+                           "axisLabel": {"color": labels_color}, "data": list(data)}
+        return self
+
+    @staticmethod
+    def _category_axis(labels, name, name_location, name_gap, labels_color, rotate_deg):
+        ax = {"type": "category"}
+        if name:
+            ax.update(name=name, nameLocation=name_location, nameGap=name_gap)
+        ax.update(data=list(labels), axisLabel={"color": labels_color, "rotate": rotate_deg})
+        return ax
+
+    def set_xaxis_category_labels(self, labels, name="", name_location="middle", name_gap=28, labels_color="#333",
+                                  rotate_deg=0):
+        self.o["xAxis"] = self._category_axis(labels, name, name_location, name_gap, labels_color, rotate_deg); return self
+
+    def set_yaxis_category_labels(self, labels, name="", name_location="middle", name_gap=28, labels_color="#333",
+                                  rotate_deg=0):
+        self.o["yAxis"] = self._category_axis(labels, name, name_location, name_gap, labels_color, rotate_deg); return self
+
     def add_datazoom_slider(self, start_pct=0, end_pct=100):
         self.datazoom.append({"type": "slider", "start": start_pct, "end": end_pct}); return self
 
@@ -260,6 +300,85 @@ class EasyOption:
 
     def add_heatmap_series_from_triplets(self, name, triplets, label_show=False):
         return self._add("heatmap", name, [list(t) for t in triplets], label={"show": bool(label_show)})
+
+    # ---- grid fields, distributions and flow lines (ez_option.mojo:2306-2610) -----------------------------------------
+    def add_heatmap_series(self, name, xs, ys, z, blur_size: int = 0):
+        """Heatmap cells ``[x, y, z[row][col]]`` of a regular grid, rows following ``ys``."""
+        data = [[xs[c], ys[r], z[r][c]] for r in range(len(ys)) for c in range(len(xs))]
+        return self._add("heatmap", name, data, blurSize=blur_size if blur_size > 0 else None, progressive=0)
+
+    def add_contour_lines(self, name_prefix, xs, ys, z, levels, color="#000000", line_width=1, opacity=100):
+        """One line series per level, traced by marching squares over the grid cells. Each crossing cell gives one
+        segment (the two saddle cases take one diagonal choice); segments are separated by nulls."""
+        H, W = len(ys), len(xs)
+        if H < 2 or W < 2:
+            return self
+
+        def lerp(a, b, za, zb, lvl):
+            return a if zb == za else a + (b - a) * (lvl - za) / (zb - za)
+
+        pairs = {1: (3, 0), 14: (3, 0), 2: (0, 1), 13: (0, 1), 3: (3, 1), 12: (3, 1), 4: (2, 3), 11: (2, 3), 5: (2, 0),
+                 6: (2, 1), 9: (2, 1), 7: (2, 1), 8: (2, 1), 10: (3, 1)}
+        for lvl in levels:
+            data = []
+            for r in range(H - 1):
+                for c in range(W - 1):
+                    xL, xR, yB, yT = xs[c], xs[c + 1], ys[r], ys[r + 1]
+                    z00, z10, z01, z11 = z[r][c], z[r][c + 1], z[r + 1][c], z[r + 1][c + 1]
+                    idx = (z00 > lvl) + 2 * (z10 > lvl) + 4 * (z01 > lvl) + 8 * (z11 > lvl)
+                    if idx in (0, 15):
+                        continue
+                    edge = {0: (lerp(xL, xR, z00, z10, lvl), yB), 1: (xR, lerp(yB, yT, z10, z11, lvl)),
+                            2: (lerp(xL, xR, z01, z11, lvl), yT), 3: (xL, lerp(yB, yT, z00, z01, lvl))}
+                    a, b = (edge[e] for e in pairs[idx])
+                    data += [[a[0], a[1]], [b[0], b[1]], None]
+            self._add("line", f"{name_prefix} {lvl}", data, symbol="none",
+                      lineStyle={"width": line_width, "color": color, "opacity": opacity / 100})
+        return self
+
+    def add_ecdf_series(self, name, samples, color, survival=False, normalized=True, step_style="end",
+                        show_symbol=False, line_width=2, area_opacity=0, show_labels=False, label_fmt="{c}"):
+        """Empirical CDF (or survival ``1 - F``) of integer samples as a step line: one point per distinct value, the
+        probability truncated to six decimals like the reference's integer arithmetic; counts when not normalised."""
+        xs = sorted(int(v) for v in samples)
+        n = len(xs)
+        data, cum, i = [], 0, 0
+        while i < n:
+            run = 1
+            while i + run < n and xs[i + run] == xs[i]:
+                run += 1
+            cum += run
+            if normalized:
+                scaled = (cum * 1_000_000) // n
+                y = (min(max(1_000_000 - scaled, 0), 1_000_000) if survival else scaled) / 1_000_000
+            else:
+                y = n - cum if survival else cum
+            data.append([xs[i], y])
+            i += run
+        kw = dict(step=step_style, lineStyle={"width": line_width}, itemStyle={"color": color})
+        if not show_symbol or n == 0:
+            kw["showSymbol"] = False
+        if area_opacity > 0:
+            kw["areaStyle"] = {"opacity": area_opacity / 100}
+        if show_labels:
+            kw["label"] = {"show": True, "position": "top", "formatter": label_fmt}
+        return self._add("line", name, data if n else [[0, 0]], **kw)
+
+    def add_survival_series(self, name, samples, color, normalized=True, step_style="end", show_symbol=False,
+                            line_width=2, area_opacity=0, show_labels=False, label_fmt="{c}"):
+        return self.add_ecdf_series(name, samples, color, True, normalized, step_style, show_symbol, line_width,
+                                    area_opacity, show_labels, label_fmt)
+
+    def add_streamlines_series(self, name, polylines_x, polylines_y, color="#5470C6", width=1, opacity=85,
+                               show_effect=True, effect_speed=20, effect_size=2, trail_length=30):
+        """Polylines on the cartesian grid (``lines`` series), optionally with the moving-dot effect; lines with fewer
+        than two points or mismatched coordinate lists are skipped."""
+        data = [{"coords": [[x, y] for x, y in zip(px, py)]} for px, py in zip(polylines_x, polylines_y)
+                if len(px) > 1 and len(px) == len(py)]
+        effect = {"show": True, "constantSpeed": effect_speed, "trailLength": trail_length / 100,
+                  "symbolSize": effect_size} if show_effect else None
+        return self._add("lines", name, data, coordinateSystem="cartesian2d", polyline=True,
+                         lineStyle={"color": color, "width": width, "opacity": opacity / 100}, effect=effect)
 
     def add_boxplot_series_from_fivenum(self, name, fivenums, color=None):
         return self._add("boxplot", name, [list(f) for f in fivenums], itemStyle={"borderColor": color} if color else None)
