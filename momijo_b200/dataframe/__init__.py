@@ -13,3 +13,4 @@ from .relational import *  # noqa: F401,F403,E402
 from .relational import eval, get  # noqa: F401,E402
 from .ops import range, filter, where, copy, rename  # noqa: F401,E402,F811
 from .frame import bool_ as bool  # noqa: F401,E402,F811
+from . import methods  # noqa: F401,E402  (binds the method spellings onto the classes above)

@@ -70,7 +70,7 @@ class Value:
 
 class Bitmap:
     def __init__(self, n=0, fill=True):
-        self.bits = [fill] * n
+        self.bits = [bool(fill)] * max(n, 0)
 
     def set(self, i, v=True):
         self.bits[i] = v
