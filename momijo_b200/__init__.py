@@ -10,3 +10,6 @@ Sub-packages
 __version__ = "0.1.0"
 
 from . import _C  # noqa: F401
+from . import _layout as _layout  # noqa: F401,E402
+
+_layout.install()       # reference module paths served from consolidated modules (``dataframe.series_bool`` ...)

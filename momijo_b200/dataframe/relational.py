@@ -877,3 +877,14 @@ def argsort_city_ts(df: DataFrame, city_col: str = "city", ts_col: str = "ts") -
 def rolling_mean(values, window: int):
     from .window import rolling_mean_f64
     return rolling_mean_f64(values, window)
+
+
+def add_schema(acc: "Acc", df: DataFrame, suffix: str = "") -> None:
+    """Function form of ``Acc.add_schema`` (the reference writes it at module level with the accumulator as its first
+    argument, legacy/src/momijo/dataframe/join.mojo:140-171)."""
+    acc.add_schema(df, suffix)
+
+
+def append_row(acc: "Acc", df: DataFrame, row: int, valid_row: bool = True) -> None:
+    """Function form of ``Acc.append_row`` (join.mojo:175-230)."""
+    acc.append_row(df, row, valid_row)

@@ -79,3 +79,7 @@ def __getattr__(name):
     value = getattr(importlib.import_module(f"..parallel.{mod}", __name__), name)
     globals()[name] = value
     return value
+
+from .. import _layout as _layout  # noqa: E402
+
+_layout.link_siblings("learn")   # names the reference keeps in another file of this package still resolve

@@ -38,3 +38,7 @@ from .device import Device, RuntimeDeviceContext, ScopedDevice, to_device, devic
 from .tensor_dyn import AnyTensor, AnyBuffer, TensorView  # noqa: F401
 from . import tensor_methods  # noqa: F401  (binds the method spellings onto Tensor)
 from . import nanops, printing, helpers, math, indexing, transform, axis, io, cast, creation, broadcast, autograd, device, errors, dtype  # noqa: F401
+
+from .. import _layout as _layout  # noqa: E402
+
+_layout.link_siblings("tensor")   # names the reference keeps in another file of this package still resolve

@@ -71,6 +71,9 @@ def write_plane(x, axis: int, index: int, plane):
     return x
 
 
+write_planeT = write_plane      # the reference spells one overload this way (legacy/src/momijo/tensor/helpers.mojo:753)
+
+
 class XorShift64:
     def __init__(self, seed: int = 88172645463325252):
         self.s = (seed or 88172645463325252) & ((1 << 64) - 1)

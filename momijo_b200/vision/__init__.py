@@ -47,3 +47,7 @@ def supports_windows() -> bool:
 
 def destroy_all_windows() -> None:
     return None
+
+from .. import _layout as _layout  # noqa: E402
+
+_layout.link_siblings("vision")   # names the reference keeps in another file of this package still resolve

@@ -10,3 +10,9 @@ from .misc import (ChartExporter, EChartsConfig, EChartsExporter, Figure, export
 from .option import EasyOption, Option, series_bar, series_line  # noqa: F401
 from .plotting import *  # noqa: F401,F403
 from .plotting import _compute_violin_curve_json, _ints  # noqa: F401
+
+from .. import _layout as _layout  # noqa: E402
+
+_layout.open_submodules()   # ``visual.core.core``, ``visual.misc.bar`` ... resolve as facades of these modules
+
+_layout.link_siblings("visual")   # names the reference keeps in another file of this package still resolve
