@@ -167,8 +167,9 @@ def prepare(model, qconfig: QConfig | None = None) -> Prepared:
     return Prepared(model)
 
 
-def convert(prepared: Prepared) -> Converted:
-    """Swap every observed ``Linear`` for a ``QuantLinear`` with symmetric int8 weights."""
+def convert(prepared: Prepared, inplace: bool = False) -> Converted:
+    """Swap every observed ``Linear`` for a ``QuantLinear`` with symmetric int8 weights. ``inplace`` is accepted for
+    the reference's signature and, as there, changes nothing (legacy/src/momijo/learn/api/sequential.mojo:436-459)."""
     for h in prepared._handles:
         h.remove()
     model = prepared.model

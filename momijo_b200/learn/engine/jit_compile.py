@@ -72,7 +72,14 @@ def compile(model, options: JITOptions | None = None):
     return model
 
 
-def compile_with(model, options: JITOptions) -> GraphExecutor:
+def compile_with(model, options: JITOptions, report: "JITReport" = None) -> GraphExecutor:
+    """``report``, when given, is filled in place like the reference's out-parameter
+    (legacy/src/momijo/learn/engine/jit_compile.mojo:121-135)."""
+    if report is not None:
+        report.graph_enabled = bool(options.graph)
+        for k in ("passes_applied", "lowered_ops"):
+            if hasattr(report, k):
+                setattr(report, k, 0)
     return GraphExecutor(model, options)
 
 

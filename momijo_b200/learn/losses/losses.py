@@ -130,3 +130,29 @@ def cosine_embedding_loss(x1, x2, target, margin: float = 0.0, eps: float = 1e-1
     n2 = ((x2 * x2).sum() + eps).sqrt()
     cos = dot / (n1 * n2)
     return torch.where(target > 0, 1.0 - cos, (cos - margin).clamp_min(0)).mean()
+
+
+# ---- the reference's tensor forms under their own names (legacy/src/momijo/learn/losses/losses.mojo:127-246) -----------
+def mse_loss(pred, target, reduction="mean"):
+    return mse(pred, target, reduction)
+
+
+def focal_loss(logits, target_index, gamma: float = 2.0, alpha=None, axis: int = -1, eps: float = 1e-12):
+    """Mean cross-entropy scaled by the batch mean of ``(1 - p_t)^gamma`` (and by ``alpha`` when given), ``p_t`` the
+    softmax probability of the true class clipped to ``[eps, 1]`` (losses.mojo:206-238). ``target_index`` holds class
+    indices."""
+    lg = logits if isinstance(logits, torch.Tensor) else torch.tensor(logits, dtype=torch.float32)
+    tg = (target_index if isinstance(target_index, torch.Tensor) else torch.tensor(target_index)).long()
+    if axis not in (-1, lg.dim() - 1):
+        lg = lg.movedim(axis, -1)
+    sm = torch.softmax(lg.float(), -1).clamp(eps, 1.0)
+    pt = sm.gather(-1, tg.unsqueeze(-1)).squeeze(-1)
+    ce = -(pt.log()).mean()
+    return ce * (1.0 if alpha is None else float(alpha)) * ((1.0 - pt) ** gamma).mean()
+
+
+def dice_loss(pred, target, eps: float = 1e-6):
+    """``1 - 2 * sum(p * t) / (sum(p) + sum(t) + eps)`` over all elements (losses.mojo:240-248)."""
+    p = pred if isinstance(pred, torch.Tensor) else torch.tensor(pred, dtype=torch.float32)
+    t = target if isinstance(target, torch.Tensor) else torch.tensor(target, dtype=torch.float32)
+    return 1.0 - 2.0 * (p * t).sum() / (p.sum() + t.sum() + eps)

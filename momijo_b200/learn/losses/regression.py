@@ -10,25 +10,32 @@ def _out(r, like):
     return r if isinstance(like, torch.Tensor) else (r.tolist() if r.dim() else float(r))
 
 
-def _red(x, reduction):
+def _red(x, reduction, sample_weight=None):
+    """``sample_weight`` scales each element; the weighted mean divides by the weight sum
+    (legacy/src/momijo/learn/losses/regression.mojo:143-185)."""
+    if sample_weight is not None:
+        w = _t(sample_weight).to(x.dtype)
+        x = x * w
+        if reduction == "mean":
+            return x.sum() / w.sum().clamp_min(1e-300)
     return x.mean() if reduction == "mean" else (x.sum() if reduction == "sum" else x)
 
 
-def mse_loss(pred, target, reduction="mean"):
-    return _out(_red((_t(pred) - _t(target)) ** 2, reduction), pred)
+def mse_loss(pred, target, reduction="mean", sample_weight=None):
+    return _out(_red((_t(pred) - _t(target)) ** 2, reduction, sample_weight), pred)
 
 
-def mae_loss(pred, target, reduction="mean"):
-    return _out(_red((_t(pred) - _t(target)).abs(), reduction), pred)
+def mae_loss(pred, target, reduction="mean", sample_weight=None):
+    return _out(_red((_t(pred) - _t(target)).abs(), reduction, sample_weight), pred)
 
 
 def rmse_loss(pred, target):
     return _out(((_t(pred) - _t(target)) ** 2).mean().sqrt(), pred)
 
 
-def huber_loss(pred, target, delta=1.0, reduction="mean"):
+def huber_loss(pred, target, delta=1.0, reduction="mean", sample_weight=None):
     d = (_t(pred) - _t(target)).abs()
-    return _out(_red(torch.where(d <= delta, 0.5 * d * d, delta * (d - 0.5 * delta)), reduction), pred)
+    return _out(_red(torch.where(d <= delta, 0.5 * d * d, delta * (d - 0.5 * delta)), reduction, sample_weight), pred)
 
 
 def smooth_l1_loss(pred, target, beta=1.0, reduction="mean"):

@@ -6,11 +6,11 @@ def _t(x):
     return x if isinstance(x, torch.Tensor) else torch.tensor(x)
 
 
-def accuracy(pred, target) -> float:
-    """``pred`` may be class indices or [N, C] scores."""
+def accuracy(pred, target, axis: int = -1) -> float:
+    """``pred`` may be class indices or scores with the classes along ``axis``."""
     p, t = _t(pred), _t(target)
     if p.dim() == t.dim() + 1:
-        p = p.argmax(-1)
+        p = p.argmax(axis)
     return float((p == t).float().mean()) if p.numel() else 0.0
 
 

@@ -18,9 +18,13 @@ def mae(pred, target):
     return float((_t(pred) - _t(target)).abs().mean())
 
 
-def mape(pred, target, eps=1e-12):
+def mape(pred, target, scale=1.0, eps=1e-12):
+    """Mean absolute relative error times ``scale`` (the reference's default scale is 100, a percentage; this
+    package's default stays a fraction). A small second positional value is read as ``eps`` for earlier callers."""
+    if scale < 1e-3:
+        scale, eps = 1.0, scale
     t = _t(target)
-    return float(((_t(pred) - t).abs() / t.abs().clamp_min(eps)).mean())
+    return float(((_t(pred) - t).abs() / t.abs().clamp_min(eps)).mean()) * scale
 
 
 def r2_score(pred, target):

@@ -27,14 +27,26 @@ def _pair(v):
     return (v, v) if isinstance(v, int) else tuple(v)
 
 
-def im2col(x, kernel, stride=(1, 1), pad=(0, 0)):
-    """[N, C, H, W] -> [N * OH * OW, C * kH * kW] (rows ordered n, oh, ow)."""
+def _ref_window_args(kernel, stride, pad, extra):
+    """The reference passes ``kH, kW, stride, padding`` as four integers; here the kernel is one pair. Four integers
+    are recognised by ``extra`` being given."""
+    if extra is not None:
+        return (kernel, stride), pad, extra
+    return kernel, stride, pad
+
+
+def im2col(x, kernel, stride=(1, 1), pad=(0, 0), padding=None):
+    """[N, C, H, W] -> [N * OH * OW, C * kH * kW] (rows ordered n, oh, ow). Also callable as
+    ``im2col(x, kH, kW, stride, padding)`` (legacy/src/momijo/learn/nn/functional.mojo:285)."""
+    kernel, stride, pad = _ref_window_args(kernel, stride, pad, padding)
     kernel, stride, pad = _pair(kernel), _pair(stride), _pair(pad)
     cols = tF.unfold(x, kernel, padding=pad, stride=stride)  # [N, C*kH*kW, L]
     return cols.transpose(1, 2).reshape(-1, cols.shape[1])
 
 
-def col2im(cols, x_shape, kernel, stride=(1, 1), pad=(0, 0)):
+def col2im(cols, x_shape, kernel, stride=(1, 1), pad=(0, 0), padding=None):
+    """Inverse of ``im2col`` (overlaps add up); also ``col2im(cols, x_shape, kH, kW, stride, padding)``."""
+    kernel, stride, pad = _ref_window_args(kernel, stride, pad, padding)
     kernel, stride, pad = _pair(kernel), _pair(stride), _pair(pad)
     N, C, H, W = x_shape
     c = cols.reshape(N, -1, cols.shape[1]).transpose(1, 2)
@@ -62,8 +74,18 @@ def conv2d_naive(x, w, b=None, stride=(1, 1), pad=(0, 0)):
     return y
 
 
-def conv2d(x, w, b=None, stride=(1, 1), pad=(0, 0)):
-    """im2col + GEMM convolution; ``w`` is [OC, C, kH, kW]."""
+def conv2d(x, w, b=None, stride=(1, 1), pad=(0, 0), dilation=1):
+    """im2col + GEMM convolution; ``w`` is [OC, C, kH, kW]. The reference's two other call forms are accepted
+    (legacy/src/momijo/learn/nn/functional.mojo:117-124, 472): nested lists ``conv2d(x, weight, bias, stride, padding,
+    dilation)`` returning lists, and the bias-free tensor form ``conv2d(x, w, stride, padding)``."""
+    if isinstance(b, int):                                   # conv2d(x, w, stride, padding)
+        b, stride, pad = None, b, (stride if isinstance(stride, int) else 0)
+    if not isinstance(x, torch.Tensor):
+        xt, wt = torch.tensor(x, dtype=torch.float32), torch.tensor(w, dtype=torch.float32)
+        bt = torch.tensor(b, dtype=torch.float32) if b is not None and len(b) else None
+        return tF.conv2d(xt, wt, bt, _pair(stride), _pair(pad), _pair(dilation)).tolist()
+    if _pair(dilation) != (1, 1):
+        return tF.conv2d(x, w, b if (b is not None and b.numel()) else None, _pair(stride), _pair(pad), _pair(dilation))
     stride, pad = _pair(stride), _pair(pad)
     if x.is_cuda and x.dtype == torch.bfloat16:
         N, C, H, W = x.shape
@@ -101,13 +123,27 @@ def separable_conv2d(x, w_depth, w_point, b=None, stride=(1, 1), pad=(0, 0)):
     return pointwise_conv2d(depthwise_conv2d(x, w_depth, None, stride, pad), w_point, b)
 
 
-def max_pool2d(x, kernel, stride=(1, 1), pad=(0, 0)):
-    """Reference default stride is 1, not the kernel size (legacy/.../nn/conv.mojo:29-46)."""
-    return tF.max_pool2d(x, _pair(kernel), _pair(stride), _pair(pad))
+def max_pool2d(x, kernel, stride=(1, 1), pad=(0, 0), ceil_mode: bool = False):
+    """Reference default stride is 1, not the kernel size (legacy/.../nn/conv.mojo:29-46); a stride of 0 means the
+    kernel size, as in the list form (functional.mojo:185-196). Nested lists are accepted and returned as lists."""
+    as_list = not isinstance(x, torch.Tensor)
+    xt = torch.tensor(x, dtype=torch.float32) if as_list else x
+    k = _pair(kernel)
+    st = k if stride in (0, (0, 0)) else _pair(stride)
+    y = tF.max_pool2d(xt, k, st, _pair(pad), ceil_mode=bool(ceil_mode))
+    return y.tolist() if as_list else y
 
 
-def linear_mse_grads(x, w, b, y_true):
-    """Gradients of mean((x W^T + b - y)^2) with respect to (W, b)."""
+def linear_mse_grads(x, w, b, y_true, dB=None):
+    """Gradients of mean((x W^T + b - y)^2) with respect to (W, b). The reference's five-argument form
+    ``linear_mse_grads(x, y_hat, y, dW, dB)`` fills ``dW`` and ``dB`` in place from the prediction
+    (legacy/src/momijo/learn/nn/functional.mojo:747-785)."""
+    if dB is not None:
+        y_hat, y, dW = w, b, y_true
+        diff = 2.0 * (y_hat - y) / y_hat.numel()
+        dW.copy_(diff.t() @ x)
+        dB.copy_(diff.sum(0))
+        return dW, dB
     pred = x @ w.t() + b
     diff = 2.0 * (pred - y_true) / pred.numel()
     return diff.t() @ x, diff.sum(0)

@@ -29,8 +29,10 @@ def global_max_pool2d(x):
     return x.amax((2, 3), keepdim=True)
 
 
-def adaptive_avg_pool2d(x, output_size):
-    return tF.adaptive_avg_pool2d(x, _pair(output_size))
+def adaptive_avg_pool2d(x, output_size, out_w=None):
+    """``adaptive_avg_pool2d(x, (oh, ow))`` or the reference's ``adaptive_avg_pool2d(x, out_h, out_w)``
+    (legacy/src/momijo/learn/nn/pool.mojo:254-256)."""
+    return tF.adaptive_avg_pool2d(x, _pair(output_size) if out_w is None else (output_size, out_w))
 
 
 def max_unpool2d(y, indices, kernel, stride=None, pad=(0, 0), output_size=None):
@@ -38,8 +40,18 @@ def max_unpool2d(y, indices, kernel, stride=None, pad=(0, 0), output_size=None):
     return tF.max_unpool2d(y, indices, k, _pair(stride) if stride is not None else k, _pair(pad), output_size)
 
 
-def avg_unpool2d(y, kernel, stride=None):
-    """Spread each pooled value uniformly over its (non-overlapping) window."""
+def avg_unpool2d(y, kernel, stride=None, padding: int = 0, y_shape=None):
+    """Spread each pooled value uniformly over its window. With ``y_shape`` (the reference's form,
+    legacy/src/momijo/learn/nn/pool.mojo:341-395) windows may overlap or hang over the border: each value is divided
+    by the number of in-bounds cells of its window and the shares add up; this is the gradient of average pooling
+    that counts in-bounds cells only."""
+    if y_shape is not None:
+        import torch
+        k = _pair(kernel)
+        s = k if not stride else _pair(stride)
+        ref = torch.zeros(list(y_shape), dtype=y.dtype, device=y.device, requires_grad=True)
+        pooled = tF.avg_pool2d(ref, k, s, _pair(padding), count_include_pad=False)
+        return torch.autograd.grad(pooled, ref, y)[0]
     k = _pair(kernel)
     s = _pair(stride) if stride is not None else k
     up = y.repeat_interleave(s[0], 2).repeat_interleave(s[1], 3)

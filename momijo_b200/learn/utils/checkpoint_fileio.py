@@ -20,8 +20,12 @@ def save_checkpoint_files(net, header_path: str, blob_path: str) -> bool:
         return False
 
 
-def load_checkpoint_files(header_path: str, blob_path: str):
-    """-> (ok, header, blob tensor)."""
+def load_checkpoint_files(header_path, blob_path: str = None, blob_path_ref: str = None):
+    """``load_checkpoint_files(header_path, blob_path)`` -> (ok, header, blob tensor); the reference's
+    ``load_checkpoint_files(net, header_path, blob_path)`` loads into ``net`` and returns whether that worked
+    (legacy/src/momijo/learn/utils/checkpoint_fileio.mojo:102-114)."""
+    if blob_path_ref is not None:
+        return load_into(header_path, blob_path, blob_path_ref)
     if not (os.path.exists(header_path) and os.path.exists(blob_path)):
         return False, "", torch.zeros(0)
     with open(header_path) as f:
