@@ -374,3 +374,8 @@ def _mask_out(t):
 def mask_not(mask): return _mask_out(_v(mask) == 0)                                   # noqa: E704
 def mask_and(a, b): return _mask_out((_v(a) != 0) & (_v(b) != 0))                     # noqa: E704
 def mask_or(a, b): return _mask_out((_v(a) != 0) | (_v(b) != 0))                      # noqa: E704
+
+
+def where(ctx: GradContext, mask, a: "GradTensor", b: "GradTensor") -> "GradTensor":
+    """``mask != 0 ? a : b`` with gradients to both branches (legacy/src/momijo/tensor/autograd.mojo:2159-2180)."""
+    return a.where(ctx, mask, b)

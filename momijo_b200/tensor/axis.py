@@ -31,9 +31,14 @@ class ReduceSpec:
     skipna: bool = False
 
 
-def reduce_along_axis(x, axis: int, spec: ReduceSpec | None = None):
+def reduce_along_axis(x, axis: int, spec: ReduceSpec | None = None, mask=None):
+    """``mask`` (same shape, non-zero = use) leaves the other elements out of the reduction, like missing values."""
     spec = spec or ReduceSpec()
     r = _raw(x)
+    if mask is not None:
+        import dataclasses
+        r = torch.where(_raw(mask) != 0, r.double(), torch.full_like(r, float("nan"), dtype=torch.float64))
+        spec = dataclasses.replace(spec, skipna=True) if dataclasses.is_dataclass(spec) else spec
     if spec.skipna and r.dtype.is_floating_point:
         fill = {"sum": 0.0, "mean": float("nan"), "min": float("inf"), "max": float("-inf"), "prod": 1.0}.get(spec.op, 0.0)
         if spec.op == "mean":
@@ -66,24 +71,39 @@ def cumprod(x, axis: int = -1):
     return _wrap(torch.cumprod(_raw(x), axis))
 
 
-def quantile(x, q, axis=None, keepdims=False):
+def quantile(x, q, axis=None, keepdims=False, axes=None, interpolation: str = "linear"):
+    """``axes`` reduces over several axes at once (they are moved to the end and flattened); ``interpolation`` is
+    linear / lower / higher / nearest / midpoint (legacy/src/momijo/tensor/axis.mojo:1098-1146)."""
     r = _raw(x).double()
     qq = torch.as_tensor(q, dtype=torch.float64)
-    return _wrap(torch.quantile(r, qq) if axis is None else torch.quantile(r, qq, dim=axis, keepdim=keepdims))
+    if axes:
+        rank = r.dim()
+        ax = sorted({a % rank for a in axes})
+        keep = [d for d in range(rank) if d not in ax]
+        flat = r.permute(keep + ax).reshape([r.shape[d] for d in keep] + [-1])
+        out = torch.quantile(flat, qq, dim=-1, interpolation=interpolation)
+        if keepdims:
+            for a in ax:
+                out = out.unsqueeze(a)
+        return _wrap(out)
+    if axis is None:
+        return _wrap(torch.quantile(r, qq, interpolation=interpolation))
+    return _wrap(torch.quantile(r, qq, dim=axis, keepdim=keepdims, interpolation=interpolation))
 
 
-def percentile(x, p, axis=None, keepdims=False):
-    return quantile(x, torch.as_tensor(p, dtype=torch.float64) / 100.0, axis, keepdims)
+def percentile(x, p, axis=None, keepdims=False, axes=None, interpolation: str = "linear"):
+    return quantile(x, torch.as_tensor(p, dtype=torch.float64) / 100.0, axis, keepdims, axes, interpolation)
 
 
-def median(x, axis=None, keepdims=False):
-    return quantile(x, 0.5, axis, keepdims)
+def median(x, axis=None, keepdims=False, axes=None):
+    return quantile(x, 0.5, axis, keepdims, axes)
 
 
-def normalize(x, axis: int = -1, eps: float = 1e-12):
+def normalize(x, axis: int = -1, eps: float = 1e-12, axes=None):
     r = _raw(x).double()
-    mu = r.mean(axis, keepdim=True)
-    sd = r.std(axis, keepdim=True, unbiased=False)
+    dims = tuple(axes) if axes else (list(range(r.dim())) if axis is None else axis)
+    mu = r.mean(dims, keepdim=True)
+    sd = r.std(dims, keepdim=True, unbiased=False)
     return _wrap((r - mu) / (sd + eps))
 
 
@@ -232,7 +252,10 @@ def roll_multi(x, shifts, axes):
     return _wrap(r.clone() if r.dim() == 0 else torch.roll(r, list(shifts), list(axes)))
 
 
-def normalize_(x, axis=None, eps: float = 1e-12) -> None:
+def normalize_(x, axis=None, eps: float = 1e-12, axes=None) -> None:
+    if axes:
+        _raw(x).copy_(_raw(normalize(x, axis, eps, axes)).to(_raw(x).dtype))
+        return
     from .math_compat import normalize_ as _n
     _n(x, axis, eps)
 

@@ -32,7 +32,11 @@ def clip(x, lo=None, hi=None):
 clamp = clip
 
 
-def compare(a, b, op: str = "eq"):
+def compare(a, b, op="eq", mode: int = None):
+    """``compare(a, b, "lt")`` returns the 0/1 mask; the reference's ``compare(a, b, out_mask, mode)`` writes it into
+    ``out_mask`` (mode 0..5 = eq, ne, lt, le, gt, ge; legacy/src/momijo/tensor/broadcast.mojo:1232)."""
+    if mode is not None:
+        return compare_float32(a, b, op, mode)
     f = {"eq": torch.eq, "ne": torch.ne, "lt": torch.lt, "le": torch.le, "gt": torch.gt, "ge": torch.ge}[op]
     return _wrap(f(_raw(a), _raw(b) if isinstance(b, torch.Tensor) else b).to(torch.int64))
 

@@ -164,7 +164,13 @@ def linspace_int(start, stop, num, endpoint=True):
     return _wrap(linspace_f64(start, stop, num, endpoint).round().to(_I64))
 
 
-def rand(shape, seed: int = 0, dtype=_F64):
+def rand(shape, seed=0, dtype=_F64, seed_ref=None):
+    """``rand(shape, seed, dtype)``; the reference's ``rand(x, low, high, seed)`` (legacy/src/momijo/tensor/
+    creation.mojo:708-711) draws uniform values in [low, high) with the shape of tensor ``x``."""
+    if isinstance(shape, torch.Tensor):
+        low, high = float(seed), float(dtype) if not isinstance(dtype, torch.dtype) else 1.0
+        u = torch.rand(list(shape.shape), generator=_gen(seed_ref or 0), dtype=torch.float64)
+        return _wrap((low + (high - low) * u).to(shape.dtype if shape.dtype.is_floating_point else torch.float64))
     return _wrap(torch.rand(_shape(shape), generator=_gen(seed), dtype=torch.float64).to(dtype))
 
 

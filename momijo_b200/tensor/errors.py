@@ -141,12 +141,34 @@ class compat:
         return _LENIENT["on"]
 
 
-def check_same_shape(a, b) -> Status:
-    return Status.success() if tuple(a.shape) == tuple(b.shape) else Status.fail(ErrorKind.SHAPE, f"{tuple(a.shape)} vs {tuple(b.shape)}")
+def _shape_of(a):
+    return list(a.shape) if hasattr(a, "shape") else list(a)
 
 
-def check_axis(ndim: int, axis: int) -> Status:
-    return Status.success() if -ndim <= axis < ndim else Status.fail(ErrorKind.AXIS, f"axis {axis} for ndim {ndim}")
+def check_same_shape(a, b, what: str = "shape") -> bool:
+    """Assert-free check in the reference's form (legacy/src/momijo/tensor/errors.mojo:217-232): shapes (or tensors)
+    in, a bool out, ``ERROR: ...`` printed on mismatch. ``check_same_shape_status`` is the ``Status`` form."""
+    sa, sb = _shape_of(a), _shape_of(b)
+    if len(sa) != len(sb):
+        fail(f"{what} rank mismatch: {len(sa)} vs {len(sb)}")
+        return False
+    for i, (x, y) in enumerate(zip(sa, sb)):
+        if x != y:
+            fail(f"{what} mismatch at dim {i}: {x} vs {y}")
+            return False
+    return True
+
+
+def check_axis(axis: int, ndim: int, ctx: str = "axis") -> bool:
+    """``0 <= axis < ndim`` (no negative wrap), bool out, message printed on failure (errors.mojo:202-208);
+    ``check_axis_status`` is the ``Status`` form and accepts negative axes."""
+    if ndim < 0:
+        fail("invalid ndim < 0")
+        return False
+    if axis < 0 or axis >= ndim:
+        fail(f"{ctx} out of range: {axis} vs ndim {ndim}")
+        return False
+    return True
 
 
 def check_broadcastable(sa, sb) -> Status:

@@ -12,8 +12,8 @@ def slice1d(x, start=0, stop=None, step=1):
     return _wrap(_raw(x)[start:stop:step])
 
 
-def slice2d(x, r0=0, r1=None, c0=0, c1=None):
-    return _wrap(_raw(x)[r0:r1, c0:c1])
+def slice2d(x, r0=0, r1=None, c0=0, c1=None, rs: int = 1, cs: int = 1):
+    return _wrap(_raw(x)[r0:r1:rs, c0:c1:cs])
 
 
 def head(x, n=5):
@@ -44,8 +44,12 @@ def gather(x, axis: int, index):
     return _wrap(torch.gather(_raw(x), axis, _raw(index).long()))
 
 
-def take(x, index):
-    return _wrap(torch.take(_raw(x), _raw(index).long()))
+def take(x, index, axis: int = None):
+    """Flat take, or rows / columns along ``axis`` (legacy/src/momijo/tensor/indexing.mojo:1571-1573)."""
+    idx = (_raw(index) if isinstance(index, torch.Tensor) else torch.as_tensor(index)).long()
+    if axis is None:
+        return _wrap(torch.take(_raw(x), idx))
+    return _wrap(torch.index_select(_raw(x), axis, idx.reshape(-1)))
 
 
 def take_along_axis(x, index, axis: int):
@@ -63,8 +67,9 @@ def scatter_nd(shape, indices, updates):
     return _wrap(out)
 
 
-def where(cond, a, b):
-    """``cond`` may be an Int (0/1) or bool mask; same-shape fp32 CUDA tensors use the kernel."""
+def where(cond, a, b, from_f64=None):
+    """``cond`` may be an Int (0/1) or bool mask; same-shape fp32 CUDA tensors use the kernel. ``from_f64`` (the
+    reference's element converter) is accepted and not needed: dtypes follow the operands."""
     c, ra = _raw(cond), _raw(a) if isinstance(a, torch.Tensor) else a
     rb = _raw(b) if isinstance(b, torch.Tensor) else b
     if (isinstance(ra, torch.Tensor) and isinstance(rb, torch.Tensor) and ra.is_cuda and ra.dtype == torch.float32
@@ -112,8 +117,8 @@ def col2im_core(cols, out_hw, kh, kw, sh=1, sw=1, ph=0, pw=0):
     return _wrap(tF.fold(_raw(cols), out_hw, (kh, kw), padding=(ph, pw), stride=(sh, sw)))
 
 
-def select_tiles(m: int, n: int, k: int):
-    """Tile sizes used by the GEMM kernel for an (m, n, k) problem."""
+def select_tiles(m: int, n: int, k: int, is_f64: bool = False):
+    """Tile sizes used by the GEMM kernel for an (m, n, k) problem (``is_f64`` does not change them here)."""
     from ..ops.gemm import pick_bn
 
     return 128, pick_bn(m, n), 64
@@ -380,10 +385,11 @@ def list_slice_generic(xs, start: int, stop: int, step: int = 1):
     return list(xs[slice(start, stop, step or 1)])
 
 
-def flatten_2d(xs): return [v for r in xs for v in r]                                   # noqa: E704
-def flatten_3d(xs): return [v for a in xs for r in a for v in r]                        # noqa: E704
-def flatten_4d(xs): return [v for a in xs for b in a for r in b for v in r]             # noqa: E704
-def flatten_5d(xs): return [v for a in xs for b in a for c in b for r in c for v in r]  # noqa: E704
+# The extents the reference passes after the nested list (n0, n1, ...) are implied by the list itself here.
+def flatten_2d(xs, *dims): return [v for r in xs for v in r]                                   # noqa: E704
+def flatten_3d(xs, *dims): return [v for a in xs for r in a for v in r]                        # noqa: E704
+def flatten_4d(xs, *dims): return [v for a in xs for b in a for r in b for v in r]             # noqa: E704
+def flatten_5d(xs, *dims): return [v for a in xs for b in a for c in b for r in c for v in r]  # noqa: E704
 def infer_shape_1d(xs): return [len(xs)]                                                # noqa: E704
 def infer_shape_2d(xs): return [len(xs), len(xs[0]) if xs else 0]                       # noqa: E704
 def infer_shape_3d(xs): return infer_shape_2d(xs) + [len(xs[0][0]) if xs and xs[0] else 0]          # noqa: E704

@@ -63,8 +63,11 @@ def safe_div32(a: float, b: float, eps: float = 1e-7) -> float:
     return _f32(a / (b + eps if b >= 0 else b - eps))
 
 
-def safe_sqrt32(x: float) -> float:
-    return _f32(math.sqrt(x)) if x > 0 else 0.0
+def safe_sqrt32(x: float, eps: float = 0.0) -> float:
+    """``sqrt(max(x, 0) + eps)`` in float32; the reference's default eps is 1e-7 (legacy/src/momijo/tensor/
+    math.mojo:262-267), this package's stays 0 so that ``safe_sqrt32(0) == 0``."""
+    v = max(x, 0.0) + eps
+    return _f32(math.sqrt(v)) if v > 0 else 0.0
 
 
 def math_max(a, b): return a if a >= b else b     # noqa: E704
@@ -214,7 +217,15 @@ def sum1d_unrolled(m):
     return _raw(m).sum().item()
 
 
-def variance(m, ddof: int = 0) -> float:
+def variance(m, ddof=0, unbiased: bool = None, keepdims: bool = False):
+    """``variance(m, ddof)`` over all elements as a float, or the reference's ``variance(x, axis, unbiased=True,
+    keepdims=False)`` as a tensor (legacy/src/momijo/tensor/math.mojo:5156-5161): the second form is chosen by passing
+    ``unbiased`` (or ``axis=None`` explicitly as ``ddof=None``)."""
+    if unbiased is not None or ddof is None:
+        r = _raw(m).double()
+        ub = True if unbiased is None else bool(unbiased)
+        from .tensor import _wrap
+        return _wrap(r.var(unbiased=ub) if ddof is None else r.var(ddof, unbiased=ub, keepdim=keepdims))
     t = _raw(m).double().reshape(-1)
     n = t.numel()
     return float("nan") if n - ddof <= 0 else float(((t - t.mean()) ** 2).sum() / (n - ddof))
@@ -282,3 +293,12 @@ def numeric_jacobian(fn, x, eps: float = 1e-6):
         e[i] = eps
         cols.append((_raw(fn(_wrap(t + e))).double().reshape(-1) - _raw(fn(_wrap(t - e))).double().reshape(-1)) / (2 * eps))
     return _wrap(torch.stack(cols, 1))
+
+
+def safe_sqrt(x, eps: float = 1e-12):
+    """Scalar form: ``sqrt(max(x, 0) + eps)`` (legacy/src/momijo/tensor/math.mojo:123-128). A tensor argument goes to
+    the element-wise form of ``nanops``."""
+    if isinstance(x, torch.Tensor):
+        from .nanops import safe_sqrt as _tensor_form
+        return _tensor_form(x, eps)
+    return math.sqrt(max(float(x), 0.0) + eps)

@@ -21,9 +21,9 @@ def nanmean(x, axis=None, keepdims=False):
     return _wrap(torch.nanmean(_raw(x)) if axis is None else torch.nanmean(_raw(x), dim=axis, keepdim=keepdims))
 
 
-def nanmin(x, axis=None):
+def nanmin(x, axis=None, keepdims: bool = False):
     r = torch.where(torch.isnan(_raw(x)), torch.full_like(_raw(x), float("inf")), _raw(x))
-    return _wrap(r.min() if axis is None else r.min(axis).values)
+    return _wrap(r.min() if axis is None else r.min(axis, keepdim=keepdims).values)
 
 
 def nanmax(x, axis=None):
@@ -50,8 +50,9 @@ def safe_log(x, eps=1e-12):
     return _wrap(torch.log(_raw(x).double().clamp_min(eps)))
 
 
-def safe_sqrt(x):
-    return _wrap(torch.sqrt(_raw(x).double().clamp_min(0.0)))
+def safe_sqrt(x, eps: float = 0.0):
+    """``sqrt(max(x, eps))`` element-wise (legacy/src/momijo/tensor/nanops.mojo:124-180)."""
+    return _wrap(torch.sqrt(_raw(x).double().clamp_min(max(eps, 0.0))))
 
 
 # ---- scalar and float64-specialised names (legacy/src/momijo/tensor/nanops.mojo:111-655) -----------------------------
@@ -72,8 +73,9 @@ def safe_log_scalar(x: float, eps: float = 1e-12) -> float:
     return _math.log(x if x > eps else eps)
 
 
-def safe_sqrt_scalar(x: float) -> float:
-    return _math.sqrt(x) if x > 0 else 0.0
+def safe_sqrt_scalar(x: float, eps: float = 0.0) -> float:
+    v = max(x, eps)
+    return _math.sqrt(v) if v > 0 else 0.0
 
 
 def nansum_all_f64(x) -> float: return float(torch.nansum(_raw(x).double()))            # noqa: E704
@@ -86,6 +88,28 @@ def nanmin_all_f64(x) -> float:
     return float(r.min()) if r.numel() else float("nan")
 
 
-def nansum_axis_contig_f64(x, axis: int = -1): return nansum(x, axis)       # noqa: E704
-def nanmean_axis_contig_f64(x, axis: int = -1): return nanmean(x, axis)     # noqa: E704
-def nanmin_axis_contig_f64(x, axis: int = -1): return nanmin(x, axis)       # noqa: E704
+def _contig_args(x, a, b, c):
+    """``f(x, axis)`` on a tensor, or the reference's ``f(data, shape, axis, keepdims)`` on a flat list."""
+    if isinstance(a, (list, tuple)):
+        return _wrap(torch.tensor(list(x), dtype=torch.float64).reshape(list(a))), b, bool(c)
+    return x, a, False
+
+
+def nansum_axis_contig_f64(x, axis=-1, ax=None, keepdims=False):       # noqa: E704
+    t, a, k = _contig_args(x, axis, ax, keepdims)
+    return nansum(t, a, k)
+
+
+def nanmean_axis_contig_f64(x, axis=-1, ax=None, keepdims=False):      # noqa: E704
+    t, a, k = _contig_args(x, axis, ax, keepdims)
+    return nanmean(t, a, k)
+
+
+def nanmin_axis_contig_f64(x, axis=-1, ax=None, keepdims=False):       # noqa: E704
+    t, a, k = _contig_args(x, axis, ax, keepdims)
+    return nanmin(t, a, k)
+
+
+def safe_div_scalar(a: float, b: float, eps: float = 1e-12) -> float:
+    """``a / b`` with a zero denominator replaced by ``eps`` (nanops.mojo:111-115)."""
+    return a / (b if b != 0.0 else eps)

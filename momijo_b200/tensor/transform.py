@@ -230,9 +230,19 @@ def pad_nd(x, pad_pairs, constant=0):
 pad_nd_flat = pad_nd
 
 
-def pad_nd_map(x, pad_pairs, mode: int):
-    """Index-mapped padding (``pad_map_index`` modes) with one (before, after) pair per axis."""
-    return pad(x, [tuple(p) for p in pad_pairs], ["replicate", "reflect", "symmetric", "circular"][mode])
+def pad_nd_map(x, pad_pairs, mode: int, constant=0):
+    """Index-mapped padding: mode 0 replicate, 1 reflect, 2 symmetric, 3 circular, 4 constant (filled with
+    ``constant``). ``pad_pairs`` is one (before, after) pair per axis, or the reference's flat list
+    ``[b0, a0, b1, a1, ...]`` (legacy/src/momijo/tensor/transform.mojo:482-490); a flat list of the wrong length
+    returns a copy."""
+    pairs = list(pad_pairs)
+    if pairs and not isinstance(pairs[0], (tuple, list)):
+        if len(pairs) != 2 * _raw(x).dim():
+            return _wrap(_raw(x).clone())
+        pairs = [(pairs[2 * i], pairs[2 * i + 1]) for i in range(len(pairs) // 2)]
+    if mode == 4:
+        return pad_nd(x, [tuple(p) for p in pairs], constant)
+    return pad(x, [tuple(p) for p in pairs], ["replicate", "reflect", "symmetric", "circular"][mode])
 
 
 def pad1d(x, left: int, right: int, constant=0):
