@@ -20,8 +20,16 @@ def compute_row_major_strides(shape) -> List[int]:
 mk_strides = compute_row_major_strides
 
 
-def is_contiguous(shape, strides) -> bool:
-    return list(strides) == compute_row_major_strides(shape)
+def is_contiguous(shape, strides, row_major: bool = True) -> bool:
+    """Strides of a dense layout: row-major, or column-major with ``row_major=False``
+    (legacy/src/momijo/tensor/helpers.mojo:841-860)."""
+    if row_major:
+        return list(strides) == compute_row_major_strides(shape)
+    exp, acc = [], 1
+    for d in shape:
+        exp.append(acc)
+        acc *= d
+    return list(strides) == exp
 
 
 def numel(shape) -> int:
@@ -132,7 +140,12 @@ def min_i(a: int, b: int) -> int: return a if a < b else b                      
 def max_i(a: int, b: int) -> int: return a if a > b else b                               # noqa: E704
 def clamp_nonneg(x: int) -> int: return x if x > 0 else 0                                # noqa: E704
 def ceil_div_pos(a: int, b: int) -> int: return (a + b - 1) // b if b > 0 else 0         # noqa: E704
-def reserve_len(n: int) -> int: return max(n, 0)                                         # noqa: E704
+def reserve_len(xs, n: int = None):
+    """``reserve_len(n)`` clamps a length at 0; the reference's ``reserve_len(list, n)`` appends ``n`` zeros to the list
+    in place (legacy/src/momijo/tensor/helpers.mojo:114-120)."""
+    if n is None:
+        return max(xs, 0)
+    xs.extend([0] * max(n, 0))
 def copy_list(xs): return list(xs)                                                       # noqa: E704
 
 
@@ -142,11 +155,18 @@ copy_list_T = copy_list_int = copy_ints = copy_list
 def copy_flat_list(x): return _flat_list(x)             # noqa: E704
 
 
-setops_copy_flat_list = tolist = copy_flat_list
+setops_copy_flat_list = copy_flat_list
 
 
-def to_int_list(x): return [int(v) for v in _flat_list(x)]        # noqa: E704
-def to_bool_list(x): return [bool(v) for v in _flat_list(x)]      # noqa: E704
+def tolist(x, f=None):
+    """Flat list of the elements, each passed through ``f`` (the reference's converter to Float64) when given."""
+    vals = copy_flat_list(x)
+    return [f(v) for v in vals] if f is not None else vals
+
+
+# ``f`` is the reference's per-element converter; without it the built-in conversion is used.
+def to_int_list(x, f=None): return [(f or int)(v) for v in _flat_list(x)]        # noqa: E704
+def to_bool_list(x, f=None): return [(f or bool)(v) for v in _flat_list(x)]      # noqa: E704
 def tensor_len(x) -> int: return _raw(x).numel()                  # noqa: E704
 def size(x) -> int: return _raw(x).numel() if _is_tensor(x) else len(x)   # noqa: E704
 def dim0_length(x) -> int: return int(_raw(x).shape[0]) if _raw(x).dim() else 1   # noqa: E704
@@ -266,10 +286,16 @@ def ensure_4d(x):
 def is_contiguous_tensor(x) -> bool: return _raw(x).is_contiguous()         # noqa: E704
 
 
-is_row_major_contiguous = is_contiguous_tensor
+def is_row_major_contiguous(x, strides=None) -> bool:
+    """A tensor, or the reference's ``(shape, strides)`` pair (legacy/src/momijo/tensor/helpers.mojo:274-286)."""
+    return is_contiguous_tensor(x) if strides is None else is_contiguous(list(x), list(strides))
 
 
-def is_contig_2d(x) -> bool:
+def is_contig_2d(x, width: int = None) -> bool:
+    """A 2-D tensor, or the reference's ``(strides, width)``: strides equal to ``[width, 1]``
+    (legacy/src/momijo/tensor/helpers.mojo:288-291)."""
+    if width is not None:
+        return list(x) == [width, 1]
     t = _raw(x)
     return t.dim() == 2 and t.is_contiguous()
 
@@ -293,7 +319,14 @@ def astype_with(src, f):
 def astype_float64(x): return _wrap(_raw(x).double())       # noqa: E704
 
 
-astype_via_f64 = astype_float64
+def astype_via_f64(src, to_f64=None, from_f64=None):
+    """Convert element by element through float64: ``from_f64(to_f64(v))`` (legacy/src/momijo/tensor/helpers.mojo:
+    973-1010). Without converters this is the float64 cast."""
+    if to_f64 is None and from_f64 is None:
+        return astype_float64(src)
+    r = _raw(src)
+    vals = [(from_f64 or float)((to_f64 or float)(v)) for v in r.reshape(-1).tolist()]
+    return _wrap(_torch.tensor(vals).reshape(list(r.shape)))
 
 
 def apply_bin_f32(a, b, op_id: int):
@@ -403,9 +436,10 @@ class UniqueResult:
         self.values, self.counts = values, counts
 
 
-def unique(x) -> UniqueResult:
+def unique(x, return_counts: bool = True) -> UniqueResult:
+    """Sorted distinct values; the counts are empty when ``return_counts`` is false."""
     vals, counts = _torch.unique(_raw(x).reshape(-1), sorted=True, return_counts=True)
-    return UniqueResult(_wrap(vals), _wrap(counts))
+    return UniqueResult(_wrap(vals), _wrap(counts if return_counts else counts[:0]))
 
 
 unique_int = unique_float32 = unique_float64 = tensor_unique_int = tensor_unique_f32 = tensor_unique_f64 = unique

@@ -28,12 +28,18 @@ def _fmt(v, dt, prec):
     return repr(float(v)) if prec >= 17 else f"{float(v):.{prec}g}"
 
 
-def _write_csv(x, path, dt, opts):
+def _write_csv(x, path, dt, opts, header=None):
+    """``opts`` is a ``CsvOptions`` or, in the reference's call form ``write_csv_f64(x, path, delim, header)``
+    (legacy/src/momijo/tensor/io.mojo:710-713), the delimiter string followed by the header names."""
+    if isinstance(opts, str):
+        opts = CsvOptions(delimiter=opts)
     opts = opts or CsvOptions()
     r = _raw(x).to(dt).cpu()
     r2 = r.reshape(1, -1) if r.dim() <= 1 else r.reshape(r.shape[0], -1)
     with open(path, "w") as f:
-        if opts.has_header:
+        if header:
+            f.write(opts.delimiter.join(str(h) for h in header) + opts.newline)
+        elif opts.has_header:
             f.write(opts.delimiter.join(f"c{i}" for i in range(r2.shape[1])) + opts.newline)
         for row in r2.tolist():
             f.write(opts.delimiter.join(_fmt(v, dt, opts.precision) for v in row) + opts.newline)
@@ -52,18 +58,19 @@ def _read_csv(path, dt, opts):
     return _wrap(torch.tensor(rows, dtype=dt))
 
 
-def write_csv_f64(x, path, opts=None): return _write_csv(x, path, torch.float64, opts)
-def write_csv_f32(x, path, opts=None): return _write_csv(x, path, torch.float32, opts)
-def write_csv_int(x, path, opts=None): return _write_csv(x, path, torch.int64, opts)
+def write_csv_f64(x, path, opts=None, header=None): return _write_csv(x, path, torch.float64, opts, header)
+def write_csv_f32(x, path, opts=None, header=None): return _write_csv(x, path, torch.float32, opts, header)
+def write_csv_int(x, path, opts=None, header=None): return _write_csv(x, path, torch.int64, opts, header)
 def read_csv_f64(path, opts=None): return _read_csv(path, torch.float64, opts)
 def read_csv_f32(path, opts=None): return _read_csv(path, torch.float32, opts)
 def read_csv_int(path, opts=None): return _read_csv(path, torch.int64, opts)
 
 
-def _write_json(x, path, dt):
+def _write_json(x, path, dt, pretty=False):
     r = _raw(x).to(dt).cpu()
     with open(path, "w") as f:
-        json.dump({"shape": list(r.shape), "dtype": str(dt).replace("torch.", ""), "data": r.reshape(-1).tolist()}, f)
+        json.dump({"shape": list(r.shape), "dtype": str(dt).replace("torch.", ""), "data": r.reshape(-1).tolist()}, f,
+                  indent=2 if pretty else None)
     return True
 
 
@@ -73,16 +80,22 @@ def _read_json(path, dt):
     return _wrap(torch.tensor(d["data"], dtype=dt).reshape(d["shape"]))
 
 
-def write_json_f64(x, path): return _write_json(x, path, torch.float64)
-def write_json_f32(x, path): return _write_json(x, path, torch.float32)
-def write_json_int(x, path): return _write_json(x, path, torch.int64)
+def write_json_f64(x, path, pretty=True): return _write_json(x, path, torch.float64, pretty)
+def write_json_f32(x, path, pretty=True): return _write_json(x, path, torch.float32, pretty)
+def write_json_int(x, path, pretty=True): return _write_json(x, path, torch.int64, pretty)
 def read_json_f64(path): return _read_json(path, torch.float64)
 def read_json_f32(path): return _read_json(path, torch.float32)
 def read_json_int(path): return _read_json(path, torch.int64)
 
 
-def _write_xml(x, path, dt):
+def _write_xml(x, path, dt, root_tag="tensor", row_tag="row", item_tag="v"):
+    """One root element carrying dtype and shape with the values as text. With non-default tags the reference's nested
+    layout ``<root><row><v>..</v>..</row>..</root>`` is written instead (legacy/src/momijo/tensor/io.mojo:729-733)."""
     r = _raw(x).to(dt).cpu()
+    if (root_tag, row_tag, item_tag) != ("tensor", "row", "v"):
+        with open(path, "w") as f:
+            f.write(tensor_to_xml_numbers(_wrap(r), None, root_tag, row_tag, item_tag))
+        return True
     name = str(dt).replace("torch.", "")
     body = " ".join(_fmt(v, dt, 17) for v in r.reshape(-1).tolist())
     with open(path, "w") as f:
@@ -90,23 +103,23 @@ def _write_xml(x, path, dt):
     return True
 
 
-def _read_xml(path, dt):
+def _read_xml(path, dt, row_tag="row", item_tag="v"):
     with open(path) as f:
         s = f.read()
     m = re.search(r'<tensor[^>]*shape="([^"]*)"[^>]*>(.*?)</tensor>', s, re.S)
-    if not m:
-        raise ValueError("not a tensor XML file")
+    if not m or f"<{item_tag}>" in s:
+        return _wrap(_raw(xml_numbers_to_tensor_with(s, None, row_tag, item_tag)).to(dt))
     shape = [int(v) for v in m.group(1).split(",") if v]
     vals = [float(v) if dt != torch.int64 else int(float(v)) for v in m.group(2).split()]
     return _wrap(torch.tensor(vals, dtype=dt).reshape(shape))
 
 
-def write_xml_f64(x, path): return _write_xml(x, path, torch.float64)
-def write_xml_f32(x, path): return _write_xml(x, path, torch.float32)
-def write_xml_int(x, path): return _write_xml(x, path, torch.int64)
-def read_xml_f64(path): return _read_xml(path, torch.float64)
-def read_xml_f32(path): return _read_xml(path, torch.float32)
-def read_xml_int(path): return _read_xml(path, torch.int64)
+def write_xml_f64(x, path, root_tag="tensor", row_tag="row", item_tag="v"): return _write_xml(x, path, torch.float64, root_tag, row_tag, item_tag)  # noqa: E501
+def write_xml_f32(x, path, root_tag="tensor", row_tag="row", item_tag="v"): return _write_xml(x, path, torch.float32, root_tag, row_tag, item_tag)  # noqa: E501
+def write_xml_int(x, path, root_tag="tensor", row_tag="row", item_tag="v"): return _write_xml(x, path, torch.int64, root_tag, row_tag, item_tag)  # noqa: E501
+def read_xml_f64(path, row_tag="row", item_tag="v"): return _read_xml(path, torch.float64, row_tag, item_tag)
+def read_xml_f32(path, row_tag="row", item_tag="v"): return _read_xml(path, torch.float32, row_tag, item_tag)
+def read_xml_int(path, row_tag="row", item_tag="v"): return _read_xml(path, torch.int64, row_tag, item_tag)
 
 
 def save_npz_f64(path, **arrays):

@@ -101,8 +101,9 @@ def to_float64_of(v) -> float:
 to_float32_of_T, to_float64_of_T = to_float32_of, to_float64_of
 
 
-def val_f64(v) -> float:
-    return float(v)
+def val_f64(v, i: int = None) -> float:
+    """``float(v)``, or element ``i`` of a list as a float (legacy/src/momijo/tensor/cast.mojo:5341-5346)."""
+    return float(v) if i is None else float(v[i])
 
 
 def from_float64_to(x: float, f):
