@@ -15,6 +15,9 @@ from .ops import range, filter, where, copy, rename  # noqa: F401,E402,F811
 from .frame import bool_ as bool  # noqa: F401,E402,F811
 from . import methods  # noqa: F401,E402  (binds the method spellings onto the classes above)
 
+int32, int64, float32, float64, string = (methods.DTYPE_CONSTRUCTORS[n] for n in ("int32", "int64", "float32", "float64", "string"))
+bool_ = methods.DTYPE_CONSTRUCTORS["bool"]
+
 from .. import _layout as _layout  # noqa: E402
 
 _layout.link_siblings("dataframe")   # names the reference keeps in another file of this package still resolve

@@ -229,7 +229,11 @@ def _col_to_string(self, show: int = 10) -> str:
 
 
 Column.clone = Column.copy
-Column.dtype_name = lambda self: {1: "f64", 2: "i64", 3: "bool", 4: "str"}[self.dtype()]
+def _col_tag(self) -> int:
+    return _COLUMN_TAG.get(self.dtype.name, 4)
+
+
+Column.dtype_name = lambda self: {1: "f64", 2: "i64", 3: "bool", 4: "str"}[_col_tag(self)]
 Column.len = lambda self: len(self.values)
 Column.is_valid = lambda self, i: 0 <= i < len(self.values) and not isna(self.values[i])
 Column.null_count = lambda self: sum(1 for v in self.values if isna(v))
@@ -240,10 +244,10 @@ Column.from_str = Column.from_i64 = Column.from_f64 = Column.from_bool = _col_fr
 Column.set_string_series = Column.set_bool_series = Column.set_f64_series = Column.set_i64_series = _col_from_series
 Column.rename = lambda self, new_name: setattr(self, "name", new_name)
 Column.get_name = lambda self: self.name
-Column.is_f64 = lambda self: self.dtype() == 1
-Column.is_i64 = lambda self: self.dtype() == 2
-Column.is_bool = lambda self: self.dtype() == 3
-Column.is_str = lambda self: self.dtype() == 4
+Column.is_f64 = lambda self: _col_tag(self) == 1
+Column.is_i64 = lambda self: _col_tag(self) == 2
+Column.is_bool = lambda self: _col_tag(self) == 3
+Column.is_str = lambda self: _col_tag(self) == 4
 Column.take, Column.gather = _col_take, _col_gather
 Column.null_mask = lambda self: R.SeriesBool([isna(v) for v in self.values], self.name)
 Column.has_none = lambda self: any(isna(v) for v in self.values)
@@ -714,3 +718,15 @@ DataFrame.pivot_table = lambda self, index, columns, values, aggfunc="mean", fil
 DataFrame.resample = lambda self, freq: R.Resampler(self, freq)
 DataFrame.to_csv, DataFrame.to_string = _df_to_csv, _df_to_string
 DataFrame.iloc, DataFrame.loc = _df_iloc, _df_loc
+
+
+# ---- dtype constructor functions (api.mojo:184-200): ``int64(nullable=False)`` gives a ``DType`` ---------------------------
+class _DTypeCtor(DType):
+    """The package-level ``bool_ / int32 / int64 / float32 / float64 / string``: equal to the plain dtype of that name
+    and, called like the reference's constructor functions, a ``DType`` with the requested nullability."""
+
+    def __call__(self, nullable: bool = False) -> DType:
+        return _dtype_with_nullable(DType(self.name), nullable)
+
+
+DTYPE_CONSTRUCTORS = {n: _DTypeCtor(n) for n in _TAGS}

@@ -34,8 +34,9 @@ def df_from_columns(names: Sequence[str], cols: Sequence[Sequence]) -> DataFrame
 df_make = df_from_columns
 
 
-def ToDataFrame(data: Dict[str, Iterable]) -> DataFrame:
-    return DataFrame(data)
+def ToDataFrame(data: Dict[str, Iterable], index=None) -> DataFrame:
+    """Frame from ``name -> values``; ``index`` gives the row labels (legacy/src/momijo/dataframe/api.mojo:506-660)."""
+    return DataFrame(data, index)
 
 
 def ToDataFrameNullable(data: Dict[str, Iterable], null_token="") -> DataFrame:
@@ -605,7 +606,16 @@ def to_datetime(values):
     return out
 
 
-def datetime_year(values):
+def datetime_year(values, col: str = None, take: int = None):
+    """Years of a list of date strings. The reference's frame form ``datetime_year(df, col, take=nrows)`` returns the
+    first ``take`` cells of the column joined by ", " (cells shorter than four characters give an empty entry), or a
+    warning text when the column is missing (legacy/src/momijo/dataframe/datetime_ops.mojo:116-150)."""
+    if col is not None:
+        if not values.has_col(col):
+            return "[WARN] datetime_year: column not found"
+        cells = ["" if isna(v) else str(v) for v in values.col(col).values]
+        n = len(cells) if take is None else min(take, len(cells))
+        return ", ".join(c if len(c) >= 4 else "" for c in cells[:n])
     return [None if d is None else d[0] for d in to_datetime(values)]
 
 
@@ -620,8 +630,23 @@ def date_range(start: str, periods: int, freq_days: int = 1):
     return [(d0 + _dt.timedelta(days=i * freq_days)).isoformat() for i in range(periods)]
 
 
-def to_category(values):
-    """-> (codes, categories)."""
+def to_category(values, col_name: str = None, new_name: str = "category_code", ordered: bool = False, categories=()):
+    """``to_category(values)`` -> (codes, categories sorted as text). The reference's frame form
+    ``to_category(df, col_name, new_name, ordered, categories)`` returns a copy of the frame with an integer code column
+    ``new_name``: categories in the given order (duplicates dropped) or in order of first appearance, -1 for values
+    outside them; an unknown column leaves the frame unchanged (legacy/src/momijo/dataframe/categorical.mojo:210-290)."""
+    if col_name is not None:
+        out = values.copy()
+        if not out.has_col(col_name):
+            return out
+        cells = ["" if isna(v) else str(v) for v in out.col(col_name).values]
+        cats_f = []
+        for v in (list(categories) if len(categories) else cells):
+            if v not in cats_f:
+                cats_f.append(v)
+        pos = {c: i for i, c in enumerate(cats_f)}
+        out[new_name] = [pos.get(v, -1) for v in cells]
+        return out
     cats = []
     for v in values:
         if not isna(v) and v not in cats:
