@@ -95,7 +95,11 @@ def write_image_any(path: str, img: Image, **kw) -> bool:
         return False
 
 
-def write_image(path: str, img: Image, **kw) -> bool:
+def write_image(path: str, img: Image, interlace: int = 0, compress: int = 2, filter_mode: int = -1,
+                palette_mode: int = 0, max_colors: int = 256, bit_depth_out: int = 8, **kw) -> bool:
+    """Format by file extension. The PNG tuning arguments of the reference (legacy/src/momijo/vision/io/
+    image_write.mojo:8-11) are accepted in its order; this encoder writes non-interlaced 8-bit true-colour / grey
+    images with per-row filters and takes no tuning, so they are not used."""
     return write_image_any(path, img, **kw)
 
 
@@ -107,7 +111,9 @@ def read_png(path: str) -> Image:
         return Image(torch.from_numpy(_png.decode_png(f.read())))
 
 
-def write_png(path: str, img: Image) -> bool:
+def write_png(path: str, img: Image, interlace: int = 0, compress: int = 2, filter_mode: int = -1,
+              palette_mode: int = 0, max_colors: int = 256, bit_depth_out: int = 8) -> bool:
+    """PNG file; the tuning arguments are accepted as in ``write_image``."""
     return write_image_any(path if path.lower().endswith(".png") else path + ".png", img)
 
 

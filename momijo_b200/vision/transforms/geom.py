@@ -200,7 +200,15 @@ def copy_make_border(img: Image, top: int, bottom: int, left: int, right: int, b
     return Image(torch.from_numpy(np.ascontiguousarray(out)).to(img.device), img.meta().copy())
 
 
-def random_horizontal_flip(img: Image, p: float = 0.5, seed: int = 0xC0FFEE1234) -> Image:
+def random_horizontal_flip(img, p=0.5, seed=0xC0FFEE1234, w: int = None, p_ref: float = 0.5, seed_ref: int = 88172645463325252):
+    """``random_horizontal_flip(image, p, seed)``. The reference's raw-buffer form ``(data, c, h, w, p, seed)``
+    (legacy/src/momijo/vision/transforms/geom.mojo:144-147) takes a float [C, H, W] tensor (or flat buffer) and goes
+    through ``RandomHorizontalFlip``."""
+    if w is not None:
+        from .random_ops import RandomHorizontalFlip
+        import torch
+        buf = torch.as_tensor(img, dtype=torch.float32).reshape(int(p), int(seed), int(w))
+        return RandomHorizontalFlip(p_ref, seed_ref)(buf)
     state = (int(seed) * 6364136223846793005 + 1) & ((1 << 64) - 1)
     r = ((state >> 33) & 0xFFFFFFFF) / 4294967296.0
     return flip(img, 1) if r < p else img.clone()

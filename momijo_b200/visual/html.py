@@ -34,8 +34,26 @@ def render_html(option_json: str, title: str = "momijo - ECharts", width_px: int
     return page
 
 
-def render_echarts(opts_json: str, outfile: str, title: str = "Chart", width_px: int = 960, height_px: int = 540,
-                   theme: str = "", auto_open: bool = False, include_gl: bool = False) -> bool:
+def _px(v, default: int) -> int:
+    """``960``, ``"480px"`` -> pixels; percentages and anything else fall back to ``default``."""
+    if isinstance(v, (int, float)):
+        return int(v)
+    s = str(v).strip().lower()
+    return int(float(s[:-2])) if s.endswith("px") and s[:-2].replace(".", "", 1).isdigit() else default
+
+
+def render_echarts(opts_json: str, outfile: str, title: str = "Chart", width_px=960, height_px=540,
+                   theme: str = "", auto_open: bool = False, include_gl: bool = False, *ref_tail) -> bool:
+    """Write a standalone page. The reference's argument order ``(opts_json, outfile, title, div_id, width, height,
+    renderer, theme, enable_download, auto_open)`` (legacy/src/momijo/visual/html/html_viewer.mojo:24-35) is recognised
+    by a string in the fourth position (the div id): CSS sizes are converted to pixels and the page is never opened
+    here (there is no browser on a server)."""
+    if isinstance(width_px, str) and not width_px.strip().lower().endswith(("px", "%")) and not width_px.isdigit():
+        width, height = height_px, theme                      # (div_id, width, height, renderer, theme, ...)
+        theme = ref_tail[0] if ref_tail else ""
+        width_px, height_px, auto_open, include_gl = _px(width, 960), _px(height, 480), False, False
+    else:
+        width_px, height_px = _px(width_px, 960), _px(height_px, 540)
     ok = write_text(outfile, echarts_html(opts_json, title, width_px, height_px, theme=theme, include_gl=include_gl))
     if ok and auto_open:
         open_in_browser(outfile)
