@@ -797,9 +797,13 @@ def from_json_lines_string(s: str) -> DataFrame:
     return _from_records(recs)
 
 
-def to_csv_string(df: DataFrame, delimiter: str = ",", header: bool = True) -> str:
+def to_csv_string(df: DataFrame, delimiter=",", header=True, quotechar: str = '"') -> str:
+    """``to_csv_string(df, delimiter, header)``, or the reference's ``(df, header, delimiter, quotechar)``: a bool in
+    the first slot selects its order (legacy/src/momijo/dataframe/io_csv.mojo:169-174)."""
+    if isinstance(delimiter, bool):
+        delimiter, header = (header if isinstance(header, str) else ","), delimiter
     buf = io.StringIO()
-    w = csv.writer(buf, delimiter=delimiter, lineterminator="\n")
+    w = csv.writer(buf, delimiter=delimiter, lineterminator="\n", quotechar=quotechar)
     if header:
         w.writerow(df.col_names())
     for i in range(df.nrows()):

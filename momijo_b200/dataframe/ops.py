@@ -55,8 +55,13 @@ def df_describe(df):
     return df.describe()
 
 
-def df_rename(df, mapping):
-    return df.rename(mapping)
+def df_rename(df, mapping, axis_name: str = ""):
+    """Rename columns from a dict or a list of ``(old, new)`` pairs; a non-empty third argument names the index
+    (legacy/src/momijo/dataframe/api.mojo:1213, 2153-2157)."""
+    out = df.rename(dict(mapping))
+    if axis_name:
+        out.index.name = axis_name
+    return out
 
 
 rename = df_rename
@@ -288,8 +293,12 @@ def head(df, n=5):
     return df.head(n)
 
 
-def set_index(df, name):
-    return df.set_index(name)
+def set_index(df, name, drop: bool = True):
+    """``drop=False`` keeps the column in the frame as well as using it for the row labels."""
+    out = df.set_index(name)
+    if not drop and not out.has_col(name):
+        out[name] = list(df.col(name).values)
+    return out
 
 
 def reset_index(df, name=None):
@@ -323,12 +332,17 @@ def fillna_value(df, col, value):
     return d
 
 
-def ffill(df, col):
-    out, last = [], None
+def ffill(df, col, limit: int = None):
+    """Carry the last present value forward; ``limit`` caps how many consecutive missing cells one value may fill
+    (the reference's default is 1, legacy/src/momijo/dataframe/missing.mojo:560; here no limit unless given)."""
+    out, last, run = [], None, 0
     for v in df.col(col).values:
         if not isna(v):
-            last = v
-        out.append(last)
+            last, run = v, 0
+            out.append(v)
+            continue
+        run += 1
+        out.append(last if (limit is None or run <= limit) else None)
     d = df.copy()
     d[col] = out
     return d
@@ -345,7 +359,9 @@ def interpolate_numeric(df, col):
     return d
 
 
-def drop_duplicates(df, subset=None):
+def drop_duplicates(df, subset=None, keep: str = "first"):
+    if keep != "first":
+        return df.drop_duplicates(subset, keep)
     names = subset or df.col_names()
     seen, keep = set(), []
     for i in range(df.nrows()):
@@ -578,7 +594,12 @@ def _smap(df, col, fn):
 def str_title(df, col): return _smap(df, col, str.title)
 def str_upper(df, col): return _smap(df, col, str.upper)
 def str_lower(df, col): return _smap(df, col, str.lower)
-def str_contains(df, col, pat): return [False if isna(v) else (pat in str(v)) for v in df.col(col).values]
+def str_contains(df, col, pat, case_insensitive: bool = False, na_false: bool = True):
+    """Per row, whether the cell contains ``pat``; missing cells give False, or None with ``na_false=False``
+    (legacy/src/momijo/dataframe/string_ops.mojo:712-718)."""
+    p = pat.lower() if case_insensitive else pat
+    return [(False if na_false else None) if isna(v) else (p in (str(v).lower() if case_insensitive else str(v)))
+            for v in df.col(col).values]
 def str_slice(df, col, start, stop=None): return _smap(df, col, lambda s: s[start:stop])
 
 
@@ -668,9 +689,18 @@ def _parse(v):
     return {"true": True, "false": False}.get(v.lower(), v)
 
 
-def read_csv(path, delimiter=",", header=True):
+def _csv_args(a, b, quotechar):
+    """This package's order is (delimiter, header); the reference's is (header, delimiter, quotechar)
+    (legacy/src/momijo/dataframe/io_csv.mojo:169-318). A bool in the first slot selects the reference's order."""
+    if isinstance(a, bool):
+        return (b if isinstance(b, str) else ","), a, quotechar
+    return a, (b if isinstance(b, bool) else True), quotechar
+
+
+def read_csv(path, delimiter=",", header=True, quotechar: str = '"'):
+    delimiter, header, quotechar = _csv_args(delimiter, header, quotechar)
     with open(path, newline="") as f:
-        rows_ = list(csv.reader(f, delimiter=delimiter))
+        rows_ = list(csv.reader(f, delimiter=delimiter, quotechar=quotechar))
     if not rows_:
         return DataFrame()
     names = rows_[0] if header else [f"c{i}" for i in range(len(rows_[0]))]
@@ -678,10 +708,12 @@ def read_csv(path, delimiter=",", header=True):
     return DataFrame({n: [_parse(r[i]) if i < len(r) else None for r in body] for i, n in enumerate(names)})
 
 
-def write_csv(df, path, delimiter=","):
+def write_csv(df, path, delimiter=",", header=True, quotechar: str = '"'):
+    delimiter, header, quotechar = _csv_args(delimiter, header, quotechar)
     with open(path, "w", newline="") as f:
-        w = csv.writer(f, delimiter=delimiter)
-        w.writerow(df.col_names())
+        w = csv.writer(f, delimiter=delimiter, quotechar=quotechar)
+        if header:
+            w.writerow(df.col_names())
         for i in range(df.nrows()):
             w.writerow(["" if isna(c.values[i]) else c.values[i] for c in df.columns])
     return True
