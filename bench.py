@@ -46,6 +46,14 @@ def parse():
                          "expert- and pipeline-parallel configs; they need the GPUs named in their docstrings.")
     ap.add_argument("--layers", type=int, default=0,
                     help="override the layer count (for smoke runs; the result is then marked 'reduced')")
+    ap.add_argument("--baseline", type=int, default=1,
+                    help="1 (default): after the native arm, time the stock-PyTorch arm of the same config in the "
+                         "same process group and report value / that as vs_baseline; 0: skip it")
+    ap.add_argument("--zero-stage", type=int, default=3, choices=[1, 2, 3],
+                    help="sharding stage of the headline config for N > 1")
+    ap.add_argument("--torch-variant", default="autocast", choices=["autocast", "bf16-master"],
+                    help="stock-PyTorch arm of the headline config: fp32 parameters under bf16 autocast, or bf16 "
+                         "parameters with an fp32 master copy")
     return ap.parse_args()
 
 
@@ -99,7 +107,7 @@ def timed(fn_step, steps, world):
     return max_over_ranks(a.elapsed_time(b)) / steps
 
 
-def build_ours(cfg, world, rank, local):
+def build_ours(cfg, world, rank, local, stage=3):
     import torch
     from momijo_b200 import ops
     from momijo_b200.models import GPT2
@@ -113,13 +121,18 @@ def build_ours(cfg, world, rank, local):
 
         comm = PeerComm.from_default_group()
     engine = ShardedDataParallel(model, AdamWConfig(lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1),
-                                 stage=3, comm=comm)
-    ops.assume_unit_loss_grad(True)
+                                 stage=stage, comm=comm)
     return engine
 
 
-def build_torch(cfg, world, local):
-    """Stock PyTorch arm: same architecture with nn.Linear / SDPA / F.cross_entropy."""
+def build_torch(cfg, world, local, variant="autocast"):
+    """Stock PyTorch arm: same architecture with nn.Linear / SDPA / F.cross_entropy. Returns
+    ``(net, opt, finish)``; ``finish()`` runs the optimizer step (and zeroes the gradients).
+
+    ``variant``: "autocast" keeps fp32 parameters and runs the forward under bf16 autocast (the usual
+    single-GPU recipe; weights are re-cast every step); "bf16-master" keeps bf16 parameters and applies
+    AdamW to an fp32 master copy (the same precision recipe as the native arm). With N > 1 both are FSDP
+    full-shard with ``MixedPrecision(param_dtype=bf16)`` over fp32 shards, one FSDP unit per block."""
     import torch
     import torch.nn as nn
     import torch.nn.functional as F
@@ -162,13 +175,35 @@ def build_torch(cfg, world, local):
             nn.init.normal_(p, 0.0, 0.02)
     if world > 1:
         from torch.distributed.fsdp import FullyShardedDataParallel as FSDP, MixedPrecision
+        from torch.distributed.fsdp.wrap import ModuleWrapPolicy
 
         net = FSDP(net, mixed_precision=MixedPrecision(param_dtype=torch.bfloat16,
                                                        reduce_dtype=torch.bfloat16),
-                   use_orig_params=True, device_id=local)
+                   auto_wrap_policy=ModuleWrapPolicy({Block}), use_orig_params=True, device_id=local)
+    elif variant == "bf16-master":
+        net = net.to(torch.bfloat16)
+        params = [p for p in net.parameters()]
+        masters = [p.detach().float().clone().requires_grad_(True) for p in params]
+        opt = torch.optim.AdamW(masters, lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
+
+        def finish():
+            for m, p in zip(masters, params):
+                m.grad = p.grad.float()
+            opt.step()
+            with torch.no_grad():
+                torch._foreach_copy_(params, masters)
+            for p in params:
+                p.grad = None
+
+        return net, opt, finish
     opt = torch.optim.AdamW(net.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1,
                             fused=True)
-    return net, opt
+
+    def finish():
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+
+    return net, opt, finish
 
 
 def _pinned_batches(vocab, shape, seed, n=4):
@@ -203,7 +238,6 @@ def setup_llama_tp(args, rank, world, local):
     with torch.device("cuda"):
         model = Llama(cfg, tp)
     engine = HybridEngine(model, AdamWConfig(lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1), rep_comm=comm)
-    ops.assume_unit_loss_grad(True)
     host_tok = _pinned_batches(cfg.vocab_size, (B, T + 1), 1000)   # same seed on every rank: same tokens
     dev_tok = [t.cuda() for t in host_tok]
 
@@ -262,7 +296,6 @@ def setup_moe_ep(args, rank, world, local):
     engine = HybridEngine(model, AdamWConfig(lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1),
                           dp_comm=comm, dp_params=dense if world > 1 else None,
                           local_grad_scale=1.0 / world)
-    ops.assume_unit_loss_grad(False)   # the loss is cross-entropy + auxiliary term
     host_tok = _pinned_batches(cfg.vocab_size, (B, T + 1), 1000 + rank)
     dev_tok = [t.cuda() for t in host_tok]
 
@@ -320,7 +353,6 @@ def setup_llama_pptp(args, rank, world, local):
         module = LlamaStage(cfg, tp, layers, first=stage_id == 0, last=stage_id == S - 1)
     module.batch_shape = (1, T)
     engine = HybridEngine(module, AdamWConfig(lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1), rep_comm=comm)
-    ops.assume_unit_loss_grad(False)   # micro-batch losses are scaled by 1/n_micro
     stage = PipelineStage(module, stage_id, S, prev_rank=rank - TP if stage_id > 0 else None,
                           next_rank=rank + TP if stage_id < S - 1 else None)
     sched = Schedule1F1B(stage, n_micro, (T // TP, cfg.d_model), torch.bfloat16, torch.device("cuda", local))
@@ -392,28 +424,68 @@ def setup_torch_arm(args, rank, world, local):
     return step_device, step_e2e, info
 
 
-def main():
-    args = parse()
-    if args.impl == "reference":
-        return reference_unavailable()
-
+def setup_torch_pptp(args, rank, world, local):
+    """Stock-PyTorch arm of the pipeline x tensor parallel config: the same 2 x (N/2) layout, Megatron-style
+    tensor parallel stages (``bench_torch.TorchLlamaTP``), 1F1B over NCCL p2p, fused AdamW on fp32 parameters
+    under bf16 autocast."""
     import torch
-    from momijo_b200 import _C
-    from momijo_b200.models import GPT2Config
-    from momijo_b200.utils import ClockSampler
+    import torch.distributed as dist
+    from bench_torch import TorchLlamaTP, run_1f1b
+    from momijo_b200.models import LlamaConfig
+    from momijo_b200.parallel.pp import partition_layers
 
-    rank, world, local = init_dist(args.gpus)
-    if args.config != "gpt2":
-        if args.impl == "torch" and args.config in ("llama8b-tp", "moe16b-ep"):
-            step_device, step_e2e, info = setup_torch_arm(args, rank, world, local)
-            return run_and_report(args, rank, world, local, step_device, step_e2e, info)
-        if args.impl != "ours":
-            if rank == 0:
-                print(json.dumps({"impl": args.impl, "unavailable": f"no {args.impl} arm for --config {args.config}"}))
-            return 0
-        setup = {"llama8b-tp": setup_llama_tp, "moe16b-ep": setup_moe_ep, "llama13b-pptp": setup_llama_pptp}[args.config]
-        step_device, step_e2e, info = setup(args, rank, world, local)
-        return run_and_report(args, rank, world, local, step_device, step_e2e, info)
+    if world % 2:
+        raise SystemExit("--config llama13b-pptp needs an even number of GPUs (2 pipeline stages)")
+    cfg = LlamaConfig.llama2_13b()
+    if args.layers:
+        cfg.n_layer = args.layers
+    S, TP = 2, world // 2
+    n_micro, T = 16, cfg.max_seq
+    stage_id = rank // TP
+    groups = [dist.new_group(list(range(s * TP, (s + 1) * TP))) for s in range(S)]
+    layers = partition_layers(cfg.n_layer, S)[stage_id]
+    torch.manual_seed(1234 + rank)
+    with torch.device("cuda"):
+        stage = TorchLlamaTP(cfg, groups[stage_id], layers=layers, first=stage_id == 0, last=stage_id == S - 1)
+    stage.batch_shape = (1, T)
+    opt = torch.optim.AdamW(stage.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
+    host_tok = _pinned_batches(cfg.vocab_size, (n_micro, T + 1), 1000)
+    dev_tok = [t.cuda() for t in host_tok]
+    dev = torch.device("cuda", local)
+
+    def run(t):
+        inputs = [t[m:m + 1, :-1] for m in range(n_micro)]
+        targets = [t[m:m + 1, 1:] for m in range(n_micro)]
+        loss = run_1f1b(stage, stage_id, S, rank - TP if stage_id > 0 else None,
+                        rank + TP if stage_id < S - 1 else None, n_micro, (T // TP, cfg.d_model), dev,
+                        inputs, targets)
+        stage.sync_replicated_grads()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    def step_device(i):
+        return run(dev_tok[i % len(dev_tok)])
+
+    def step_e2e(i):
+        loss = run(host_tok[i % len(host_tok)].cuda(non_blocking=True))
+        return float(loss) if loss is not None else None
+
+    info = {"tokens_per_step": n_micro * T, "scaling": "strong", "flops_per_token": cfg.flops_per_token(T),
+            "h2d_bytes": n_micro * (T + 1) * 8,
+            "config": {"model": f"llama-2-13b shape ({cfg.n_layer}L d5120 40H ff13824 vocab32000 seq4096)",
+                       "global_batch": n_micro, "seq_len": T,
+                       "parallelism": f"pp2 x tp{TP}, 1F1B, {n_micro} micro-batches (torch.distributed, cuBLAS, SDPA)",
+                       "optimizer": "torch.optim.AdamW(fused) on fp32 parameters, bf16 autocast, step inside the timed region",
+                       "l2": "working set of tens of GB per step >> 126 MB L2; no flush"}}
+    return step_device, step_e2e, info
+
+
+def setup_gpt2(args, rank, world, local, impl):
+    """Headline config: GPT-2 small, micro-batch 16 x 1024 per GPU, sharded data parallel for N > 1."""
+    import torch
+    from momijo_b200.models import GPT2Config
+
     cfg = GPT2Config.small() if args.model == "gpt2-small" else GPT2Config.tiny()
     B, T = args.micro_batch, min(args.seq, cfg.max_seq)
     tokens_per_step = B * T * world
@@ -424,9 +496,10 @@ def main():
     host_tok = [torch.randint(0, cfg.vocab_size, (B, T + 1), generator=g).pin_memory()
                 for _ in range(n_batches)]
     dev_tok = [t.cuda() for t in host_tok]
+    extra = {}
 
-    if args.impl == "ours":
-        engine = build_ours(cfg, world, rank, local)
+    if impl == "ours":
+        engine = build_ours(cfg, world, rank, local, stage=args.zero_stage)
 
         def step_device(i):
             t = dev_tok[i % n_batches]
@@ -439,26 +512,34 @@ def main():
 
         def step_e2e(i):
             return train_step_e2e(engine, host_tok[i % n_batches])
-    else:
-        net, opt = build_torch(cfg, world, local)
 
-        def step_device(i):
-            t = dev_tok[i % n_batches]
-            with torch.autocast("cuda", dtype=torch.bfloat16):
+        par = "single" if world == 1 else f"zero{args.zero_stage}-dp{world}"
+        optim = "AdamW fp32 master, step inside the timed region"
+        if world > 1:
+            extra["memory"] = engine.memory_report()
+    else:
+        variant = args.torch_variant
+        net, opt, finish = build_torch(cfg, world, local, variant)
+
+        def torch_step(t):
+            if variant == "bf16-master" and world == 1:
                 loss = net(t[:, :-1], t[:, 1:])
+            else:
+                with torch.autocast("cuda", dtype=torch.bfloat16):
+                    loss = net(t[:, :-1], t[:, 1:])
             loss.backward()
-            opt.step()
-            opt.zero_grad(set_to_none=True)
+            finish()
             return loss
 
+        def step_device(i):
+            return torch_step(dev_tok[i % n_batches])
+
         def step_e2e(i):
-            t = host_tok[i % n_batches].cuda(non_blocking=True)
-            with torch.autocast("cuda", dtype=torch.bfloat16):
-                loss = net(t[:, :-1], t[:, 1:])
-            loss.backward()
-            opt.step()
-            opt.zero_grad(set_to_none=True)
-            return float(loss)
+            return float(torch_step(host_tok[i % n_batches].cuda(non_blocking=True)))
+
+        par = ("single" if world == 1 else f"fsdp-full-shard-dp{world}") + " (stock PyTorch: cuBLAS, SDPA, NCCL)"
+        optim = ("torch.optim.AdamW(fused) on fp32 parameters, bf16 autocast" if variant == "autocast" or world > 1
+                 else "bf16 parameters, torch.optim.AdamW(fused) on an fp32 master copy") + ", step inside the timed region"
 
     info = {
         "tokens_per_step": tokens_per_step,
@@ -469,72 +550,133 @@ def main():
             "model": "gpt2-small (12L d768 12H ff3072 vocab50257 seq1024)" if args.model == "gpt2-small" else args.model,
             "global_batch": B * world,
             "seq_len": T,
-            "parallelism": "single" if world == 1 else f"zero3-dp{world}",
-            "optimizer": "AdamW fp32 master, step inside the timed region",
+            "parallelism": par,
+            "optimizer": optim,
             "l2": "per-step working set (0.25 GB weights + GBs of activations) >> 126 MB L2; no flush",
         },
+        "extra": extra,
     }
-    return run_and_report(args, rank, world, local, step_device, step_e2e, info)
+    return step_device, step_e2e, info
 
 
-def run_and_report(args, rank, world, local, step_device, step_e2e, info):
+def run_arm(args, impl, rank, world, local):
+    """Build one arm (native or stock PyTorch) of the selected config, time it, free it. Returns the
+    result dict on rank 0 (None elsewhere, or when the arm does not exist)."""
+    import gc
+
     import torch
-    from momijo_b200 import _C
-    from momijo_b200.utils import ClockSampler
 
-    for i in range(max(args.warmup, 3)):
-        last = step_device(i)
-    torch.cuda.synchronize()
+    if args.config == "gpt2":
+        setup = lambda: setup_gpt2(args, rank, world, local, impl)
+    elif impl == "torch":
+        if args.config == "llama13b-pptp":
+            setup = lambda: setup_torch_pptp(args, rank, world, local)
+        else:
+            setup = lambda: setup_torch_arm(args, rank, world, local)
+    else:
+        fn = {"llama8b-tp": setup_llama_tp, "moe16b-ep": setup_moe_ep, "llama13b-pptp": setup_llama_pptp}[args.config]
+        setup = lambda: fn(args, rank, world, local)
+    step_device, step_e2e, info = setup()
+    out = time_arm(args, impl, rank, world, local, step_device, step_e2e, info)
+    del step_device, step_e2e, info, setup
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
 
-    sampler = ClockSampler(local).start() if rank == 0 else None
-    launches0 = _C.launches
-    ms = timed(step_device, args.steps, world)
-    launches = _C.launches - launches0
-    ms_e2e = timed(step_e2e, args.steps, world)
-    clocks = sampler.stop() if sampler is not None else None
-    loss_val = float(last) if last is not None else None
-    if args.impl == "ours":
-        _C.check_status()
 
-    if rank == 0:
-        tokens_per_step = info["tokens_per_step"]
-        tok_s = tokens_per_step / (ms / 1e3)
-        tok_s_e2e = tokens_per_step / (ms_e2e / 1e3)
-        out = {
-            "metric": "train tokens/s/box (device-timed, max over ranks)",
-            "value": tok_s,
-            "unit": "tokens/s",
-            "n_gpus": world,
-            "steps": args.steps,
-            "warmup": max(args.warmup, 3),
-            "ms_per_step": ms,
-            "higher_is_better": True,
-            "scaling": info["scaling"],
-            "vs_baseline": None,
-            "dtype": "bf16",
-            "data": "synthetic uniform-random tokens, random-init weights N(0,0.02)",
-            "impl": args.impl,
-            "config": info["config"],
-            "e2e": {
-                "value": tok_s_e2e,
-                "unit": "tokens/s",
-                "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": info["h2d_bytes"],
-                "d2h_bytes_per_step": 4,
-            },
-            "gpu_launches": launches if args.impl == "ours" else 0,
-            "clocks": clocks,
-            "final_loss": loss_val,
-            "model_tflops": info["flops_per_token"] * tok_s / 1e12,
-        }
-        if args.layers:
-            out["reduced"] = f"layer count overridden to {args.layers}: not a result for the named model"
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return reference_unavailable()
+
+    rank, world, local = init_dist(args.gpus)
+    out = run_arm(args, args.impl, rank, world, local)
+    if args.impl == "ours" and args.baseline:
+        # The reference has no buildable multi-GPU (or GPU) path, so the baseline named for this benchmark is
+        # the same model and config in stock PyTorch (cuBLAS, SDPA, NCCL: FSDP / tensor / expert / pipeline
+        # parallel), timed here with the same steps, warm-up, data and clocks, right after the native arm.
+        try:
+            base = run_arm(args, "torch", rank, world, local)
+        except Exception as e:  # the comparison must never cost the native number
+            base = {"error": f"{type(e).__name__}: {e}"[:300]} if rank == 0 else None
+        if rank == 0 and out is not None and base is not None:
+            if "value" in base:
+                out["vs_baseline"] = out["value"] / base["value"]
+                out["baseline"] = {"impl": base["config"]["parallelism"], "value": base["value"],
+                                   "ms_per_step": base["ms_per_step"], "e2e": base["e2e"]["value"],
+                                   "e2e_ratio": out["e2e"]["value"] / base["e2e"]["value"],
+                                   "optimizer": base["config"]["optimizer"], "clocks": base["clocks"],
+                                   "loss_after_timed_steps": base["loss_after_timed_steps"]}
+            else:
+                out["baseline"] = base
+    if rank == 0 and out is not None:
         print(json.dumps(out))
     if world > 1:
         import torch.distributed as dist
 
         dist.destroy_process_group()
     return 0
+
+
+def time_arm(args, impl, rank, world, local, step_device, step_e2e, info):
+    import torch
+    from momijo_b200 import _C
+    from momijo_b200.utils import ClockSampler
+
+    for i in range(max(args.warmup, 3)):
+        step_device(i)
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local).start() if rank == 0 else None
+    launches0 = _C.launches
+    last = []
+    def counted(i):
+        r = step_device(i)
+        if i == args.steps - 1:
+            last.append(r)
+    ms = timed(counted, args.steps, world)
+    launches = _C.launches - launches0
+    ms_e2e = timed(step_e2e, args.steps, world)
+    clocks = sampler.stop() if sampler is not None else None
+    loss_val = float(last[0]) if last and last[0] is not None else None
+    if impl == "ours":
+        _C.check_status()
+    if rank != 0:
+        return None
+    tokens_per_step = info["tokens_per_step"]
+    tok_s = tokens_per_step / (ms / 1e3)
+    tok_s_e2e = tokens_per_step / (ms_e2e / 1e3)
+    out = {
+        "metric": "train tokens/s/box (device-timed, max over ranks)",
+        "value": tok_s,
+        "unit": "tokens/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": max(args.warmup, 3),
+        "ms_per_step": ms,
+        "higher_is_better": True,
+        "scaling": info["scaling"],
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic uniform-random tokens, random-init weights N(0,0.02)",
+        "impl": impl,
+        "config": info["config"],
+        "e2e": {
+            "value": tok_s_e2e,
+            "unit": "tokens/s",
+            "ms_per_step": ms_e2e,
+            "h2d_bytes_per_step": info["h2d_bytes"],
+            "d2h_bytes_per_step": 4,
+        },
+        "gpu_launches": launches if impl == "ours" else 0,
+        "clocks": clocks,
+        "loss_after_timed_steps": loss_val,
+        "model_tflops": info["flops_per_token"] * tok_s / 1e12,
+    }
+    out.update(info.get("extra", {}))
+    if args.layers:
+        out["reduced"] = f"layer count overridden to {args.layers}: not a result for the named model"
+    return out
 
 
 if __name__ == "__main__":

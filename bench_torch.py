@@ -100,9 +100,15 @@ def _rope(x, theta):
 
 
 class TorchLlamaTP(nn.Module):
-    def __init__(self, cfg, group=None):
+    """``layers`` / ``first`` / ``last`` select one pipeline stage: the first stage owns the embedding,
+    the last one the final norm, the head and the loss; a middle or first stage returns its
+    sequence-sharded activation ``[M/W, C]``."""
+
+    def __init__(self, cfg, group=None, layers=None, first=True, last=True):
         super().__init__()
         self.cfg, self.group = cfg, group
+        self.first, self.last = first, last
+        n_local_layers = cfg.n_layer if layers is None else len(layers)
         W, R = _world(group), _rank(group)
         self.W, self.R = W, R
         c, D = cfg.d_model, cfg.head_dim
@@ -111,9 +117,10 @@ class TorchLlamaTP(nn.Module):
         self.v_local = v_pad // W
         std = cfg.init_std
         P = lambda *s: nn.Parameter(torch.randn(*s) * std)
-        self.embed = P(self.v_local, c)
+        if first:
+            self.embed = P(self.v_local, c)
         self.layers = nn.ModuleList()
-        for _ in range(cfg.n_layer):
+        for _ in range(n_local_layers):
             m = nn.Module()
             m.attn_norm = nn.Parameter(torch.ones(c))
             m.mlp_norm = nn.Parameter(torch.ones(c))
@@ -122,21 +129,28 @@ class TorchLlamaTP(nn.Module):
             m.w_gu = P(2 * cfg.d_ff // W, c)
             m.w_down = P(c, cfg.d_ff // W)
             self.layers.append(m)
-        self.final_norm = nn.Parameter(torch.ones(c))
-        self.head = P(self.v_local, c)
-        self.replicated = [self.final_norm] + [p for m in self.layers for p in (m.attn_norm, m.mlp_norm)]
+        self.replicated = [p for m in self.layers for p in (m.attn_norm, m.mlp_norm)]
+        if last:
+            self.final_norm = nn.Parameter(torch.ones(c))
+            self.head = P(self.v_local, c)
+            self.replicated.append(self.final_norm)
+        self.batch_shape = None   # (B, T) of a micro-batch, needed by stages that receive activations
 
-    def forward(self, tokens, targets):
+    def forward(self, tokens, targets=None):
         cfg, g, W = self.cfg, self.group, self.W
-        B, T = tokens.shape
+        lo = self.R * self.v_local
+        if self.first:
+            B, T = tokens.shape
+            # vocabulary-parallel embedding: local rows, zeros elsewhere, summed and scattered over rows
+            local = tokens.reshape(-1) - lo
+            ok = (local >= 0) & (local < self.v_local)
+            e = F.embedding(local.clamp(0, self.v_local - 1), self.embed) * ok[:, None].to(self.embed.dtype)
+            x = _ReduceScatterRows.apply(e, g)                               # [M/W, C]
+        else:
+            B, T = self.batch_shape
+            x = tokens
         M = B * T
         D = cfg.head_dim
-        # vocabulary-parallel embedding: local rows, zeros elsewhere, summed and scattered over rows
-        lo = self.R * self.v_local
-        local = tokens.reshape(-1) - lo
-        ok = (local >= 0) & (local < self.v_local)
-        e = F.embedding(local.clamp(0, self.v_local - 1), self.embed) * ok[:, None].to(self.embed.dtype)
-        x = _ReduceScatterRows.apply(e, g)                                   # [M/W, C]
         for m in self.layers:
             h = _AllGatherRows.apply(F.rms_norm(x, (cfg.d_model,), m.attn_norm, cfg.rms_eps), g)
             qkv = F.linear(h, m.wqkv).view(B, T, self.hq + 2 * self.hkv, D)
@@ -150,6 +164,8 @@ class TorchLlamaTP(nn.Module):
             gu = F.linear(h, m.w_gu)
             gate, up = gu.chunk(2, dim=-1)
             x = x + _ReduceScatterRows.apply(F.linear(F.silu(gate) * up, m.w_down), g)
+        if not self.last:
+            return x
         h = _AllGatherRows.apply(F.rms_norm(x, (cfg.d_model,), self.final_norm, cfg.rms_eps), g)
         logits = F.linear(h, self.head).float()                              # [M, V/W]
         valid = min(self.v_local, max(0, cfg.vocab_size - lo))
@@ -291,6 +307,59 @@ class _AllToAll(torch.autograd.Function):
         out = g.new_empty((sum(ctx.in_split),) + g.shape[1:])
         dist.all_to_all_single(out, g.contiguous(), ctx.in_split, ctx.out_split, group=ctx.group)
         return out, None, None, None
+
+
+def run_1f1b(stage, stage_id, n_stages, prev_rank, next_rank, n_micro, act_shape, device, micro_inputs,
+             micro_targets, device_type="cuda"):
+    """Plain 1F1B over torch.distributed p2p (``batch_isend_irecv``), written out here so that this arm shares
+    no code with the package: warm-up forwards, one-forward-one-backward, drain. Activations cross stages in
+    bf16. Returns the mean loss on the last stage."""
+    first, last = stage_id == 0, stage_id == n_stages - 1
+    warm = min(n_stages - 1 - stage_id, n_micro)
+    saved, losses, keep = [], [], []
+
+    def recv(src):
+        buf = torch.empty(act_shape, dtype=torch.bfloat16, device=device)
+        for w in dist.batch_isend_irecv([dist.P2POp(dist.irecv, buf, src)]):
+            w.wait()
+        return buf
+
+    def send(t, dst):
+        t = t.contiguous()
+        keep.append((dist.batch_isend_irecv([dist.P2POp(dist.isend, t, dst)]), t))
+
+    def fwd(i):
+        x = micro_inputs[i] if first else recv(prev_rank).requires_grad_(True)
+        with torch.autocast(device_type, dtype=torch.bfloat16):
+            y = stage(x, micro_targets[i] if last else None)
+        if last:
+            losses.append(y.detach())
+            saved.append((x, y / n_micro))
+        else:
+            send(y.detach().to(torch.bfloat16), next_rank)
+            saved.append((x, y))
+
+    def bwd():
+        x, y = saved.pop(0)
+        if last:
+            y.backward()
+        else:
+            y.backward(recv(next_rank).to(y.dtype))
+        if not first:
+            send(x.grad, prev_rank)
+
+    fi = 0
+    for _ in range(warm):
+        fwd(fi); fi += 1
+    for _ in range(n_micro - warm):
+        fwd(fi); fi += 1
+        bwd()
+    for _ in range(warm):
+        bwd()
+    for works, _ in keep:
+        for w in works:
+            w.wait()
+    return torch.stack([l.float() for l in losses]).mean() if last else None
 
 
 def make_step(model, kind, device_type):

@@ -53,10 +53,12 @@ _SIGS = {
     "mmj_dropout_f32": ([P, P, P, L, F, c_ulonglong, P], 1),
     "mmj_dropout_bf16": ([P, P, L, F, c_ulonglong, P], 1),
     "mmj_pack_nchw": ([P, P, I, I, I, I, I, P], 1),
-    "mmj_ce_fwd_bwd": ([P, L, I, P, P, L, F, L, I, P], 1),
+    "mmj_ce_fwd_bwd": ([P, L, I, P, P, L, F, P, L, I, P], 1),
+    "mmj_ce_count_valid": ([P, L, L, P, P], 1),
+    "mmj_scale_bf16_dev": ([P, L, L, I, P, P], 1),
     "mmj_ce_vp_stats": ([P, L, I, L, P, P, P, P, L, P], 1),
     "mmj_ce_vp_grad": ([P, L, I, L, P, P, P, L, F, P], 1),
-    "mmj_reduce_mean": ([P, P, L, F, P], 1),
+    "mmj_reduce_mean": ([P, P, L, F, P, P], 1),
     "mmj_adamw": ([P, I, P, P, P, P, L, F, F, F, F, F, F, F, F, P, P, P], 1),
     "mmj_sgd": ([P, I, P, P, P, L, F, F, F, F, P], 1),
     "mmj_sqnorm_parts": ([], 0),

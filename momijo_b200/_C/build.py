@@ -27,8 +27,12 @@ NVCC_FLAGS = [
     "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr",
     "-Xcompiler", "-fPIC,-fvisibility=hidden",
-    "--use_fast_math",
 ]
+# Approximate division / square root / exp are fine where results are rounded to bf16 (GEMM epilogues,
+# attention, activations); the optimizer and the collectives that carry the optimizer update keep IEEE
+# division and sqrtf, so the update matches a plain fp32 AdamW bit for bit.
+FAST_MATH = ["--use_fast_math"]
+EXACT_MATH_SOURCES = {"loss_optim.cu", "comm.cu"}
 
 
 def _nvcc() -> str:
@@ -75,6 +79,8 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False,
         if not force and _newer(obj, [src, *headers]):
             return obj
         flags = list(NVCC_FLAGS)
+        if src.name not in EXACT_MATH_SOURCES:
+            flags += FAST_MATH
         if debug_bounds:
             flags += ["-DMMJ_DEBUG_BOUNDS"]
         if ptxas_info:

@@ -320,6 +320,28 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ parts, long long 
   }
 }
 
+// ---- in-place scaling by a device scalar, skipped when the scalar is exactly 1 -------------------
+// Backward passes receive the gradient of the loss as a device scalar; it is 1 for a plain
+// `loss.backward()`. Every CTA reads it first and leaves at once in that case, so the common path
+// costs one empty launch and no host synchronisation; any other value scales the matrix in place.
+__global__ void scale_bf16_dev_kernel(__nv_bfloat16* __restrict__ x, long long ld, long long rows,
+                                      int cols, const float* __restrict__ s) {
+  const float sc = *s;
+  if (sc == 1.0f) return;
+  const int vec_per_row = cols >> 3;  // cols % 8 == 0 and ld % 8 == 0
+  const long long nvec = rows * vec_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / vec_per_row;
+    const int c = (int)(i - r * vec_per_row) * 8;
+    float f[8];
+    ld8(x + r * ld + c, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] *= sc;
+    st8(x + r * ld + c, f);
+  }
+}
+
 // ---- casts, fills, axpy ------------------------------------------------------------------------
 __global__ void cast_f32_to_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y,
                                         long long n) {
@@ -602,6 +624,13 @@ MMJ_API int mmj_fill(void* y, double v, long long n, int dtype, void* stream) {
   if (dtype == 0) fill_f32_kernel<<<g, 256, 0, STREAM>>>((float*)y, (float)v, n);
   else if (dtype == 1) fill_f64_kernel<<<g, 256, 0, STREAM>>>((double*)y, v, n);
   else fill_bf16_kernel<<<g, 256, 0, STREAM>>>((__nv_bfloat16*)y, (float)v, n);
+  return (int)cudaGetLastError();
+}
+MMJ_API int mmj_scale_bf16_dev(void* x, long long ld, long long rows, int cols, const float* s,
+                               void* stream) {
+  if ((cols & 7) || (ld & 7)) return -1;
+  if (rows == 0 || cols == 0) return 0;
+  scale_bf16_dev_kernel<<<148 * 8, 256, 0, STREAM>>>((__nv_bfloat16*)x, ld, rows, cols, s);
   return (int)cudaGetLastError();
 }
 MMJ_API int mmj_axpby_bf16(const void* x, void* y, float a, float b, long long n, void* stream) {

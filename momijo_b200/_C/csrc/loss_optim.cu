@@ -41,7 +41,8 @@ __device__ __forceinline__ float block_reduce_sum(float v, float* red) {
 template <bool kCache>
 __global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long ld, int V,
                                   const long long* __restrict__ targets, float* __restrict__ loss_row,
-                                  float dscale, long long ignore_index, int write_grad) {
+                                  float dscale, const float* __restrict__ dscale_dev,
+                                  long long ignore_index, int write_grad) {
   extern __shared__ __align__(16) uint8_t ce_smem[];
   __shared__ float red[32];
   __nv_bfloat16* cache = reinterpret_cast<__nv_bfloat16*>(ce_smem);
@@ -90,7 +91,7 @@ __global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long 
   if (!write_grad) return;
   __syncthreads();  // everyone has read srcp[tgt] before the in-place overwrite (non-cached path)
   const float inv = 1.0f / sum;
-  const float sc = ignored ? 0.f : dscale;
+  const float sc = ignored ? 0.f : dscale * (dscale_dev != nullptr ? *dscale_dev : 1.0f);
   for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
     uint4 q = reinterpret_cast<const uint4*>(srcp)[v];
     const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&q);
@@ -180,12 +181,23 @@ __global__ void ce_vp_grad_kernel(__nv_bfloat16* __restrict__ logits, long long 
 
 // Deterministic mean (or sum) of n floats into out[0]; single CTA.
 __global__ void reduce_mean_kernel(const float* __restrict__ x, float* __restrict__ out,
-                                   long long n, float scale) {
+                                   long long n, float scale, const float* __restrict__ scale_dev) {
   __shared__ float red[32];
   float s = 0.f;
   for (long long i = threadIdx.x; i < n; i += blockDim.x) s += x[i];
   s = block_reduce_sum(s, red);
-  if (threadIdx.x == 0) out[0] = s * scale;
+  if (threadIdx.x == 0) out[0] = s * scale * (scale_dev != nullptr ? *scale_dev : 1.0f);
+}
+
+// out[0] = 1 / max(1, number of targets that differ from ignore_index): the factor of a mean over
+// the rows that count. Single CTA; runs before the cross-entropy kernel, which reads the factor.
+__global__ void ce_count_valid_kernel(const long long* __restrict__ targets, long long n,
+                                      long long ignore_index, float* __restrict__ out) {
+  __shared__ float red[32];
+  float c = 0.f;
+  for (long long i = threadIdx.x; i < n; i += blockDim.x) c += (targets[i] != ignore_index) ? 1.f : 0.f;
+  c = block_reduce_sum(c, red);
+  if (threadIdx.x == 0) out[0] = 1.0f / fmaxf(c, 1.0f);
 }
 
 // ---- fused AdamW over a flat shard -------------------------------------------------------------
@@ -309,8 +321,8 @@ static bool g_ce_attr = false;
 
 // logits [rows, ld] bf16 (ld % 8 == 0, V <= ld); targets int64; loss_row [rows] fp32.
 MMJ_API int mmj_ce_fwd_bwd(void* logits, long long ld, int V, const long long* targets,
-                           float* loss_row, long long rows, float dscale, long long ignore_index,
-                           int write_grad, void* stream) {
+                           float* loss_row, long long rows, float dscale, const float* dscale_dev,
+                           long long ignore_index, int write_grad, void* stream) {
   if (ld % 8 || V > ld) return -1;
   if (rows == 0) return 0;
   const size_t bytes = (size_t)ld * 2;
@@ -325,7 +337,7 @@ MMJ_API int mmj_ce_fwd_bwd(void* logits, long long ld, int V, const long long* t
   }
   if (ce_mode != 0) {
     ce_fwd_bwd_kernel<false><<<(unsigned)rows, 512, 0, STREAM>>>(
-        (__nv_bfloat16*)logits, ld, V, targets, loss_row, dscale, ignore_index, write_grad);
+        (__nv_bfloat16*)logits, ld, V, targets, loss_row, dscale, dscale_dev, ignore_index, write_grad);
     return (int)cudaGetLastError();
   }
   if (bytes <= 200 * 1024) {
@@ -335,10 +347,10 @@ MMJ_API int mmj_ce_fwd_bwd(void* logits, long long ld, int V, const long long* t
       g_ce_attr = true;
     }
     ce_fwd_bwd_kernel<true><<<(unsigned)rows, 512, bytes, STREAM>>>(
-        (__nv_bfloat16*)logits, ld, V, targets, loss_row, dscale, ignore_index, write_grad);
+        (__nv_bfloat16*)logits, ld, V, targets, loss_row, dscale, dscale_dev, ignore_index, write_grad);
   } else {
     ce_fwd_bwd_kernel<false><<<(unsigned)rows, 1024, 0, STREAM>>>(
-        (__nv_bfloat16*)logits, ld, V, targets, loss_row, dscale, ignore_index, write_grad);
+        (__nv_bfloat16*)logits, ld, V, targets, loss_row, dscale, dscale_dev, ignore_index, write_grad);
   }
   return (int)cudaGetLastError();
 }
@@ -361,8 +373,15 @@ MMJ_API int mmj_ce_vp_grad(void* logits, long long ld, int Vloc, long long vocab
                                                         vocab_start, targets, gmax, gsum, dscale);
   return (int)cudaGetLastError();
 }
-MMJ_API int mmj_reduce_mean(const float* x, float* out, long long n, float scale, void* stream) {
-  reduce_mean_kernel<<<1, 1024, 0, STREAM>>>(x, out, n, scale);
+// out[0] = scale * (*scale_dev, when given) * sum(x)
+MMJ_API int mmj_reduce_mean(const float* x, float* out, long long n, float scale,
+                            const float* scale_dev, void* stream) {
+  reduce_mean_kernel<<<1, 1024, 0, STREAM>>>(x, out, n, scale, scale_dev);
+  return (int)cudaGetLastError();
+}
+MMJ_API int mmj_ce_count_valid(const long long* targets, long long n, long long ignore_index,
+                               float* out_inv, void* stream) {
+  ce_count_valid_kernel<<<1, 1024, 0, STREAM>>>(targets, n, ignore_index, out_inv);
   return (int)cudaGetLastError();
 }
 

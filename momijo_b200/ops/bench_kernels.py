@@ -116,7 +116,7 @@ def bench_ce(small):
 
     lr = torch.empty(R, device="cuda")
     f = lambda: _C.call("mmj_ce_fwd_bwd", _C.ptr(logits), Vp, V, _C.ptr(tgt), _C.ptr(lr), R, 1.0 / R,
-                        -100, 1, _C.current_stream())
+                        None, -100, 1, _C.current_stream())
     med, _ = cuda_time_ms(f)
     by = 2.0 * R * Vp * 2
     return [{"op": "softmax_ce_fwd_bwd", "rows": R, "V": V, "ms": med, "GBs": by / med / 1e6,

@@ -516,24 +516,32 @@ def pad_vocab(V: int, mult: int = 128) -> int:
     return (V + mult - 1) // mult * mult
 
 
+def _inv_valid(t1, ignore_index):
+    """Device scalar 1 / max(1, #targets != ignore_index): the factor of a mean over counted rows."""
+    inv = torch.empty(1, dtype=torch.float32, device=t1.device)
+    _C.call("mmj_ce_count_valid", _C.ptr(t1), t1.numel(), ignore_index, _C.ptr(inv), _C.current_stream())
+    return inv
+
+
 def softmax_cross_entropy(logits, targets, ignore_index=-100, reduction="mean"):
     """Fused softmax cross-entropy returning (loss, dlogits) like the reference's
     ``softmax_cross_entropy`` (legacy/src/momijo/learn/losses/losses.mojo:72-85);
-    ``dlogits`` is the gradient of the reduced loss with respect to the logits."""
+    ``dlogits`` is the gradient of the reduced loss with respect to the logits. The mean runs over
+    the rows whose target is not ``ignore_index`` (on both the CUDA and the CPU path)."""
     V = logits.shape[-1]
     l2 = logits.reshape(-1, V)
-    t1 = targets.reshape(-1)
+    t1 = targets.reshape(-1).contiguous()
     n = l2.shape[0]
     if l2.is_cuda and l2.dtype == bf16:
         work_buf = torch.empty((n, (V + 7) // 8 * 8), dtype=bf16, device=l2.device)
         work = work_buf[:, :V]
         work.copy_(l2)
         loss_row = torch.empty(n, dtype=torch.float32, device=l2.device)
-        nvalid = n if reduction == "mean" else 1
+        inv = _inv_valid(t1, ignore_index) if reduction == "mean" else None
         _C.call("mmj_ce_fwd_bwd", _C.ptr(work), work.stride(0), V, _C.ptr(t1), _C.ptr(loss_row), n,
-                1.0 / nvalid, ignore_index, 1, _C.current_stream())
+                1.0, _C.ptr(inv), ignore_index, 1, _C.current_stream())
         loss = torch.empty(1, dtype=torch.float32, device=l2.device)
-        _C.call("mmj_reduce_mean", _C.ptr(loss_row), _C.ptr(loss), n, 1.0 / nvalid,
+        _C.call("mmj_reduce_mean", _C.ptr(loss_row), _C.ptr(loss), n, 1.0, _C.ptr(inv),
                 _C.current_stream())
         return loss[0], work.reshape(logits.shape)
     lf = l2.float()
@@ -543,13 +551,17 @@ def softmax_cross_entropy(logits, targets, ignore_index=-100, reduction="mean"):
     loss_row = -(logp.gather(1, tt[:, None])[:, 0]) * valid
     d = (torch.softmax(lf, -1) - tF.one_hot(tt, V).float()) * valid[:, None]
     if reduction == "mean":
-        return loss_row.sum() / n, (d / n).to(logits.dtype).view(logits.shape)
+        nv = valid.sum().clamp(min=1)
+        return loss_row.sum() / nv, (d / nv).to(logits.dtype).view(logits.shape)
     return loss_row.sum(), d.to(logits.dtype).view(logits.shape)
 
 
 class _LMHeadCE(torch.autograd.Function):
-    """logits = x @ wte.T, mean cross-entropy, with dlogits produced in the forward pass (in
-    place over the logits) so the backward is two GEMMs."""
+    """logits = x @ wte.T, cross-entropy averaged over the counted rows, with dlogits produced in the
+    forward pass (in place over the logits) so the backward is two GEMMs. The incoming loss gradient is
+    a device scalar: a kernel that leaves at once when it equals 1 scales dlogits by it otherwise, so
+    that both gradient products (the weight gradient written straight into a flat ``main_grad`` buffer
+    included) carry the factor, without a host synchronisation."""
 
     @staticmethod
     def forward(ctx, x, wte, targets, V, ignore_index):
@@ -560,43 +572,31 @@ class _LMHeadCE(torch.autograd.Function):
         gemm(x2, wte, out=logits[:, :wte.shape[0]] if wte.shape[0] != Vp else logits)
         t1 = targets.reshape(-1).contiguous()
         loss_row = torch.empty(M, dtype=torch.float32, device=x.device)
+        inv = _inv_valid(t1, ignore_index)
         _C.call("mmj_ce_fwd_bwd", _C.ptr(logits), logits.stride(0), V, _C.ptr(t1), _C.ptr(loss_row),
-                M, 1.0 / M, ignore_index, 1, _C.current_stream())
+                M, 1.0, _C.ptr(inv), ignore_index, 1, _C.current_stream())
         loss = torch.empty(1, dtype=torch.float32, device=x.device)
-        _C.call("mmj_reduce_mean", _C.ptr(loss_row), _C.ptr(loss), M, 1.0 / M, _C.current_stream())
+        _C.call("mmj_reduce_mean", _C.ptr(loss_row), _C.ptr(loss), M, 1.0, _C.ptr(inv), _C.current_stream())
         ctx.save_for_backward(x2, wte, logits)
         ctx.w_ref = wte
         ctx.xshape = x.shape
+        ctx.consumed = False
         return loss[0]
 
     @staticmethod
     def backward(ctx, dloss):
         x2, wte, dlogits = ctx.saved_tensors
+        if ctx.consumed:
+            raise RuntimeError("lm_head_cross_entropy keeps its logit gradient in place: backward runs once")
+        ctx.consumed = True
         nrow = wte.shape[0]
         dl = dlogits[:, :nrow]
-        # dloss is 1 for a plain ``loss.backward()``; other values (loss scaling) are folded in
-        # by scaling the two gradient products afterwards.
+        ds = dloss.detach().reshape(1).to(torch.float32)
+        _C.call("mmj_scale_bf16_dev", _C.ptr(dlogits), dlogits.stride(0), dlogits.shape[0],
+                dlogits.shape[1], _C.ptr(ds), _C.current_stream())
         dx = gemm(dl, wte, b_mn=True)
         dw = _weight_grad(ctx.w_ref, dl, x2)
-        if not (isinstance(dloss, torch.Tensor) and dloss.numel() == 1 and _is_one(dloss)):
-            dx = dx * dloss.to(dx.dtype)
-            if dw is not None:
-                dw = dw * dloss.to(dw.dtype)
         return dx.view(ctx.xshape), dw, None, None, None
-
-
-_UNIT = {"assume": False}
-
-
-def assume_unit_loss_grad(flag: bool = True):
-    """Skip the host check of the incoming loss gradient (it is 1 for ``loss.backward()``)."""
-    _UNIT["assume"] = bool(flag)
-
-
-def _is_one(t):
-    if _UNIT["assume"]:
-        return True
-    return float(t) == 1.0
 
 
 def lm_head_cross_entropy(x, wte, targets, vocab_size, ignore_index=-100):

@@ -2,9 +2,19 @@
 
 The reference has no pipeline parallelism (``learn/data/pipeline.mojo`` is an input pipeline).
 Inter-stage activations and gradients travel over torch.distributed point-to-point (NCCL on GPUs,
-gloo on CPU) issued asynchronously: receives for the next micro-batch are posted before the
-current one is computed and sends are not waited on until their buffers are reused, so transfers
-overlap with compute. Inside a stage any module may be used, including tensor-parallel blocks.
+gloo on CPU) issued asynchronously, so transfers overlap with compute:
+
+* the last stage posts the receive of the next micro-batch's activation before it computes the
+  current one;
+* in the steady state a stage sends its activation forward and posts the receive of the matching
+  gradient in ONE grouped call, so the gradient is already in flight when the backward starts;
+* sends are not waited on until their buffers are reused.
+
+All p2p operations of a communicator run in issue order on one stream, so a receive posted early
+blocks every later send of this rank until its peer has sent. A middle stage therefore does not
+post its forward receive ahead of time (its own forward send could end up queued behind a receive
+whose sender is, transitively, waiting for that send); only the last stage, which never sends
+forward, does. Inside a stage any module may be used, including tensor-parallel blocks.
 
 1F1B with ``S`` stages and ``m`` micro-batches: stage ``s`` runs ``S - 1 - s`` warm-up forwards,
 then alternates one forward / one backward, then drains the remaining backwards; at most
@@ -90,24 +100,34 @@ class Schedule1F1B:
         saved = []          # (input, output) pairs awaiting their backward
         losses = []
         fwd_i = bwd_i = 0
-        next_act = self._irecv(st.prev_rank) if (not st.is_first and m > 0) else None
+        prefetch_fwd = st.is_last   # see the module docstring: safe only where nothing is sent forward
+        next_act = self._irecv(st.prev_rank) if (prefetch_fwd and not st.is_first and m > 0) else None
+        grad_in_flight = []   # receives of output gradients posted together with the forward send
 
-        def forward_one():
+        def forward_one(steady=False):
             nonlocal fwd_i, next_act
             if st.is_first:
                 x = micro_inputs[fwd_i]
             else:
-                buf, w = next_act
+                buf, w = next_act if next_act is not None else self._irecv(st.prev_rank)
                 w.wait()
                 x = buf.requires_grad_(True)
-                next_act = self._irecv(st.prev_rank) if fwd_i + 1 < m else None
+                next_act = self._irecv(st.prev_rank) if (prefetch_fwd and fwd_i + 1 < m) else None
             y = st(x)
             if st.is_last:
                 loss = loss_fn(y, micro_targets[fwd_i]) if loss_fn is not None else y
                 losses.append(loss.detach())
                 saved.append((x, loss / m))
             else:
-                self._isend(y.detach(), st.next_rank)
+                if steady:
+                    # send the activation and post the receive of the oldest pending gradient together
+                    yd = y.detach().contiguous()
+                    gbuf = torch.empty(self.act_shape, dtype=self.act_dtype, device=self.device)
+                    works = dist.batch_isend_irecv([dist.P2POp(dist.isend, yd, st.next_rank, st.group),
+                                                    dist.P2POp(dist.irecv, gbuf, st.next_rank, st.group)])
+                    grad_in_flight.append((gbuf, _Works(works), yd))
+                else:
+                    self._isend(y.detach(), st.next_rank)
                 saved.append((x, y))
             fwd_i += 1
 
@@ -117,7 +137,10 @@ class Schedule1F1B:
             if st.is_last:
                 y.backward()
             else:
-                g, w = self._irecv(st.next_rank)
+                if grad_in_flight:
+                    g, w, _keep = grad_in_flight.pop(0)
+                else:
+                    g, w = self._irecv(st.next_rank)
                 w.wait()
                 y.backward(g)
             if not st.is_first:
@@ -127,7 +150,7 @@ class Schedule1F1B:
         for _ in range(warm):
             forward_one()
         for _ in range(m - warm):
-            forward_one()
+            forward_one(steady=True)
             backward_one()
         for _ in range(warm):
             backward_one()

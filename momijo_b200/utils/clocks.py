@@ -28,10 +28,31 @@ class ClockSampler:
 
             pynvml.nvmlInit()
             self._nv = pynvml
-            self._h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            self._h = self._handle_of(pynvml, device_index)
             self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
         except Exception:
             self._nv = None
+
+    @staticmethod
+    def _handle_of(nv, cuda_index: int):
+        """NVML handle of the CUDA device ``cuda_index``. CUDA ordinals follow CUDA_VISIBLE_DEVICES,
+        NVML indices do not, so the device is looked up by its UUID (falling back to the PCI bus id,
+        then to the plain index when torch is not importable)."""
+        try:
+            import torch
+
+            props = torch.cuda.get_device_properties(cuda_index)
+            uuid = getattr(props, "uuid", None)
+            if uuid is not None:
+                try:
+                    return nv.nvmlDeviceGetHandleByUUID(("GPU-" + str(uuid)).encode())
+                except Exception:
+                    pass
+            bus = "%08x:%02x:%02x.0" % (getattr(props, "pci_domain_id", 0), props.pci_bus_id,
+                                        props.pci_device_id)
+            return nv.nvmlDeviceGetHandleByPciBusId(bus.encode())
+        except Exception:
+            return nv.nvmlDeviceGetHandleByIndex(cuda_index)
 
     def _loop(self):
         nv = self._nv
