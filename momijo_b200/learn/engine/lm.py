@@ -20,4 +20,4 @@ def train_step_e2e(engine, host_tokens: torch.Tensor) -> float:
     """host_tokens: pinned int64 [B, T+1]. Includes the H2D copy and the D2H loss read."""
     dev = next(engine.parameters()).device
     tok = host_tokens.to(dev, non_blocking=True)
-    return float(train_step(engine, tok))
+    return float(train_step(engine, tok).detach())

@@ -17,10 +17,13 @@ def _rand(*s, scale=1.0, grad=False):
     return t.requires_grad_(grad)
 
 
-def _close(out, ref, tol=2e-2):
+def _close(out, ref, tol=2e-2, fro=1e-2):
+    """Max error relative to the largest reference entry, and the relative Frobenius error."""
     out, ref = out.float(), ref.float()
     err = ((out - ref).abs().max() / ref.abs().max().clamp_min(1e-6)).item()
     assert err < tol, f"relative max error {err}"
+    ferr = ((out - ref).norm() / ref.norm().clamp_min(1e-6)).item()
+    assert ferr < fro, f"relative Frobenius error {ferr}"
 
 
 @pytest.mark.parametrize("C", [768, 2048, 4096, 5120, 136])
@@ -117,7 +120,7 @@ def test_cross_entropy(V):
     tgt[3] = -100
     loss, dl = ops.softmax_cross_entropy(logits, tgt)
     lr = logits.detach().float().requires_grad_(True)
-    ref = F.cross_entropy(lr, tgt, ignore_index=-100, reduction="sum") / n
+    ref = F.cross_entropy(lr, tgt, ignore_index=-100)   # mean over the rows that count
     ref.backward()
     assert abs(loss.item() - ref.item()) < 2e-2 * abs(ref.item())
     _close(dl, lr.grad, 3e-2)
@@ -136,6 +139,28 @@ def test_lm_head_ce():
     assert abs(loss.item() - ref.item()) < 1e-2 * abs(ref.item())
     _close(x.grad, xr.grad, 4e-2)
     _close(w.grad, wr.grad, 4e-2)
+
+
+def test_lm_head_ce_scaled_loss_reaches_main_grad():
+    """(loss * s).backward() must scale the head's weight gradient too when that gradient is written straight
+    into a flat main_grad buffer (autograd then never sees it), and ignored targets must not count."""
+    torch.manual_seed(5)
+    M, C, V = 256, 128, 1000
+    x = _rand(M, C, grad=True)
+    w = _rand(ops.pad_vocab(V), C, scale=0.05, grad=True)
+    w.main_grad = torch.zeros_like(w)
+    w._mg_fresh = True
+    tgt = torch.randint(0, V, (M,), device="cuda")
+    tgt[:17] = -100
+    loss = ops.lm_head_cross_entropy(x, w, tgt, V)
+    (loss * 0.25).backward()
+    assert w.grad is None
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    ref = F.cross_entropy((xr @ wr.t())[:, :V], tgt, ignore_index=-100)
+    (ref * 0.25).backward()
+    assert abs(loss.item() - ref.item()) < 1e-2 * abs(ref.item())
+    _close(x.grad, xr.grad, 4e-2, 2e-2)
+    _close(w.main_grad, wr.grad, 4e-2, 2e-2)
 
 
 def test_adamw_and_sqnorm():
