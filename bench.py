@@ -51,6 +51,8 @@ def parse():
                          "same process group and report value / that as vs_baseline; 0: skip it")
     ap.add_argument("--zero-stage", type=int, default=3, choices=[1, 2, 3],
                     help="sharding stage of the headline config for N > 1")
+    ap.add_argument("--fuse-first-gemm", type=int, default=1,
+                    help="stages 1-2: gather each block's first weight inside the GEMM that consumes it")
     ap.add_argument("--torch-variant", default="autocast", choices=["autocast", "bf16-master"],
                     help="stock-PyTorch arm of the headline config: fp32 parameters under bf16 autocast, or bf16 "
                          "parameters with an fp32 master copy")
@@ -107,7 +109,7 @@ def timed(fn_step, steps, world):
     return max_over_ranks(a.elapsed_time(b)) / steps
 
 
-def build_ours(cfg, world, rank, local, stage=3):
+def build_ours(cfg, world, rank, local, stage=3, fuse_first_gemm=True):
     import torch
     from momijo_b200 import ops
     from momijo_b200.models import GPT2
@@ -121,7 +123,7 @@ def build_ours(cfg, world, rank, local, stage=3):
 
         comm = PeerComm.from_default_group()
     engine = ShardedDataParallel(model, AdamWConfig(lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1),
-                                 stage=stage, comm=comm)
+                                 stage=stage, comm=comm, fuse_first_gemm=fuse_first_gemm)
     return engine
 
 
@@ -499,7 +501,7 @@ def setup_gpt2(args, rank, world, local, impl):
     extra = {}
 
     if impl == "ours":
-        engine = build_ours(cfg, world, rank, local, stage=args.zero_stage)
+        engine = build_ours(cfg, world, rank, local, stage=args.zero_stage, fuse_first_gemm=bool(args.fuse_first_gemm))
 
         def step_device(i):
             t = dev_tok[i % n_batches]
@@ -638,7 +640,7 @@ def time_arm(args, impl, rank, world, local, step_device, step_e2e, info):
     launches = _C.launches - launches0
     ms_e2e = timed(step_e2e, args.steps, world)
     clocks = sampler.stop() if sampler is not None else None
-    loss_val = float(last[0]) if last and last[0] is not None else None
+    loss_val = float(last[0].detach()) if last and last[0] is not None else None
     if impl == "ours":
         _C.check_status()
     if rank != 0:

@@ -33,12 +33,16 @@ def main(argv=None):
         if cuda:
             from momijo_b200.parallel.peer import PeerComm
             comm = PeerComm.from_default_group()
+        else:
+            from momijo_b200.parallel.peer import TorchDistComm
+            comm = TorchDistComm()
     cfg = GPT2Config.small() if args.model == "small" else GPT2Config.tiny()
     torch.manual_seed(0)
     model = GPT2(cfg)
     if cuda:
         model = model.cuda()
-    engine = ShardedDataParallel(model, AdamWConfig(lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1), comm=comm)
+    engine = ShardedDataParallel(model, AdamWConfig(lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1), comm=comm,
+                                 overlap=cuda)
     g = torch.Generator().manual_seed(100 + rank)
     T = min(cfg.max_seq, 128)
     losses = []

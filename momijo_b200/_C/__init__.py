@@ -80,7 +80,9 @@ _SIGS = {
     "mmj_barrier": ([P, I, I, I, I, P, P], 1),
     "mmj_signal_peers": ([P, I, I, I, I, P], 1),
     "mmj_wait_flag": ([P, I, P, P], 1),
-    "mmj_rs_adamw": ([P, P, P, P, P, P, P, L, L, F, F, F, F, F, F, F, F, I, I, I, I, P, P, P, P], 1),
+    "mmj_rs_adamw": ([P, P, P, P, P, P, P, L, L, F, F, F, F, F, F, F, F, P, P, I, I, I, I, I, P, P, P, P], 1),
+    "mmj_gather_bucket": ([P, P, P, L, L, P, I, I, I, I, I, I, I, P, P], 1),
+    "mmj_allreduce_small_f32": ([P, P, P, P, I, I, I, I, I, P, P], 1),
     "mmj_allgather_ranges": ([P, P, L, P, I, I, I, I, I, P, P], 1),
     "mmj_allreduce_bf16": ([P, P, P, L, F, I, I, I, I, P, P, P, P], 1),
     "mmj_reduce_slots_bf16": ([P, P, L, P, P, L, I, I, I, I, P, P], 1),

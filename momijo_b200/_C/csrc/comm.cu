@@ -143,6 +143,10 @@ struct RsAdamwParams {
   long long shard_off;    // first element of the local shard in the flat buffers
   long long shard_elems;  // multiple of 8
   float lr, b1, b2, eps, wd, inv_bc1, inv_bc2, grad_scale;
+  const float* grad_scale_dev;  // optional device factor on top of grad_scale (gradient clipping)
+  float* reduced_out;     // optional [shard_elems] fp32: write the reduced, scaled gradient shard here
+                          // and leave master / m / v / param untouched (the update then runs later,
+                          // once a global gradient norm is known)
   int slot_base;          // uses slots [slot_base, slot_base + 2*world)
   int epoch;
   unsigned int* block_counter;
@@ -152,12 +156,14 @@ struct RsAdamwParams {
 
 __global__ void __launch_bounds__(256) rs_adamw_kernel(const RsAdamwParams p) {
   __shared__ int ok;
-  // entry: every rank has finished writing its gradients
-  if (!block_barrier(p.t, p.slot_base, p.epoch, p.status, &ok)) return;
+  // entry: every rank has finished writing its gradients. A block whose barrier ran out of time skips
+  // the work but still takes part in the block count below, so the wrapping counter ends at zero.
+  const bool entered = block_barrier(p.t, p.slot_base, p.epoch, p.status, &ok);
 
   const int W = p.t.world;
-  const float scale = p.grad_scale / (float)W;
-  const long long nvec = p.shard_elems >> 3;
+  float scale = p.grad_scale / (float)W;
+  if (p.grad_scale_dev != nullptr) scale *= *p.grad_scale_dev;
+  const long long nvec = entered ? (p.shard_elems >> 3) : 0;
   float sq = 0.f;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
        i += (long long)gridDim.x * blockDim.x) {
@@ -181,6 +187,16 @@ __global__ void __launch_bounds__(256) rs_adamw_kernel(const RsAdamwParams p) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) acc[j] += f[j];
         }
+    }
+    if (p.reduced_out != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        acc[j] *= scale;
+        sq += acc[j] * acc[j];
+      }
+      *reinterpret_cast<float4*>(p.reduced_out + i * 8) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      *reinterpret_cast<float4*>(p.reduced_out + i * 8 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      continue;
     }
     float4 w0 = *reinterpret_cast<float4*>(p.master + i * 8), w1 = *reinterpret_cast<float4*>(p.master + i * 8 + 4);
     float4 m0 = *reinterpret_cast<float4*>(p.m + i * 8), m1 = *reinterpret_cast<float4*>(p.m + i * 8 + 4);
@@ -211,8 +227,84 @@ __global__ void __launch_bounds__(256) rs_adamw_kernel(const RsAdamwParams p) {
   }
   // exit: nobody leaves before every rank has finished pulling gradients and publishing its
   // parameter shard (so the next step may overwrite gradients and read peer parameters)
-  if (last_block_done(p.block_counter))
+  if (last_block_done(p.block_counter) && entered)
     block_barrier(p.t, p.slot_base + W, p.epoch, p.status, &ok);
+}
+
+// ================================================================================================
+// Bucket all-gather: a bucket of `world * shard_bytes` bytes is cut into one contiguous shard per
+// rank. Each rank pulls the shards it does not own into dst (bucket layout: shard r at r * shard_bytes)
+// from src[r] + r * src_stride (src_stride = shard_bytes when the peers keep the bucket in the same
+// full layout, 0 when every peer keeps only its own shard in a compact buffer; copy_self then also
+// copies the local shard). Up to four byte ranges of the bucket can be left out: the GEMM that
+// consumes such a range first gathers it itself.
+// ================================================================================================
+struct GatherBucketParams {
+  PeerTable t;
+  const uint8_t* src[kMaxWorld];
+  uint8_t* dst;
+  long long shard_bytes, src_stride;
+  long long skip_lo[4], skip_hi[4];
+  int n_skip, copy_self;
+  int slot_base, epoch;  // entry barrier slots (skipped when epoch < 0)
+  int* status;
+};
+
+__global__ void __launch_bounds__(256) gather_bucket_kernel(const GatherBucketParams p) {
+  __shared__ int ok;
+  if (p.epoch >= 0 && !block_barrier(p.t, p.slot_base, p.epoch, p.status, &ok)) return;
+  const long long n16 = p.shard_bytes >> 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (int rr = 0; rr < p.t.world; ++rr) {
+    const int r = (p.t.rank + rr) % p.t.world;  // every rank starts at a different owner
+    if (r == p.t.rank && !p.copy_self) continue;
+    const uint8_t* s = p.src[r] + (long long)r * p.src_stride;
+    uint8_t* d = p.dst + (long long)r * p.shard_bytes;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n16; i += stride) {
+      const long long off = (long long)r * p.shard_bytes + (i << 4);
+      bool skip = false;
+      for (int k = 0; k < p.n_skip; ++k) skip |= (off >= p.skip_lo[k] && off < p.skip_hi[k]);
+      if (skip) continue;
+      *reinterpret_cast<uint4*>(d + (i << 4)) = *reinterpret_cast<const uint4*>(s + (i << 4));
+    }
+  }
+}
+
+// ================================================================================================
+// Small fp32 all-reduce (sum) of n <= 64 values: every rank stores its values into slot `rank` of
+// every peer's staging buffer ([world][64] floats, symmetric), one barrier, then each rank adds the
+// world slots in rank order (the same order everywhere: bitwise equal results on every rank). Single
+// block. Used for gradient-norm and loss-statistic scalars, where a library collective's launch and
+// synchronisation would cost more than the data.
+// ================================================================================================
+struct SmallAllReduceParams {
+  PeerTable t;
+  float* stage[kMaxWorld];
+  const float* in;
+  float* out;
+  int n;
+  int slot_base, epoch;
+  int* status;
+};
+
+__global__ void __launch_bounds__(64) allreduce_small_kernel(const SmallAllReduceParams p) {
+  __shared__ int ok;
+  const int W = p.t.world;
+  // two staging halves used alternately: a rank may start the next call while a slow peer still
+  // reads the values of this one
+  const int half = (p.epoch & 1) * kMaxWorld * 64;
+  if ((int)threadIdx.x < p.n) {
+    const float v = p.in[threadIdx.x];
+    for (int r = 0; r < W; ++r) p.stage[r][half + p.t.rank * 64 + threadIdx.x] = v;
+  }
+  __threadfence_system();
+  if (!block_barrier(p.t, p.slot_base, p.epoch, p.status, &ok)) return;
+  if ((int)threadIdx.x < p.n) {
+    float s = 0.f;
+    const volatile float* mine = p.stage[p.t.rank] + half;
+    for (int r = 0; r < W; ++r) s += mine[r * 64 + threadIdx.x];
+    p.out[threadIdx.x] = s;
+  }
 }
 
 // ================================================================================================
@@ -614,7 +706,8 @@ MMJ_API int mmj_wait_flag(const int* slot, int epoch, int* status, void* stream)
 MMJ_API int mmj_rs_adamw(void* const* sig, void* const* grads, const void* grad_mc, void* param,
                          float* master, float* m, float* v, long long shard_off,
                          long long shard_elems, float lr, float b1, float b2, float eps, float wd,
-                         float bc1, float bc2, float grad_scale, int world, int rank, int slot_base,
+                         float bc1, float bc2, float grad_scale, const float* grad_scale_dev,
+                         float* reduced_out, int max_blocks, int world, int rank, int slot_base,
                          int epoch, unsigned int* block_counter, float* sqnorm_out, int* status,
                          void* stream) {
   if (world < 1 || world > kMaxWorld) return -1;
@@ -629,14 +722,63 @@ MMJ_API int mmj_rs_adamw(void* const* sig, void* const* grads, const void* grad_
   p.lr = lr; p.b1 = b1; p.b2 = b2; p.eps = eps; p.wd = wd;
   p.inv_bc1 = 1.0f / bc1; p.inv_bc2 = 1.0f / bc2;
   p.grad_scale = grad_scale;
+  p.grad_scale_dev = grad_scale_dev;
+  p.reduced_out = reduced_out;
   p.slot_base = slot_base; p.epoch = epoch;
   p.block_counter = block_counter;
   p.sqnorm_out = sqnorm_out;
   p.status = status;
   long long want = (shard_elems / 8 + 255) / 256;
   int grid = resident_grid(4);
+  // a launch that runs beside the backward pass is given fewer blocks, so that it does not crowd
+  // the GEMM CTAs out of issue slots and memory bandwidth
+  if (max_blocks > 0 && max_blocks < grid) grid = max_blocks;
   if (want < grid) grid = (int)(want < 1 ? 1 : want);
   rs_adamw_kernel<<<grid, 256, 0, STREAM>>>(p);
+  return (int)cudaGetLastError();
+}
+
+MMJ_API int mmj_gather_bucket(void* const* sig, void* const* srcs, void* dst, long long shard_bytes,
+                              long long src_stride, const long long* skip_ranges, int n_skip,
+                              int copy_self, int max_blocks, int world, int rank, int slot_base,
+                              int epoch, int* status, void* stream) {
+  if (world < 1 || world > kMaxWorld) return -1;
+  if ((shard_bytes & 15) || (src_stride & 15) || n_skip < 0 || n_skip > 4) return -2;
+  GatherBucketParams p;
+  p.t = make_table(world, rank, sig);
+  for (int r = 0; r < kMaxWorld; ++r) p.src[r] = (r < world) ? (const uint8_t*)srcs[r] : nullptr;
+  p.dst = (uint8_t*)dst;
+  p.shard_bytes = shard_bytes;
+  p.src_stride = src_stride;
+  for (int k = 0; k < 4; ++k) {
+    p.skip_lo[k] = (k < n_skip) ? skip_ranges[2 * k] : 0;       // host array
+    p.skip_hi[k] = (k < n_skip) ? skip_ranges[2 * k + 1] : 0;
+  }
+  p.n_skip = n_skip;
+  p.copy_self = copy_self;
+  p.slot_base = slot_base; p.epoch = epoch;
+  p.status = status;
+  int grid = resident_grid(2);
+  if (max_blocks > 0 && max_blocks < grid) grid = max_blocks;
+  long long want = (shard_bytes / 16 + 255) / 256;
+  if (want < grid) grid = (int)(want < 1 ? 1 : want);
+  gather_bucket_kernel<<<grid, 256, 0, STREAM>>>(p);
+  return (int)cudaGetLastError();
+}
+
+// stage[r]: rank r's staging buffer of 2 * 8 * 64 floats (symmetric); in / out: n <= 64 local floats.
+MMJ_API int mmj_allreduce_small_f32(void* const* sig, void* const* stage, const float* in, float* out,
+                                    int n, int world, int rank, int slot_base, int epoch, int* status,
+                                    void* stream) {
+  if (world < 1 || world > kMaxWorld) return -1;
+  if (n < 1 || n > 64) return -2;
+  SmallAllReduceParams p;
+  p.t = make_table(world, rank, sig);
+  for (int r = 0; r < kMaxWorld; ++r) p.stage[r] = (r < world) ? (float*)stage[r] : nullptr;
+  p.in = in; p.out = out; p.n = n;
+  p.slot_base = slot_base; p.epoch = epoch;
+  p.status = status;
+  allreduce_small_kernel<<<1, 64, 0, STREAM>>>(p);
   return (int)cudaGetLastError();
 }
 

@@ -55,6 +55,9 @@ class GPT2Config:
 
 
 class GPT2Block(nn.Module):
+    # sharded data parallel: the all-gather of this weight is fused into the GEMM that first uses it
+    zero_first_gemm_weight = "w_qkv"
+
     def __init__(self, cfg: GPT2Config):
         super().__init__()
         c, f, dt = cfg.d_model, cfg.d_ff, cfg.dtype

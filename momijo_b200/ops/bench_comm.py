@@ -87,16 +87,16 @@ def main():
             def __init__(s):
                 super().__init__()
                 s.w = torch.nn.Parameter(torch.zeros(n_param, dtype=bf16, device="cuda"))
-        sdp = ShardedDataParallel(Box(), AdamWConfig(lr=1e-4), stage=3, comm=comm)
-        sdp.flat.grad.fill_(0.01)
-        sdp.step_count = 1
+        sdp = ShardedDataParallel(Box(), AdamWConfig(lr=1e-4), stage=1, comm=comm)
+        sdp.grad_buf.fill_(0.01)
+        b0 = sdp.buckets[0]
 
         def zstep():
-            comm.reduce_scatter_adamw(sdp, 1e-4)
-            comm.all_gather_params(sdp)
+            comm.rs_adamw_bucket(sdp, b0, 1e-4, 1)
+            comm.gather_bucket(sdp, b0, compact=False)
         ms = timed(zstep)
-        ms_rs = timed(lambda: comm.reduce_scatter_adamw(sdp, 1e-4))
-        N = sdp.flat.layout.total
+        ms_rs = timed(lambda: comm.rs_adamw_bucket(sdp, b0, 1e-4, 1))
+        N = sdp.total
         link_bytes = 2 * frac * N * 2              # RS pulls + AG pulls, per GPU
         hbm_bytes = N * 2 + (N // W) * (2 + 12 * 2 + 2) + N * 2   # read grads, update shard, write gathered params
         roof = max(link_bytes / LINK, hbm_bytes / hbm) * 1e3

@@ -80,7 +80,13 @@ class _Linear(torch.autograd.Function):
     def forward(ctx, x, w, b, residual):
         x2 = x.reshape(-1, x.shape[-1])
         res2 = residual.reshape(-1, w.shape[0]) if residual is not None else None
-        y = gemm(x2, w, bias=b, add_aux=res2)
+        zg = getattr(w, "_zero_gather", None)
+        if zg is not None and zg.pending:
+            # sharded data parallel: the other ranks' pieces of this weight have not been gathered
+            # yet; this GEMM pulls them over NVLink while it computes (and leaves w complete)
+            y = zg.gemm(x2, w, bias=b, add_aux=res2)
+        else:
+            y = gemm(x2, w, bias=b, add_aux=res2)
         ctx.save_for_backward(x2, w)
         ctx.b = b
         ctx.w_ref = w

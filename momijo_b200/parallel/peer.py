@@ -64,6 +64,7 @@ class PeerComm:
         self._next_slot = 0
         self._epochs = {}
         self.counters = torch.zeros(64, dtype=torch.int32, device=self.device)
+        self._counter_blocks = []
         self._next_counter = 0
         self.status = _C.status_tensor(self.device)
 
@@ -111,9 +112,28 @@ class PeerComm:
         return self._epochs[base]
 
     def new_counter(self, n: int = 1) -> torch.Tensor:
+        """``n`` zeroed int32 counters (wrapping block counters / grid flags of one call site)."""
+        if self._next_counter + n > self.counters.numel():
+            # a fresh block: earlier slices keep pointing into the old tensors, which stay alive
+            self._counter_blocks.append(self.counters)
+            self.counters = torch.zeros(max(64, n), dtype=torch.int32, device=self.device)
+            self._next_counter = 0
         c = self.counters[self._next_counter:self._next_counter + n]
         self._next_counter += n
         return c
+
+    def reset_after_timeout(self):
+        """After a bounded wait ran out (``_C.check_status`` raised): blocks that gave up may have left
+        wrapping block counters and grid flags mid-count; zero them before the communicator is used
+        again. Collective: every rank calls it."""
+        for t in self._counter_blocks + [self.counters]:
+            t.zero_()
+        self.status.zero_()
+        self.host_barrier()
+
+    def host_barrier(self):
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
 
     # ---- collectives ----
     def barrier(self, slots: Optional[int] = None):
@@ -159,37 +179,109 @@ class PeerComm:
                 _C.ptr(self.status), _C.current_stream())
         return full
 
-    # ---- ZeRO step (called by ShardedDataParallel) ----
-    def reduce_scatter_adamw(self, sdp, lr: float):
-        flat, o = sdp.flat, sdp.optim
-        if not hasattr(sdp, "_rs"):
-            sdp._rs = (self.new_slots(2 * self.world), self.new_counter(1))
-            sdp._grad_ptrs = self.peer_ptrs(flat.grad)
-        slots, ctr = sdp._rs
-        a, _ = flat.layout.shard_range(self.rank)
-        step = sdp.step_count
-        _C.call("mmj_rs_adamw", self._sig_ptrs, sdp._grad_ptrs, self.mc_ptr(flat.grad),
-                _C.ptr(flat.param), _C.ptr(sdp.master), _C.ptr(sdp.m), _C.ptr(sdp.v), a,
-                flat.layout.shard, lr, o.betas[0], o.betas[1], o.eps, o.weight_decay,
-                1.0 - o.betas[0] ** step, 1.0 - o.betas[1] ** step, 1.0, self.world, self.rank,
-                slots, self.next_epoch(slots), _C.ptr(ctr), None, _C.ptr(self.status),
+    # ---- bucket operations of ShardedDataParallel ----
+    def new_fused_site(self):
+        from ..ops.fused_comm import FusedSite
+
+        return FusedSite(self)
+
+    def rs_adamw_bucket(self, eng, b, lr: float, step: int, reduce_only: bool = False, max_blocks: int = 0):
+        """Gradient reduce-scatter of bucket ``b`` over peer memory fused with the 1/world scaling and the
+        AdamW update of the local shard (one kernel). ``reduce_only``: write the reduced fp32 gradient
+        shard and its sum of squares instead of updating (gradient clipping needs the global norm first)."""
+        h, o = b.handle, eng.optim
+        if "rs" not in h:
+            h["rs"] = (self.new_slots(2 * self.world), self.new_counter(1), self.peer_ptrs(b.gview))
+        slots, ctr, gptrs = h["rs"]
+        shard_off = self.rank * b.shard
+        if eng.stage <= 2:
+            param_ptr = b.pview.data_ptr()                       # kernel writes at + shard_off
+        else:
+            param_ptr = eng.pshard.data_ptr() + (b.moff - shard_off) * 2
+        mo = b.moff * 4
+        _C.call("mmj_rs_adamw", self._sig_ptrs, gptrs, self.mc_ptr(b.gview), param_ptr,
+                eng.master.data_ptr() + mo, eng.m.data_ptr() + mo, eng.v.data_ptr() + mo, shard_off, b.shard,
+                lr, o.betas[0], o.betas[1], o.eps, o.weight_decay, 1.0 - o.betas[0] ** step,
+                1.0 - o.betas[1] ** step, eng.grad_scale, None,
+                (eng.reduced.data_ptr() + mo) if reduce_only else None, max_blocks, self.world, self.rank,
+                slots, self.next_epoch(slots), _C.ptr(ctr), _C.ptr(eng.gnorm_sq) if reduce_only else None,
+                _C.ptr(self.status), _C.current_stream())
+
+    def gather_bucket(self, eng, b, compact: bool, skip=None, max_blocks: int = 0):
+        """Pull the shards of bucket ``b`` that other ranks own into ``b.pview``. ``compact``: the peers keep
+        only their own shard (``eng.pshard``); otherwise they keep the bucket in the same full layout.
+        ``skip``: a byte range of the bucket left to the GEMM that gathers it itself. Follows a kernel
+        that ended with a cross-GPU barrier (or an explicit one), so it has no entry barrier."""
+        h = b.handle
+        key = "gc" if compact else "gf"
+        if key not in h:
+            src = eng.pshard[b.moff:b.moff + b.shard] if compact else b.pview
+            h[key] = self.peer_ptrs(src)
+            if not hasattr(self, "_gb_slots"):
+                self._gb_slots = self.new_slots(self.world)
+        skip_arr = (ctypes.c_longlong * 2)(*skip) if skip is not None else None
+        _C.call("mmj_gather_bucket", self._sig_ptrs, h[key], b.pview.data_ptr(), b.shard * 2,
+                0 if compact else b.shard * 2, skip_arr, 1 if skip is not None else 0, int(compact),
+                max_blocks, self.world, self.rank, self._gb_slots, -1, _C.ptr(self.status),
                 _C.current_stream())
 
-    def all_gather_params(self, sdp, ranges=None):
-        """Pull the parameter shards owned by the other ranks (byte ``ranges`` of the flat buffer,
-        default: everything)."""
-        flat = sdp.flat
-        if not hasattr(sdp, "_ag"):
-            sdp._ag_slots = self.new_slots(self.world)
-            sdp._param_ptrs = self.peer_ptrs(flat.param)
-            sdp._ag = {}
-        key = None if ranges is None else tuple(map(tuple, ranges))
-        dev_ranges = sdp._ag.get(key)
-        if dev_ranges is None:
-            rs = [(0, flat.layout.total * 2)] if ranges is None else list(ranges)
-            dev_ranges = torch.tensor(rs, dtype=torch.int64, device=self.device).reshape(-1)
-            sdp._ag[key] = dev_ranges
-        # the reduce-scatter kernel ends with a barrier, so no entry barrier is needed (epoch -1)
-        _C.call("mmj_allgather_ranges", self._sig_ptrs, sdp._param_ptrs, flat.layout.shard * 2,
-                _C.ptr(dev_ranges), dev_ranges.numel() // 2, self.world, self.rank, sdp._ag_slots,
-                -1, _C.ptr(self.status), _C.current_stream())
+    def all_reduce_small(self, t: torch.Tensor) -> torch.Tensor:
+        """Sum of a small fp32 tensor (<= 64 values) over the ranks; the same bits on every rank."""
+        n = t.numel()
+        if not hasattr(self, "_ars"):
+            stage = self.alloc(2 * 8 * 64, torch.float32)
+            self._ars = (stage, self.peer_ptrs(stage), self.new_slots(self.world))
+            self.host_barrier()
+        stage, ptrs, slots = self._ars
+        out = torch.empty_like(t)
+        _C.call("mmj_allreduce_small_f32", self._sig_ptrs, ptrs, _C.ptr(t), _C.ptr(out), n, self.world,
+                self.rank, slots, self.next_epoch(slots), _C.ptr(self.status), _C.current_stream())
+        return out
+
+
+class TorchDistComm:
+    """The same bucket operations through torch.distributed (gloo on CPU, NCCL on GPUs without peer
+    memory): the host-side logic of ``ShardedDataParallel`` (buckets, stages, hooks, clipping) runs and
+    is tested with it; the fused peer-memory kernels are ``PeerComm``'s."""
+
+    def __init__(self, group=None):
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+
+    def alloc(self, n, dtype=torch.float32, device=None):
+        return torch.zeros(n, dtype=dtype, device=device)
+
+    def barrier(self):
+        dist.barrier(self.group)
+
+    host_barrier = barrier
+
+    def all_reduce_small(self, t):
+        out = t.clone()
+        dist.all_reduce(out, group=self.group)
+        return out
+
+    def rs_adamw_bucket(self, eng, b, lr, step, reduce_only=False, max_blocks=0):
+        from ..ops.optim import adamw_flat
+
+        o = eng.optim
+        g = b.gview.float()
+        dist.all_reduce(g, group=self.group)
+        lo = self.rank * b.shard
+        mine = g[lo:lo + b.shard] * (eng.grad_scale / self.world)
+        sl = slice(b.moff, b.moff + b.shard)
+        if reduce_only:
+            eng.reduced[sl].copy_(mine)
+            eng.gnorm_sq += mine.pow(2).sum()
+            return
+        p_out = b.pview[lo:lo + b.shard] if eng.stage <= 2 else eng.pshard[sl]
+        adamw_flat(mine, eng.master[sl], eng.m[sl], eng.v[sl], p_out, lr=lr, beta1=o.betas[0], beta2=o.betas[1],
+                   eps=o.eps, weight_decay=o.weight_decay, step=step)
+
+    def gather_bucket(self, eng, b, compact, skip=None, max_blocks=0):
+        lo = self.rank * b.shard
+        mine = (eng.pshard[b.moff:b.moff + b.shard] if compact else b.pview[lo:lo + b.shard]).clone()
+        parts = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(parts, mine, group=self.group)
+        b.pview.copy_(torch.cat(parts))

@@ -18,10 +18,13 @@ from momijo_b200.parallel.peer import PeerComm  # noqa: E402
 bf16 = torch.bfloat16
 
 
-def close(a, b, tol, what):
+def close(a, b, tol, what, fro=None):
     a, b = a.float(), b.float()
     err = ((a - b).abs().max() / b.abs().max().clamp_min(1e-6)).item()
     assert err < tol, f"{what}: relative max error {err}"
+    if fro is not None:
+        ferr = ((a - b).norm() / b.norm().clamp_min(1e-6)).item()
+        assert ferr < fro, f"{what}: relative Frobenius error {ferr}"
 
 
 def sc_allreduce(comm):
@@ -43,33 +46,60 @@ def sc_allreduce(comm):
 
 
 def sc_zero(comm):
-    """2+ rank sharded engine == single-rank engine on the concatenated batch."""
+    """2+ rank sharded engine == single-rank engine on the concatenated batch, for every stage: buckets per
+    block reduced and updated during the backward pass, gradient pool (stage 2), parameter window (stage 3),
+    the first weight of every block gathered by its GEMM (stages 1-2), and a scaled loss."""
     from momijo_b200.models import GPT2, GPT2Config
     from momijo_b200.parallel import ShardedDataParallel, AdamWConfig
 
-    cfg = GPT2Config.tiny()
-    torch.manual_seed(0)
-    m_dist = GPT2(cfg).cuda()
-    torch.manual_seed(0)
-    m_ref = GPT2(cfg).cuda()
+    cfg = GPT2Config(vocab_size=1000, n_layer=5, n_head=2, d_model=128, d_ff=512, max_seq=256)
     oc = AdamWConfig(lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
-    eng = ShardedDataParallel(m_dist, oc, comm=comm)
-    ref = ShardedDataParallel(m_ref, oc)
-    g = torch.Generator().manual_seed(7)
     B = 2
-    for step in range(3):
-        full = torch.randint(0, cfg.vocab_size, (B * comm.world, 129), generator=g).cuda()
-        mine = full[comm.rank * B:(comm.rank + 1) * B]
-        loss = eng(mine[:, :-1], mine[:, 1:])
-        loss.backward()
-        eng.step()
-        lr_ = ref(full[:, :-1], full[:, 1:])
-        lr_.backward()
-        ref.step()
-    torch.cuda.synchronize()
-    close(eng.flat.param, ref.flat.param, 2e-2, "zero params after 3 steps")
-    a, b = eng.flat.layout.shard_range(comm.rank)
-    close(eng.master, ref.master[a:b], 2e-2, "zero master shard")
+    for stage, clip in ((1, None), (2, None), (3, None), (2, 0.5)):
+        torch.manual_seed(0)
+        m_dist = GPT2(cfg).cuda()
+        torch.manual_seed(0)
+        m_ref = GPT2(cfg).cuda()
+        eng = ShardedDataParallel(m_dist, oc, stage=stage, comm=comm, grad_clip=clip, window=2, grad_slots=2)
+        ref = ShardedDataParallel(m_ref, oc, grad_clip=clip)
+        assert len(eng.buckets) == cfg.n_layer + 1
+        if stage <= 2:
+            assert all(b.fused is not None for b in eng.unit_buckets)
+        g = torch.Generator().manual_seed(7)
+        for step in range(4):
+            full = torch.randint(0, cfg.vocab_size, (B * comm.world, 129), generator=g).cuda()
+            mine = full[comm.rank * B:(comm.rank + 1) * B]
+            s = 0.5 if step == 2 else 1.0     # a scaled loss must scale every gradient, the tied head included
+            loss = eng(mine[:, :-1], mine[:, 1:])
+            (loss * s).backward()
+            eng.step()
+            lr_ = ref(full[:, :-1], full[:, 1:])
+            (lr_ * s).backward()
+            ref.step()
+        got = eng.materialize()
+        want = ref.materialize()
+        torch.cuda.synchronize()
+        # Adam turns a noise-sized gradient difference (two half-batch bf16 gradients summed against one
+        # full-batch bf16 gradient) into a full-sized step for single elements, and some parameters (the key
+        # bias, whose true gradient is zero) move by such noise only. So: per parameter an absolute bound of
+        # the size of four Adam steps, and a Frobenius bound over all parameters together (a bucket whose
+        # update went missing or landed in the wrong place would read about 0.2 there).
+        for name in want:
+            d = (got[name].float() - want[name].float()).abs().max().item()
+            assert d < 8e-2 * max(want[name].float().abs().max().item(), 0.06), \
+                f"zero stage {stage} clip {clip}: {name} after 4 steps: max abs error {d}"
+        ga = torch.cat([got[n].float().reshape(-1) for n in want])
+        wa = torch.cat([want[n].float().reshape(-1) for n in want])
+        close(ga, wa, 8e-2, f"zero stage {stage} clip {clip}: all parameters", fro=1e-2)
+        rep = eng.memory_report()
+        if stage >= 2:
+            assert rep["grad_bytes"] < rep["unsharded_param_bytes"], rep
+        if stage == 3:
+            assert rep["param_bytes"] < rep["unsharded_param_bytes"], rep
+        if comm.rank == 0:
+            print("zero memory", {k: rep[k] for k in ("stage", "param_bytes", "grad_bytes", "optimizer_bytes")}, flush=True)
+        del eng, ref, m_dist, m_ref
+        comm.host_barrier()
 
 
 def sc_ag_gemm(comm):
