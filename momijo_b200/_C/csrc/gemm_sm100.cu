@@ -363,13 +363,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           const int owner = (int)(abs_off / p.shard_bytes);
           long long seg_hi = (long long)(owner + 1) * p.shard_bytes - p.gather_flat_off;
           if (seg_hi > hi) seg_hi = hi;
-          if (owner != p.rank && owner < p.world) {
-            if (p.peer_ready != nullptr)
+          if ((owner != p.rank || p.src_compact) && owner < p.world) {
+            if (p.peer_ready != nullptr && owner != p.rank)
               ok = wait_flag_ge(p.peer_ready + owner, p.ready_epoch, true, &abort_flag, p.status,
                                 100 + owner);
             if (!ok) break;
             const long long nbytes = seg_hi - lo;
-            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.peer_src[owner]) + lo;
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.peer_src[owner]) +
+                                 (p.src_compact ? (abs_off - (long long)owner * p.shard_bytes) : lo);
             uint8_t* dst = reinterpret_cast<uint8_t*>(p.gather_dst) + lo;
             const int nchunks = (int)((nbytes + kBufBytes - 1) / kBufBytes);
             int next_load = 0;
@@ -1201,6 +1202,8 @@ MMJ_API int mmj_gemm_bf16_allgather(const void* const* peer_src, void* gathered,
                                     int* status, void* stream) {
   if (world < 1 || world > kMaxPeers) return -5;
   GemmParams p = {};
+  p.src_compact = (gather_a >> 1) & 1;   // bit 1 of gather_a: peers keep compact shards
+  gather_a &= 1;
   p.M = M; p.N = N; p.K = K;
   p.bn = bn & 0xfff;          // bit 12 of `bn` asks for 256-row tiles
   p.bm2 = (bn >> 12) & 1;

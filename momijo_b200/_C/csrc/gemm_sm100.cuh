@@ -73,6 +73,10 @@ struct GemmParams {
   // of a flat symmetric buffer that is sharded in equal pieces of shard_bytes per rank: the
   // byte at flat offset o is owned by rank o / shard_bytes. peer_src[r] points at the start of
   // the window in rank r's memory.
+  // src_compact: every rank keeps only its own shard, and peer_src[r] points at the start of rank
+  // r's shard (not at the window): the byte at flat offset o is read from
+  // peer_src[o / shard_bytes] + o % shard_bytes, and the local rank's piece is copied as well.
+  int src_compact;
   long long shard_bytes;
   long long gather_flat_off;
   long long gather_total_bytes;

@@ -44,7 +44,7 @@ def signal_shard_ready(site: FusedSite, epoch: int):
 
 def allgather_gemm(site: FusedSite, gathered, other, *, gather_a=True, other_mn=False, out=None,
                    bias=None, gelu=False, pre_out=None, add_aux=None, bn=None, comm_ctas=8, tall=None,
-                   signal=True, shard_bytes=None, flat_off_bytes=0, wait_peers=True):
+                   signal=True, shard_bytes=None, flat_off_bytes=0, wait_peers=True, compact_src=None):
     """D = A @ B^T where one operand is the row-wise concatenation of per-rank shards.
 
     ``gathered``: symmetric [rows, K] bf16 buffer whose local part is already filled; the kernel
@@ -52,6 +52,8 @@ def allgather_gemm(site: FusedSite, gathered, other, *, gather_a=True, other_mn=
     with ``shard_bytes``/``flat_off_bytes`` the matrix is a window of a flat buffer sharded in
     equal byte ranges (ZeRO parameters). ``other`` is the local operand ([N, K], or [K, N] with
     ``other_mn``; for ``gather_a=False`` it plays the role of A).
+    ``compact_src``: peer pointer table of the ranks' own shards when every rank keeps only its shard
+    (stage-3 parameters); ``gathered`` is then a local buffer that receives the local piece too.
     After the call ``gathered`` holds the full matrix (reusable by the backward pass).
     """
     c = site.comm
@@ -84,7 +86,8 @@ def allgather_gemm(site: FusedSite, gathered, other, *, gather_a=True, other_mn=
     n_tiles = -(-rows // (128 if gather_a else bn))
     if n_tiles > site.flags.numel():
         site.flags = torch.zeros(n_tiles, dtype=torch.int32, device=c.device)
-    _C.call("mmj_gemm_bf16_allgather", site.peer_ptrs(gathered), _C.ptr(gathered), int(gather_a),
+    _C.call("mmj_gemm_bf16_allgather", compact_src if compact_src is not None else site.peer_ptrs(gathered),
+            _C.ptr(gathered), int(gather_a) | (2 if compact_src is not None else 0),
             _C.ptr(other), gathered.stride(0), other.stride(0), int(other_mn), _C.ptr(out),
             out.stride(0), M, N, K, epi, _C.ptr(bias), _C.ptr(add_aux),
             add_aux.stride(0) if add_aux is not None else 0, _C.ptr(pre_out),

@@ -26,9 +26,10 @@ Stages (``stage=``):
    rotating window of ``window`` bucket-sized buffers just before their forward (one unit ahead) and
    again before their backward. The root bucket stays resident between steps.
 
-With stages 1 and 2 the weight named by a unit's ``zero_first_gemm_weight`` attribute is left out of
-the bucket all-gather: the first GEMM that consumes it pulls the missing pieces from the peers
-itself (all-gather fused into the GEMM, ``ops.fused_comm.allgather_gemm``).
+The weight named by a unit's ``zero_first_gemm_weight`` attribute is left out of the bucket
+all-gather that precedes a forward pass: the first GEMM that consumes it pulls the missing pieces
+from the peers itself (all-gather fused into the GEMM, ``ops.fused_comm.allgather_gemm``; with
+stage 3 from the peers' compact shards into the window slot).
 
 With one rank the same class degenerates to the fused AdamW kernel on one flat buffer.
 
@@ -105,6 +106,7 @@ class _FusedWeight:
     def __init__(self, engine, bucket, site, rel_off_bytes):
         self.engine, self.bucket, self.site, self.rel_off_bytes = engine, bucket, site, rel_off_bytes
         self.pending = False
+        self.compact_src = None   # stage 3: peer pointers of the ranks' own shards of this bucket
 
     def gemm(self, x2, w, bias=None, add_aux=None):
         from ..ops.fused_comm import allgather_gemm
@@ -113,7 +115,7 @@ class _FusedWeight:
         return allgather_gemm(self.site, w, x2, gather_a=False, bias=bias, add_aux=add_aux,
                               bn=ops.pick_bn(x2.shape[0], w.shape[0]), comm_ctas=self.engine.fused_comm_ctas,
                               signal=False, wait_peers=False, shard_bytes=self.bucket.shard * 2,
-                              flat_off_bytes=self.rel_off_bytes)
+                              flat_off_bytes=self.rel_off_bytes, compact_src=self.compact_src)
 
 
 class ShardedDataParallel(nn.Module):
@@ -304,8 +306,8 @@ class ShardedDataParallel(nn.Module):
             u.register_full_backward_pre_hook(self._make_pre_backward(i))
             u.register_full_backward_hook(self._make_post_backward(i))
 
-        # ---- GEMM-fused all-gather of each unit's first weight (stages 1 and 2, CUDA peer memory) ----
-        if fuse_first_gemm and self.stage <= 2 and self.is_cuda and hasattr(comm, "new_fused_site"):
+        # ---- GEMM-fused all-gather of each unit's first weight (CUDA peer memory) ----
+        if fuse_first_gemm and self.is_cuda and hasattr(comm, "new_fused_site"):
             for b in self.unit_buckets:
                 name = getattr(b.unit, "zero_first_gemm_weight", None)
                 w = getattr(b.unit, name, None) if name else None
@@ -313,6 +315,8 @@ class ShardedDataParallel(nn.Module):
                     continue
                 o = b.offsets[[i for i, p in enumerate(b.params) if p is w][0]]
                 fw = _FusedWeight(self, b, comm.new_fused_site(), o * esz)
+                if self.stage == 3:
+                    fw.compact_src = comm.peer_ptrs(self.pshard[b.moff:b.moff + b.shard])
                 b.fused = (w, fw, (o * esz, (o + w.numel()) * esz))
                 w._zero_gather = fw
         comm.host_barrier()
@@ -322,9 +326,9 @@ class ShardedDataParallel(nn.Module):
         def hook(module, args):
             if self.stage == 3:
                 b = self.unit_buckets[i]
-                self._ensure_params(b)
+                self._ensure_params(b, forward=True)
                 if i + 1 < len(self.unit_buckets):
-                    self._gather_params(self.unit_buckets[i + 1])
+                    self._gather_params(self.unit_buckets[i + 1], forward=True)
         return hook
 
     def _make_post_forward(self, i):
@@ -370,21 +374,26 @@ class ShardedDataParallel(nn.Module):
             self._sync_enabled = old
 
     # ---- parameter window (stage 3) ----
-    def _gather_params(self, b: _Bucket):
+    def _gather_params(self, b: _Bucket, forward: bool = False):
+        """Bring bucket ``b`` into its window slot (side stream). Before a forward pass the weight that
+        its first GEMM gathers itself is left out; before a backward pass everything is fetched."""
         slot = b.pslot
         occ = self._pslot_holds[slot]
         if occ is b:
             return
+        fuse = forward and b.fused is not None
         with self._side():
             if occ is not None and self.is_cuda:
                 self.side.wait_event(occ.use_ev)
-            self.comm.gather_bucket(self, b, compact=True)
+            self.comm.gather_bucket(self, b, compact=True, skip=b.fused[2] if fuse else None)
             if self.is_cuda:
                 b.gather_ev.record(self.side)
+        if b.fused is not None:
+            b.fused[1].pending = fuse
         self._pslot_holds[slot] = b
 
-    def _ensure_params(self, b: _Bucket):
-        self._gather_params(b)
+    def _ensure_params(self, b: _Bucket, forward: bool = False):
+        self._gather_params(b, forward)
         if self.is_cuda:
             torch.cuda.current_stream().wait_event(b.gather_ev)
 

@@ -76,6 +76,25 @@ def sc_zero(comm):
             lr_ = ref(full[:, :-1], full[:, 1:])
             (lr_ * s).backward()
             ref.step()
+            # same parameters, same tokens: the mean of the ranks' losses is the full-batch loss
+            lsum = loss.detach().clone()
+            dist.all_reduce(lsum)
+            lmean, lref = lsum.item() / comm.world, lr_.item()
+            assert abs(lmean - lref) < 2e-3 * abs(lref), f"zero stage {stage} clip {clip} step {step}: loss {lmean} vs {lref}"
+        # One more forward pass: every block's first weight is now gathered by its own GEMM and the rest by
+        # the bucket gather. What sits in the parameter storage afterwards must equal, bit for bit, an NCCL
+        # all-gather of the shards the ranks own.
+        with torch.no_grad():
+            eng(mine[:, :-1], mine[:, 1:])
+        torch.cuda.synchronize()
+        for b in eng.unit_buckets:
+            if stage == 3 and eng._pslot_holds[b.pslot] is not b:
+                continue   # not in the window any more
+            own = (eng.pshard[b.moff:b.moff + b.shard] if stage == 3
+                   else b.pview[comm.rank * b.shard:(comm.rank + 1) * b.shard]).clone()
+            full_b = torch.empty(b.size, dtype=own.dtype, device=own.device)
+            dist.all_gather_into_tensor(full_b, own)
+            assert torch.equal(full_b, b.pview), f"zero stage {stage}: bucket {b.idx} differs from the gathered shards"
         got = eng.materialize()
         want = ref.materialize()
         torch.cuda.synchronize()
@@ -86,7 +105,7 @@ def sc_zero(comm):
         # update went missing or landed in the wrong place would read about 0.2 there).
         for name in want:
             d = (got[name].float() - want[name].float()).abs().max().item()
-            assert d < 8e-2 * max(want[name].float().abs().max().item(), 0.06), \
+            assert d < max(8e-2 * want[name].float().abs().max().item(), 1e-2), \
                 f"zero stage {stage} clip {clip}: {name} after 4 steps: max abs error {d}"
         ga = torch.cat([got[n].float().reshape(-1) for n in want])
         wa = torch.cat([want[n].float().reshape(-1) for n in want])
