@@ -84,7 +84,7 @@ _SIGS = {
     "mmj_gather_bucket": ([P, P, P, L, L, P, I, I, I, I, I, I, I, P, P], 1),
     "mmj_allreduce_small_f32": ([P, P, P, P, I, I, I, I, I, P, P], 1),
     "mmj_allgather_ranges": ([P, P, L, P, I, I, I, I, I, P, P], 1),
-    "mmj_allreduce_bf16": ([P, P, P, L, F, I, I, I, I, P, P, P, P], 1),
+    "mmj_allreduce_bf16": ([P, P, P, L, F, I, I, I, I, I, P, P, P, P], 1),
     "mmj_reduce_slots_bf16": ([P, P, L, P, P, L, I, I, I, I, P, P], 1),
     "mmj_moe_count": ([P, P, I, I, P, P, I, I, I, I, P, P], 1),
     "mmj_moe_offsets": ([P, I, I, I, P, P, P, P, P, P, I, P], 1),

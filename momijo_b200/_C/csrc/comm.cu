@@ -800,7 +800,7 @@ MMJ_API int mmj_allgather_ranges(void* const* sig, void* const* bufs, long long 
 }
 
 MMJ_API int mmj_allreduce_bf16(void* const* sig, void* const* bufs, const void* buf_mc, long long n,
-                               float scale, int world, int rank, int slot_base, int epoch,
+                               float scale, int max_blocks, int world, int rank, int slot_base, int epoch,
                                unsigned int* block_counters, int* grid_flag, int* status,
                                void* stream) {
   if (world < 1 || world > kMaxWorld) return -1;
@@ -816,6 +816,8 @@ MMJ_API int mmj_allreduce_bf16(void* const* sig, void* const* bufs, const void* 
   p.status = status;
   // every block spins on a flag set by another block: the whole grid must be resident
   int grid = resident_grid(2);
+  // beside a running GEMM only part of that fits on the SMs at once: such launches ask for fewer blocks
+  if (max_blocks > 0 && max_blocks < grid) grid = max_blocks;
   long long want = (n / world / 8 + 255) / 256;
   if (want < grid) grid = (int)(want < 1 ? 1 : want);
   allreduce_kernel<<<grid, 256, 0, STREAM>>>(p);

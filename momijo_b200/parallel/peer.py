@@ -145,17 +145,25 @@ class PeerComm:
         _C.call("mmj_barrier", self._sig_ptrs, self.world, self.rank, slots, self.next_epoch(slots),
                 _C.ptr(self.status), _C.current_stream())
 
-    def all_reduce_(self, t: torch.Tensor, scale: float = 1.0):
-        """In-place sum all-reduce of a bf16 tensor that lives in the symmetric heap."""
+    def new_allreduce_state(self):
+        """Signal slots, block counters and the grid flag of one all-reduce call site (call sites that may
+        run on different streams need one each)."""
+        return (self.new_slots(3 * self.world), self.new_counter(2), self.new_counter(1))
+
+    def all_reduce_(self, t: torch.Tensor, scale: float = 1.0, max_blocks: int = 0, state=None):
+        """In-place sum all-reduce of a bf16 tensor that lives in the symmetric heap. ``max_blocks`` limits
+        the grid of a launch that runs beside other kernels (every block of it must be resident)."""
         if t.dtype != torch.bfloat16:
             raise TypeError("peer all-reduce works on bf16 buffers")
         n = t.numel()
         if n % (8 * self.world):
             raise ValueError("element count must be a multiple of 8 * world")
-        if not hasattr(self, "_ar"):
-            self._ar = (self.new_slots(3 * self.world), self.new_counter(2), self.new_counter(1))
-        slots, ctr, flag = self._ar
-        _C.call("mmj_allreduce_bf16", self._sig_ptrs, self.peer_ptrs(t), self.mc_ptr(t), n, scale,
+        if state is None:
+            if not hasattr(self, "_ar"):
+                self._ar = self.new_allreduce_state()
+            state = self._ar
+        slots, ctr, flag = state
+        _C.call("mmj_allreduce_bf16", self._sig_ptrs, self.peer_ptrs(t), self.mc_ptr(t), n, scale, max_blocks,
                 self.world, self.rank, slots, self.next_epoch(slots), _C.ptr(ctr), _C.ptr(flag),
                 _C.ptr(self.status), _C.current_stream())
         return t

@@ -121,6 +121,72 @@ def sc_zero(comm):
         comm.host_barrier()
 
 
+def sc_ddp(comm):
+    """Bucketed data parallel: per-block all-reduce launched from the backward pass == single rank on the
+    concatenated batch."""
+    from momijo_b200.models import GPT2, GPT2Config
+    from momijo_b200.parallel import DistributedDataParallel, ShardedDataParallel, AdamWConfig
+
+    cfg = GPT2Config(vocab_size=1000, n_layer=4, n_head=2, d_model=128, d_ff=512, max_seq=256)
+    oc = AdamWConfig(lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
+    torch.manual_seed(0)
+    m_dist = GPT2(cfg).cuda()
+    torch.manual_seed(0)
+    m_ref = GPT2(cfg).cuda()
+    eng = DistributedDataParallel(m_dist, oc, comm=comm)
+    ref = ShardedDataParallel(m_ref, oc)
+    assert len([b for b in eng.buckets if b.unit is not None]) == cfg.n_layer
+    g = torch.Generator().manual_seed(9)
+    B = 2
+    for step in range(4):
+        full = torch.randint(0, cfg.vocab_size, (B * comm.world, 129), generator=g).cuda()
+        mine = full[comm.rank * B:(comm.rank + 1) * B]
+        loss = eng(mine[:, :-1], mine[:, 1:])
+        loss.backward()
+        if step >= 1:
+            assert all(b.launched for b in eng.buckets if b.unit is not None), "buckets not sent off during backward"
+        eng.step()
+        lr_ = ref(full[:, :-1], full[:, 1:])
+        lr_.backward()
+        ref.step()
+    torch.cuda.synchronize()
+    assert all(b.mode == "native" for b in eng.buckets if b.unit is not None)
+    close(eng.flat.param, ref.flat.param, 8e-2, "ddp params after 4 steps", fro=1e-2)
+    # every rank holds the same parameters, bit for bit
+    mine = eng.flat.param.clone()
+    other = mine.clone()
+    dist.broadcast(other, 0)
+    assert torch.equal(mine, other), "ddp replicas diverged"
+
+
+def sc_allreduce_nvls(comm):
+    """The in-switch reduction path of the all-reduce kernel (multimem.ld_reduce through an NVSwitch
+    multicast mapping of the symmetric heap) against NCCL. Passes without testing where the heap has no
+    multicast mapping."""
+    c2 = PeerComm(comm.group, heap_bytes=64 << 20, use_multicast=True)
+    if not c2.mc_base:
+        if comm.rank == 0:
+            print("allreduce_nvls: no multicast mapping on this box, not exercised", flush=True)
+        return
+    torch.manual_seed(20 + comm.rank)
+    n = 8 * comm.world * 4096
+    x = c2.alloc(n, bf16)
+    src = torch.randn(n, device="cuda").to(bf16)
+    for it in range(2):
+        x.copy_(src)
+        ref = src.float().clone()
+        dist.all_reduce(ref)
+        torch.cuda.synchronize()
+        dist.barrier()
+        c2.all_reduce_(x)
+        torch.cuda.synchronize()
+        close(x, ref, 2e-2, "nvls allreduce", fro=1e-2)
+    if comm.rank == 0:
+        print("allreduce_nvls: multimem.ld_reduce path exercised", flush=True)
+    c2.barrier()
+    torch.cuda.synchronize()
+
+
 def sc_ag_gemm(comm):
     from momijo_b200.ops.fused_comm import FusedSite, allgather_gemm
 
@@ -385,7 +451,8 @@ def sc_timeout(comm):
 
 SCENARIOS = {"allreduce": sc_allreduce, "zero": sc_zero, "ag_gemm": sc_ag_gemm,
              "gemm_rs": sc_gemm_rs, "moe": sc_moe, "moe_layer": sc_moe_layer, "tp_llama": sc_tp_llama,
-             "moe_drop": sc_moe_drop, "determinism": sc_determinism, "timeout": sc_timeout}
+             "moe_drop": sc_moe_drop, "determinism": sc_determinism, "timeout": sc_timeout, "ddp": sc_ddp,
+             "allreduce_nvls": sc_allreduce_nvls}
 
 
 def main():

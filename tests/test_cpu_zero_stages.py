@@ -133,3 +133,44 @@ def test_sharded_stages_match_plain_adamw(tmp_path, stage, clip):
         assert rep["grad_bytes"] < full
     if stage == 3:
         assert rep["param_bytes"] < full
+
+
+def _ddp_worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    from momijo_b200.parallel import AdamWConfig, DistributedDataParallel
+
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    xs, ys = _data()
+    eng = DistributedDataParallel(_net(), AdamWConfig(lr=1e-2, weight_decay=0.1), dtype=torch.float32)
+    lo, hi = rank * 4, rank * 4 + 4
+    sent = []
+    for s in range(xs.shape[0]):
+        loss = ((eng(xs[s, lo:hi]) - ys[s, lo:hi]) ** 2).mean()
+        loss.backward()
+        sent.append(sum(b.launched for b in eng.buckets))
+        eng.step()
+    if rank == 0:
+        torch.save({"params": {n: p.detach().clone() for n, p in eng.module.named_parameters()}, "sent": sent,
+                    "modes": [b.mode for b in eng.buckets]}, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_bucketed_ddp_overlaps_and_matches_plain_adamw(tmp_path):
+    xs, ys = _data()
+    net = _net()
+    opt = torch.optim.AdamW(net.parameters(), lr=1e-2, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.1)
+    for s in range(xs.shape[0]):
+        opt.zero_grad()
+        ((net(xs[s]) - ys[s]) ** 2).mean().backward()
+        opt.step()
+    out = str(tmp_path / "d.pt")
+    mp.spawn(_ddp_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    got = torch.load(out)
+    for name, p in net.named_parameters():
+        assert torch.allclose(got["params"][name], p.detach(), atol=3e-5), name
+    # first step learns how gradients arrive; afterwards the five block buckets leave during backward
+    assert got["sent"][0] == 0 and all(n == 5 for n in got["sent"][1:]), got["sent"]
+    assert got["modes"].count("native") == 5

@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 def _run(scenarios, nproc=None, timeout=600):
-    n = nproc or min(torch.cuda.device_count(), 4)
+    n = nproc or min(torch.cuda.device_count(), 8)   # every visible GPU of the node
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
            "--master-addr", "127.0.0.1", "--master-port", "29533",
@@ -31,6 +31,14 @@ def test_peer_allreduce_and_timeout_status():
 
 def test_zero_engine_matches_single_rank():
     _run(["zero"])
+
+
+def test_bucketed_ddp_matches_single_rank():
+    _run(["ddp"])
+
+
+def test_nvls_allreduce_path():
+    _run(["allreduce_nvls"])
 
 
 def test_fused_allgather_gemm_and_gemm_reduce_scatter():
