@@ -590,6 +590,11 @@ def main():
     args = parse()
     if args.impl == "reference":
         return reference_unavailable()
+    if os.environ.get("MOMIJO_DUMP_STACKS_AFTER"):
+        # debugging aid for a run that stops making progress: print every thread's Python stack after N seconds
+        import faulthandler
+
+        faulthandler.dump_traceback_later(float(os.environ["MOMIJO_DUMP_STACKS_AFTER"]), repeat=False)
 
     rank, world, local = init_dist(args.gpus)
     out = run_arm(args, args.impl, rank, world, local)

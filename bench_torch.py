@@ -311,54 +311,65 @@ class _AllToAll(torch.autograd.Function):
 
 def run_1f1b(stage, stage_id, n_stages, prev_rank, next_rank, n_micro, act_shape, device, micro_inputs,
              micro_targets, device_type="cuda"):
-    """Plain 1F1B over torch.distributed p2p (``batch_isend_irecv``), written out here so that this arm shares
-    no code with the package: warm-up forwards, one-forward-one-backward, drain. Activations cross stages in
-    bf16. Returns the mean loss on the last stage."""
+    """Plain 1F1B over torch.distributed p2p, written out here so that this arm shares no code with the
+    package. It follows the usual pairing of transfers: in the steady state a stage sends its activation
+    forward and receives the matching gradient in ONE grouped call, and sends a gradient back and receives
+    the next activation in one grouped call (NCCL transfers rendezvous, so two stages that each post a send
+    first would wait for each other). Activations cross stages in bf16. Returns the mean loss on the last
+    stage."""
     first, last = stage_id == 0, stage_id == n_stages - 1
     warm = min(n_stages - 1 - stage_id, n_micro)
-    saved, losses, keep = [], [], []
+    remaining = n_micro - warm
+    saved, losses = [], []
 
-    def recv(src):
-        buf = torch.empty(act_shape, dtype=torch.bfloat16, device=device)
-        for w in dist.batch_isend_irecv([dist.P2POp(dist.irecv, buf, src)]):
-            w.wait()
+    def exchange(send_t=None, send_to=None, recv_from=None):
+        ops, buf = [], None
+        if send_t is not None and send_to is not None:
+            send_t = send_t.contiguous()
+            ops.append(dist.P2POp(dist.isend, send_t, send_to))
+        if recv_from is not None:
+            buf = torch.empty(act_shape, dtype=torch.bfloat16, device=device)
+            ops.append(dist.P2POp(dist.irecv, buf, recv_from))
+        if ops:
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
         return buf
 
-    def send(t, dst):
-        t = t.contiguous()
-        keep.append((dist.batch_isend_irecv([dist.P2POp(dist.isend, t, dst)]), t))
-
-    def fwd(i):
-        x = micro_inputs[i] if first else recv(prev_rank).requires_grad_(True)
+    def fwd(i, x):
+        x = micro_inputs[i] if first else x.requires_grad_(True)
         with torch.autocast(device_type, dtype=torch.bfloat16):
             y = stage(x, micro_targets[i] if last else None)
         if last:
             losses.append(y.detach())
             saved.append((x, y / n_micro))
-        else:
-            send(y.detach().to(torch.bfloat16), next_rank)
-            saved.append((x, y))
+            return None
+        saved.append((x, y))
+        return y.detach().to(torch.bfloat16)
 
-    def bwd():
+    def bwd(g):
         x, y = saved.pop(0)
         if last:
             y.backward()
         else:
-            y.backward(recv(next_rank).to(y.dtype))
-        if not first:
-            send(x.grad, prev_rank)
+            y.backward(g.to(y.dtype))
+        return None if first else x.grad
 
     fi = 0
     for _ in range(warm):
-        fwd(fi); fi += 1
-    for _ in range(n_micro - warm):
-        fwd(fi); fi += 1
-        bwd()
+        x = exchange(recv_from=prev_rank)
+        y = fwd(fi, x); fi += 1
+        exchange(send_t=y, send_to=next_rank)
+    x = exchange(recv_from=prev_rank) if remaining > 0 else None
+    for k in range(remaining):
+        y = fwd(fi, x); fi += 1
+        g = exchange(send_t=y, send_to=next_rank, recv_from=next_rank)          # send forward, receive backward
+        dx = bwd(g)
+        more = k + 1 < remaining
+        x = exchange(send_t=dx, send_to=prev_rank, recv_from=prev_rank if more else None)  # send backward, receive forward
     for _ in range(warm):
-        bwd()
-    for works, _ in keep:
-        for w in works:
-            w.wait()
+        g = exchange(recv_from=next_rank)
+        dx = bwd(g)
+        exchange(send_t=dx, send_to=prev_rank)
     return torch.stack([l.float() for l in losses]).mean() if last else None
 
 

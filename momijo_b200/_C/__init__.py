@@ -74,6 +74,16 @@ _SIGS = {
     "mmj_vis_hist": ([P, L, I, I, P, P], 1),
     "mmj_vis_lut": ([P, P, L, P, P], 1),
     "mmj_vis_binary": ([P, P, P, L, I, F, F, F, P], 1),
+    "mmj_im2col": ([P, P, P, L, I, P], 1),
+    "mmj_col2im": ([P, P, P, L, I, P], 1),
+    "mmj_conv2d_fwd": ([P, P, P, P, P, I, P], 1),
+    "mmj_conv2d_dx": ([P, P, P, P, P, I, P], 1),
+    "mmj_conv2d_dw": ([P, P, P, P, I, P], 1),
+    "mmj_channel_sum": ([P, P, I, I, L, I, P], 1),
+    "mmj_maxpool2d_fwd": ([P, P, P, P, I, P], 1),
+    "mmj_maxpool2d_bwd": ([P, P, P, P, I, P], 1),
+    "mmj_avgpool2d_fwd": ([P, P, P, I, P], 1),
+    "mmj_avgpool2d_bwd": ([P, P, P, I, P], 1),
     "mmj_attn_set_trace": ([P, L], 0),
     "mmj_attn_bwd": ([P, L, I, P, L, I, P, L, I, P, L, I, P, L, I, P, P, P, L, I, P, L, I, P, L, I,
                       I, I, I, I, I, F, I, P, P], 2),

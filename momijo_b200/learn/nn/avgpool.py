@@ -1,6 +1,6 @@
 """``AvgPool2d(kernel_size, stride=(0,0)->kernel, padding=(0,0))``: averages over the in-bounds
 elements only (legacy/src/momijo/learn/nn/avgpool.mojo:9-57)."""
-import torch.nn.functional as tF
+from ...ops import conv as _cv
 
 from .module import Module
 from .functional import _pair
@@ -15,7 +15,7 @@ class AvgPool2d(Module):
         self.padding = _pair(padding)
 
     def forward(self, x, ctx=None):
-        return tF.avg_pool2d(x, self.kernel_size, self.stride, self.padding, count_include_pad=False)
+        return _cv.avg_pool2d(x, self.kernel_size, self.stride, self.padding, count_include_pad=False)
 
     def backward(self, x, grad_y):
         """``dx``: each output gradient is shared equally among the in-bounds inputs of its window
@@ -23,5 +23,5 @@ class AvgPool2d(Module):
         import torch
 
         xr = x.detach().requires_grad_(True)
-        y = tF.avg_pool2d(xr, self.kernel_size, self.stride, self.padding, count_include_pad=False)
+        y = _cv.avg_pool2d(xr, self.kernel_size, self.stride, self.padding, count_include_pad=False)
         return torch.autograd.grad(y, xr, grad_y)[0]

@@ -35,7 +35,7 @@ class Conv2d(Module):
         """Explicit ``(dW, db, dx)`` like the reference's CPU backward (conv.mojo:722-853)."""
         xr = x.detach().requires_grad_(True)
         w = self.weight.detach().requires_grad_(True)
-        y = tF.conv2d(xr, w, None, self.stride, self.pad)
+        y = F.conv2d(xr, w, None, self.stride, self.pad)
         dx, dw = torch.autograd.grad(y, (xr, w), dy)
         return dw, dy.sum((0, 2, 3)), dx
 
@@ -50,11 +50,11 @@ class MaxPool2d(Module):
         self.kernel, self.stride, self.pad = F._pair(kernel), F._pair(stride), F._pair(pad)
 
     def forward(self, x, ctx=None):
-        return tF.max_pool2d(x, self.kernel, self.stride, self.pad)
+        return F._cv.max_pool2d(x, self.kernel, self.stride, self.pad)
 
     def backward(self, x, dy):
         xr = x.detach().requires_grad_(True)
-        y = tF.max_pool2d(xr, self.kernel, self.stride, self.pad)
+        y = F._cv.max_pool2d(xr, self.kernel, self.stride, self.pad)
         return torch.autograd.grad(y, xr, dy)[0]
 
 

@@ -4,7 +4,7 @@ import math
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as tF
+from ...ops import conv as _cv
 
 from .module import Module
 from .functional import _pair
@@ -20,7 +20,7 @@ class ConvTranspose2d(Module):
         self.bias = nn.Parameter(torch.zeros(out_channels, dtype=dtype))
 
     def forward(self, x, ctx=None):
-        return tF.conv_transpose2d(x, self.weight, self.bias, self.stride, self.padding)
+        return _cv.conv_transpose2d(x, self.weight, self.bias, self.stride, self.padding)
 
     def out_shape(self, H: int, W: int):
         """``(OH, OW) = ((H - 1) * stride - 2 * pad + kernel)`` per axis (conv_transpose.mojo:40-43)."""
@@ -31,6 +31,6 @@ class ConvTranspose2d(Module):
         """Explicit ``(dW, db, dx)`` (conv_transpose.mojo:91-140)."""
         xr = x.detach().requires_grad_(True)
         w = self.weight.detach().requires_grad_(True)
-        y = tF.conv_transpose2d(xr, w, None, self.stride, self.padding)
+        y = _cv.conv_transpose2d(xr, w, None, self.stride, self.padding)
         dx, dw = torch.autograd.grad(y, (xr, w), grad_y)
         return dw, grad_y.sum((0, 2, 3)), dx

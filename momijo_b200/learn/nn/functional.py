@@ -2,8 +2,10 @@
 
 Names follow legacy/src/momijo/learn/nn/functional.mojo: ``im2col/col2im`` (:285-424),
 ``conv2d_naive`` and ``conv2d`` (im2col + GEMM, :472), ``conv1d``, depthwise / pointwise /
-separable convolutions (:573-652), ``max_pool2d`` (:185), ``linear_mse_grads`` (:747). On CUDA
-bf16 tensors ``conv2d`` lowers to im2col followed by the tcgen05 GEMM of ``momijo_b200.ops``.
+separable convolutions (:573-652), ``max_pool2d`` (:185), ``linear_mse_grads`` (:747). CUDA tensors
+(fp32 / bf16) run this library's own kernels (``momijo_b200.ops.conv``: direct convolution with groups and
+dilation, im2col + tcgen05 GEMM + col2im for bf16, pooling with deterministic backward); CPU tensors
+take the plain torch path.
 """
 from __future__ import annotations
 
@@ -14,6 +16,7 @@ import torch
 import torch.nn.functional as tF
 
 from ... import ops
+from ...ops import conv as _cv
 
 
 @dataclass
@@ -40,6 +43,8 @@ def im2col(x, kernel, stride=(1, 1), pad=(0, 0), padding=None):
     ``im2col(x, kH, kW, stride, padding)`` (legacy/src/momijo/learn/nn/functional.mojo:285)."""
     kernel, stride, pad = _ref_window_args(kernel, stride, pad, padding)
     kernel, stride, pad = _pair(kernel), _pair(stride), _pair(pad)
+    if _cv.native_ok(x):
+        return _cv.im2col(x, kernel, stride, pad)
     cols = tF.unfold(x, kernel, padding=pad, stride=stride)  # [N, C*kH*kW, L]
     return cols.transpose(1, 2).reshape(-1, cols.shape[1])
 
@@ -49,6 +54,8 @@ def col2im(cols, x_shape, kernel, stride=(1, 1), pad=(0, 0), padding=None):
     kernel, stride, pad = _ref_window_args(kernel, stride, pad, padding)
     kernel, stride, pad = _pair(kernel), _pair(stride), _pair(pad)
     N, C, H, W = x_shape
+    if _cv.native_ok(cols):
+        return _cv.col2im(cols, (N, C, H, W), kernel, stride, pad)
     c = cols.reshape(N, -1, cols.shape[1]).transpose(1, 2)
     return tF.fold(c, (H, W), kernel, padding=pad, stride=stride)
 
@@ -84,32 +91,20 @@ def conv2d(x, w, b=None, stride=(1, 1), pad=(0, 0), dilation=1):
         xt, wt = torch.tensor(x, dtype=torch.float32), torch.tensor(w, dtype=torch.float32)
         bt = torch.tensor(b, dtype=torch.float32) if b is not None and len(b) else None
         return tF.conv2d(xt, wt, bt, _pair(stride), _pair(pad), _pair(dilation)).tolist()
-    if _pair(dilation) != (1, 1):
-        return tF.conv2d(x, w, b if (b is not None and b.numel()) else None, _pair(stride), _pair(pad), _pair(dilation))
-    stride, pad = _pair(stride), _pair(pad)
-    if x.is_cuda and x.dtype == torch.bfloat16:
-        N, C, H, W = x.shape
-        OC, _, kH, kW = w.shape
-        OH, OW = conv_out_size(H, kH, stride[0], pad[0]), conv_out_size(W, kW, stride[1], pad[1])
-        K = C * kH * kW
-        Kp = (K + 7) // 8 * 8
-        cols = im2col(x, (kH, kW), stride, pad)
-        w2 = w.reshape(OC, K)
-        if Kp != K:  # TMA rows must be 16-byte multiples
-            cols = tF.pad(cols, (0, Kp - K))
-            w2 = tF.pad(w2, (0, Kp - K))
-        y = ops.linear(cols.contiguous(), w2.contiguous(), b if (b is not None and b.numel()) else None)
-        return y.reshape(N, OH, OW, OC).permute(0, 3, 1, 2).contiguous()
-    return tF.conv2d(x, w, b if (b is not None and b.numel()) else None, stride, pad)
+    return _cv.conv2d(x, w, b if (b is not None and b.numel()) else None, _pair(stride), _pair(pad), _pair(dilation))
 
 
 def conv1d(x, w, b=None, stride=1, pad=0):
+    """[N, C, L] convolution, run as a height-1 2-D convolution on the same kernels."""
+    if _cv.native_ok(x):
+        y = _cv.conv2d(x.unsqueeze(2), w.unsqueeze(2), b, (1, stride), (0, pad))
+        return y.squeeze(2)
     return tF.conv1d(x, w, b, stride, pad)
 
 
 def depthwise_conv2d(x, w, b=None, stride=(1, 1), pad=(0, 0)):
     """``w`` is [C, 1, kH, kW]."""
-    return tF.conv2d(x, w, b, _pair(stride), _pair(pad), groups=x.shape[1])
+    return _cv.conv2d(x, w, b, _pair(stride), _pair(pad), (1, 1), groups=x.shape[1])
 
 
 def pointwise_conv2d(x, w, b=None):
@@ -130,7 +125,7 @@ def max_pool2d(x, kernel, stride=(1, 1), pad=(0, 0), ceil_mode: bool = False):
     xt = torch.tensor(x, dtype=torch.float32) if as_list else x
     k = _pair(kernel)
     st = k if stride in (0, (0, 0)) else _pair(stride)
-    y = tF.max_pool2d(xt, k, st, _pair(pad), ceil_mode=bool(ceil_mode))
+    y = _cv.max_pool2d(xt, k, st, _pair(pad), ceil_mode=bool(ceil_mode))
     return y.tolist() if as_list else y
 
 

@@ -3,22 +3,23 @@ import torch
 import torch.nn.functional as tF
 
 from .functional import _pair
+from ...ops import conv as _cv
 
 
 def maxpool2d(x, kernel, stride=None, pad=(0, 0)):
     k = _pair(kernel)
-    return tF.max_pool2d(x, k, _pair(stride) if stride is not None else k, _pair(pad))
+    return _cv.max_pool2d(x, k, _pair(stride) if stride is not None else k, _pair(pad))
 
 
 def maxpool2d_with_indices(x, kernel, stride=None, pad=(0, 0)):
     k = _pair(kernel)
-    return tF.max_pool2d(x, k, _pair(stride) if stride is not None else k, _pair(pad), return_indices=True)
+    return _cv.max_pool2d(x, k, _pair(stride) if stride is not None else k, _pair(pad), return_indices=True)
 
 
 def avgpool2d(x, kernel, stride=None, pad=(0, 0)):
     k = _pair(kernel)
-    return tF.avg_pool2d(x, k, _pair(stride) if stride is not None else k, _pair(pad),
-                         count_include_pad=False)
+    return _cv.avg_pool2d(x, k, _pair(stride) if stride is not None else k, _pair(pad),
+                          count_include_pad=False)
 
 
 def global_avg_pool2d(x):
@@ -50,7 +51,7 @@ def avg_unpool2d(y, kernel, stride=None, padding: int = 0, y_shape=None):
         k = _pair(kernel)
         s = k if not stride else _pair(stride)
         ref = torch.zeros(list(y_shape), dtype=y.dtype, device=y.device, requires_grad=True)
-        pooled = tF.avg_pool2d(ref, k, s, _pair(padding), count_include_pad=False)
+        pooled = _cv.avg_pool2d(ref, k, s, _pair(padding), count_include_pad=False)
         return torch.autograd.grad(pooled, ref, y)[0]
     k = _pair(kernel)
     s = _pair(stride) if stride is not None else k
@@ -63,5 +64,5 @@ def pool2d_core(x, k: int, stride: int = 0, padding: int = 0, mode: int = 0):
     of 0 (or less) means the window size (legacy/src/momijo/learn/nn/pool.mojo:74-137)."""
     st = stride if stride > 0 else k
     if mode == 0:
-        return tF.max_pool2d(x, k, st, padding)
-    return tF.avg_pool2d(x, k, st, padding, count_include_pad=False)
+        return _cv.max_pool2d(x, k, st, padding)
+    return _cv.avg_pool2d(x, k, st, padding, count_include_pad=False)

@@ -70,6 +70,31 @@ class Schedule1F1B:
         self.act_shape, self.act_dtype = tuple(act_shape), act_dtype
         self.device = device if device is not None else next(stage.parameters()).device
         self._pending = []
+        self._connect()
+
+    def _connect(self):
+        """Exchange one dummy element with both neighbours in a single grouped call. The first transfer
+        between two ranks sets up their connection and blocks the host until the peer takes part; doing it
+        here, where every stage issues the matching calls at the same time, keeps that out of the
+        schedule, whose sends and receives are deliberately not issued in lock step (a stage whose host
+        waits for a connection while its peer's stream waits for that stage's next launch would hang)."""
+        st = self.stage
+        if not (dist.is_available() and dist.is_initialized()):
+            return
+        ops, keep = [], []
+        for peer in (st.prev_rank, st.next_rank):
+            if peer is None:
+                continue
+            a = torch.zeros(1, dtype=self.act_dtype, device=self.device)
+            b = torch.zeros(1, dtype=self.act_dtype, device=self.device)
+            keep += [a, b]
+            ops.append(dist.P2POp(dist.isend, a, peer, st.group))
+            ops.append(dist.P2POp(dist.irecv, b, peer, st.group))
+        if ops:
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+            if self.device is not None and torch.device(self.device).type == "cuda":
+                torch.cuda.synchronize(self.device)
 
     # ---- p2p helpers ----
     # Every transfer goes through ``batch_isend_irecv`` (a batch of one): with an eagerly initialised
