@@ -84,6 +84,15 @@ _SIGS = {
     "mmj_maxpool2d_bwd": ([P, P, P, P, I, P], 1),
     "mmj_avgpool2d_fwd": ([P, P, P, I, P], 1),
     "mmj_avgpool2d_bwd": ([P, P, P, I, P], 1),
+    "mmj_vis_median": ([P, P, I, I, I, I, P], 1),
+    "mmj_vis_bilateral": ([P, P, I, I, I, I, F, F, P], 1),
+    "mmj_vis_canny_nms": ([P, P, I, I, I, I, P], 1),
+    "mmj_vis_canny_hysteresis": ([P, I, I, P, P], 1),
+    "mmj_vis_canny_finish": ([P, P, L, P], 1),
+    "mmj_vis_clahe_luts": ([P, I, P, P, I, I, F, P, P], 1),
+    "mmj_vis_clahe_apply": ([P, P, I, I, P, P, I, I, P, P], 1),
+    "mmj_vis_cc_init": ([P, I, P, L, P], 1),
+    "mmj_vis_cc_pass": ([P, I, I, I, P, P], 1),
     "mmj_attn_set_trace": ([P, L], 0),
     "mmj_attn_bwd": ([P, L, I, P, L, I, P, L, I, P, L, I, P, L, I, P, P, P, L, I, P, L, I, P, L, I,
                       I, I, I, I, I, F, I, P, P], 2),

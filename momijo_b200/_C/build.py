@@ -70,7 +70,7 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False,
     obj_dir.mkdir(exist_ok=True)
     headers = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
     cu = sorted(CSRC.glob("*.cu"))
-    cpp = sorted(CSRC.glob("*.cpp"))
+    cpp = [c for c in sorted(CSRC.glob("*.cpp")) if not c.name.endswith("_selftest.cpp")]
     nvcc = _nvcc()
     log = []
 
@@ -106,6 +106,26 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False,
     if cpp_objs and (force or not _newer(LIB_HOST, cpp_objs)):
         log.append(_run(["g++", "-shared", "-pthread", "-o", LIB_HOST, *cpp_objs], verbose))
     return {"cuda": str(lib_cuda), "host": str(LIB_HOST), "log": "\n".join(log)}
+
+
+SANITIZERS = {
+    "asan_ubsan": ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined", "-fno-omit-frame-pointer"],
+    "tsan": ["-fsanitize=thread"],
+}
+
+
+def build_sanitized(kind: str, out_dir=None, verbose: bool = False) -> Path:
+    """Build the host runtime together with its self-test driver (``csrc/host_runtime_selftest.cpp``) under
+    a sanitizer: ``kind`` is "asan_ubsan" (AddressSanitizer + UndefinedBehaviorSanitizer) or "tsan"
+    (ThreadSanitizer). Returns the executable; running it exits non-zero on a failed check or a sanitizer
+    report. The device library has its own checked variant (``debug_bounds``)."""
+    flags = SANITIZERS[kind]
+    out_dir = Path(out_dir) if out_dir is not None else (HERE / "build")
+    out_dir.mkdir(exist_ok=True)
+    exe = out_dir / f"host_runtime_selftest_{kind}"
+    srcs = [CSRC / "host_runtime.cpp", CSRC / "host_runtime_selftest.cpp"]
+    _run(["g++", "-O1", "-g", "-std=c++17", "-pthread", *flags, *srcs, "-o", exe], verbose)
+    return exe
 
 
 if __name__ == "__main__":

@@ -280,3 +280,85 @@ def binary(a: torch.Tensor, b, op: int, alpha: float = 1.0, beta: float = 1.0, g
         f = x.astype(np.float32) * np.float32(alpha) + y.astype(np.float32) * np.float32(beta) + np.float32(gamma)
         r = (np.clip(f, 0, 255) + np.float32(0.5)).astype(np.uint8)
     return torch.from_numpy(np.ascontiguousarray(r))
+
+
+# ---- neighbourhood / region kernels (device tensors only; the transforms keep their host restatements) ----
+def median(src: torch.Tensor, ksize: int) -> torch.Tensor:
+    """k x k median with a replicated border (k odd, <= 9); ``src`` is a CUDA HWC uint8 tensor."""
+    src = _prep(src)
+    h, w, c = src.shape
+    dst = torch.empty_like(src)
+    _launch("mmj_vis_median", _C.ptr(src), _C.ptr(dst), h, w, c, int(ksize), _stream())
+    return dst
+
+
+def bilateral(src: torch.Tensor, radius: int, sigma_color: float, sigma_space: float) -> torch.Tensor:
+    src = _prep(src)
+    h, w, c = src.shape
+    dst = torch.empty_like(src)
+    sc2 = 2.0 * max(float(sigma_color), 1e-6) ** 2
+    ss2 = 2.0 * max(float(sigma_space), 1e-6) ** 2
+    _launch("mmj_vis_bilateral", _C.ptr(src), _C.ptr(dst), h, w, c, int(radius), sc2, ss2, _stream())
+    return dst
+
+
+def canny(gray: torch.Tensor, lo: int, hi: int) -> torch.Tensor:
+    """Sobel + L1 magnitude + non-maximum suppression + hysteresis on a CUDA [H, W, 1] uint8 image."""
+    gray = _prep(gray)
+    h, w, _ = gray.shape
+    cls = torch.empty((h, w), dtype=torch.uint8, device=gray.device)
+    _launch("mmj_vis_canny_nms", _C.ptr(gray), _C.ptr(cls), h, w, int(lo), int(hi), _stream())
+    changed = torch.zeros(1, dtype=torch.int32, device=gray.device)
+    for _ in range(h + w):   # a path can wind through the tiles; in practice a handful of passes
+        changed.zero_()
+        _launch("mmj_vis_canny_hysteresis", _C.ptr(cls), h, w, _C.ptr(changed), _stream())
+        if int(changed.item()) == 0:
+            break
+    out = torch.empty((h, w, 1), dtype=torch.uint8, device=gray.device)
+    _launch("mmj_vis_canny_finish", _C.ptr(cls), _C.ptr(out), h * w, _stream())
+    return out
+
+
+def clahe_plane(plane: torch.Tensor, clip_limit: float, tile: int) -> torch.Tensor:
+    """Contrast-limited adaptive equalisation of a CUDA [H, W] uint8 plane (tile grid ``tile`` x ``tile``)."""
+    plane = plane.contiguous()
+    h, w = plane.shape
+    ty, tx = max(1, min(tile, h)), max(1, min(tile, w))
+    ys = np.linspace(0, h, ty + 1).astype(np.int32)
+    xs = np.linspace(0, w, tx + 1).astype(np.int32)
+    cy = (ys[:-1] + ys[1:]) / 2.0
+    cx = (xs[:-1] + xs[1:]) / 2.0
+    fi = np.clip(np.interp(np.arange(h) + 0.5, cy, np.arange(ty)), 0, ty - 1).astype(np.float32)
+    fj = np.clip(np.interp(np.arange(w) + 0.5, cx, np.arange(tx)), 0, tx - 1).astype(np.float32)
+    dev = plane.device
+    ys_d, xs_d = torch.from_numpy(ys).to(dev), torch.from_numpy(xs).to(dev)
+    fi_d, fj_d = torch.from_numpy(fi).to(dev), torch.from_numpy(fj).to(dev)
+    luts = torch.empty((ty * tx, 256), dtype=torch.float32, device=dev)
+    _launch("mmj_vis_clahe_luts", _C.ptr(plane), w, _C.ptr(ys_d), _C.ptr(xs_d), ty, tx, float(clip_limit),
+            _C.ptr(luts), _stream())
+    out = torch.empty_like(plane)
+    _launch("mmj_vis_clahe_apply", _C.ptr(plane), _C.ptr(out), h, w, _C.ptr(fi_d), _C.ptr(fj_d), ty, tx,
+            _C.ptr(luts), _stream())
+    return out
+
+
+def connected_components(bw: torch.Tensor, connectivity: int = 4):
+    """``(count, labels)``: int64 [H, W] labels 1..count in row-major order of each component's first pixel,
+    0 for background; ``bw`` is a CUDA uint8 [H, W] or [H, W, C] tensor (channel 0 decides)."""
+    if bw.dim() == 3:
+        stride, (h, w) = bw.shape[2], bw.shape[:2]
+    else:
+        stride, (h, w) = 1, bw.shape
+    bw = bw.contiguous()
+    labels = torch.empty(h * w, dtype=torch.int32, device=bw.device)
+    _launch("mmj_vis_cc_init", _C.ptr(bw), stride, _C.ptr(labels), h * w, _stream())
+    changed = torch.zeros(1, dtype=torch.int32, device=bw.device)
+    for _ in range(h * w):
+        changed.zero_()
+        _launch("mmj_vis_cc_pass", _C.ptr(labels), h, w, int(connectivity == 8), _C.ptr(changed), _stream())
+        if int(changed.item()) == 0:
+            break
+    roots, inverse = torch.unique(labels, sorted=True, return_inverse=True)   # roots ascend = discovery order
+    has_bg = bool(roots.numel() and roots[0].item() == 0)
+    out = inverse.to(torch.int64) + (0 if has_bg else 1)
+    return int(roots.numel() - (1 if has_bg else 0)), out.reshape(h, w)

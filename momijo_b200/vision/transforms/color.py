@@ -126,6 +126,19 @@ def _clahe_plane(a: np.ndarray, clip_limit: float, tile: int) -> np.ndarray:
 def clahe_color_bgr(img, clip_limit: float = 2.0, tile: int = 8):
     """Contrast-limited adaptive equalisation of the luma of a BGR image; chroma is kept."""
     is_img = isinstance(img, Image)
+    if is_img and img.data.is_cuda:
+        d = img.ensure_packed_hwc_u8().data
+        if d.shape[2] == 1:
+            out_t = K.clahe_plane(d[..., 0], clip_limit, tile).unsqueeze(-1)
+        else:
+            f = d[..., :3].to(torch.float32)
+            y = f[..., 2] * 0.299 + f[..., 1] * 0.587 + f[..., 0] * 0.114
+            y8 = (y + 0.5).clamp(0, 255).to(torch.uint8)
+            y2 = K.clahe_plane(y8, clip_limit, tile).to(torch.float32)
+            out_t = (f + (y2 - y).unsqueeze(-1) + 0.5).clamp(0, 255).to(torch.uint8)
+            if d.shape[2] > 3:
+                out_t = torch.cat([out_t, d[..., 3:]], dim=-1)
+        return Image(out_t.contiguous(), img.meta().copy())
     a = img.numpy() if is_img else np.asarray(img, dtype=np.uint8)
     if a.ndim == 2 or a.shape[2] == 1:
         out = _clahe_plane(a.reshape(a.shape[0], a.shape[1]), clip_limit, tile)[..., None]

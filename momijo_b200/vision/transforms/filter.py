@@ -34,6 +34,8 @@ def gaussian_blur(img: Image, kx: int, ky=None, sigma: float = None) -> Image:
 
 def median_blur(img: Image, ksize: int) -> Image:
     k = _odd(ksize)
+    if img.data.is_cuda and k <= 9:
+        return _like(img, K.median(img.ensure_packed_hwc_u8().data, k))
     r = k // 2
     a = img.numpy()
     p = np.pad(a, ((r, r), (r, r), (0, 0)), mode="edge")
@@ -45,6 +47,8 @@ def median_blur(img: Image, ksize: int) -> Image:
 def bilateral_filter(img: Image, d: int, sigma_color: float, sigma_space: float) -> Image:
     d = _odd(d if d > 0 else int(round(sigma_space * 1.5)) * 2 + 1, 3)
     r = d // 2
+    if img.data.is_cuda and img.ensure_packed_hwc_u8().data.shape[2] <= 4:
+        return _like(img, K.bilateral(img.ensure_packed_hwc_u8().data, r, sigma_color, sigma_space))
     a = img.numpy().astype(np.float32)
     h, w = a.shape[:2]
     p = np.pad(a, ((r, r), (r, r), (0, 0)), mode="edge")
@@ -88,6 +92,8 @@ def magnitude_u8(gx: Image, gy: Image) -> Image:
 
 def canny(img: Image, t1: int, t2: int, aperture: int = 3) -> Image:
     lo, hi = (t1, t2) if t1 <= t2 else (t2, t1)
+    if img.data.is_cuda:
+        return Image(K.canny(_gray_data(img), lo, hi))
     g = _gray_data(img).cpu().numpy()[..., 0].astype(np.int32)
     h, w = g.shape
     p = np.pad(g, 1, mode="edge")

@@ -10,6 +10,11 @@ from ..image import Image
 
 
 def connected_components(bw, connectivity: int = 4) -> Tuple[int, List[List[int]]]:
+    if isinstance(bw, Image) and bw.data.is_cuda:
+        from .. import kernels as K
+
+        count, labels = K.connected_components(bw.ensure_packed_hwc_u8().data, connectivity)
+        return count, labels.cpu().tolist()
     a = bw.numpy() if isinstance(bw, Image) else np.asarray(bw)
     if a.ndim == 3:
         a = a[..., 0]

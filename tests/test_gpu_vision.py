@@ -64,3 +64,33 @@ def test_vision_pipeline_on_device():
     _close(out.data, ref.data, 1)
     eq = V.equalize_hist(out)
     _close(eq.data, V.equalize_hist(ref).data, 0 if torch.equal(out.data.cpu(), ref.data) else 255)
+
+
+def test_neighbourhood_and_region_kernels_match_host_transforms():
+    """Median, bilateral, Canny (NMS + hysteresis), CLAHE and connected components: the CUDA kernels against
+    the host implementations of the same transforms."""
+    import momijo_b200.vision as V
+    from momijo_b200.vision.transforms import filter as Fl, color as Cl, segmentation as Sg
+
+    rng = np.random.default_rng(5)
+    # a smooth image with structure (random noise alone makes every pixel an edge)
+    yy, xx = np.mgrid[0:150, 0:201]
+    base = (127 + 90 * np.sin(xx / 11.0) * np.cos(yy / 7.0)).astype(np.float32)
+    img = np.clip(base[..., None] + rng.normal(0, 6, (150, 201, 3)), 0, 255).astype(np.uint8)
+    host = V.Image(torch.from_numpy(img))
+    dev = host.cuda()
+    for k in (3, 5):
+        _close(Fl.median_blur(dev, k).data, Fl.median_blur(host, k).data)
+    _close(Fl.bilateral_filter(dev, 5, 30.0, 3.0).data, Fl.bilateral_filter(host, 5, 30.0, 3.0).data, 1)
+    a, b = Fl.canny(dev, 60, 150).data.cpu(), Fl.canny(host, 60, 150).data
+    assert a.shape == b.shape and (a != b).sum().item() == 0, (a != b).sum().item()
+    assert 0 < (b > 0).sum().item() < b.numel() // 2
+    _close(Cl.clahe_color_bgr(dev, 2.0, 8).data, Cl.clahe_color_bgr(host, 2.0, 8).data, 1)
+    gray = V.Image(torch.from_numpy(img[..., :1].copy()))
+    _close(Cl.clahe_color_bgr(gray.cuda(), 3.0, 4).data, Cl.clahe_color_bgr(gray, 3.0, 4).data, 1)
+    bw = (rng.random((90, 120)) < 0.45).astype(np.uint8) * 255
+    bimg = V.Image(torch.from_numpy(bw[..., None].copy()))
+    for conn in (4, 8):
+        n_d, l_d = Sg.connected_components(bimg.cuda(), conn)
+        n_h, l_h = Sg.connected_components(bimg, conn)
+        assert n_d == n_h and l_d == l_h
