@@ -93,6 +93,9 @@ _SIGS = {
     "mmj_vis_clahe_apply": ([P, P, I, I, P, P, I, I, P, P], 1),
     "mmj_vis_cc_init": ([P, I, P, L, P], 1),
     "mmj_vis_cc_pass": ([P, I, I, I, P, P], 1),
+    "mmj_moe_router_parts": ([], 0),
+    "mmj_moe_router_fwd": ([P, L, I, I, I, F, P, P, P, P, P, P, P, P], 2),
+    "mmj_moe_router_bwd": ([P, L, I, I, I, P, P, P, P, P, F, P, L, P], 1),
     "mmj_attn_set_trace": ([P, L], 0),
     "mmj_attn_bwd": ([P, L, I, P, L, I, P, L, I, P, L, I, P, L, I, P, P, P, L, I, P, L, I, P, L, I,
                       I, I, I, I, I, F, I, P, P], 2),

@@ -226,6 +226,42 @@ class _ExpertsEP(torch.autograd.Function):
                 None if buf is not None else dw_down, None)
 
 
+class _RouterTopK(torch.autograd.Function):
+    """softmax -> top-k -> renormalise -> per-expert counts / probability sums -> auxiliary loss, as one
+    device pass (``csrc/moe_router.cu``); the backward pass is one kernel as well."""
+
+    @staticmethod
+    def forward(ctx, logits, k, coef):
+        logits = logits.contiguous()
+        n, E = logits.shape
+        dev = logits.device
+        w = torch.empty((n, k), dtype=torch.float32, device=dev)
+        idx = torch.empty((n, k), dtype=torch.int32, device=dev)
+        cnt = torch.empty(E, dtype=torch.int32, device=dev)
+        psum = torch.empty(E, dtype=torch.float32, device=dev)
+        aux = torch.empty(1, dtype=torch.float32, device=dev)
+        parts = _C.lib().mmj_moe_router_parts()
+        pc = torch.empty(parts * E, dtype=torch.int32, device=dev)
+        pp = torch.empty(parts * E, dtype=torch.float32, device=dev)
+        _C.call("mmj_moe_router_fwd", _C.ptr(logits), logits.stride(0), n, E, k, float(coef), _C.ptr(w), _C.ptr(idx),
+                _C.ptr(cnt), _C.ptr(psum), _C.ptr(aux), _C.ptr(pc), _C.ptr(pp), _C.current_stream())
+        ctx.save_for_backward(logits, w, idx, cnt)
+        ctx.k, ctx.coef = k, float(coef)
+        ctx.mark_non_differentiable(idx)
+        return w, idx, aux[0]
+
+    @staticmethod
+    def backward(ctx, dw, _didx, daux):
+        logits, w, idx, cnt = ctx.saved_tensors
+        n, E = logits.shape
+        dl = torch.empty_like(logits)
+        dw = None if dw is None else dw.contiguous().float()
+        da = None if daux is None else daux.reshape(1).float().contiguous()
+        _C.call("mmj_moe_router_bwd", _C.ptr(logits), logits.stride(0), n, E, ctx.k, _C.ptr(w), _C.ptr(idx),
+                _C.ptr(dw), _C.ptr(da), _C.ptr(cnt), ctx.coef, _C.ptr(dl), dl.stride(0), _C.current_stream())
+        return dl, None, None
+
+
 class TopKRouter(nn.Module):
     """Softmax router with top-k selection, renormalised weights and the load-balance auxiliary
     loss ``aux = coef * E * sum_e f_e * P_e`` (f_e: fraction of assignments, P_e: mean router
@@ -238,6 +274,8 @@ class TopKRouter(nn.Module):
         self.E, self.k, self.aux_coef = n_experts, top_k, aux_coef
 
     def forward(self, x):
+        if x.is_cuda and x.dtype == bf16 and self.E <= 256 and self.k <= 32:
+            return _RouterTopK.apply(ops.linear(x, self.weight), self.k, self.aux_coef)
         logits = ops.linear(x, self.weight).float()
         probs = torch.softmax(logits, dim=-1)
         w, idx = torch.topk(probs, self.k, dim=-1)

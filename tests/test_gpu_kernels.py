@@ -258,3 +258,35 @@ def test_debug_bounds_build_records_bad_index(tmp_path):
     env = dict(os.environ, MOMIJO_DEBUG_BOUNDS="1", PYTHONPATH=root)
     out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
     assert "BOUNDS_OK" in out.stdout, out.stdout + out.stderr
+
+
+@pytest.mark.parametrize("n,E,k", [(1000, 64, 6), (257, 8, 2), (64, 160, 4)])
+def test_moe_router_kernel_matches_torch(n, E, k):
+    """Device router (softmax, top-k, renormalise, counts, auxiliary loss) and its backward against torch."""
+    from momijo_b200.parallel.ep import _RouterTopK
+
+    torch.manual_seed(9)
+    coef = 0.01
+    logits = (torch.randn(n, E, device="cuda") * 2).to(bf16).requires_grad_(True)
+    w, idx, aux = _RouterTopK.apply(logits, k, coef)
+    lr = logits.detach().float().requires_grad_(True)
+    probs = torch.softmax(lr, -1)
+    wr, ir = torch.topk(probs, k, dim=-1)
+    wr = wr / wr.sum(-1, keepdim=True)
+    f = torch.zeros(E, device="cuda").scatter_add_(0, ir.reshape(-1), torch.ones(ir.numel(), device="cuda")) / ir.numel()
+    auxr = coef * E * (f * probs.mean(0)).sum()
+    assert torch.equal(idx.long().sort(-1).values, ir.sort(-1).values)
+    order = idx.long().argsort(-1)
+    order_r = ir.argsort(-1)
+    _close(w.gather(1, order), wr.gather(1, order_r), 1e-4, 1e-4)
+    assert abs(aux.item() - auxr.item()) < 1e-5 * max(1.0, abs(auxr.item()))
+    gw = torch.randn(n, k, device="cuda")
+    # the same upstream gradient for the same (token, expert) pairs
+    loss = (w.gather(1, order) * gw).sum() + 3.0 * aux
+    loss.backward()
+    loss_r = (wr.gather(1, order_r) * gw).sum() + 3.0 * auxr
+    loss_r.backward()
+    _close(logits.grad, lr.grad, 3e-2, 1e-2)
+    # bitwise reproducible
+    w2, idx2, aux2 = _RouterTopK.apply(logits.detach(), k, coef)
+    assert torch.equal(w2, w.detach()) and torch.equal(idx2, idx) and aux2.item() == aux.item()
