@@ -354,7 +354,9 @@ def setup_llama_pptp(args, rank, world, local):
     with torch.device("cuda"):
         module = LlamaStage(cfg, tp, layers, first=stage_id == 0, last=stage_id == S - 1)
     module.batch_shape = (1, T)
-    engine = HybridEngine(module, AdamWConfig(lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1), rep_comm=comm)
+    # 16 micro-batch gradients are summed before one update: accumulate them in fp32
+    engine = HybridEngine(module, AdamWConfig(lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1), rep_comm=comm,
+                          local_grad_dtype=torch.float32)
     stage = PipelineStage(module, stage_id, S, prev_rank=rank - TP if stage_id > 0 else None,
                           next_rank=rank + TP if stage_id < S - 1 else None)
     sched = Schedule1F1B(stage, n_micro, (T // TP, cfg.d_model), torch.bfloat16, torch.device("cuda", local))
@@ -380,7 +382,8 @@ def setup_llama_pptp(args, rank, world, local):
             "h2d_bytes": n_micro * (T + 1) * 8,
             "config": {"model": f"llama-2-13b shape ({cfg.n_layer}L d5120 40H ff13824 vocab32000 seq4096)",
                        "global_batch": n_micro, "seq_len": T, "parallelism": f"pp2 x tp{TP}, 1F1B, {n_micro} micro-batches",
-                       "optimizer": "AdamW fp32 master on local shards, step inside the timed region",
+                       "optimizer": "AdamW fp32 master on local shards, fp32 gradient accumulation over the micro-batches, "
+                                    "step inside the timed region",
                        "l2": "working set of tens of GB per step >> 126 MB L2; no flush"}}
     return step_device, step_e2e, info
 

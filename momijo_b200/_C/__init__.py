@@ -57,7 +57,7 @@ _SIGS = {
     "mmj_ce_count_valid": ([P, L, L, P, P], 1),
     "mmj_scale_bf16_dev": ([P, L, L, I, P, P], 1),
     "mmj_ce_vp_stats": ([P, L, I, L, P, P, P, P, L, P], 1),
-    "mmj_ce_vp_grad": ([P, L, I, L, P, P, P, L, F, P], 1),
+    "mmj_ce_vp_grad": ([P, L, I, L, P, P, P, L, F, P, P], 1),
     "mmj_reduce_mean": ([P, P, L, F, P, P], 1),
     "mmj_adamw": ([P, I, P, P, P, P, L, F, F, F, F, F, F, F, F, P, P, P], 1),
     "mmj_sgd": ([P, I, P, P, P, L, F, F, F, F, P], 1),

@@ -600,17 +600,26 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     constexpr float kTau = 8.0f;
     uint32_t sn = 0, on = 0;
     bool ok = true;
+    // timeline (optional): thread 0 of each softmax group stamps the first item of its CTA; slots
+    // 8 + 24 t + 4 j + {0: S arrived, 1: S in registers, 2: maximum known, 3: P stored}, j < 6
+    const bool tracer = (p.trace != nullptr) && (lane == 0) && (quad == 0);
     for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
       int qp, h, b;
       decode(w, qp, h, b);
       const int nkv = blocks_of(qp, t);
       if (nkv == 0) continue;
+      const bool tr = tracer && (w == (int)blockIdx.x);
+      if (tr && t == 0) {
+        p.trace[(long long)blockIdx.x * kTraceSlots + 7] = nkv;
+        trace_stamp(p.trace, blockIdx.x, 0);
+      }
       const int q0 = qp * 256 + t * 128;
       const int q_idx = q0 + row;
       float m_used = -1.0e30f, l = 0.f;
       for (int j = 0; j < nkv; ++j, ++sn) {
         if (!mbar_wait_warp(&s_full[t], sn & 1, &abort_flag, p.status, kTimeoutTmemFull, j)) { ok = false; break; }
         tc_fence_after();
+        if (tr && j < 6) trace_stamp(p.trace, blockIdx.x, 8 + 24 * t + 4 * j + 0);
         const int kv0 = j * 128;
         const bool need_mask = (p.causal && (kv0 + 127 > q0)) || (kv0 + 128 > p.T);
         uint32_t s[128];
@@ -619,6 +628,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_ld_32x32(t_lane + colS + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
         tmem_ld_32x32(t_lane + colS + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
         tmem_ld_wait();
+        if (tr && j < 6) trace_stamp(p.trace, blockIdx.x, 8 + 24 * t + 4 * j + 1);
         if (need_mask) {
 #pragma unroll
           for (int i = 0; i < 128; ++i) {
@@ -635,6 +645,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
         }
         const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        if (tr && j < 6) trace_stamp(p.trace, blockIdx.x, 8 + 24 * t + 4 * j + 2);
         const bool grow = (mx - m_used) * c > kTau;  // false for fully masked rows (mx = -inf)
         if (__any_sync(0xffffffffu, grow ? 1 : 0)) {
           float alpha = 1.0f;
@@ -679,8 +690,10 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[t]);
+        if (tr && j < 6) trace_stamp(p.trace, blockIdx.x, 8 + 24 * t + 4 * j + 3);
       }
       if (!ok) break;
+      if (tr) trace_stamp(p.trace, blockIdx.x, 2 + 2 * t);
       // final: wait for the last P V of this tile, normalise and store
       if (!mbar_wait_warp(&o_full[t], on & 1, &abort_flag, p.status, kTimeoutTmemFull, 999)) { ok = false; break; }
       ++on;
@@ -712,6 +725,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       if (q_idx < p.T && p.lse != nullptr)
         p.lse[((long long)b * p.Hq + h) * p.T + q_idx] = (l > 0.f) ? (m_used * p.scale + __logf(l)) : -INFINITY;
+      if (tr) trace_stamp(p.trace, blockIdx.x, 3 + 2 * t);
     }
   }
 
@@ -1314,6 +1328,7 @@ MMJ_API int mmj_attn_fwd(const void* q, long long ldq, int q_col0, const void* k
     }
     const long long n_items = (long long)((T + 255) / 256) * Hq * B;
     const unsigned g = (unsigned)(n_items < sms ? n_items : sms);
+    p.trace = (g_attn_trace && (long long)g <= g_attn_trace_ctas) ? g_attn_trace : nullptr;
     if (D == 64) {
       const int smem = (2 + 3 + 3) * kPanelBytes + 1024;
       if (!a64) {

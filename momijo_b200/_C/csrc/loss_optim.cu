@@ -152,7 +152,8 @@ __global__ void ce_vp_stats_kernel(const __nv_bfloat16* __restrict__ logits, lon
 __global__ void ce_vp_grad_kernel(__nv_bfloat16* __restrict__ logits, long long ld, int Vloc,
                                   long long vocab_start, const long long* __restrict__ targets,
                                   const float* __restrict__ gmax, const float* __restrict__ gsum,
-                                  float dscale) {
+                                  float dscale, const float* __restrict__ dscale_dev) {
+  if (dscale_dev != nullptr) dscale *= *dscale_dev;   // gradient of the loss, folded in here (no extra pass)
   const long long row = blockIdx.x;
   __nv_bfloat16* g = logits + row * ld;
   const int nvec = (int)(ld >> 3);
@@ -366,11 +367,11 @@ MMJ_API int mmj_ce_vp_stats(const void* logits, long long ld, int Vloc, long lon
 }
 MMJ_API int mmj_ce_vp_grad(void* logits, long long ld, int Vloc, long long vocab_start,
                            const long long* targets, const float* gmax, const float* gsum,
-                           long long rows, float dscale, void* stream) {
+                           long long rows, float dscale, const float* dscale_dev, void* stream) {
   if (ld % 8 || Vloc > ld) return -1;
   if (rows == 0) return 0;
   ce_vp_grad_kernel<<<(unsigned)rows, 512, 0, STREAM>>>((__nv_bfloat16*)logits, ld, Vloc,
-                                                        vocab_start, targets, gmax, gsum, dscale);
+                                                        vocab_start, targets, gmax, gsum, dscale, dscale_dev);
   return (int)cudaGetLastError();
 }
 // out[0] = scale * (*scale_dev, when given) * sum(x)

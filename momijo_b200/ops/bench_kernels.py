@@ -59,7 +59,7 @@ def bench_gemm(small):
 
 def bench_attn(small):
     flops_peak, _, tag = peaks()
-    cfgs = [(2, 1024, 12, 12, 64)] if small else [(16, 1024, 12, 12, 64), (2, 4096, 32, 8, 128),
+    cfgs = [(2, 1024, 12, 12, 64), (1, 2048, 16, 4, 128)] if small else [(16, 1024, 12, 12, 64), (2, 4096, 32, 8, 128),
                                                      (8, 4096, 16, 16, 128)]
     rows = []
     for B, T, Hq, Hkv, D in cfgs:

@@ -48,8 +48,9 @@ def _colsum(x2d, out=None, accumulate=False):
         return out
     S = _C.lib().mmj_colsum_splits(M)
     scratch = torch.empty(S * N, dtype=torch.float32, device=x2d.device)
-    _C.call("mmj_colsum_bf16", _C.ptr(x2d), x2d.stride(0), _C.ptr(out), None, _C.ptr(scratch), M, N,
-            int(accumulate), _C.current_stream())
+    f32 = out.dtype == torch.float32   # fp32 gradient buffers take the sums unrounded
+    _C.call("mmj_colsum_bf16", _C.ptr(x2d), x2d.stride(0), None if f32 else _C.ptr(out), _C.ptr(out) if f32 else None,
+            _C.ptr(scratch), M, N, int(accumulate), _C.current_stream())
     return out
 
 
@@ -269,7 +270,7 @@ class _Norm(torch.autograd.Function):
         scratch = torch.empty(2 * nparts * C, dtype=torch.float32, device=xin.device)
         gbuf, gacc = _wgrad_target(rgamma)
         bbuf, bacc = _wgrad_target(rbeta) if rbeta is not None else (None, False)
-        direct = gbuf is not None and (rbeta is None or bbuf is not None) and (
+        direct = gbuf is not None and gbuf.dtype == bf16 and (rbeta is None or bbuf is not None) and (
             rbeta is None or gacc == bacc)
         if direct:
             dg, db, acc = gbuf, bbuf, gacc
@@ -483,22 +484,35 @@ class _Embedding(torch.autograd.Function):
         d2 = dout.reshape(-1, C).contiguous()
         rows = d2.shape[0]
         ebuf, eacc = _wgrad_target(wte)
-        if ebuf is None:
+        fold_wte = ebuf is not None and ebuf.dtype != bf16   # fp32 gradient buffer: scatter in bf16, then fold
+        if ebuf is None or fold_wte:
             dwte = torch.zeros_like(wte)
         else:
             dwte = ebuf
             if not eacc:
                 dwte.zero_()
-        dwpe, pacc = None, False
+        dwpe, pacc, fold_wpe = None, False, False
         if wpe is not None:
             pbuf, pacc = _wgrad_target(wpe)
-            dwpe = pbuf if pbuf is not None else torch.empty_like(wpe)
-            if pbuf is None:
+            fold_wpe = pbuf is not None and pbuf.dtype != bf16
+            pacc_buf = pacc
+            dwpe = pbuf if (pbuf is not None and not fold_wpe) else torch.empty_like(wpe)
+            if pbuf is None or fold_wpe:
                 pacc = False
             if wpe.shape[0] > ctx.T and not pacc:
                 dwpe.zero_()
         _C.call("mmj_embedding_bwd", _C.ptr(tok1), _C.ptr(d2), _C.ptr(dwte), _C.ptr(dwpe), rows, C,
                 ctx.T, wte.shape[0], int(pacc), _C.current_stream())
+        if fold_wte:
+            if eacc:
+                ebuf.add_(dwte)
+            else:
+                ebuf.copy_(dwte)
+        if wpe is not None and fold_wpe:
+            if pacc_buf:
+                pbuf.add_(dwpe)
+            else:
+                pbuf.copy_(dwpe)
         return (None, None if ebuf is not None else dwte,
                 None if (wpe is None or getattr(wpe, "main_grad", None) is not None) else dwpe, None)
 

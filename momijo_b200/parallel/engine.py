@@ -35,17 +35,19 @@ def mark_replicated(params: Iterable[nn.Parameter]) -> None:
 class HybridEngine(nn.Module):
     def __init__(self, module: nn.Module, optim: Optional[AdamWConfig] = None, *, dp_comm=None,
                  dp_params: Optional[List[nn.Parameter]] = None, rep_comm=None, rep_group=None,
-                 local_grad_scale: float = 1.0):
+                 local_grad_scale: float = 1.0, local_grad_dtype: Optional[torch.dtype] = None):
         """``dp_params`` (with ``dp_comm``): parameters updated through the sharded data-parallel path;
         everything else is local. ``rep_comm`` / ``rep_group``: where to sum the gradients of parameters
-        flagged ``tp_replicated`` (a ``PeerComm`` of the tensor-parallel group, or a process group)."""
+        flagged ``tp_replicated`` (a ``PeerComm`` of the tensor-parallel group, or a process group).
+        ``local_grad_dtype=torch.float32``: accumulate the local parameters' gradients in fp32 (pipeline
+        schedules add many micro-batch gradients before one update)."""
         super().__init__()
         self.module = module
         self.optim = optim or AdamWConfig()
         dp_ids = {id(p) for p in (dp_params or [])}
         local = [p for p in module.parameters() if p.requires_grad and id(p) not in dp_ids]
         self.local = ShardedDataParallel(module, self.optim, stage=3, comm=None, params=local,
-                                         grad_scale=local_grad_scale) if local else None
+                                         grad_scale=local_grad_scale, grad_dtype=local_grad_dtype) if local else None
         self.dp = ShardedDataParallel(module, self.optim, stage=3, comm=dp_comm, params=list(dp_params)) \
             if dp_params else None
         self.rep_comm, self.rep_group = rep_comm, rep_group
@@ -68,9 +70,10 @@ class HybridEngine(nn.Module):
                 self._rep_buf = self.rep_comm.alloc(pad, torch.bfloat16)
             buf = self._rep_buf
             off = 0
-            for p in self._rep:
-                buf[off:off + p.numel()].copy_(p.main_grad.reshape(-1))
-                off += p.numel()
+            # one gather of the (small, scattered) replicated gradients into the symmetric buffer
+            torch.cat([p.main_grad.reshape(-1) for p in self._rep], out=buf[:n]) if all(
+                p.main_grad.dtype == buf.dtype for p in self._rep) else buf[:n].copy_(
+                torch.cat([p.main_grad.reshape(-1).to(buf.dtype) for p in self._rep]))
             self.rep_comm.all_reduce_(buf)
         else:
             buf = torch.cat([p.main_grad.reshape(-1) for p in self._rep])

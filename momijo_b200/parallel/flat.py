@@ -39,7 +39,11 @@ class FlatParams:
 
     def __init__(self, module: nn.Module, world: int = 1, rank: int = 0,
                  alloc: Optional[Callable[[int, torch.dtype, torch.device], torch.Tensor]] = None,
-                 dtype: torch.dtype = torch.bfloat16, device=None, params: Optional[List[nn.Parameter]] = None):
+                 dtype: torch.dtype = torch.bfloat16, device=None, params: Optional[List[nn.Parameter]] = None,
+                 grad_dtype: Optional[torch.dtype] = None):
+        """``grad_dtype``: element type of the gradient buffer (default: the parameter type). fp32 keeps
+        the sum over many micro-batches exact to fp32 rounding: the weight-gradient GEMMs accumulate into it
+        directly, the few non-GEMM gradients are folded in by a conversion."""
         source = list(params) if params is not None else list(module.parameters())
         seen, params = set(), []
         for p in source:
@@ -55,7 +59,8 @@ class FlatParams:
         if alloc is None:
             alloc = lambda n, dt, dev: torch.zeros(n, dtype=dt, device=dev)
         self.param = alloc(self.layout.total, dtype, device)
-        self.grad = alloc(self.layout.total, dtype, device)
+        self.grad_dtype = grad_dtype or dtype
+        self.grad = alloc(self.layout.total, self.grad_dtype, device)
         with torch.no_grad():
             for p, off in zip(params, self.layout.offsets):
                 view = self.param[off:off + p.numel()].view(p.shape)

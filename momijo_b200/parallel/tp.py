@@ -320,9 +320,10 @@ class _VocabParallelCE(torch.autograd.Function):
         vocab_start, v_local = ctx.cfg
         M = logits.shape[0]
         if logits.is_cuda and logits.dtype == bf16 and logits.stride(0) % 8 == 0:
+            ds = dloss.detach().reshape(1).to(torch.float32)
             _C.call("mmj_ce_vp_grad", _C.ptr(logits), logits.stride(0), v_local, vocab_start, _C.ptr(t1),
-                    _C.ptr(gmax), _C.ptr(gsum), M, 1.0 / M, _C.current_stream())
-            d = logits
+                    _C.ptr(gmax), _C.ptr(gsum), M, 1.0 / M, _C.ptr(ds), _C.current_stream())
+            return logits, None, None, None, None
         else:
             lf = logits.float()
             p = torch.exp(lf - gmax[:, None]) / gsum[:, None]

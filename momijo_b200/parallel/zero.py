@@ -122,14 +122,15 @@ class ShardedDataParallel(nn.Module):
     def __init__(self, module: nn.Module, optim: Optional[AdamWConfig] = None, stage: int = 3,
                  comm=None, grad_clip: Optional[float] = None, params=None, grad_scale: float = 1.0,
                  units: Optional[Sequence[nn.Module]] = None, overlap: bool = True, window: int = 3,
-                 grad_slots: int = 3, fuse_first_gemm: bool = True):
+                 grad_slots: int = 3, fuse_first_gemm: bool = True, grad_dtype: Optional[torch.dtype] = None):
         """``comm``: a ``parallel.peer.PeerComm`` (NVLink peer memory, CUDA) or a
         ``parallel.peer.TorchDistComm`` (torch.distributed: gloo on CPU); ``None`` = single rank.
         ``params``: restrict the wrapper to these parameters of ``module`` (default: all of them).
         ``grad_scale``: constant factor on the gradients (a rank that owns its parameters outright but
         whose loss is a per-rank mean needs 1/world here). ``grad_clip``: clip by the global gradient
         norm; the update of every bucket then waits for the norm (reduce-scatter during backward, one
-        scalar all-reduce, AdamW afterwards). ``units``: the modules that get a bucket each."""
+        scalar all-reduce, AdamW afterwards). ``units``: the modules that get a bucket each.
+        ``grad_dtype`` (single rank only): torch.float32 accumulates micro-batch gradients in fp32."""
         super().__init__()
         if stage not in (1, 2, 3):
             raise ValueError("stage must be 1, 2 or 3")
@@ -149,15 +150,17 @@ class ShardedDataParallel(nn.Module):
         self.side_blocks = 2 * 148   # grid limit of kernels that run beside the backward pass
         self._sync_enabled = True
         if self.world == 1:
-            self._init_single(params)
+            self._init_single(params, grad_dtype)
         else:
+            if grad_dtype not in (None, torch.bfloat16):
+                raise NotImplementedError("the peer reduce-scatter kernel reads bf16 gradients")
             self._init_sharded(params, units, window, grad_slots, fuse_first_gemm)
 
     # ------------------------------------------------------------------------------------------
     # single rank: one flat buffer, fused AdamW
     # ------------------------------------------------------------------------------------------
-    def _init_single(self, params):
-        self.flat = FlatParams(self.module, 1, 0, alloc=None, params=params)
+    def _init_single(self, params, grad_dtype=None):
+        self.flat = FlatParams(self.module, 1, 0, alloc=None, params=params, grad_dtype=grad_dtype)
         dev = self.flat.param.device
         n = self.flat.layout.total
         self.master = self.flat.param.float().clone()

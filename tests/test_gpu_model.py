@@ -45,3 +45,33 @@ def test_engine_trains_and_counts_launches():
         losses.append(loss.item())
     assert _C.launches - before > 8 * 20
     assert losses[-1] < losses[0]
+
+
+def test_micro_batch_accumulation_in_fp32_matches_reference():
+    """Four micro-batches of (loss / 4).backward() into an fp32 gradient buffer == the gradient of the mean loss
+    over the four micro-batches from the fp32 reference path; then one optimizer step."""
+    torch.manual_seed(0)
+    cfg = GPT2Config(vocab_size=1000, n_layer=2, n_head=2, d_model=128, d_ff=512, max_seq=256)
+    model = GPT2(cfg).cuda()
+    ref = GPT2(cfg)
+    ref.load_state_dict(model.state_dict())
+    ref = ref.float()
+    ref.cfg.dtype = torch.float32
+    eng = ShardedDataParallel(model, AdamWConfig(lr=1e-3), grad_dtype=torch.float32)
+    assert eng.flat.grad.dtype == torch.float32
+    tok = torch.randint(0, cfg.vocab_size, (8, 129), device="cuda")
+    for m in range(4):
+        t = tok[2 * m:2 * m + 2]
+        (eng(t[:, :-1], t[:, 1:]) / 4).backward()
+    tc = tok.cpu()
+    ref(tc[:, :-1], tc[:, 1:]).backward()
+    got = dict(model.named_parameters())
+    num = den = 0.0
+    for name, p in ref.named_parameters():
+        g = got[name].main_grad.float().cpu()
+        num += (g - p.grad).pow(2).sum().item()
+        den += p.grad.pow(2).sum().item()
+    assert (num / den) ** 0.5 < 2e-2, (num / den) ** 0.5
+    before = model.wte.detach().float().clone()
+    eng.step()
+    assert (model.wte.detach().float() - before).abs().max().item() > 0
