@@ -738,6 +738,387 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 }
 
 // =============================================================================================
+// Forward, two query tiles per CTA, 64-key blocks, double-buffered score tiles (the default)
+// =============================================================================================
+// Same work split as attn_fwd2_kernel (persistent CTAs, items of 256 query rows, three warpgroups), with
+// two changes that take the tensor core out of the softmax groups' dependency chain:
+//   * each query tile has its own MMA-issuing thread (warps 1 and 2);
+//   * a key block is 64 keys and every query tile owns TWO score buffers in tensor memory
+//     (S_t[0], S_t[1], 64 columns each): the MMA thread issues S_t(j+1) before the group has finished
+//     block j, so a group that has stored P_t(j) finds S_t(j+1) waiting and starts on it at once;
+//     per key block the MMA thread does  [wait P_t(j)]  P_t(j) V_j -> O_t,  Q_t K_(j+2)^T -> S_t[j & 1];
+//   * probabilities are rounded to bf16 with integer arithmetic (add half an ulp, take the upper
+//     halves with one byte permute) instead of the conversion instruction, which shares the
+//     transcendental pipe with the exponentials.
+// Tensor memory: S0[0] S0[1] S1[0] S1[1] | O0 | O1 = 256 + 2 D columns; P_t(j) overwrites the first 32
+// columns of S_t[j & 1] (64 probabilities as bf16 pairs). Every P_t(j) V_j commits to o_done[t][j & 1];
+// a group waits on it only before it rescales O_t (rare: the running maximum must have grown by more
+// than 2^8) and before the final normalisation.
+__device__ __forceinline__ uint32_t pack_bf16x2_halfup(float lo, float hi) {
+  // lo, hi >= 0 (probabilities): adding 0x8000 to the bit pattern rounds the upper 16 bits half-up
+  const uint32_t a = __float_as_uint(lo) + 0x8000u, b = __float_as_uint(hi) + 0x8000u;
+  return __byte_perm(a, b, 0x7632);
+}
+
+template <int D>
+__global__ void __launch_bounds__(384, 1)
+attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+  constexpr int NP = D / 64;
+  constexpr int kQTile = NP * kPanelBytes;         // 128 query rows
+  constexpr int kKVPanel = 64 * 128;               // 64 key rows x 64 bf16
+  constexpr int kKVTile = NP * kKVPanel;           // 64 key rows x D
+  constexpr int KS = (D == 64) ? 6 : 4;            // K and V stages
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kColO = 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* sQ = smem;                   // 2 tiles
+  uint8_t* sK = sQ + 2 * kQTile;        // KS stages
+  uint8_t* sV = sK + KS * kKVTile;      // KS stages
+
+  __shared__ __align__(8) uint64_t q_full[2], q_empty[2], o_free[2];
+  __shared__ __align__(8) uint64_t s_full[2][2], p_full[2][2], o_done[2][2];
+  __shared__ __align__(8) uint64_t k_full[KS], k_empty[KS], v_full[KS], v_empty[KS];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqp = (p.T + 255) / 256;
+  const int nbh = p.B * p.Hq;
+  const int n_items = nqp * nbh;
+  const int group = p.Hq / p.Hkv;
+
+  if (threadIdx.x == 0) {
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&q_full[t], 1);
+      mbar_init(&q_empty[t], 1);
+      mbar_init(&o_free[t], 4);
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(&s_full[t][b], 1);
+        mbar_init(&p_full[t][b], 4);
+        mbar_init(&o_done[t][b], 1);
+      }
+    }
+    for (int s = 0; s < KS; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 2);   // one arrival per query tile (its MMA thread)
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 2);
+    }
+    abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  auto decode = [&](int w, int& qp, int& h, int& b) {
+    qp = nqp - 1 - w / nbh;  // later (longer) query pairs first
+    const int bh = w % nbh;
+    h = bh % p.Hq;
+    b = bh / p.Hq;
+  };
+  // 64-key blocks of tile t of query pair qp (0 when the tile lies beyond T)
+  auto blocks_of = [&](int qp, int t) -> int {
+    const int q0 = qp * 256 + t * 128;
+    if (q0 >= p.T) return 0;
+    const int kv_end = p.causal ? min(p.T, q0 + 128) : p.T;
+    return (kv_end + 63) / 64;
+  };
+
+  if (warp == 0) {
+    // ======================= TMA producer =======================
+    if (lane == 0) {
+      uint32_t qn[2] = {0, 0};
+      uint32_t kc = 0;  // ring position of this item's block 0 (K and V rings advance together per item)
+      bool ok = true;
+      for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+        int qp, h, b;
+        decode(w, qp, h, b);
+        const int hkv = h / group;
+        const int nb[2] = {blocks_of(qp, 0), blocks_of(qp, 1)};
+        const int n1 = max(nb[0], nb[1]);
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (nb[t] == 0) continue;
+          if (!mbar_wait(&q_empty[t], (qn[t] & 1) ^ 1, &abort_flag, p.status, kTimeoutEmpty, 300 + t)) { ok = false; break; }
+          ++qn[t];
+          mbar_expect_tx(&q_full[t], kQTile);
+#pragma unroll
+          for (int pn = 0; pn < NP; ++pn)
+            tma_load_3d(sQ + t * kQTile + pn * kPanelBytes, &tmQ, &q_full[t], p.q_col0 + h * D + pn * 64,
+                        qp * 256 + t * 128, b);
+        }
+        auto load_k = [&](int j) -> bool {
+          const uint32_t c = kc + (uint32_t)j;
+          const int s = c % KS;
+          if (!mbar_wait(&k_empty[s], ((c / KS) & 1) ^ 1, &abort_flag, p.status, kTimeoutEmpty, j)) return false;
+          mbar_expect_tx(&k_full[s], kKVTile);
+#pragma unroll
+          for (int pn = 0; pn < NP; ++pn)
+            tma_load_3d(sK + s * kKVTile + pn * kKVPanel, &tmK, &k_full[s], p.k_col0 + hkv * D + pn * 64, j * 64, b);
+          return true;
+        };
+        auto load_v = [&](int j) -> bool {
+          const uint32_t c = kc + (uint32_t)j;
+          const int s = c % KS;
+          if (!mbar_wait(&v_empty[s], ((c / KS) & 1) ^ 1, &abort_flag, p.status, kTimeoutEmpty, 100 + j)) return false;
+          mbar_expect_tx(&v_full[s], kKVTile);
+#pragma unroll
+          for (int pn = 0; pn < NP; ++pn)
+            tma_load_3d(sV + s * kKVTile + pn * kKVPanel, &tmV, &v_full[s], p.v_col0 + hkv * D + pn * 64, j * 64, b);
+          return true;
+        };
+        // the order the MMA thread consumes them in: K0 K1 V0 K2 V1 K3 ...
+        for (int j = 0; j < n1 && ok; ++j) {
+          ok = load_k(j);
+          if (ok && j >= 1) ok = load_v(j - 1);
+        }
+        if (ok && n1 > 0) ok = load_v(n1 - 1);
+        kc += (uint32_t)n1;
+      }
+    }
+  } else if (warp == 1 || warp == 2) {
+    // ======================= MMA issuers: warp 1 drives query tile 0, warp 2 tile 1 =======================
+    // (a single issuing thread spends about 1400 cycles per tile and key block on waits, descriptors,
+    // MMAs and commits; with one thread per tile the two tiles' chains no longer queue behind each other)
+    if (lane == 0) {
+      const int t = warp - 1;
+      const uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);
+      const uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);
+      uint32_t qn = 0;
+      uint32_t pc[2] = {0, 0};  // P tiles consumed so far, per buffer
+      uint32_t on = 0;
+      uint32_t kc = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+        int qp, h, b;
+        decode(w, qp, h, b);
+        const int nbt = blocks_of(qp, t);
+        const int n1 = max(blocks_of(qp, 0), blocks_of(qp, 1));
+        // S_t(j) = Q_t K_j^T into buffer j & 1
+        auto issue_s = [&](int j) -> bool {
+          const uint32_t c = kc + (uint32_t)j;
+          const int s = c % KS;
+          if (!mbar_wait(&k_full[s], (c / KS) & 1, &abort_flag, p.status, kTimeoutFull, j)) return false;
+          tc_fence_after();
+          const uint32_t aQ = smem_u32(sQ + t * kQTile), aK = smem_u32(sK + s * kKVTile);
+          const uint32_t d = tmem_base + (uint32_t)(t * 128 + (j & 1) * 64);
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            // K tile: 64 rows, 64-column panels of 8 KiB
+            const uint64_t dk = make_smem_desc(aK + (uint32_t)(k >> 2) * kKVPanel + (uint32_t)(k & 3) * 32, 16, 1024);
+            umma_bf16_ss(d, desc_kmajor(aQ, k), dk, idesc_s, k > 0 ? 1u : 0u);
+          }
+          umma_commit(&k_empty[s]);   // this tile's share of the K block's release
+          if (j + 1 == nbt) umma_commit(&q_empty[t]);
+          umma_commit(&s_full[t][j & 1]);
+          return true;
+        };
+        if (nbt > 0) {
+          if (!mbar_wait(&q_full[t], qn & 1, &abort_flag, p.status, kTimeoutFull, 400 + t)) { ok = false; break; }
+          ++qn;
+          ok = issue_s(0);
+          if (ok && nbt > 1) ok = issue_s(1);
+        }
+        for (int j = 0; j < n1 && ok; ++j) {
+          const uint32_t c = kc + (uint32_t)j;
+          const int sv = c % KS;
+          if (j >= nbt) {
+            // a key block only the other tile reads: hand in this tile's share of its release, but only
+            // once the block has been loaded (an earlier arrival would count for the stage's previous block)
+            if (!mbar_wait(&k_full[sv], (c / KS) & 1, &abort_flag, p.status, kTimeoutFull, 800 + j)) { ok = false; break; }
+            mbar_arrive(&k_empty[sv]);
+            if (!mbar_wait(&v_full[sv], (c / KS) & 1, &abort_flag, p.status, kTimeoutFull, 900 + j)) { ok = false; break; }
+            mbar_arrive(&v_empty[sv]);
+            continue;
+          }
+          const int bf = j & 1;
+          if (!mbar_wait(&p_full[t][bf], pc[bf] & 1, &abort_flag, p.status, kTimeoutFlag, 500 + j)) { ok = false; break; }
+          ++pc[bf];
+          if (j == 0 && on > 0) {
+            if (!mbar_wait(&o_free[t], (on - 1) & 1, &abort_flag, p.status, kTimeoutTmemEmpty, 600 + t)) { ok = false; break; }
+          }
+          if (!mbar_wait(&v_full[sv], (c / KS) & 1, &abort_flag, p.status, kTimeoutFull, 100 + j)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t aV = smem_u32(sV + sv * kKVTile);
+          const uint32_t aP = tmem_base + (uint32_t)(t * 128 + bf * 64);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            // V tile as an MN-major B operand: 16 key rows per step, 64-wide panels 8 KiB apart
+            const uint64_t dv = make_smem_desc(aV + (uint32_t)k * 2048, kKVPanel, 1024);
+            umma_bf16_ts(tmem_base + kColO + t * D, aP + k * 8, dv, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&v_empty[sv]);
+          umma_commit(&o_done[t][bf]);   // P_t(j) V_j has landed in O_t
+          if (j + 1 == nbt) ++on;
+          if (j + 2 < nbt) ok = issue_s(j + 2);
+        }
+        kc += (uint32_t)n1;
+      }
+    }
+  } else if (warp >= 4) {
+    // ======================= softmax groups: one query row per thread =======================
+    const int t = (warp - 4) >> 2;
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const uint32_t colO = kColO + t * D;
+    const float c = p.scale * 1.4426950408889634f;
+    constexpr float kTau = 8.0f;
+    uint32_t sn[2] = {0, 0};   // score tiles consumed so far, per buffer
+    uint32_t pn[2] = {0, 0};   // P tiles produced so far, per buffer (= P V products expected)
+    bool ok = true;
+    const bool tracer = (p.trace != nullptr) && (lane == 0) && (quad == 0) && (t == 0);
+    for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+      int qp, h, b;
+      decode(w, qp, h, b);
+      const int nkv = blocks_of(qp, t);
+      if (nkv == 0) continue;
+      const int q0 = qp * 256 + t * 128;
+      const int q_idx = q0 + row;
+      const bool tr = tracer && (w == (int)blockIdx.x);
+      if (tr && t == 0) {
+        p.trace[(long long)blockIdx.x * kTraceSlots + 7] = nkv;
+        trace_stamp(p.trace, blockIdx.x, 0);
+      }
+      float m_used = -1.0e30f, l = 0.f;
+      for (int j = 0; j < nkv; ++j) {
+        const int bf = j & 1;
+        const uint32_t colS = (uint32_t)(t * 128 + bf * 64);
+        if (!mbar_wait_warp(&s_full[t][bf], sn[bf] & 1, &abort_flag, p.status, kTimeoutTmemFull, j)) { ok = false; break; }
+        ++sn[bf];
+        tc_fence_after();
+        if (tr && j < 6) trace_stamp(p.trace, blockIdx.x, 8 + 24 * t + 4 * j + 0);
+        const int kv0 = j * 64;
+        const bool need_mask = (p.causal && (kv0 + 63 > q0)) || (kv0 + 64 > p.T);
+        uint32_t s[64];
+        tmem_ld_32x32(t_lane + colS + 0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+        tmem_ld_32x32(t_lane + colS + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+        tmem_ld_wait();
+        if (tr && j < 6) trace_stamp(p.trace, blockIdx.x, 8 + 24 * t + 4 * j + 1);
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const int kv = kv0 + i;
+            if (kv >= p.T || (p.causal && kv > q_idx)) s[i] = 0xff800000u;  // -inf
+          }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 64; i += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(s[i + 0]));
+          mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
+        }
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        if (tr && j < 6) trace_stamp(p.trace, blockIdx.x, 8 + 24 * t + 4 * j + 2);
+        const bool grow = (mx - m_used) * c > kTau;  // false for fully masked rows (mx = -inf)
+        if (__any_sync(0xffffffffu, grow ? 1 : 0)) {
+          float alpha = 1.0f;
+          if (grow) {
+            alpha = exp2f((m_used - mx) * c);
+            l *= alpha;
+            m_used = mx;
+          }
+          if (j > 0) {
+            // O_t holds the blocks up to j - 1 once P_t(j-1) V has landed (its commit is the newest on
+            // the other buffer's barrier; never more than one completion away, so the parity is safe)
+            const int ob = bf ^ 1;
+            if (!mbar_wait_warp(&o_done[t][ob], (pn[ob] - 1) & 1, &abort_flag, p.status, kTimeoutTmemFull, 700 + j)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int cc = 0; cc < D / 32; ++cc) {
+              uint32_t r[32];
+              tmem_ld_32x32(t_lane + colO + cc * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st_32x32(t_lane + colO + cc * 32, r);
+            }
+          }
+        }
+        const float mc = m_used * c;
+        float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+        // 64 probabilities as bf16 pairs, packed in place: pair m lands in s[m], which the loop has
+        // already consumed (it reads s[2m ...], never behind its writes)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float e0 = exp2f(fmaf(__uint_as_float(s[2 * i + 0]), c, -mc));
+          const float e1 = exp2f(fmaf(__uint_as_float(s[2 * i + 1]), c, -mc));
+          const float e2 = exp2f(fmaf(__uint_as_float(s[2 * i + 2]), c, -mc));
+          const float e3 = exp2f(fmaf(__uint_as_float(s[2 * i + 3]), c, -mc));
+          sum0 += e0; sum1 += e1; sum2 += e2; sum3 += e3;
+          s[i + 0] = pack_bf16x2_halfup(e0, e1);
+          s[i + 1] = pack_bf16x2_halfup(e2, e3);
+        }
+        tmem_st_32x32(t_lane + colS, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+        l += (sum0 + sum1) + (sum2 + sum3);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[t][bf]);
+        ++pn[bf];
+        if (tr && j < 6) trace_stamp(p.trace, blockIdx.x, 8 + 24 * t + 4 * j + 3);
+      }
+      if (!ok) break;
+      if (tr) trace_stamp(p.trace, blockIdx.x, 2 + 2 * t);
+      // final: wait for the last P V of this tile, normalise and store
+      {
+        const int lb = (nkv - 1) & 1;
+        if (!mbar_wait_warp(&o_done[t][lb], (pn[lb] - 1) & 1, &abort_flag, p.status, kTimeoutTmemFull, 999)) { ok = false; break; }
+      }
+      tc_fence_after();
+      const float inv = (l > 0.f) ? 1.0f / l : 0.f;
+      __nv_bfloat16* dst = p.O + ((long long)b * p.T + q_idx) * p.ldo + p.o_col0 + h * D;
+#pragma unroll
+      for (int cc = 0; cc < D / 32; ++cc) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_lane + colO + cc * 32, r);
+        tmem_ld_wait();
+        if (cc == D / 32 - 1) {
+          // the accumulator is in registers: the next item may overwrite O_t
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&o_free[t]);
+        }
+        if (q_idx < p.T) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 q;
+            q.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]) * inv, __uint_as_float(r[8 * i + 1]) * inv);
+            q.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv);
+            q.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv);
+            q.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv);
+            reinterpret_cast<uint4*>(dst + cc * 32)[i] = q;
+          }
+        }
+      }
+      if (q_idx < p.T && p.lse != nullptr)
+        p.lse[((long long)b * p.Hq + h) * p.T + q_idx] = (l > 0.f) ? (m_used * p.scale + __logf(l)) : -INFINITY;
+      if (tr) trace_stamp(p.trace, blockIdx.x, 3 + 2 * t);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// =============================================================================================
 // Backward
 // =============================================================================================
 // delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; D/8 lanes per (row, head), 16 bytes per
@@ -1255,14 +1636,14 @@ static EncodeTiledFn attn_encode_fn() {
 
 // [B, T, cols] bf16 view with row stride ld: dims {cols, T, B}, box {64, 128, 1}.
 static int make_tmap_btc(CUtensorMap* out, const void* base, int B, int T, long long cols,
-                         long long ld) {
+                         long long ld, int box_rows = 128) {
   EncodeTiledFn fn = attn_encode_fn();
   if (fn == nullptr) return -1;
   ensure_context();
   if (ld % 8 || ((uintptr_t)base & 15)) return -2;
   cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)T, (cuuint64_t)B};
   cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)ld * 2 * (cuuint64_t)T};
-  cuuint32_t box[3] = {64, 128, 1};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -1311,12 +1692,44 @@ MMJ_API int mmj_attn_fwd(const void* q, long long ldq, int q_col0, const void* k
   p.O = (__nv_bfloat16*)O; p.ldo = ldo; p.o_col0 = o_col0;
   p.lse = lse;
   p.status = status;
-  // Default: the persistent kernel with two query tiles per CTA. MOMIJO_ATTN_FWD=1 selects the
-  // one-tile-per-CTA kernel (kept for comparison and for the in-kernel timeline).
+  // Default (3): persistent kernel, two query tiles per CTA, 64-key blocks with double-buffered score
+  // tiles. MOMIJO_ATTN_FWD=2 selects its 128-key single-buffered predecessor, =1 the one-tile-per-CTA
+  // kernel (both kept for comparison).
   static int fwd_mode = -1;
   if (fwd_mode < 0) {
     const char* e = getenv("MOMIJO_ATTN_FWD");
-    fwd_mode = e ? atoi(e) : 2;
+    fwd_mode = e ? atoi(e) : 3;
+  }
+  if (fwd_mode == 3) {
+    static bool b64 = false, b128 = false;
+    static int sms3 = 0;
+    if (sms3 == 0) {
+      int dev = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms3, cudaDevAttrMultiProcessorCount, dev);
+    }
+    CUtensorMap tk64, tv64;
+    if ((rc = make_tmap_btc(&tk64, k, B, T, ldk, ldk, 64))) return rc;
+    if ((rc = make_tmap_btc(&tv64, v, B, T, ldv, ldv, 64))) return rc;
+    const long long n_items = (long long)((T + 255) / 256) * Hq * B;
+    const unsigned g = (unsigned)(n_items < sms3 ? n_items : sms3);
+    p.trace = (g_attn_trace && (long long)g <= g_attn_trace_ctas) ? g_attn_trace : nullptr;
+    if (D == 64) {
+      const int smem = 2 * kPanelBytes + 2 * 6 * 8192 + 1024;
+      if (!b64) {
+        cudaFuncSetAttribute(attn_fwd3_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        b64 = true;
+      }
+      attn_fwd3_kernel<64><<<g, 384, smem, (cudaStream_t)stream>>>(tq, tk64, tv64, p);
+    } else {
+      const int smem = 2 * 2 * kPanelBytes + 2 * 4 * 16384 + 1024;
+      if (!b128) {
+        cudaFuncSetAttribute(attn_fwd3_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        b128 = true;
+      }
+      attn_fwd3_kernel<128><<<g, 384, smem, (cudaStream_t)stream>>>(tq, tk64, tv64, p);
+    }
+    return (int)cudaGetLastError();
   }
   if (fwd_mode == 2) {
     static bool a64 = false, a128 = false;
