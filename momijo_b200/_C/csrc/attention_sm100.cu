@@ -394,354 +394,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 }
 
 // =============================================================================================
-// Forward, two query tiles per CTA (the default forward kernel)
-// =============================================================================================
-// One persistent CTA per SM walks a list of work items, heaviest first; an item is 256 query rows
-// (two 128-row tiles) of one (batch, head). Three warpgroups: warps 0..3 = TMA producer (warp 0), MMA
-// issuer and TMEM owner (warp 1) and two idle warps; warps 4..7 = softmax group of tile 0; warps 8..11 =
-// softmax group of tile 1 (one query row per thread). The first warpgroup hands most of its registers
-// to the other two (setmaxnreg), which keep a whole 128-value score row per thread.
-//
-// Tensor memory: S0 | S1 | O0 | O1 (128 + 128 + D + D columns). A softmax group reads its score tile,
-// writes the probabilities back over the first 64 columns of the same tile as packed bf16 pairs, and
-// the P V product takes them from there as its tensor-memory A operand: P never touches shared
-// memory. The MMA thread issues, per key block j:  P0(j) V -> O0,  Q0 K(j+1)^T -> S0,  P1(j) V -> O1,
-// Q1 K(j+1)^T -> S1, so the two groups run half a block apart: one exponentiates while the tensor
-// core works for the other. MMAs complete in issue order, so a score tile that has arrived implies
-// that the previous P V of the same tile has landed (the lazy rescale of O relies on it).
-template <int D>
-__global__ void __launch_bounds__(384, 1)
-attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
-  constexpr int NP = D / 64;
-  constexpr int kTile = NP * kPanelBytes;
-  constexpr int KS = (D == 64) ? 3 : 2;  // K and V stages
-  constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kColS = 0, kColO = 256;
-
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  uint8_t* sQ = smem;                  // 2 tiles
-  uint8_t* sK = sQ + 2 * kTile;        // KS stages
-  uint8_t* sV = sK + KS * kTile;       // KS stages
-
-  __shared__ __align__(8) uint64_t q_full[2], q_empty[2], s_full[2], p_full[2], o_full[2], o_free[2];
-  __shared__ __align__(8) uint64_t k_full[KS], k_empty[KS], v_full[KS], v_empty[KS];
-  __shared__ uint32_t tmem_slot;
-  __shared__ int abort_flag;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nqp = (p.T + 255) / 256;  // query pairs per (batch, head)
-  const int nbh = p.B * p.Hq;
-  const int n_items = nqp * nbh;
-  const int group = p.Hq / p.Hkv;
-
-  if (threadIdx.x == 0) {
-    for (int t = 0; t < 2; ++t) {
-      mbar_init(&q_full[t], 1);
-      mbar_init(&q_empty[t], 1);
-      mbar_init(&s_full[t], 1);
-      mbar_init(&p_full[t], 4);
-      mbar_init(&o_full[t], 1);
-      mbar_init(&o_free[t], 4);
-    }
-    for (int s = 0; s < KS; ++s) {
-      mbar_init(&k_full[s], 1);
-      mbar_init(&k_empty[s], 1);
-      mbar_init(&v_full[s], 1);
-      mbar_init(&v_empty[s], 1);
-    }
-    abort_flag = 0;
-    mbar_fence_init();
-    prefetch_tmap(&tmQ);
-    prefetch_tmap(&tmK);
-    prefetch_tmap(&tmV);
-  }
-  if (warp == 1) {
-    tmem_alloc(&tmem_slot, kTmemCols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = tmem_slot;
-
-  // item w -> (query pair, head, batch); later (longer) query pairs first
-  auto decode = [&](int w, int& qp, int& h, int& b) {
-    qp = nqp - 1 - w / nbh;
-    const int bh = w % nbh;
-    h = bh % p.Hq;
-    b = bh / p.Hq;
-  };
-  // key blocks of tile t of query pair qp (0 when the tile lies beyond T)
-  auto blocks_of = [&](int qp, int t) -> int {
-    const int q0 = qp * 256 + t * 128;
-    if (q0 >= p.T) return 0;
-    const int kv_end = p.causal ? min(p.T, q0 + 128) : p.T;
-    return (kv_end + 127) / 128;
-  };
-
-  if (warp == 0) {
-    // ======================= TMA producer =======================
-    if (lane == 0) {
-      uint32_t qn[2] = {0, 0};  // fills of each Q tile so far
-      uint32_t kc = 0;          // K/V blocks loaded so far (ring position)
-      bool ok = true;
-      for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
-        int qp, h, b;
-        decode(w, qp, h, b);
-        const int hkv = h / group;
-        const int nb[2] = {blocks_of(qp, 0), blocks_of(qp, 1)};
-        const int n1 = max(nb[0], nb[1]);
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (nb[t] == 0) continue;
-          if (!mbar_wait(&q_empty[t], (qn[t] & 1) ^ 1, &abort_flag, p.status, kTimeoutEmpty, 300 + t)) { ok = false; break; }
-          ++qn[t];
-          mbar_expect_tx(&q_full[t], kTile);
-#pragma unroll
-          for (int pn = 0; pn < NP; ++pn)
-            tma_load_3d(sQ + t * kTile + pn * kPanelBytes, &tmQ, &q_full[t], p.q_col0 + h * D + pn * 64,
-                        qp * 256 + t * 128, b);
-        }
-        for (int j = 0; j < n1 && ok; ++j, ++kc) {
-          const int s = kc % KS;
-          const uint32_t ph = (kc / KS) & 1;
-          if (!mbar_wait(&k_empty[s], ph ^ 1, &abort_flag, p.status, kTimeoutEmpty, j)) { ok = false; break; }
-          mbar_expect_tx(&k_full[s], kTile);
-#pragma unroll
-          for (int pn = 0; pn < NP; ++pn)
-            tma_load_3d(sK + s * kTile + pn * kPanelBytes, &tmK, &k_full[s], p.k_col0 + hkv * D + pn * 64,
-                        j * 128, b);
-          if (!mbar_wait(&v_empty[s], ph ^ 1, &abort_flag, p.status, kTimeoutEmpty, 100 + j)) { ok = false; break; }
-          mbar_expect_tx(&v_full[s], kTile);
-#pragma unroll
-          for (int pn = 0; pn < NP; ++pn)
-            tma_load_3d(sV + s * kTile + pn * kPanelBytes, &tmV, &v_full[s], p.v_col0 + hkv * D + pn * 64,
-                        j * 128, b);
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // ======================= MMA issuer =======================
-    if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
-      const uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);
-      uint32_t qn[2] = {0, 0};   // uses of each Q tile so far
-      uint32_t pn_[2] = {0, 0};  // P tiles consumed so far, per tile
-      uint32_t on[2] = {0, 0};   // items in which tile t produced an output so far
-      uint32_t kc = 0;           // ring position of this item's block 0
-      bool ok = true;
-      for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
-        int qp, h, b;
-        decode(w, qp, h, b);
-        const int nb[2] = {blocks_of(qp, 0), blocks_of(qp, 1)};
-        const int n1 = max(nb[0], nb[1]);
-        // S_t(j) = Q_t K_j^T; K stage of block j is released after its last reader
-        auto issue_s = [&](int t, int j) -> bool {
-          const uint32_t c = kc + (uint32_t)j;
-          const int s = c % KS;
-          if (!mbar_wait(&k_full[s], (c / KS) & 1, &abort_flag, p.status, kTimeoutFull, j)) return false;
-          tc_fence_after();
-          const uint32_t aQ = smem_u32(sQ + t * kTile), aK = smem_u32(sK + s * kTile);
-#pragma unroll
-          for (int k = 0; k < D / 16; ++k)
-            umma_bf16_ss(tmem_base + kColS + t * 128, desc_kmajor(aQ, k), desc_kmajor(aK, k), idesc_s,
-                         k > 0 ? 1u : 0u);
-          // last reader of this K block: tile 1 when it takes part in block j, else tile 0
-          if (t == 1 || j >= nb[1]) umma_commit(&k_empty[s]);
-          if (j + 1 == nb[t]) umma_commit(&q_empty[t]);  // Q_t is not needed any more
-          umma_commit(&s_full[t]);
-          return true;
-        };
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (nb[t] == 0) continue;
-          if (!mbar_wait(&q_full[t], qn[t] & 1, &abort_flag, p.status, kTimeoutFull, 400 + t)) { ok = false; break; }
-          ++qn[t];
-          ok = issue_s(t, 0);
-        }
-        for (int j = 0; j < n1 && ok; ++j) {
-          const uint32_t c = kc + (uint32_t)j;
-          const int sv = c % KS;
-          for (int t = 0; t < 2 && ok; ++t) {
-            if (j >= nb[t]) continue;
-            if (!mbar_wait(&p_full[t], pn_[t] & 1, &abort_flag, p.status, kTimeoutFlag, 500 + j)) { ok = false; break; }
-            ++pn_[t];
-            if (j == 0 && on[t] > 0) {
-              // the previous item's output of this tile must have been read out of O_t
-              if (!mbar_wait(&o_free[t], (on[t] - 1) & 1, &abort_flag, p.status, kTimeoutTmemEmpty, 600 + t)) { ok = false; break; }
-            }
-            if (!mbar_wait(&v_full[sv], (c / KS) & 1, &abort_flag, p.status, kTimeoutFull, 100 + j)) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t aV = smem_u32(sV + sv * kTile);
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-              umma_bf16_ts(tmem_base + kColO + t * D, tmem_base + kColS + t * 128 + k * 8, desc_mnmajor(aV, k),
-                           idesc_o, (j > 0 || k > 0) ? 1u : 0u);
-            if (t == 1 || j >= nb[1]) umma_commit(&v_empty[sv]);
-            if (j + 1 == nb[t]) {
-              umma_commit(&o_full[t]);
-              ++on[t];
-            } else {
-              ok = issue_s(t, j + 1);
-            }
-          }
-        }
-        kc += (uint32_t)n1;
-      }
-    }
-  } else if (warp >= 4) {
-    // ======================= softmax groups: one query row per thread =======================
-    const int t = (warp - 4) >> 2;   // tile of this group
-    const int quad = warp & 3;       // TMEM lane quadrant this warp can reach
-    const int row = quad * 32 + lane;
-    const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
-    const uint32_t colS = kColS + t * 128, colO = kColO + t * D;
-    const float c = p.scale * 1.4426950408889634f;
-    constexpr float kTau = 8.0f;
-    uint32_t sn = 0, on = 0;
-    bool ok = true;
-    // timeline (optional): thread 0 of each softmax group stamps the first item of its CTA; slots
-    // 8 + 24 t + 4 j + {0: S arrived, 1: S in registers, 2: maximum known, 3: P stored}, j < 6
-    const bool tracer = (p.trace != nullptr) && (lane == 0) && (quad == 0);
-    for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
-      int qp, h, b;
-      decode(w, qp, h, b);
-      const int nkv = blocks_of(qp, t);
-      if (nkv == 0) continue;
-      const bool tr = tracer && (w == (int)blockIdx.x);
-      if (tr && t == 0) {
-        p.trace[(long long)blockIdx.x * kTraceSlots + 7] = nkv;
-        trace_stamp(p.trace, blockIdx.x, 0);
-      }
-      const int q0 = qp * 256 + t * 128;
-      const int q_idx = q0 + row;
-      float m_used = -1.0e30f, l = 0.f;
-      for (int j = 0; j < nkv; ++j, ++sn) {
-        if (!mbar_wait_warp(&s_full[t], sn & 1, &abort_flag, p.status, kTimeoutTmemFull, j)) { ok = false; break; }
-        tc_fence_after();
-        if (tr && j < 6) trace_stamp(p.trace, blockIdx.x, 8 + 24 * t + 4 * j + 0);
-        const int kv0 = j * 128;
-        const bool need_mask = (p.causal && (kv0 + 127 > q0)) || (kv0 + 128 > p.T);
-        uint32_t s[128];
-        tmem_ld_32x32(t_lane + colS + 0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-        tmem_ld_32x32(t_lane + colS + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-        tmem_ld_32x32(t_lane + colS + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
-        tmem_ld_32x32(t_lane + colS + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
-        tmem_ld_wait();
-        if (tr && j < 6) trace_stamp(p.trace, blockIdx.x, 8 + 24 * t + 4 * j + 1);
-        if (need_mask) {
-#pragma unroll
-          for (int i = 0; i < 128; ++i) {
-            const int kv = kv0 + i;
-            if (kv >= p.T || (p.causal && kv > q_idx)) s[i] = 0xff800000u;  // -inf
-          }
-        }
-        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < 128; i += 4) {
-          mx0 = fmaxf(mx0, __uint_as_float(s[i + 0]));
-          mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
-          mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
-        }
-        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-        if (tr && j < 6) trace_stamp(p.trace, blockIdx.x, 8 + 24 * t + 4 * j + 2);
-        const bool grow = (mx - m_used) * c > kTau;  // false for fully masked rows (mx = -inf)
-        if (__any_sync(0xffffffffu, grow ? 1 : 0)) {
-          float alpha = 1.0f;
-          if (grow) {
-            alpha = exp2f((m_used - mx) * c);
-            l *= alpha;
-            m_used = mx;
-          }
-          if (j > 0) {
-            // S_t(j) has arrived, so P_t(j-1) V(j-1), issued before it, has landed in O_t
-#pragma unroll
-            for (int cc = 0; cc < D / 32; ++cc) {
-              uint32_t r[32];
-              tmem_ld_32x32(t_lane + colO + cc * 32, r);
-              tmem_ld_wait();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-              tmem_st_32x32(t_lane + colO + cc * 32, r);
-            }
-          }
-        }
-        const float mc = m_used * c;
-        float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-#pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          // 64 probabilities as bf16 pairs, packed in place: pair m of this half lands in s[cc*32 + m],
-          // which the loop has already consumed (it reads s[cc*64 + 2m ...], never behind its writes)
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float e0 = exp2f(fmaf(__uint_as_float(s[cc * 64 + 2 * i + 0]), c, -mc));
-            const float e1 = exp2f(fmaf(__uint_as_float(s[cc * 64 + 2 * i + 1]), c, -mc));
-            const float e2 = exp2f(fmaf(__uint_as_float(s[cc * 64 + 2 * i + 2]), c, -mc));
-            const float e3 = exp2f(fmaf(__uint_as_float(s[cc * 64 + 2 * i + 3]), c, -mc));
-            sum0 += e0; sum1 += e1; sum2 += e2; sum3 += e3;
-            s[cc * 32 + i + 0] = pack_bf16x2(e0, e1);
-            s[cc * 32 + i + 1] = pack_bf16x2(e2, e3);
-          }
-          tmem_st_32x32(t_lane + colS + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[cc * 32]));
-        }
-        l += (sum0 + sum1) + (sum2 + sum3);
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&p_full[t]);
-        if (tr && j < 6) trace_stamp(p.trace, blockIdx.x, 8 + 24 * t + 4 * j + 3);
-      }
-      if (!ok) break;
-      if (tr) trace_stamp(p.trace, blockIdx.x, 2 + 2 * t);
-      // final: wait for the last P V of this tile, normalise and store
-      if (!mbar_wait_warp(&o_full[t], on & 1, &abort_flag, p.status, kTimeoutTmemFull, 999)) { ok = false; break; }
-      ++on;
-      tc_fence_after();
-      const float inv = (l > 0.f) ? 1.0f / l : 0.f;
-      __nv_bfloat16* dst = p.O + ((long long)b * p.T + q_idx) * p.ldo + p.o_col0 + h * D;
-#pragma unroll
-      for (int cc = 0; cc < D / 32; ++cc) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_lane + colO + cc * 32, r);
-        tmem_ld_wait();
-        if (cc == D / 32 - 1) {
-          // the accumulator is in registers: the next item may overwrite O_t
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&o_free[t]);
-        }
-        if (q_idx < p.T) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint4 q;
-            q.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]) * inv, __uint_as_float(r[8 * i + 1]) * inv);
-            q.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv);
-            q.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv);
-            q.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv);
-            reinterpret_cast<uint4*>(dst + cc * 32)[i] = q;
-          }
-        }
-      }
-      if (q_idx < p.T && p.lse != nullptr)
-        p.lse[((long long)b * p.Hq + h) * p.T + q_idx] = (l > 0.f) ? (m_used * p.scale + __logf(l)) : -INFINITY;
-      if (tr) trace_stamp(p.trace, blockIdx.x, 3 + 2 * t);
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    __syncwarp();
-    tmem_dealloc(tmem_base, kTmemCols);
-  }
-}
-
-// =============================================================================================
 // Forward, two query tiles per CTA, 64-key blocks, double-buffered score tiles (the default)
 // =============================================================================================
-// Same work split as attn_fwd2_kernel (persistent CTAs, items of 256 query rows, three warpgroups), with
-// two changes that take the tensor core out of the softmax groups' dependency chain:
+// One persistent CTA per SM walks a list of work items, heaviest first; an item is 256 query rows (two
+// 128-row tiles) of one (batch, head). Three warpgroups: warps 0..3 = TMA producer (warp 0), one MMA issuer
+// per query tile (warps 1 and 2; warp 1 owns the TMEM allocation) and an idle warp; warps 4..7 = softmax
+// group of tile 0; warps 8..11 = softmax group of tile 1 (one query row per thread). A softmax group reads
+// its score tile from tensor memory, writes the probabilities back over the first columns of the same tile
+// as packed bf16 pairs, and the P V product takes them from there as its tensor-memory A operand: P never
+// touches shared memory. Three things keep the tensor core out of the groups' dependency chain:
 //   * each query tile has its own MMA-issuing thread (warps 1 and 2);
 //   * a key block is 64 keys and every query tile owns TWO score buffers in tensor memory
 //     (S_t[0], S_t[1], 64 columns each): the MMA thread issues S_t(j+1) before the group has finished
@@ -1693,8 +1354,7 @@ MMJ_API int mmj_attn_fwd(const void* q, long long ldq, int q_col0, const void* k
   p.lse = lse;
   p.status = status;
   // Default (3): persistent kernel, two query tiles per CTA, 64-key blocks with double-buffered score
-  // tiles. MOMIJO_ATTN_FWD=2 selects its 128-key single-buffered predecessor, =1 the one-tile-per-CTA
-  // kernel (both kept for comparison).
+  // tiles. MOMIJO_ATTN_FWD=1 selects the older one-tile-per-CTA kernel (kept for comparison).
   static int fwd_mode = -1;
   if (fwd_mode < 0) {
     const char* e = getenv("MOMIJO_ATTN_FWD");
@@ -1728,34 +1388,6 @@ MMJ_API int mmj_attn_fwd(const void* q, long long ldq, int q_col0, const void* k
         b128 = true;
       }
       attn_fwd3_kernel<128><<<g, 384, smem, (cudaStream_t)stream>>>(tq, tk64, tv64, p);
-    }
-    return (int)cudaGetLastError();
-  }
-  if (fwd_mode == 2) {
-    static bool a64 = false, a128 = false;
-    static int sms = 0;
-    if (sms == 0) {
-      int dev = 0;
-      cudaGetDevice(&dev);
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    }
-    const long long n_items = (long long)((T + 255) / 256) * Hq * B;
-    const unsigned g = (unsigned)(n_items < sms ? n_items : sms);
-    p.trace = (g_attn_trace && (long long)g <= g_attn_trace_ctas) ? g_attn_trace : nullptr;
-    if (D == 64) {
-      const int smem = (2 + 3 + 3) * kPanelBytes + 1024;
-      if (!a64) {
-        cudaFuncSetAttribute(attn_fwd2_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        a64 = true;
-      }
-      attn_fwd2_kernel<64><<<g, 384, smem, (cudaStream_t)stream>>>(tq, tk, tv, p);
-    } else {
-      const int smem = (2 + 2 + 2) * 2 * kPanelBytes + 1024;
-      if (!a128) {
-        cudaFuncSetAttribute(attn_fwd2_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        a128 = true;
-      }
-      attn_fwd2_kernel<128><<<g, 384, smem, (cudaStream_t)stream>>>(tq, tk, tv, p);
     }
     return (int)cudaGetLastError();
   }
