@@ -113,7 +113,8 @@ _SIGS = {
     "mmj_moe_zero_pad": ([P, I, P, I, I, P], 1),
     "mmj_moe_gate_grad": ([P, P, P, P, P, I, I, I, I, I, P], 1),
     "mmj_moe_dispatch": ([P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P, P], 1),
-    "mmj_moe_combine": ([P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P], 1),
+    "mmj_moe_combine": ([P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P], 1),
+    "mmj_set_signal_slots": ([I], 0),
 }
 
 _OPTIONAL = {}
@@ -210,7 +211,9 @@ def call(name: str, *args):
     return rc
 
 
-BOUNDS_SITES = {1: "embedding forward: token id", 2: "embedding backward: token id", 3: "cross-entropy: target id"}
+BOUNDS_SITES = {1: "embedding forward: token id", 2: "embedding backward: token id", 3: "cross-entropy: target id",
+                10: "MoE count: expert index", 11: "MoE dispatch: expert index", 12: "MoE combine: expert index",
+                13: "MoE combine: source row"}
 
 
 def debug_bounds():
@@ -220,7 +223,8 @@ def debug_bounds():
 
     torch.cuda.synchronize()
     out = []
-    for unit, fn in (("elementwise", "mmj_debug_bounds_elementwise"), ("loss", "mmj_debug_bounds_loss")):
+    for unit, fn in (("elementwise", "mmj_debug_bounds_elementwise"), ("loss", "mmj_debug_bounds_loss"),
+                     ("comm", "mmj_debug_bounds_comm")):
         buf = (ctypes.c_longlong * 6)()
         f = getattr(lib(), fn)
         f.argtypes = [ctypes.POINTER(ctypes.c_longlong)]

@@ -490,6 +490,10 @@ __global__ void __launch_bounds__(1024) moe_count_kernel(const MoeCountParams p)
   __syncthreads();
   for (int i = threadIdx.x; i < p.n_assign; i += blockDim.x) {
     const int e = p.expert_idx[i];
+    if (!index_ok(e, p.n_experts, /*site=*/10)) {   // a router index outside [0, E): counted nowhere
+      p.local_pos[i] = 0;
+      continue;
+    }
     p.local_pos[i] = atomicAdd(&hist[e], 1);
   }
   __syncthreads();
@@ -600,9 +604,13 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const MoeDispatchPara
   for (int a = blockIdx.x * warps_per_block + (threadIdx.x >> 5); a < p.n_assign;
        a += gridDim.x * warps_per_block) {
     const int e = p.expert_idx[a];
+    if (!index_ok(e, p.n_experts, /*site=*/11)) {
+      if (lane == 0) p.src_row_of[a] = -1;
+      continue;
+    }
     const int d = e / epr, le = e - d * epr;
     const int row = p.seg_off[(d * epr + le) * W + p.t.rank] + p.local_pos[a];
-    if (row >= p.cap_rows) {  // over capacity: the assignment is dropped (contributes nothing)
+    if (row >= p.cap_rows || row < 0) {  // over capacity: the assignment is dropped (contributes nothing)
       if (lane == 0) p.src_row_of[a] = -1;
       continue;
     }
@@ -634,6 +642,7 @@ struct MoeCombineParams {
   __nv_bfloat16* out;   // [n_tokens, H]
   const __nv_bfloat16* residual;  // optional [n_tokens, H] (shared-expert output etc.)
   int n_tokens, top_k, H, n_experts;
+  int cap_rows;          // rows of every rank's expert-output buffer (bound of src_row_of)
   int slot_base, epoch;  // entry barrier: all ranks' expert outputs are complete
   int* status;
 };
@@ -653,8 +662,10 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombineParams
         bf16x8_to_f32(*reinterpret_cast<const uint4*>(p.residual + (long long)tk * p.H + c * 8), acc);
       for (int k = 0; k < p.top_k; ++k) {
         const int a = tk * p.top_k + k;
+        if (!index_ok(p.expert_idx[a], p.n_experts, /*site=*/12)) continue;
         const int d = p.expert_idx[a] / epr;
         if (p.src_row_of[a] < 0) continue;  // dropped at capacity
+        if (!index_ok(p.src_row_of[a], p.cap_rows, /*site=*/13)) continue;
         const float w = (p.gate_w != nullptr) ? p.gate_w[a] : 1.0f;
         float f[8];
         bf16x8_to_f32(*reinterpret_cast<const uint4*>(p.y[d] + (long long)p.src_row_of[a] * p.H + c * 8), f);
@@ -681,14 +692,31 @@ static int resident_grid(int per_sm) {
   return sms * per_sm;
 }
 
+// Signal pads have a fixed number of int32 slots (set once by the communicator). Every launcher checks the
+// slot range a kernel is about to use on the host, before the launch: a range past the pad would make a
+// peer store land in whatever follows the pad in the peer's heap.
+static int g_signal_slots = 0;
+static inline bool slots_ok(int slot_base, int count) {
+  if (slot_base < 0 || count < 0) return false;
+  return g_signal_slots == 0 || slot_base + count <= g_signal_slots;
+}
+
 }  // namespace mmj
 
 using namespace mmj;
 #define STREAM ((cudaStream_t)stream)
 
+MMJ_API int mmj_set_signal_slots(int n) {
+  g_signal_slots = n > 0 ? n : 0;
+  return 0;
+}
+
+MMJ_BOUNDS_READER(mmj_debug_bounds_comm)
+
 MMJ_API int mmj_barrier(void* const* sig, int world, int rank, int slot_base, int epoch,
                         int* status, void* stream) {
   if (world < 1 || world > kMaxWorld) return -1;
+  if (!slots_ok(slot_base, world)) return -9;
   barrier_kernel<<<1, 32, 0, STREAM>>>(make_table(world, rank, sig), slot_base, epoch, status);
   return (int)cudaGetLastError();
 }
@@ -711,6 +739,7 @@ MMJ_API int mmj_rs_adamw(void* const* sig, void* const* grads, const void* grad_
                          int epoch, unsigned int* block_counter, float* sqnorm_out, int* status,
                          void* stream) {
   if (world < 1 || world > kMaxWorld) return -1;
+  if (!slots_ok(slot_base, 2 * world)) return -9;
   if (shard_elems % 8 || shard_off % 8) return -2;
   RsAdamwParams p;
   p.t = make_table(world, rank, sig);
@@ -743,6 +772,7 @@ MMJ_API int mmj_gather_bucket(void* const* sig, void* const* srcs, void* dst, lo
                               int copy_self, int max_blocks, int world, int rank, int slot_base,
                               int epoch, int* status, void* stream) {
   if (world < 1 || world > kMaxWorld) return -1;
+  if (epoch >= 0 && !slots_ok(slot_base, world)) return -9;
   if ((shard_bytes & 15) || (src_stride & 15) || n_skip < 0 || n_skip > 4) return -2;
   GatherBucketParams p;
   p.t = make_table(world, rank, sig);
@@ -771,6 +801,7 @@ MMJ_API int mmj_allreduce_small_f32(void* const* sig, void* const* stage, const 
                                     int n, int world, int rank, int slot_base, int epoch, int* status,
                                     void* stream) {
   if (world < 1 || world > kMaxWorld) return -1;
+  if (!slots_ok(slot_base, world)) return -9;
   if (n < 1 || n > 64) return -2;
   SmallAllReduceParams p;
   p.t = make_table(world, rank, sig);
@@ -786,6 +817,7 @@ MMJ_API int mmj_allgather_ranges(void* const* sig, void* const* bufs, long long 
                                  const long long* ranges_dev, int n_ranges, int world, int rank,
                                  int slot_base, int epoch, int* status, void* stream) {
   if (world < 1 || world > kMaxWorld) return -1;
+  if (epoch >= 0 && !slots_ok(slot_base, world)) return -9;
   AllGatherParams p;
   p.t = make_table(world, rank, sig);
   for (int r = 0; r < kMaxWorld; ++r) p.src[r] = (r < world) ? (const uint8_t*)bufs[r] : nullptr;
@@ -804,6 +836,7 @@ MMJ_API int mmj_allreduce_bf16(void* const* sig, void* const* bufs, const void* 
                                unsigned int* block_counters, int* grid_flag, int* status,
                                void* stream) {
   if (world < 1 || world > kMaxWorld) return -1;
+  if (!slots_ok(slot_base, 3 * world)) return -9;
   if (n % (8 * world)) return -2;
   AllReduceParams p;
   p.t = make_table(world, rank, sig);
@@ -828,6 +861,7 @@ MMJ_API int mmj_reduce_slots_bf16(void* const* sig, const void* stage, long long
                                   void* out, const void* residual, long long n, int world, int rank,
                                   int slot_base, int epoch, int* status, void* stream) {
   if (world < 1 || world > kMaxWorld) return -1;
+  if (!slots_ok(slot_base, world)) return -9;
   if (n % 8 || slot_stride % 8) return -2;
   long long want = (n / 8 + 255) / 256;
   int grid = resident_grid(4);
@@ -843,6 +877,7 @@ MMJ_API int mmj_moe_count(void* const* sig, const int* expert_idx, int n_assign,
                           void* const* counts, int* local_pos, int world, int rank, int slot_base,
                           int epoch, int* status, void* stream) {
   if (world < 1 || world > kMaxWorld) return -1;
+  if (!slots_ok(slot_base, world)) return -9;
   MoeCountParams p;
   p.t = make_table(world, rank, sig);
   p.expert_idx = expert_idx;
@@ -892,6 +927,7 @@ MMJ_API int mmj_moe_dispatch(void* const* sig, const void* x, const int* expert_
                              int world, int rank, int slot_base, int epoch,
                              unsigned int* block_counter, int* status, void* stream) {
   if (world < 1 || world > kMaxWorld) return -1;
+  if (!slots_ok(slot_base, world)) return -9;
   if (H % 8) return -2;
   MoeDispatchParams p;
   p.t = make_table(world, rank, sig);
@@ -914,10 +950,11 @@ MMJ_API int mmj_moe_dispatch(void* const* sig, const void* x, const int* expert_
 MMJ_API int mmj_moe_combine(void* const* sig, void* const* y, const int* expert_idx,
                             const int* src_row_of, const float* gate_w, void* out,
                             const void* residual, int n_tokens, int top_k, int H, int n_experts,
-                            int world, int rank, int slot_base, int epoch, int* status,
+                            int cap_rows, int world, int rank, int slot_base, int epoch, int* status,
                             void* stream) {
   if (world < 1 || world > kMaxWorld) return -1;
   if (H % 8) return -2;
+  if (epoch >= 0 && !slots_ok(slot_base, world)) return -9;
   MoeCombineParams p;
   p.t = make_table(world, rank, sig);
   for (int r = 0; r < kMaxWorld; ++r) p.y[r] = (r < world) ? (const __nv_bfloat16*)y[r] : nullptr;
@@ -925,6 +962,7 @@ MMJ_API int mmj_moe_combine(void* const* sig, void* const* y, const int* expert_
   p.out = (__nv_bfloat16*)out;
   p.residual = (const __nv_bfloat16*)residual;
   p.n_tokens = n_tokens; p.top_k = top_k; p.H = H; p.n_experts = n_experts;
+  p.cap_rows = cap_rows;
   p.slot_base = slot_base; p.epoch = epoch;
   p.status = status;
   int grid = resident_grid(4);

@@ -963,8 +963,38 @@ void ensure_context() {
 }
 
 // 2-D bf16 tensor map: `inner` contiguous elements, `outer` rows `row_stride_elems` apart.
+// A descriptor is a pure function of (address, extents, stride, box), and a training step asks for the
+// same few hundred of them every iteration, so encoded maps are kept in a small per-thread
+// direct-mapped cache instead of calling into the driver twice per GEMM launch.
+struct TmapKey {
+  const void* base;
+  uint64_t inner, outer, stride;
+  uint32_t box_inner, box_outer;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && inner == o.inner && outer == o.outer && stride == o.stride &&
+           box_inner == o.box_inner && box_outer == o.box_outer;
+  }
+};
+struct TmapSlot {
+  TmapKey key;
+  CUtensorMap map;
+  bool used;
+};
+constexpr int kTmapCacheSlots = 1024;
+
 int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
                       uint64_t row_stride_elems, uint32_t box_inner, uint32_t box_outer) {
+  static thread_local TmapSlot* cache = nullptr;
+  if (cache == nullptr) cache = new TmapSlot[kTmapCacheSlots]();
+  const TmapKey key{base, inner, outer, row_stride_elems, box_inner, box_outer};
+  uint64_t h = (uint64_t)(uintptr_t)base * 0x9E3779B97F4A7C15ull;
+  h ^= (inner * 0xC2B2AE3D27D4EB4Full) ^ (outer * 0x165667B19E3779F9ull) ^ (row_stride_elems << 17) ^
+       ((uint64_t)box_inner << 40) ^ ((uint64_t)box_outer << 48);
+  TmapSlot& slot = cache[(h >> 20) & (kTmapCacheSlots - 1)];
+  if (slot.used && slot.key == key) {
+    *out = slot.map;
+    return 0;
+  }
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return -1;
   ensure_context();
@@ -975,7 +1005,11 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return (r == CUDA_SUCCESS) ? 0 : (int)r;
+  if (r != CUDA_SUCCESS) return (int)r;
+  slot.key = key;
+  slot.map = *out;
+  slot.used = true;
+  return 0;
 }
 
 static int g_sm_count = 0;

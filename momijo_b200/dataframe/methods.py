@@ -614,7 +614,10 @@ def _df_assign(self, mapping) -> DataFrame:
     out = self.copy()
     for name in sorted(mapping):
         v = mapping[name]
-        _df_put_column(out, Column(name, list(v(out) if callable(v) else v)))
+        v = v(out) if callable(v) else v
+        if isinstance(v, (str, bytes, int, float, bool)) or v is None:
+            v = [v] * out.nrows()      # a scalar (strings included) fills the whole column
+        _df_put_column(out, Column(name, list(v)))
     return out
 
 

@@ -119,6 +119,8 @@ def set_null(df, row, col):
 def assign(df, newcols: Dict[str, Iterable]):
     d = df.copy()
     for k, v in newcols.items():
+        if isinstance(v, (str, bytes, int, float, bool)) or v is None:
+            v = [v] * df.nrows()       # a scalar (strings included) fills the whole column
         d[k] = list(v)
     return d
 
@@ -466,6 +468,22 @@ class Agg:
 
     def __init__(self, col: str, fn: str, out: Optional[str] = None):
         self.col, self.fn, self.out = col, fn, out or f"{col}_{fn}"
+
+    # the spellings of ``AggSpec`` (relational.py), so that either record works with either group-by
+    @property
+    def column(self) -> str:
+        return self.col
+
+    @property
+    def op(self) -> str:
+        return self.fn
+
+    @property
+    def alias(self) -> str:
+        return self.out
+
+    def out_name(self) -> str:
+        return self.out
 
 
 def _groups(df, by):

@@ -129,7 +129,7 @@ class MoEDispatcher:
         gw = None if gate_w is None else gate_w.reshape(-1).float().contiguous()
         ep = c.next_epoch(self.slots + 2 * c.world)
         _C.call("mmj_moe_combine", c._sig_ptrs, self.ptrs_of(y), _C.ptr(r.idx), _C.ptr(r.src_row), _C.ptr(gw),
-                _C.ptr(out), _C.ptr(residual), r.n_tokens, self.k, self.H, self.E, c.world, c.rank,
+                _C.ptr(out), _C.ptr(residual), r.n_tokens, self.k, self.H, self.E, self.cap_rows, c.world, c.rank,
                 self.slots + 2 * c.world, ep, _C.ptr(c.status), _C.current_stream())
         return out
 

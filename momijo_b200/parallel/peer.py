@@ -60,6 +60,7 @@ class PeerComm:
         torch.cuda.synchronize()
         dist.barrier(self.group)
         self.sig = self.alloc(self.SLOTS, torch.int32)
+        _C.call("mmj_set_signal_slots", self.SLOTS)   # launchers check their slot ranges against it
         self._sig_ptrs = self.peer_ptrs(self.sig)
         self._next_slot = 0
         self._epochs = {}

@@ -165,6 +165,14 @@ class Tensor(torch.Tensor):
             idx = idx.to_index()
         elif isinstance(idx, tuple):
             idx = tuple(j for i in idx for j in (i.to_index() if isinstance(i, S) else (i,)))
+        src, idx2, flips = _resolve_negative_steps(self, idx, want_flips=True)
+        if flips:
+            # negative-step selector: assign into the flipped copy (where the slice runs forwards) and
+            # write the result back (the reference normalises such slices itself, tensor.mojo:676-718)
+            torch.Tensor.__setitem__(src, idx2, value)
+            with torch.no_grad():
+                self.as_subclass(torch.Tensor).copy_(torch.flip(src.as_subclass(torch.Tensor), flips))
+            return None
         return super().__setitem__(idx, value)
 
     # ---- promotion rules ------------------------------------------------------------------------
@@ -505,12 +513,12 @@ def _all_py_float32(data) -> bool:
     return False
 
 
-def _resolve_negative_steps(t, idx):
+def _resolve_negative_steps(t, idx, want_flips=False):
     """torch has no negative-step slices: flip the affected axes and rewrite the slice so that the
     result equals NumPy's (the reference normalises such slices itself, tensor.mojo:676-718)."""
     keys = idx if isinstance(idx, tuple) else (idx,)
     if not any(isinstance(k, slice) and k.step is not None and k.step < 0 for k in keys):
-        return t, idx
+        return (t, idx, []) if want_flips else (t, idx)
     n_real = sum(1 for k in keys if k is not None and k is not Ellipsis)
     out, dim, flips = [], 0, []
     for k in keys:
@@ -530,7 +538,8 @@ def _resolve_negative_steps(t, idx):
             out.append(k)
         dim += 1
     src = torch.flip(t.as_subclass(torch.Tensor), flips).as_subclass(type(t))
-    return src, (tuple(out) if isinstance(idx, tuple) else out[0])
+    new_idx = tuple(out) if isinstance(idx, tuple) else out[0]
+    return (src, new_idx, flips) if want_flips else (src, new_idx)
 
 
 def as_tensor(x) -> Tensor:
