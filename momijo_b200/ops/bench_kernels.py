@@ -87,6 +87,54 @@ def bench_attn(small):
     return rows
 
 
+def bench_attn_kernel(small):
+    """Kernel-level timing of the attention forward: back-to-back launches over rotating inputs that together
+    exceed L2, CUDA events around the whole batch (no per-call host overhead in the number)."""
+    import math
+
+    from .. import _C
+
+    rows = []
+    cfgs = [(2, 1024, 12, 12, 64)] if small else [(16, 1024, 12, 12, 64), (2, 4096, 32, 8, 128),
+                                                    (8, 4096, 16, 16, 128), (4, 4096, 16, 16, 64)]
+    n = 24
+    for B, T, Hq, Hkv, D in cfgs:
+        cols = (Hq + 2 * Hkv) * D
+        nb = max(3, int(300e6 // (B * T * cols * 2)) + 1)
+        qs = [torch.randn(B * T, cols, device="cuda").to(bf16) for _ in range(nb)]
+        out = torch.empty(B * T, Hq * D, dtype=bf16, device="cuda")
+        lse = torch.empty(B, Hq, T, dtype=torch.float32, device="cuda")
+        st = _C.status_tensor("cuda")
+
+        def fwd(q):
+            _C.call("mmj_attn_fwd", _C.ptr(q), cols, 0, _C.ptr(q), cols, Hq * D, _C.ptr(q), cols, (Hq + Hkv) * D,
+                    _C.ptr(out), Hq * D, 0, _C.ptr(lse), B, T, Hq, Hkv, D, 1.0 / math.sqrt(D), 1, _C.ptr(st),
+                    _C.current_stream())
+
+        q4 = [torch.randn(B, Hq, T, D, device="cuda", dtype=bf16) for _ in range(nb)]
+        k4 = [torch.randn(B, Hkv, T, D, device="cuda", dtype=bf16) for _ in range(nb)]
+        v4 = [torch.randn(B, Hkv, T, D, device="cuda", dtype=bf16) for _ in range(nb)]
+        sd = lambda i: torch.nn.functional.scaled_dot_product_attention(q4[i], k4[i], v4[i], is_causal=True,
+                                                                        enable_gqa=Hq != Hkv)
+        res = []
+        for f in (lambda i: fwd(qs[i]), sd):
+            for i in range(4):
+                f(i % nb)
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for i in range(n):
+                f(i % nb)
+            b.record()
+            torch.cuda.synchronize()
+            res.append(a.elapsed_time(b) / n)
+        _C.check_status()
+        fl = 4.0 * B * Hq * T * T * D / 2
+        rows.append({"op": "attn_fwd_kernel", "B": B, "T": T, "Hq": Hq, "Hkv": Hkv, "D": D, "fwd_ms": res[0],
+                     "fwd_tflops": fl / res[0] / 1e9, "sdpa_fwd_ms": res[1], "speed_vs_sdpa": res[1] / res[0]})
+    return rows
+
+
 def bench_norm(small):
     _, bw_peak, tag = peaks()
     rows = []
@@ -142,7 +190,7 @@ def main():
     ap.add_argument("--op", default="all")
     ap.add_argument("--small", action="store_true")
     a = ap.parse_args()
-    table = {"gemm": bench_gemm, "attn": bench_attn, "norm": bench_norm, "ce": bench_ce,
+    table = {"gemm": bench_gemm, "attn": bench_attn, "attn_kernel": bench_attn_kernel, "norm": bench_norm, "ce": bench_ce,
              "adamw": bench_adamw}
     for name, fn in table.items():
         if a.op in ("all", name):
