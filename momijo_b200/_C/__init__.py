@@ -29,9 +29,9 @@ _SIGS = {
     "mmj_gemm_bf16_allgather": ([P, P, I, P, L, L, I, P, L, I, I, I, I, P, P, L, P, L, I, I, I, L,
                                  L, P, P, I, I, P, P], 1),
     "mmj_gemm_bf16_reduce_scatter": ([P, L, P, L, I, P, L, L, I, I, I, I, I, I, P, P], 1),
-    "mmj_norm_fwd": ([P, P, P, P, P, P, P, P, I, I, F, I, P], 1),
+    "mmj_norm_fwd": ([P, P, P, P, P, P, P, P, I, I, F, I, P, P], 1),
     "mmj_norm_bwd_parts": ([I], 0),
-    "mmj_norm_bwd": ([P, P, P, P, P, P, P, P, P, P, I, I, I, I, P], 2),
+    "mmj_norm_bwd": ([P, P, P, P, P, P, P, P, P, P, I, I, I, I, P, P], 2),
     "mmj_act_fwd": ([P, P, L, I, F, P], 1),
     "mmj_act_bwd": ([P, P, P, L, I, F, P], 1),
     "mmj_swiglu_fwd": ([P, P, L, I, P], 1),

@@ -136,21 +136,36 @@ def bench_attn_kernel(small):
 
 
 def bench_norm(small):
+    """LayerNorm forward and backward launchers timed directly (no autograd, no allocation in the timed call).
+    ``MOMIJO_NORM_STREAM=0`` selects the row-per-CTA kernels."""
+    from .. import _C
+
     _, bw_peak, tag = peaks()
     rows = []
-    for R, C in ([(16384, 768)] if small else [(16384, 768), (32768, 4096), (262144, 768)]):
-        x = torch.randn(R, C, device="cuda").to(bf16).requires_grad_(True)
-        g = torch.ones(C, device="cuda", dtype=bf16, requires_grad=True)
-        b = torch.zeros(C, device="cuda", dtype=bf16, requires_grad=True)
-        f = lambda: ops.layer_norm(x, g, b)
+    for R, C in ([(131072, 768)] if small else [(16384, 768), (32768, 4096), (262144, 768)]):
+        x = torch.randn(R, C, device="cuda").to(bf16)
+        g = torch.ones(C, device="cuda", dtype=bf16)
+        b = torch.zeros(C, device="cuda", dtype=bf16)
+        y, dy, dx = torch.empty_like(x), torch.randn_like(x), torch.empty_like(x)
+        mean = torch.empty(R, device="cuda")
+        rstd = torch.empty(R, device="cuda")
+        dg, db = torch.empty_like(g), torch.empty_like(b)
+        nparts = _C.lib().mmj_norm_bwd_parts(R)
+        scratch = torch.empty(2 * nparts * C, device="cuda")
+        st = _C.ptr(_C.status_tensor(x.device))
+        f = lambda: _C.call("mmj_norm_fwd", _C.ptr(x), None, None, _C.ptr(g), _C.ptr(b), _C.ptr(y), _C.ptr(mean),
+                            _C.ptr(rstd), R, C, 1e-5, 0, st, _C.current_stream())
+        bk = lambda: _C.call("mmj_norm_bwd", _C.ptr(dy), _C.ptr(x), _C.ptr(g), _C.ptr(mean), _C.ptr(rstd), None,
+                             _C.ptr(dx), _C.ptr(dg), _C.ptr(db), _C.ptr(scratch), R, C, 0, 0, st,
+                             _C.current_stream())
         med, _ = cuda_time_ms(f)
-        y = f()
-        dy = torch.randn_like(y)
-        bmed, _ = cuda_time_ms(lambda: y.backward(dy, retain_graph=True))
+        bmed, _ = cuda_time_ms(bk)
+        _C.check_status()
         by = 2.0 * R * C * 2
         rows.append({"op": "layernorm", "rows": R, "C": C, "fwd_ms": med, "fwd_GBs": by / med / 1e6,
                      f"fwd_frac_of_{tag}_bw": by / (med * 1e-3) / bw_peak, "bwd_ms": bmed,
-                     "bwd_GBs": 1.5 * by / bmed / 1e6})
+                     "bwd_GBs": 1.5 * by / bmed / 1e6,
+                     f"bwd_frac_of_{tag}_bw": 1.5 * by / (bmed * 1e-3) / bw_peak})
     return rows
 
 

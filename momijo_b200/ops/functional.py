@@ -240,7 +240,7 @@ class _Norm(torch.autograd.Function):
         res_out = torch.empty_like(x2) if residual is not None else None
         _C.call("mmj_norm_fwd", _C.ptr(x2), _C.ptr(res2), _C.ptr(res_out), _C.ptr(gamma),
                 _C.ptr(beta), _C.ptr(y), _C.ptr(mean), _C.ptr(rstd), rows, C, eps, mode,
-                _C.current_stream())
+                _C.ptr(_C.status_tensor(x.device)), _C.current_stream())
         xin = res_out if residual is not None else x2
         ctx.save_for_backward(xin, gamma, mean if mean is not None else rstd, rstd)
         ctx.refs = (gamma, beta)
@@ -281,7 +281,7 @@ class _Norm(torch.autograd.Function):
         _C.call("mmj_norm_bwd", _C.ptr(dy2), _C.ptr(xin), _C.ptr(gamma),
                 _C.ptr(mean) if ctx.mode == 0 else None, _C.ptr(rstd), _C.ptr(dres2), _C.ptr(dx),
                 _C.ptr(dg), _C.ptr(db), _C.ptr(scratch), rows, C, ctx.mode, int(acc),
-                _C.current_stream())
+                _C.ptr(_C.status_tensor(xin.device)), _C.current_stream())
         if direct:
             dg_ret, db_ret = None, None
         else:
@@ -311,7 +311,7 @@ def _norm_ref(x, gamma, beta, residual, eps, mode):
 
 def layer_norm(x, gamma, beta, eps=1e-5, residual=None):
     """LayerNorm over the last dim. With ``residual`` returns (norm(x + residual), x + residual)."""
-    if x.dtype != bf16 or not x.is_cuda or x.shape[-1] % 8:
+    if x.dtype != bf16 or not x.is_cuda or x.shape[-1] % 8 or x.shape[-1] > 8192:
         y, r = _norm_ref(x, gamma, beta, residual, eps, 0)
     else:
         y, r = _Norm.apply(x.contiguous(), gamma, beta,
@@ -320,7 +320,7 @@ def layer_norm(x, gamma, beta, eps=1e-5, residual=None):
 
 
 def rms_norm(x, gamma, eps=1e-5, residual=None):
-    if x.dtype != bf16 or not x.is_cuda or x.shape[-1] % 8:
+    if x.dtype != bf16 or not x.is_cuda or x.shape[-1] % 8 or x.shape[-1] > 8192:
         y, r = _norm_ref(x, gamma, None, residual, eps, 1)
     else:
         y, r = _Norm.apply(x.contiguous(), gamma, None,

@@ -26,12 +26,13 @@ def _close(out, ref, tol=2e-2, fro=1e-2):
     assert ferr < fro, f"relative Frobenius error {ferr}"
 
 
-@pytest.mark.parametrize("C", [768, 2048, 4096, 5120, 136])
+@pytest.mark.parametrize("C", [768, 1600, 2048, 4096, 5120, 8192, 136])
 @pytest.mark.parametrize("mode", ["ln", "rms"])
 @pytest.mark.parametrize("fused_res", [False, True])
-def test_norm(C, mode, fused_res):
+@pytest.mark.parametrize("rows", [300, 20011])
+def test_norm(C, mode, fused_res, rows):
+    # 20011 rows: more tiles per CTA than the shared-memory ring has stages, and a ragged last tile
     torch.manual_seed(0)
-    rows = 300
     x, g, b = _rand(rows, C, grad=True), _rand(C, grad=True), _rand(C, grad=True)
     res = _rand(rows, C, grad=True) if fused_res else None
     if mode == "ln":
