@@ -346,6 +346,21 @@ __device__ __forceinline__ float2 group_sum2(float a, float b, float2* red, int 
   return make_float2(x, y);
 }
 
+template <int G>
+__device__ __forceinline__ float group_sum1(float a, float2* red, int warp, int& flip) {
+  a = warp_sum(a);
+  if (G == 1) return a;
+  float2* r = red + flip * kNormWarps;
+  flip ^= 1;
+  if ((threadIdx.x & 31) == 0) r[warp].x = a;
+  __syncthreads();
+  const int g0 = (warp / G) * G;
+  float x = 0.f;
+#pragma unroll
+  for (int i = 0; i < G; ++i) x += r[g0 + i].x;
+  return x;
+}
+
 // The copies of this CTA's `k`-th tile (global tile k * gridDim.x + blockIdx.x) into its stage.
 struct NormFetch {
   const __nv_bfloat16* src[3];
@@ -360,8 +375,10 @@ struct NormFetch {
     const uint32_t bytes = (uint32_t)nr * C * 2;
     uint8_t* dst = smem + (size_t)s * ntens * ring.tensor_bytes;
     mbar_expect_tx(&full[s], bytes * ntens);
-    for (int t = 0; t < ntens; ++t)
-      bulk_load_1d(dst + (size_t)t * ring.tensor_bytes, src[t] + (size_t)r0 * C, bytes, &full[s]);
+#pragma unroll
+    for (int t = 0; t < 3; ++t)  // constant indices keep `src` in registers
+      if (t < ntens)
+        bulk_load_1d(dst + (size_t)t * ring.tensor_bytes, src[t] + (size_t)r0 * C, bytes, &full[s]);
   }
 };
 
@@ -477,8 +494,7 @@ norm_fwd_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
           d2 += p;
         }
       }
-      float2 t2 = group_sum2<G>(d2, 0.f, red, warp, flip);
-      rstd = rsqrtf(t2.x * invC + eps);
+      rstd = rsqrtf(group_sum1<G>(d2, red, warp, flip) * invC + eps);
     } else {
       rstd = rsqrtf(t.y * invC + eps);
     }
