@@ -186,6 +186,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  pdl_wait();  // the set-up above read no tensor of the step
+  pdl_trigger();
   if (tracer) trace_stamp(p.trace, cta_lin, 2);
 
   if (warp == 0) {
@@ -482,6 +484,8 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  pdl_wait();  // the set-up above touched no global memory
+  pdl_trigger();
 
   auto decode = [&](int w, int& qp, int& h, int& b) {
     qp = nqp - 1 - w / nbh;  // later (longer) query pairs first
@@ -787,6 +791,8 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ O, long long ldo, int o_col0,
                                   const __nv_bfloat16* __restrict__ dO, long long lddo, int do_col0,
                                   float* __restrict__ delta, int B, int T, int H, int D) {
+  pdl_wait();
+  pdl_trigger();
   const int lp = D >> 3;  // lanes per item: 8 or 16
   const long long gt = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   const long long item = gt / lp;
@@ -939,6 +945,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  pdl_wait();  // the set-up above read no tensor of the step
+  pdl_trigger();
   if (tracer) trace_stamp(p.trace, cta_lin, 2);
 
   if (warp == 0) {
@@ -1380,14 +1388,16 @@ MMJ_API int mmj_attn_fwd(const void* q, long long ldq, int q_col0, const void* k
         cudaFuncSetAttribute(attn_fwd3_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         b64 = true;
       }
-      attn_fwd3_kernel<64><<<g, 384, smem, (cudaStream_t)stream>>>(tq, tk64, tv64, p);
+      launch_pdl(attn_fwd3_kernel<64>, dim3(g), dim3(384), (size_t)smem, (cudaStream_t)stream, tq, tk64, tv64,
+                 p);
     } else {
       const int smem = 2 * 2 * kPanelBytes + 2 * 4 * 16384 + 1024;
       if (!b128) {
         cudaFuncSetAttribute(attn_fwd3_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         b128 = true;
       }
-      attn_fwd3_kernel<128><<<g, 384, smem, (cudaStream_t)stream>>>(tq, tk64, tv64, p);
+      launch_pdl(attn_fwd3_kernel<128>, dim3(g), dim3(384), (size_t)smem, (cudaStream_t)stream, tq, tk64, tv64,
+                 p);
     }
     return (int)cudaGetLastError();
   }
@@ -1446,9 +1456,8 @@ MMJ_API int mmj_attn_bwd(const void* q, long long ldq, int q_col0, const void* k
     const long long lanes = (long long)B * T * Hq * (D / 8);
     const int threads = 256;
     const long long blocks = (lanes + threads - 1) / threads;
-    attn_delta_kernel<<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>(
-        (const __nv_bfloat16*)O, ldo, o_col0, (const __nv_bfloat16*)dO, lddo, do_col0, delta, B, T,
-        Hq, D);
+    launch_pdl(attn_delta_kernel, dim3((unsigned)blocks), dim3(threads), 0, (cudaStream_t)stream,
+               (const __nv_bfloat16*)O, ldo, o_col0, (const __nv_bfloat16*)dO, lddo, do_col0, delta, B, T, Hq, D);
   }
   AttnParams p = {};
   p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
@@ -1473,14 +1482,16 @@ MMJ_API int mmj_attn_bwd(const void* q, long long ldq, int q_col0, const void* k
       cudaFuncSetAttribute(attn_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       attr64 = true;
     }
-    attn_bwd_kernel<64><<<grid, kAttnBwdThreads, smem, (cudaStream_t)stream>>>(tq, tk, tv, tdo, tdq, p);
+    launch_pdl(attn_bwd_kernel<64>, grid, dim3(kAttnBwdThreads), (size_t)smem, (cudaStream_t)stream, tq, tk, tv,
+               tdo, tdq, p);
   } else {
     const int smem = 232448;  // 224 KB of tiles as well: K,V + Q,dO + P^T,dS^T + dQ staging
     if (!attr128) {
       cudaFuncSetAttribute(attn_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       attr128 = true;
     }
-    attn_bwd_kernel<128><<<grid, kAttnBwdThreads, smem, (cudaStream_t)stream>>>(tq, tk, tv, tdo, tdq, p);
+    launch_pdl(attn_bwd_kernel<128>, grid, dim3(kAttnBwdThreads), (size_t)smem, (cudaStream_t)stream, tq, tk, tv,
+               tdo, tdq, p);
   }
   return (int)cudaGetLastError();
 }

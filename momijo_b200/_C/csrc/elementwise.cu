@@ -56,6 +56,8 @@ __device__ __forceinline__ float act_bwd(float x, int op, float alpha) {
 
 __global__ void act_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
                                long long n8, int op, float alpha) {
+  pdl_wait();
+  pdl_trigger();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8;
        i += (long long)gridDim.x * blockDim.x) {
     float f[8];
@@ -68,6 +70,8 @@ __global__ void act_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat1
 __global__ void act_bwd_kernel(const __nv_bfloat16* __restrict__ x,
                                const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dx,
                                long long n8, int op, float alpha) {
+  pdl_wait();
+  pdl_trigger();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8;
        i += (long long)gridDim.x * blockDim.x) {
     float f[8], g[8];
@@ -231,6 +235,8 @@ __global__ void embedding_bwd_wpe_kernel(const __nv_bfloat16* __restrict__ dout,
 // N = 768, where 256-column strips left most of the load latency exposed. Stage 2 folds the S rows.
 __global__ void colsum_partial_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                                       float* __restrict__ scratch, int M, int N) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float sm[8][64];
   const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
   const int col = (blockIdx.x * 8 + tx) * 8;
@@ -278,6 +284,8 @@ __global__ void colsum_partial_kernel(const __nv_bfloat16* __restrict__ x, long 
 __global__ void colsum_finalize_kernel(const float* __restrict__ scratch,
                                        __nv_bfloat16* __restrict__ out_bf16,
                                        float* __restrict__ out_f32, int S, int N, int accumulate) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float sm[8][33];
   const int c = blockIdx.x * 32 + threadIdx.x;
   float s = 0.f;
@@ -301,6 +309,8 @@ __global__ void colsum_finalize_kernel(const float* __restrict__ scratch,
 // ---- split-K reduction: out[i] (+)= sum_s parts[s][i]  (fp32 slabs -> bf16) ---------------------
 __global__ void splitk_reduce_kernel(const float* __restrict__ parts, long long slab, int S,
                                      __nv_bfloat16* __restrict__ out, long long n, int accumulate) {
+  pdl_wait();
+  pdl_trigger();
   for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8; i < n;
        i += (long long)gridDim.x * blockDim.x * 8) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -489,6 +499,8 @@ __global__ void pack_nchw_kernel(const float* __restrict__ src, float* __restric
 __global__ void cast_f32_to_bf16_2d_kernel(const float* __restrict__ src, long long lds,
                                            __nv_bfloat16* __restrict__ dst, long long ldd,
                                            long long rows, int cols) {
+  pdl_wait();
+  pdl_trigger();
   const int c4 = cols >> 2;
   const long long total = rows * c4;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -518,16 +530,16 @@ using namespace mmj;
 MMJ_API int mmj_act_fwd(const void* x, void* y, long long n, int op, float alpha, void* stream) {
   if (n % 8) return -1;
   if (n == 0) return 0;
-  act_fwd_kernel<<<grid_for(n / 8, 256), 256, 0, STREAM>>>((const __nv_bfloat16*)x,
-                                                         (__nv_bfloat16*)y, n / 8, op, alpha);
+  launch_pdl(act_fwd_kernel, dim3(grid_for(n / 8, 256)), dim3(256), 0, STREAM, (const __nv_bfloat16*)x,
+             (__nv_bfloat16*)y, n / 8, op, alpha);
   return (int)cudaGetLastError();
 }
 MMJ_API int mmj_act_bwd(const void* x, const void* dy, void* dx, long long n, int op, float alpha,
                         void* stream) {
   if (n % 8) return -1;
   if (n == 0) return 0;
-  act_bwd_kernel<<<grid_for(n / 8, 256), 256, 0, STREAM>>>(
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, n / 8, op, alpha);
+  launch_pdl(act_bwd_kernel, dim3(grid_for(n / 8, 256)), dim3(256), 0, STREAM, (const __nv_bfloat16*)x,
+             (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, n / 8, op, alpha);
   return (int)cudaGetLastError();
 }
 MMJ_API int mmj_swiglu_fwd(const void* gu, void* y, long long rows, int F, void* stream) {
@@ -590,9 +602,9 @@ MMJ_API int mmj_colsum_bf16(const void* x, long long ldx, void* out_bf16, float*
   if (ldx % 8) return -1;
   const int S = mmj_colsum_splits(M);
   dim3 grid((N + 63) / 64, S);
-  colsum_partial_kernel<<<grid, 256, 0, STREAM>>>((const __nv_bfloat16*)x, ldx, scratch, M, N);
-  colsum_finalize_kernel<<<(N + 31) / 32, dim3(32, 8), 0, STREAM>>>(scratch, (__nv_bfloat16*)out_bf16,
-                                                              out_f32, S, N, accumulate);
+  launch_pdl(colsum_partial_kernel, grid, dim3(256), 0, STREAM, (const __nv_bfloat16*)x, ldx, scratch, M, N);
+  launch_pdl(colsum_finalize_kernel, dim3((N + 31) / 32), dim3(32, 8), 0, STREAM, (const float*)scratch,
+             (__nv_bfloat16*)out_bf16, out_f32, S, N, accumulate);
   return (int)cudaGetLastError();
 }
 
@@ -601,8 +613,8 @@ MMJ_API int mmj_splitk_reduce(const float* parts, long long slab, int S, void* o
                               int accumulate, void* stream) {
   if (n == 0) return 0;
   if (n % 8 || slab % 4 || S < 1) return -1;
-  splitk_reduce_kernel<<<grid_for(n / 8, 256), 256, 0, STREAM>>>(parts, slab, S, (__nv_bfloat16*)out, n,
-                                                                accumulate);
+  launch_pdl(splitk_reduce_kernel, dim3(grid_for(n / 8, 256)), dim3(256), 0, STREAM, parts, slab, S,
+             (__nv_bfloat16*)out, n, accumulate);
   return (int)cudaGetLastError();
 }
 
@@ -764,8 +776,8 @@ MMJ_API int mmj_cast_f32_to_bf16_2d(const float* src, long long lds, void* dst, 
                                     long long rows, int cols, void* stream) {
   if (cols % 4 || lds % 4 || ldd % 4) return -1;
   if (rows == 0 || cols == 0) return 0;
-  cast_f32_to_bf16_2d_kernel<<<grid_for(rows * (cols / 4), 256), 256, 0, STREAM>>>(
-      src, lds, (__nv_bfloat16*)dst, ldd, rows, cols);
+  launch_pdl(cast_f32_to_bf16_2d_kernel, dim3(grid_for(rows * (cols / 4), 256)), dim3(256), 0, STREAM, src, lds,
+             (__nv_bfloat16*)dst, ldd, rows, cols);
   return (int)cudaGetLastError();
 }
 

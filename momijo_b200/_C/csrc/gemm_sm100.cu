@@ -463,6 +463,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  // everything above touched no global memory: it may run under the previous kernel's tail
+  pdl_wait();
+  pdl_trigger();
 
   const int num_m = (p.num_m_tiles_dev != nullptr) ? *p.num_m_tiles_dev
                                                    : (p.M + bm - 1) / bm;
@@ -740,6 +743,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  pdl_wait();  // nothing above touched global memory
+  pdl_trigger();
 
   const int num_m = (p.M + 2 * kGemmBM - 1) / (2 * kGemmBM);
   const int num_n = (p.N + kPairBN - 1) / kPairBN;
@@ -1087,6 +1092,13 @@ int launch_gemm(GemmParams& p, const void* A, long long lda, long long a_rows, c
   if (gemm_ctas < 1) gemm_ctas = 1;
   if (tiles < gemm_ctas) gemm_ctas = (int)tiles;
   p.gemm_ctas = gemm_ctas;
+  if (comm_ctas == 0 && p.flag_mode == 0) {
+    // plain product: set-up may overlap the previous kernel's tail
+    cudaError_t e = launch_pdl(gemm_bf16_tcgen05_kernel, dim3(gemm_ctas), dim3(kThreads), (size_t)smem_bytes,
+                               stream, tmA, tmB, p);
+    return (int)(e != cudaSuccess ? e : cudaGetLastError());
+  }
+  // products fused with a collective wait on other ranks: ordinary stream order
   gemm_bf16_tcgen05_kernel<<<gemm_ctas + comm_ctas, kThreads, smem_bytes, stream>>>(tmA, tmB, p);
   return (int)cudaGetLastError();
 }
@@ -1159,7 +1171,11 @@ int launch_gemm_pair(GemmParams& p, const void* A, long long lda, long long a_ro
   int pairs = g_pair_clusters;
   if (tiles < pairs) pairs = (int)tiles;
   p.gemm_ctas = 2 * pairs;
-  gemm_bf16_pair_kernel<<<2 * pairs, kThreads, smem_bytes, stream>>>(tmA, tmB, p);
+  {
+    cudaError_t e = launch_pdl(gemm_bf16_pair_kernel, dim3(2 * pairs), dim3(kThreads), (size_t)smem_bytes, stream,
+                               tmA, tmB, p);
+    if (e != cudaSuccess) return (int)e;
+  }
   return (int)cudaGetLastError();
 }
 

@@ -252,6 +252,8 @@ __global__ void norm_bwd_finalize_kernel(const float* __restrict__ partial_dg,
                                          __nv_bfloat16* __restrict__ dgamma,
                                          __nv_bfloat16* __restrict__ dbeta, int nparts, int C,
                                          int accumulate) {
+  pdl_wait();
+  pdl_trigger();
   // block (16, 64): 16 adjacent columns (one 64-byte piece per partial row), the partial rows split over
   // threadIdx.y; narrow column strips give 48 CTAs for C = 768 where 32-column strips gave 24 and left
   // the 7 MB of partials to two dozen SMs
@@ -393,6 +395,8 @@ norm_fwd_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
   __shared__ uint64_t full[kNormMaxStages], empty[kNormMaxStages];
   __shared__ float2 red[2 * kNormWarps];
   __shared__ int abort_flag, issued_sh;
+  pdl_wait();  // the set-up below already requests the first tiles
+  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ntiles = (rows + ring.tile_rows - 1) / ring.tile_rows;
   const int my_tiles = (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
@@ -534,6 +538,8 @@ norm_bwd_stream_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16
   __shared__ uint64_t full[kNormMaxStages], empty[kNormMaxStages];
   __shared__ float2 red[2 * kNormWarps];
   __shared__ int abort_flag, issued_sh;
+  pdl_wait();  // the set-up below already requests the first tiles
+  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ntiles = (rows + ring.tile_rows - 1) / ring.tile_rows;
   const int my_tiles = (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
@@ -769,10 +775,10 @@ MMJ_API int mmj_norm_fwd(const void* x, const void* res, void* res_out, const vo
       const int smem = ring.stages * ntens * ring.tensor_bytes;
       bool launched = false;
       MMJ_NORM_ALL((norm_opt_in(norm_fwd_stream_kernel<kNV, kG>, smem),
-                    norm_fwd_stream_kernel<kNV, kG><<<grid, kNormThreads, smem, (cudaStream_t)stream>>>(
-                        xs, (const __nv_bfloat16*)res, (__nv_bfloat16*)res_out,
-                        (const __nv_bfloat16*)gamma, (const __nv_bfloat16*)beta, (__nv_bfloat16*)y, mean,
-                        rstd, rows, C, eps, mode, ring, status)))
+                    launch_pdl(norm_fwd_stream_kernel<kNV, kG>, dim3(grid), dim3(kNormThreads), (size_t)smem,
+                               (cudaStream_t)stream, xs, (const __nv_bfloat16*)res, (__nv_bfloat16*)res_out,
+                               (const __nv_bfloat16*)gamma, (const __nv_bfloat16*)beta, (__nv_bfloat16*)y, mean,
+                               rstd, rows, C, eps, mode, ring, status)))
       if (launched) return (int)cudaGetLastError();
     }
   }
@@ -823,20 +829,21 @@ MMJ_API int mmj_norm_bwd(const void* dy, const void* x, const void* gamma, const
       bool launched = false;
       if (with_beta) {
         MMJ_NORM_ALL((norm_opt_in(norm_bwd_stream_kernel<kNV, kG, true>, smem),
-                      norm_bwd_stream_kernel<kNV, kG, true><<<grid, kNormThreads, smem, (cudaStream_t)stream>>>(
-                          (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, mean,
-                          rstd, (const __nv_bfloat16*)dres_in, (__nv_bfloat16*)dx, sdg, sdb, rows, C, mode, ring,
-                          status)))
+                      launch_pdl(norm_bwd_stream_kernel<kNV, kG, true>, dim3(grid), dim3(kNormThreads), (size_t)smem,
+                                 (cudaStream_t)stream, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                 (const __nv_bfloat16*)gamma, mean, rstd, (const __nv_bfloat16*)dres_in,
+                                 (__nv_bfloat16*)dx, sdg, sdb, rows, C, mode, ring, status)))
       } else {
         MMJ_NORM_ALL((norm_opt_in(norm_bwd_stream_kernel<kNV, kG, false>, smem),
-                      norm_bwd_stream_kernel<kNV, kG, false><<<grid, kNormThreads, smem, (cudaStream_t)stream>>>(
-                          (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, mean,
-                          rstd, (const __nv_bfloat16*)dres_in, (__nv_bfloat16*)dx, sdg, sdb, rows, C, mode, ring,
-                          status)))
+                      launch_pdl(norm_bwd_stream_kernel<kNV, kG, false>, dim3(grid), dim3(kNormThreads), (size_t)smem,
+                                 (cudaStream_t)stream, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                 (const __nv_bfloat16*)gamma, mean, rstd, (const __nv_bfloat16*)dres_in,
+                                 (__nv_bfloat16*)dx, sdg, sdb, rows, C, mode, ring, status)))
       }
       if (launched) {
-        norm_bwd_finalize_kernel<<<(C + 15) / 16, dim3(16, 64), 0, (cudaStream_t)stream>>>(
-            sdg, sdb, (__nv_bfloat16*)dgamma, (__nv_bfloat16*)dbeta, grid, C, accumulate);
+        launch_pdl(norm_bwd_finalize_kernel, dim3((C + 15) / 16), dim3(16, 64), 0, (cudaStream_t)stream,
+                   (const float*)sdg, (const float*)sdb, (__nv_bfloat16*)dgamma, (__nv_bfloat16*)dbeta, grid, C,
+                   accumulate);
         return (int)cudaGetLastError();
       }
     }

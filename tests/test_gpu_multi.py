@@ -20,9 +20,12 @@ def _run(scenarios, nproc=None, timeout=600):
            os.path.join(HERE, "mp_worker.py"), *scenarios]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
     out = r.stdout + r.stderr
-    assert r.returncode == 0, out[-4000:]
+    # the first traceback names the cause; the tail is the launcher's summary of every rank
+    first = out.find("Traceback")
+    shown = (out[first:first + 3000] + "\n...\n" if first >= 0 else "") + out[-2500:]
+    assert r.returncode == 0, shown
     for s in scenarios:
-        assert f"SCENARIO_OK {s}" in out, out[-4000:]
+        assert f"SCENARIO_OK {s}" in out, shown
 
 
 def test_peer_allreduce_and_timeout_status():
