@@ -788,9 +788,11 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 // =============================================================================================
 // delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; D/8 lanes per (row, head), 16 bytes per
 // lane and tensor, so a warp covers 4 (head_dim 64) or 2 (head_dim 128) heads of a row at once.
+// The same lanes clear the fp32 dQ accumulator (8 values each) that the backward kernel adds into.
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ O, long long ldo, int o_col0,
                                   const __nv_bfloat16* __restrict__ dO, long long lddo, int do_col0,
-                                  float* __restrict__ delta, int B, int T, int H, int D) {
+                                  float* __restrict__ delta, float* __restrict__ dq_zero, long long ld_dq,
+                                  int dq_col0, int B, int T, int H, int D) {
   pdl_wait();
   pdl_trigger();
   const int lp = D >> 3;  // lanes per item: 8 or 16
@@ -807,6 +809,11 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ O, long long
     bt = item / H;
     const uint4 a = *reinterpret_cast<const uint4*>(O + bt * ldo + o_col0 + h * D + sub * 8);
     const uint4 c = *reinterpret_cast<const uint4*>(dO + bt * lddo + do_col0 + h * D + sub * 8);
+    if (dq_zero != nullptr) {
+      float4* z = reinterpret_cast<float4*>(dq_zero + bt * ld_dq + dq_col0 + h * D + sub * 8);
+      z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+      z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     const uint32_t av[4] = {a.x, a.y, a.z, a.w}, cv[4] = {c.x, c.y, c.z, c.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -1430,7 +1437,8 @@ MMJ_API int mmj_attn_set_trace(void* buf, long long ctas) {
   return 0;
 }
 
-// dQ_accum: fp32 [B*T, ld_dq], must be zero on entry (the kernel adds into it).
+// dQ_accum: fp32 [B*T, ld_dq]; its Hq*D columns from dq_col0 are cleared by the delta kernel, then the
+// backward kernel adds into them.
 // delta: fp32 scratch [B, Hq, T] (filled here). dK/dV: bf16 outputs.
 MMJ_API int mmj_attn_bwd(const void* q, long long ldq, int q_col0, const void* k, long long ldk,
                          int k_col0, const void* v, long long ldv, int v_col0, const void* O,
@@ -1457,7 +1465,8 @@ MMJ_API int mmj_attn_bwd(const void* q, long long ldq, int q_col0, const void* k
     const int threads = 256;
     const long long blocks = (lanes + threads - 1) / threads;
     launch_pdl(attn_delta_kernel, dim3((unsigned)blocks), dim3(threads), 0, (cudaStream_t)stream,
-               (const __nv_bfloat16*)O, ldo, o_col0, (const __nv_bfloat16*)dO, lddo, do_col0, delta, B, T, Hq, D);
+               (const __nv_bfloat16*)O, ldo, o_col0, (const __nv_bfloat16*)dO, lddo, do_col0, delta,
+               (((uintptr_t)dQ_accum & 15) == 0) ? dQ_accum : (float*)nullptr, ld_dq, dq_col0, B, T, Hq, D);
   }
   AttnParams p = {};
   p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv;

@@ -86,6 +86,8 @@ __global__ void act_bwd_kernel(const __nv_bfloat16* __restrict__ x,
 // ---- SwiGLU: y = silu(gate) * up; gate/up are column halves of a [rows, 2F] matrix --------
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ y,
                                   long long rows, int F) {
+  pdl_wait();
+  pdl_trigger();
   const int f8 = F >> 3;
   const long long total = rows * f8;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -103,6 +105,8 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfl
 __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu,
                                   const __nv_bfloat16* __restrict__ dy,
                                   __nv_bfloat16* __restrict__ dgu, long long rows, int F) {
+  pdl_wait();
+  pdl_trigger();
   const int f8 = F >> 3;
   const long long total = rows * f8;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -129,6 +133,8 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu,
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float2* __restrict__ cs,
                             long long rows, long long ld, int head_off, int n_heads, int D, int T,
                             float sign) {
+  pdl_wait();
+  pdl_trigger();
   const int half = D >> 1;
   const int per_row = n_heads * (half >> 3);  // 8 pairs per thread
   const long long total = rows * per_row;
@@ -545,16 +551,16 @@ MMJ_API int mmj_act_bwd(const void* x, const void* dy, void* dx, long long n, in
 MMJ_API int mmj_swiglu_fwd(const void* gu, void* y, long long rows, int F, void* stream) {
   if (F % 8) return -1;
   if (rows == 0) return 0;
-  swiglu_fwd_kernel<<<grid_for(rows * (F / 8), 256), 256, 0, STREAM>>>(
-      (const __nv_bfloat16*)gu, (__nv_bfloat16*)y, rows, F);
+  launch_pdl(swiglu_fwd_kernel, dim3(grid_for(rows * (F / 8), 256)), dim3(256), 0, STREAM,
+             (const __nv_bfloat16*)gu, (__nv_bfloat16*)y, rows, F);
   return (int)cudaGetLastError();
 }
 MMJ_API int mmj_swiglu_bwd(const void* gu, const void* dy, void* dgu, long long rows, int F,
                            void* stream) {
   if (F % 8) return -1;
   if (rows == 0) return 0;
-  swiglu_bwd_kernel<<<grid_for(rows * (F / 8), 256), 256, 0, STREAM>>>(
-      (const __nv_bfloat16*)gu, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dgu, rows, F);
+  launch_pdl(swiglu_bwd_kernel, dim3(grid_for(rows * (F / 8), 256)), dim3(256), 0, STREAM,
+             (const __nv_bfloat16*)gu, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dgu, rows, F);
   return (int)cudaGetLastError();
 }
 MMJ_API int mmj_rope(void* x, const void* cos_sin, long long rows, long long ld, int head_off,
@@ -562,8 +568,8 @@ MMJ_API int mmj_rope(void* x, const void* cos_sin, long long rows, long long ld,
   if (D % 16 || ld % 8 || head_off % 8) return -1;
   if (rows == 0 || n_heads == 0) return 0;
   const long long work = rows * n_heads * (D / 16);
-  rope_kernel<<<grid_for(work, 256), 256, 0, STREAM>>>((__nv_bfloat16*)x, (const float2*)cos_sin,
-                                                       rows, ld, head_off, n_heads, D, T, sign);
+  launch_pdl(rope_kernel, dim3(grid_for(work, 256)), dim3(256), 0, STREAM, (__nv_bfloat16*)x,
+             (const float2*)cos_sin, rows, ld, head_off, n_heads, D, T, sign);
   return (int)cudaGetLastError();
 }
 MMJ_API int mmj_embedding_fwd(const long long* tok, const void* wte, const void* wpe, void* out,

@@ -413,7 +413,7 @@ class _AttnPacked(torch.autograd.Function):
         qc, kc, vc = 0, Hq * D, (Hq + Hkv) * D
         dout = dout.contiguous()
         dqkv = torch.empty_like(qkv)
-        dq_acc = torch.zeros((B * T, Hq * D), dtype=torch.float32, device=qkv.device)
+        dq_acc = torch.empty((B * T, Hq * D), dtype=torch.float32, device=qkv.device)   # cleared by the kernel
         delta = torch.empty((B, Hq, T), dtype=torch.float32, device=qkv.device)
         st = _C.status_tensor(qkv.device)
         _C.call("mmj_attn_bwd", _C.ptr(qkv), ld, qc, _C.ptr(qkv), ld, kc, _C.ptr(qkv), ld, vc,
