@@ -899,15 +899,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   int& abort_flag = ctl.abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int jb = blockIdx.x;  // key block
-  const int hkv = blockIdx.y, b = blockIdx.z;
+  // One-dimensional grid ordered by work: with a causal mask key block 0 meets every query block and
+  // the last key block only one, so all CTAs of key block 0 are dispatched first, then those of key
+  // block 1 and so on (longest first; the tail of the grid is made of the one-block CTAs).
+  const int n_heads_b = p.Hkv * p.B;
+  const int jb = (int)blockIdx.x / n_heads_b;  // key block
+  const int hb = (int)blockIdx.x - jb * n_heads_b;
+  const int hkv = hb % p.Hkv, b = hb / p.Hkv;
   const int group = p.Hq / p.Hkv;
   const int num_qb = (p.T + 127) / 128;
   const int kv0 = jb * 128;
   const int i_begin = p.causal ? jb : 0;
   const int n_i = num_qb - i_begin;   // query blocks per head
   const int n_iter = n_i * group;     // (query head in group) x (query block)
-  const int cta_lin = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+  const int cta_lin = (int)blockIdx.x;
   const bool tracer = (threadIdx.x == 64);
   if (tracer) {
     trace_stamp(p.trace, cta_lin, 0);
@@ -1480,8 +1485,8 @@ MMJ_API int mmj_attn_bwd(const void* q, long long ldq, int q_col0, const void* k
   p.dV = (__nv_bfloat16*)dV; p.ld_dv = ld_dv; p.dv_col0 = dv_col0;
   p.status = status;
   p.trace = g_attn_trace;
-  dim3 grid((T + 127) / 128, Hkv, B);
-  if (g_attn_trace && (long long)grid.x * grid.y * grid.z > g_attn_trace_ctas) p.trace = nullptr;
+  dim3 grid((unsigned)(((T + 127) / 128) * Hkv * B));
+  if (g_attn_trace && (long long)grid.x > g_attn_trace_ctas) p.trace = nullptr;
   static bool attr64 = false, attr128 = false;
   if (D == 64) {
     // K,V + 3x(Q,dO) + P^T,dS^T + dQ staging = 224 KB of tiles; the control block and the alignment

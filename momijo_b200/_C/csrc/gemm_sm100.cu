@@ -133,6 +133,15 @@ __device__ __forceinline__ TileCoord tile_of(int t, int num_m, int num_n, const 
   return c;
 }
 
+// Byte offset of 16-byte piece `c` (0..3) of row `row` (0..31) in a per-warp staging area of 32 rows x
+// 64 bytes. The piece index is XORed with bits 1-2 of the row: the eight lanes of a quarter warp then hit
+// eight different 16-byte bank groups both when every lane writes piece c of its own row and when four
+// neighbouring lanes read the four pieces of one row (a padded pitch of 80 bytes left the reads of two
+// adjacent rows sharing a bank group).
+__device__ __forceinline__ int stage_off(int row, int c) {
+  return row * 64 + ((c ^ ((row >> 1) & 3)) << 4);
+}
+
 // Stores a 32-row x 32-column bf16 chunk (lane = row, v = its 32 columns) through a per-warp
 // staging area so that four neighbouring lanes write 64 contiguous bytes of one row: full 32-byte
 // sectors per request instead of 32 half-sector pieces. `tile` points at (first row, first column).
@@ -145,13 +154,13 @@ __device__ __forceinline__ void staged_store_bf16(uint8_t* st, int lane, const f
     q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
     q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
     q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
-    *reinterpret_cast<uint4*>(st + lane * 80 + i * 16) = q;
+    *reinterpret_cast<uint4*>(st + stage_off(lane, i)) = q;
   }
   __syncwarp();
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int rr = 8 * i + (lane >> 2);
-    const uint4 q = *reinterpret_cast<const uint4*>(st + rr * 80 + (lane & 3) * 16);
+    const uint4 q = *reinterpret_cast<const uint4*>(st + stage_off(rr, lane & 3));
     *reinterpret_cast<uint4*>(tile + rr * ld + (lane & 3) * 8) = q;
   }
   __syncwarp();
@@ -327,8 +336,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   __shared__ __align__(8) uint64_t tempty_bar[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
-  // per-warp staging for the scatter epilogue: 32 rows x 64 bytes, rows 80 bytes apart (conflict free)
-  __shared__ __align__(16) uint8_t epi_stage[kEpiWarps][32 * 80];
+  // per-warp staging for the transposing stores: 32 rows x 64 bytes, pieces swizzled (stage_off)
+  __shared__ __align__(16) uint8_t epi_stage[kEpiWarps][32 * 64];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -640,14 +649,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                 q.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
                 q.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
                 q.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
-                *reinterpret_cast<uint4*>(st + lane * 80 + i * 16) = q;
+                *reinterpret_cast<uint4*>(st + stage_off(lane, i)) = q;
               }
               __syncwarp();
               const int row_base = m0 + sub * kGemmBM + quad * 32;
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
                 const int rr = 8 * i + (lane >> 2);
-                const uint4 q = *reinterpret_cast<const uint4*>(st + rr * 80 + (lane & 3) * 16);
+                const uint4 q = *reinterpret_cast<const uint4*>(st + stage_off(rr, lane & 3));
                 const int grow = row_base + rr;
                 if (grow < p.M) {
                   const int owner = grow / p.rows_per_rank;
@@ -710,7 +719,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   __shared__ __align__(8) uint64_t tempty_bar[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
-  __shared__ __align__(16) uint8_t epi_stage[kEpiWarps][32 * 80];
+  __shared__ __align__(16) uint8_t epi_stage[kEpiWarps][32 * 64];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;

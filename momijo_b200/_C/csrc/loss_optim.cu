@@ -32,6 +32,16 @@ __device__ __forceinline__ float block_reduce_sum(float v, float* red) {
   return warp_sum(x);
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void unpack_bf16x8(const uint4& q, float (&f)[8]) {
+  float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y), c = unpack_bf16x2(q.z), d = unpack_bf16x2(q.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+
 // One CTA per row. logits: [rows, ld] bf16, columns >= V are padding. When the row fits in
 // shared memory (kCache) it is read from HBM once; dlogits overwrite the logits.
 //   loss_row[r] = logsumexp(row) - row[target]           (0 for ignored targets)
@@ -54,31 +64,39 @@ __global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long 
 
   // One pass over the row: running maximum and running sum of exp(x - maximum), rescaled whenever a
   // vector raises the maximum. The exponentials run while later loads are still in flight, instead of
-  // in a second pass over the cached row.
+  // in a second pass over the cached row. Everything is in base 2 (one fused multiply-add and one
+  // `ex2` per element), and only the vectors that reach past V test their columns.
+  constexpr float kL2e = 1.4426950408889634f;
   float mx = -INFINITY, sum = 0.f;
 #pragma unroll 4
   for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
     uint4 q = reinterpret_cast<const uint4*>(g)[v];
     if (kCache) reinterpret_cast<uint4*>(cache)[v] = q;
-    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&q);
     float x[8];
-    float vm = -INFINITY;
+    unpack_bf16x8(q, x);
+    if (v * 8 + 8 > V) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      x[j] = (v * 8 + j < V) ? __bfloat162float(e[j]) : -INFINITY;
-      vm = fmaxf(vm, x[j]);
+      for (int j = 0; j < 8; ++j)
+        if (v * 8 + j >= V) x[j] = -INFINITY;
     }
+    float vm = fmaxf(fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3])), fmaxf(fmaxf(x[4], x[5]), fmaxf(x[6], x[7])));
     if (vm > mx) {
-      sum *= __expf(mx - vm);  // exp(-inf) = 0 on the first vector
+      sum *= ex2_approx((mx - vm) * kL2e);  // 2^(-inf) = 0 on the first vector
       mx = vm;
     }
     if (mx > -INFINITY) {
+      const float nm = -mx * kL2e;
+      float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) sum += __expf(x[j] - mx);
+      for (int j = 0; j < 8; j += 2) {
+        s0 += ex2_approx(fmaf(x[j], kL2e, nm));
+        s1 += ex2_approx(fmaf(x[j + 1], kL2e, nm));
+      }
+      sum += s0 + s1;
     }
   }
   const float bmx = block_reduce_max(mx, red);
-  sum = (mx > -INFINITY) ? sum * __expf(mx - bmx) : 0.f;
+  sum = (mx > -INFINITY) ? sum * ex2_approx((mx - bmx) * kL2e) : 0.f;
   mx = bmx;
   const __nv_bfloat16* srcp = kCache ? cache : g;
   sum = block_reduce_sum(sum, red);
@@ -90,18 +108,37 @@ __global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long 
   }
   if (!write_grad) return;
   __syncthreads();  // everyone has read srcp[tgt] before the in-place overwrite (non-cached path)
-  const float inv = 1.0f / sum;
   const float sc = ignored ? 0.f : dscale * (dscale_dev != nullptr ? *dscale_dev : 1.0f);
+  if (sc == 0.f) {
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x)
+      reinterpret_cast<uint4*>(g)[v] = make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+  // dlogit = softmax * sc = sign(sc) * 2^(x * log2(e) - lse * log2(e) + log2|sc|): the normaliser and the
+  // scale ride in the exponent's offset
+  const float off = -lse * kL2e + __log2f(fabsf(sc));
+  const float sgn = sc < 0.f ? -1.f : 1.f;
+  const int tv = (int)(tgt >> 3), tj = (int)(tgt & 7);
+#pragma unroll 2
   for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
     uint4 q = reinterpret_cast<const uint4*>(srcp)[v];
-    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&q);
-    float o[8];
+    float x[8], o[8];
+    unpack_bf16x8(q, x);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int c = v * 8 + j;
-      float p = (c < V) ? __expf(__bfloat162float(e[j]) - mx) * inv : 0.f;
-      if (c == tgt) p -= 1.f;
-      o[j] = p * sc;
+    for (int j = 0; j < 8; ++j) o[j] = ex2_approx(fmaf(x[j], kL2e, off));
+    if (sgn < 0.f) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = -o[j];
+    }
+    if (v * 8 + 8 > V) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (v * 8 + j >= V) o[j] = 0.f;
+    }
+    if (v == tv) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j == tj) o[j] -= sc;
     }
     uint4 w;
     w.x = pack_bf16x2(o[0], o[1]);
