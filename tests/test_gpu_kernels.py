@@ -291,3 +291,49 @@ def test_moe_router_kernel_matches_torch(n, E, k):
     # bitwise reproducible
     w2, idx2, aux2 = _RouterTopK.apply(logits.detach(), k, coef)
     assert torch.equal(w2, w.detach()) and torch.equal(idx2, idx) and aux2.item() == aux.item()
+
+
+_CHAIN = r'''
+import hashlib, torch
+from momijo_b200 import ops
+from momijo_b200.ops import functional as fn
+bf16 = torch.bfloat16
+torch.manual_seed(5)
+R, C, F_ = 4096, 768, 3072
+x = (torch.randn(R, C, device="cuda")).to(bf16).requires_grad_(True)
+g, b = [torch.randn(C, device="cuda").to(bf16).requires_grad_(True) for _ in range(2)]
+w1 = (torch.randn(F_, C, device="cuda") * 0.02).to(bf16).requires_grad_(True)
+b1 = torch.zeros(F_, device="cuda", dtype=bf16, requires_grad=True)
+w2 = (torch.randn(C, F_, device="cuda") * 0.02).to(bf16).requires_grad_(True)
+b2 = torch.zeros(C, device="cuda", dtype=bf16, requires_grad=True)
+outs = []
+for it in range(3):   # the same chain three times: launches follow each other without a gap
+    h = ops.layer_norm(x, g, b)
+    y = fn.mlp_gelu(h, w1, b1, w2, b2, residual=x)
+    z, r = ops.layer_norm(y, g, b, residual=x)
+    (z.float().sum() * 1e-3 + r.float().mean()).backward()
+    outs += [y, z, r]
+outs += [x.grad, g.grad, b.grad, w1.grad, b1.grad, w2.grad, b2.grad]
+torch.cuda.synchronize()
+hsh = hashlib.sha256()
+for t in outs:
+    hsh.update(t.detach().float().cpu().numpy().tobytes())
+print("CHAIN", hsh.hexdigest())
+'''
+
+
+def test_dependent_launch_gives_the_same_bits_as_plain_stream_order():
+    """Norm -> GEMM(+GELU) -> GEMM -> norm forward and backward, three times back to back: kernels launched
+    with programmatic stream serialization (each waits for its predecessor before its first global access)
+    must produce exactly the bits of the same chain launched in plain stream order."""
+    import os
+    import subprocess
+    import sys
+    res = {}
+    for pdl in ("1", "0"):
+        env = dict(os.environ, MOMIJO_PDL=pdl)
+        r = subprocess.run([sys.executable, "-c", _CHAIN], capture_output=True, text=True, env=env, timeout=300,
+                           cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+        res[pdl] = [l for l in r.stdout.splitlines() if l.startswith("CHAIN")][0]
+    assert res["1"] == res["0"]
