@@ -53,6 +53,9 @@ def parse():
                     help="sharding stage of the headline config for N > 1")
     ap.add_argument("--fuse-first-gemm", type=int, default=1,
                     help="stages 1-2: gather each block's first weight inside the GEMM that consumes it")
+    ap.add_argument("--tp-fuse-min-rows", type=int, default=-1,
+                    help="tensor-parallel products with fewer gathered rows run as two launches instead of one "
+                         "fused kernel (-1: the library default)")
     ap.add_argument("--torch-variant", default="autocast", choices=["autocast", "bf16-master"],
                     help="stock-PyTorch arm of the headline config: fp32 parameters under bf16 autocast, or bf16 "
                          "parameters with an fp32 master copy")
@@ -236,6 +239,8 @@ def setup_llama_tp(args, rank, world, local):
 
         comm = PeerComm.from_default_group(heap_bytes=12 << 30)
     tp = TPContext(comm=comm) if comm is not None else TPContext.single()
+    if args.tp_fuse_min_rows >= 0:
+        tp.fuse_min_rows = args.tp_fuse_min_rows
     torch.manual_seed(1234 + rank)
     with torch.device("cuda"):
         model = Llama(cfg, tp)
@@ -349,6 +354,8 @@ def setup_llama_pptp(args, rank, world, local):
     groups = [dist.new_group(list(range(s * TP, (s + 1) * TP))) for s in range(S)]
     comm = PeerComm(groups[stage_id], heap_bytes=6 << 30) if TP > 1 else None
     tp = TPContext(comm=comm) if comm is not None else TPContext.single()
+    if args.tp_fuse_min_rows >= 0:
+        tp.fuse_min_rows = args.tp_fuse_min_rows
     layers = partition_layers(cfg.n_layer, S)[stage_id]
     torch.manual_seed(1234 + rank)
     with torch.device("cuda"):

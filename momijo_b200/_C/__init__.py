@@ -108,6 +108,7 @@ _SIGS = {
     "mmj_allgather_ranges": ([P, P, L, P, I, I, I, I, I, P, P], 1),
     "mmj_allreduce_bf16": ([P, P, P, L, F, I, I, I, I, I, P, P, P, P], 1),
     "mmj_reduce_slots_bf16": ([P, P, L, P, P, L, I, I, I, I, P, P], 1),
+    "mmj_reduce_pull_bf16": ([P, P, P, P, L, I, I, I, I, P, P], 1),
     "mmj_moe_count": ([P, P, I, I, P, P, I, I, I, I, P, P], 1),
     "mmj_moe_offsets": ([P, I, I, I, P, P, P, P, P, P, I, P], 1),
     "mmj_moe_zero_pad": ([P, I, P, I, I, P], 1),

@@ -330,6 +330,23 @@ __global__ void __launch_bounds__(256) allgather_ranges_kernel(const AllGatherPa
     const long long n16 = (hi - lo) >> 4;
     long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
     const long long stride = (long long)gridDim.x * blockDim.x;
+    // four independent 16-byte loads per thread and trip: one NVLink round trip (2-3 us) per trip,
+    // so a thread that waits for each load before asking for the next leaves the links mostly idle
+    for (; i + 3 * stride < n16; i += 4 * stride) {
+      uint4 q[4];
+      long long off[4];
+      bool mine[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        off[u] = lo + ((i + u * stride) << 4);
+        const int owner = (int)(off[u] / p.shard_bytes);
+        mine[u] = owner == p.t.rank;
+        if (!mine[u]) q[u] = *reinterpret_cast<const uint4*>(p.src[owner] + off[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (!mine[u]) *reinterpret_cast<uint4*>(p.dst + off[u]) = q[u];
+    }
     for (; i < n16; i += stride) {
       const long long off = lo + (i << 4);
       const int owner = (int)(off / p.shard_bytes);
@@ -452,6 +469,52 @@ reduce_slots_kernel(PeerTable t, const __nv_bfloat16* stage, long long slot_stri
       for (int j = 0; j < 8; ++j) acc[j] += f[j];
     }
     *reinterpret_cast<uint4*>(out + i * 8) = f32_to_bf16x8(acc);
+  }
+}
+
+// ================================================================================================
+// Reduce-scatter by pulls: every rank holds a full partial product [world * n] in symmetric memory
+// and sums its own block of n elements over all ranks (peer loads), plus an optional residual.
+// The unfused counterpart of GEMM -> reduce-scatter for products of a few thousand rows, where the
+// epilogue's 64-byte peer stores and the slot pass cost more than a plain GEMM followed by this.
+// ================================================================================================
+struct ReducePullParams {
+  PeerTable t;
+  const __nv_bfloat16* src[kMaxWorld];  // every rank's partial buffer
+  __nv_bfloat16* out;                   // [n]
+  const __nv_bfloat16* residual;        // [n] or null
+  long long n;                          // elements of one block, multiple of 8
+  int slot_base, epoch;
+  int* status;
+};
+
+__global__ void __launch_bounds__(256) reduce_pull_kernel(const ReducePullParams p) {
+  __shared__ int ok;
+  // every rank's product is complete (its GEMM precedes this kernel in stream order)
+  if (!block_barrier(p.t, p.slot_base, p.epoch, p.status, &ok)) return;
+  const int W = p.t.world;
+  const long long nvec = p.n >> 3;
+  const long long base = (long long)p.t.rank * p.n;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    // all loads of a vector are requested before the first is used; ranks are added in the order
+    // 0..W-1 on every rank, so the sum does not depend on who owns the block
+    uint4 q[kMaxWorld];
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r)
+      if (r < W) q[r] = *reinterpret_cast<const uint4*>(p.src[r] + base + i * 8);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (p.residual != nullptr) bf16x8_to_f32(*reinterpret_cast<const uint4*>(p.residual + i * 8), acc);
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r) {
+      if (r < W) {
+        float f[8];
+        bf16x8_to_f32(q[r], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += f[j];
+      }
+    }
+    *reinterpret_cast<uint4*>(p.out + i * 8) = f32_to_bf16x8(acc);
   }
 }
 
@@ -854,6 +917,27 @@ MMJ_API int mmj_allreduce_bf16(void* const* sig, void* const* bufs, const void* 
   long long want = (n / world / 8 + 255) / 256;
   if (want < grid) grid = (int)(want < 1 ? 1 : want);
   allreduce_kernel<<<grid, 256, 0, STREAM>>>(p);
+  return (int)cudaGetLastError();
+}
+
+MMJ_API int mmj_reduce_pull_bf16(void* const* sig, void* const* partials, void* out, const void* residual,
+                                 long long n, int world, int rank, int slot_base, int epoch, int* status,
+                                 void* stream) {
+  if (world < 1 || world > kMaxWorld) return -1;
+  if (!slots_ok(slot_base, world)) return -9;
+  if (n % 8) return -2;
+  ReducePullParams p;
+  p.t = make_table(world, rank, sig);
+  for (int r = 0; r < kMaxWorld; ++r) p.src[r] = (r < world) ? (const __nv_bfloat16*)partials[r] : nullptr;
+  p.out = (__nv_bfloat16*)out;
+  p.residual = (const __nv_bfloat16*)residual;
+  p.n = n;
+  p.slot_base = slot_base; p.epoch = epoch;
+  p.status = status;
+  long long want = (n / 8 + 255) / 256;
+  int grid = resident_grid(4);
+  if (want < grid) grid = (int)(want < 1 ? 1 : want);
+  reduce_pull_kernel<<<grid, 256, 0, STREAM>>>(p);
   return (int)cudaGetLastError();
 }
 

@@ -45,6 +45,9 @@ def timed(fn, iters=10, warm=3):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--small", action="store_true")
+    ap.add_argument("--tp-shape", default="",
+                    help="rows,hidden,ffn of the tensor-parallel section (default: the Llama-8B MLP at 32768 rows), "
+                         "e.g. 4096,5120,13824 for one 4096-token micro-batch of the Llama-13B shape")
     ap.add_argument("--only", default="all_reduce,zero,tp,moe",
                     help="comma list of sections: all_reduce, zero, tp (all-gather->GEMM, GEMM->reduce-scatter), moe")
     args = ap.parse_args()
@@ -121,6 +124,9 @@ def main():
         M = 2048 * W if args.small else 32768
         C = 1024 if args.small else 4096
         Fl = (4096 if args.small else 14336) // W
+        if args.tp_shape:
+            M, C, Fl = (int(v) for v in args.tp_shape.split(","))
+            Fl //= W
         site = FusedSite(comm)
         xa = comm.alloc(M * C, bf16).view(M, C)
         xa.normal_()
@@ -138,8 +144,17 @@ def main():
             dist.all_gather_into_tensor(xfull, xs)
             torch.matmul(xfull, w_gu.t(), out=out)
         ms_nccl = timed(nccl_ag_gemm)
+
+        # the same product from two launches: peer-pull all-gather kernel, then the plain GEMM at full width
+        def peer_ag_then_gemm():
+            comm.all_gather_rows(xa)
+            ops.gemm(xa, w_gu, out=out)
+        ms_two = timed(peer_ag_then_gemm)
+        by_ctas = {str(n): timed(lambda n=n: allgather_gemm(site, xa, w_gu, gather_a=True, out=out, comm_ctas=n))
+                   for n in (4, 16)}
         emit(op="allgather->gemm", M=M, N=2 * Fl, K=C, world=W, ms=ms, tflops=fl / ms / 1e9, roofline_ms=roof,
-             frac_of_roofline=roof / ms, local_gemm_only_ms=ms_gemm, nccl_allgather_plus_cublas_ms=ms_nccl)
+             frac_of_roofline=roof / ms, local_gemm_only_ms=ms_gemm, nccl_allgather_plus_cublas_ms=ms_nccl,
+             peer_allgather_then_gemm_ms=ms_two, fused_ms_by_comm_ctas=by_ctas)
 
         site2 = FusedSite(comm)
         a = (torch.randn(M, Fl, device="cuda")).to(bf16)
@@ -155,8 +170,15 @@ def main():
             torch.matmul(a, w_down.t(), out=full)
             dist.reduce_scatter_tensor(o, full)
         ms_nccl = timed(nccl_gemm_rs)
+        ms_gemm2 = timed(lambda: ops.gemm(a, w_down, out=full))
+        # the same result from two launches: plain GEMM into a symmetric buffer, then the pull reduce-scatter kernel
+        from .fused_comm import gemm_reduce_scatter_pull
+        site3 = FusedSite(comm)
+        partial = comm.alloc(M * C, bf16).view(M, C)
+        ms_pull = timed(lambda: gemm_reduce_scatter_pull(site3, a, w_down, partial, o))
         emit(op="gemm->reduce_scatter", M=M, N=C, K=Fl, world=W, ms=ms, tflops=fl / ms / 1e9, roofline_ms=roof,
-             frac_of_roofline=roof / ms, cublas_plus_nccl_reduce_scatter_ms=ms_nccl)
+             frac_of_roofline=roof / ms, cublas_plus_nccl_reduce_scatter_ms=ms_nccl, local_gemm_only_ms=ms_gemm2,
+             gemm_then_pull_reduce_scatter_ms=ms_pull)
 
     # ---- MoE dispatch / combine at the 16B shape (top-6 of 64 experts, hidden 2048, 16384 tokens per rank) ----
     n_tok, H, E, k = (2048, 1024, 8 * W, 2) if args.small else (16384, 2048, 64, 6)

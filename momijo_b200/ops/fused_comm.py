@@ -116,3 +116,20 @@ def gemm_reduce_scatter(site: FusedSite, a, b, stage, out, *, b_mn=False, residu
             _C.ptr(residual), rows * N, c.world, c.rank, site.slots + c.world, site.epoch,
             _C.ptr(c.status), _C.current_stream())
     return out
+
+
+def gemm_reduce_scatter_pull(site: FusedSite, a, b, partial, out, *, b_mn=False, residual=None):
+    """The result of ``gemm_reduce_scatter`` from two launches: the plain GEMM (full width, no peer stores in
+    its epilogue) into ``partial`` (symmetric ``[M, N]``), then every rank sums its own row block over all
+    ranks' partials by peer loads (``reduce_pull_kernel``, cross-rank barrier at its entry). Faster than the
+    fused kernel for products of a few thousand rows."""
+    from .gemm import gemm
+
+    c = site.comm
+    M, N = partial.shape
+    rows = M // c.world
+    gemm(a, b, b_mn=b_mn, out=partial)
+    site.epoch += 1
+    _C.call("mmj_reduce_pull_bf16", c._sig_ptrs, site.peer_ptrs(partial), _C.ptr(out), _C.ptr(residual), rows * N,
+            c.world, c.rank, site.slots + c.world, site.epoch, _C.ptr(c.status), _C.current_stream())
+    return out

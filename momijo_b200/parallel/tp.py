@@ -17,6 +17,8 @@ run on torch.distributed collectives (gloo on CPU), which is what the CPU tests 
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.nn as nn
 
@@ -67,6 +69,13 @@ class TPContext:
             self.world, self.rank = 1, 0
         self.pool = SymPool(comm) if comm is not None else None
         self._sites = {}
+        # Products with fewer gathered rows than this run as two launches (peer all-gather kernel + plain
+        # GEMM, plain GEMM + pull reduce-scatter kernel) instead of one fused kernel. Measured at 4 ranks,
+        # hidden 5120: at 4096 rows GEMM -> reduce-scatter takes 0.213 ms fused and 0.179 ms as two launches
+        # (the epilogue's 64-byte peer stores and the slot pass cost more than they hide under a 0.11 ms
+        # product), all-gather -> GEMM 0.307 against 0.293; at 8192 rows the two forms of the reduce-scatter
+        # tie and the fused all-gather wins (0.454 against 0.544), at 16384 rows both fused kernels win.
+        self.fuse_min_rows = int(os.environ.get("MOMIJO_TP_FUSE_MIN_ROWS", "8192"))
 
     @staticmethod
     def single():
@@ -128,19 +137,24 @@ class _AGLinearFused(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_shard, w, b, tp, key):
         from ..ops.fused_comm import allgather_gemm
+        from ..ops.gemm import gemm
 
         rows, K = x_shard.shape
         M = rows * tp.world
         full = tp.pool.get((M, K))
         full[tp.rank * rows:(tp.rank + 1) * rows].copy_(x_shard)
-        y = allgather_gemm(tp.site((key, "ag")), full, w, gather_a=True, bias=b)
+        if M >= tp.fuse_min_rows:
+            y = allgather_gemm(tp.site((key, "ag")), full, w, gather_a=True, bias=b)
+        else:
+            tp.comm.all_gather_rows(full)
+            y = gemm(full, w, bias=b)
         ctx.save_for_backward(x_shard, w)
         ctx.tp, ctx.key, ctx.refs = tp, key, (w, b)
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        from ..ops.fused_comm import gemm_reduce_scatter
+        from ..ops.fused_comm import gemm_reduce_scatter, gemm_reduce_scatter_pull
 
         x_shard, w = ctx.saved_tensors
         tp, key = ctx.tp, ctx.key
@@ -149,9 +163,12 @@ class _AGLinearFused(torch.autograd.Function):
         rows, K = x_shard.shape
         M = rows * tp.world
         # dX: partial [M, K] on every rank, summed and scattered over rows by the GEMM epilogue
-        stage = tp.pool.get((tp.world, rows, K))
         dx = torch.empty((rows, K), dtype=bf16, device=dy.device)
-        gemm_reduce_scatter(tp.site((key, "rs_b")), dy, w, stage, dx, b_mn=True)
+        if M >= tp.fuse_min_rows:
+            stage = tp.pool.get((tp.world, rows, K))
+            gemm_reduce_scatter(tp.site((key, "rs_b")), dy, w, stage, dx, b_mn=True)
+        else:
+            gemm_reduce_scatter_pull(tp.site((key, "rs_b")), dy, w, tp.pool.get((M, K)), dx, b_mn=True)
         # dW needs the gathered input again (not kept from the forward to save memory)
         full = tp.pool.get((M, K))
         full[tp.rank * rows:(tp.rank + 1) * rows].copy_(x_shard)
@@ -167,17 +184,20 @@ class _LinearRSFused(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w, b, residual_shard, tp, key):
-        from ..ops.fused_comm import gemm_reduce_scatter
+        from ..ops.fused_comm import gemm_reduce_scatter, gemm_reduce_scatter_pull
 
         M, K = x.shape
         N = w.shape[0]
         rows = M // tp.world
-        stage = tp.pool.get((tp.world, rows, N))
         out = torch.empty((rows, N), dtype=bf16, device=x.device)
         res = residual_shard
         if b is not None:  # the bias is added once, after the reduction
             res = (residual_shard + b) if residual_shard is not None else b.expand(rows, N).contiguous()
-        gemm_reduce_scatter(tp.site((key, "rs")), x.contiguous(), w, stage, out, residual=res)
+        if M >= tp.fuse_min_rows:
+            stage = tp.pool.get((tp.world, rows, N))
+            gemm_reduce_scatter(tp.site((key, "rs")), x.contiguous(), w, stage, out, residual=res)
+        else:
+            gemm_reduce_scatter_pull(tp.site((key, "rs")), x.contiguous(), w, tp.pool.get((M, N)), out, residual=res)
         ctx.save_for_backward(x, w)
         ctx.tp, ctx.key, ctx.refs = tp, key, (w, b)
         ctx.has_res = residual_shard is not None
@@ -186,6 +206,7 @@ class _LinearRSFused(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy_shard):
         from ..ops.fused_comm import allgather_gemm
+        from ..ops.gemm import gemm
 
         x, w = ctx.saved_tensors
         tp, key = ctx.tp, ctx.key
@@ -194,7 +215,11 @@ class _LinearRSFused(torch.autograd.Function):
         M = rows * tp.world
         full = tp.pool.get((M, N))
         full[tp.rank * rows:(tp.rank + 1) * rows].copy_(dy_shard)
-        dx = allgather_gemm(tp.site((key, "ag_b")), full, w, gather_a=True, other_mn=True)
+        if M >= tp.fuse_min_rows:
+            dx = allgather_gemm(tp.site((key, "ag_b")), full, w, gather_a=True, other_mn=True)
+        else:
+            tp.comm.all_gather_rows(full)
+            dx = gemm(full, w, b_mn=True)
         dw = _weight_grad(rw, full, x)       # `full` now holds every rank's dy rows
         db = _bias_grad(rb, dy_shard.contiguous()) if rb is not None else None
         if db is not None:

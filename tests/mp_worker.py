@@ -318,8 +318,15 @@ def sc_moe_layer(comm):
         close(getattr(ep, name).grad, g[R * epr:(R + 1) * epr], 8e-2, f"expert {name} grad")
 
 
-def sc_tp_llama(comm):
-    """Tensor-parallel Llama on the fused kernels == the same model on one rank."""
+def sc_tp_llama_two_launch(comm):
+    """The same with every tensor-parallel product below the fusion threshold: peer all-gather kernel + plain
+    GEMM, plain GEMM + pull reduce-scatter kernel."""
+    sc_tp_llama(comm, fuse_min_rows=1 << 30)
+
+
+def sc_tp_llama(comm, fuse_min_rows=0):
+    """Tensor-parallel Llama on the fused kernels (fusion threshold 0: every product fused) == the same model
+    on one rank."""
     from momijo_b200.models import Llama, LlamaConfig
     from momijo_b200.parallel.tp import TPContext
 
@@ -329,6 +336,8 @@ def sc_tp_llama(comm):
     torch.manual_seed(0)
     full = Llama(cfg, TPContext.single()).cuda()
     tp = TPContext(comm=comm)
+    if fuse_min_rows is not None:
+        tp.fuse_min_rows = fuse_min_rows
     model = Llama(cfg, tp).cuda()
     with torch.no_grad():
         V = model.embed.vocab_local
@@ -454,6 +463,7 @@ def sc_timeout(comm):
 
 SCENARIOS = {"allreduce": sc_allreduce, "zero": sc_zero, "ag_gemm": sc_ag_gemm,
              "gemm_rs": sc_gemm_rs, "moe": sc_moe, "moe_layer": sc_moe_layer, "tp_llama": sc_tp_llama,
+             "tp_llama_two_launch": sc_tp_llama_two_launch,
              "moe_drop": sc_moe_drop, "determinism": sc_determinism, "timeout": sc_timeout, "ddp": sc_ddp,
              "allreduce_nvls": sc_allreduce_nvls}
 

@@ -53,7 +53,7 @@ def test_moe_dispatch_combine_and_layer():
 
 
 def test_tensor_parallel_llama_matches_single_rank():
-    _run(["tp_llama"])
+    _run(["tp_llama", "tp_llama_two_launch"])
 
 
 def test_fused_collectives_are_deterministic():
