@@ -1,6 +1,6 @@
 """Per-kernel microbenchmarks with roofline fractions.
 
-    python -m momijo_b200.ops.bench_kernels --op gemm|attn|norm|ce|adamw|all [--small]
+    python -m momijo_b200.ops.bench_kernels --op gemm|attn|attn_kernel|norm|ce|adamw|misc|all [--small]
 
 Each kernel is timed with CUDA events on the launching stream after warm-up, with an L2-sized
 buffer rewritten between iterations. Achieved FLOP/s or bytes/s are reported against the measured
@@ -200,13 +200,115 @@ def bench_adamw(small):
              f"frac_of_{tag}_bw": by / (med * 1e-3) / bw_peak}]
 
 
+def bench_misc(small):
+    """The remaining bandwidth-bound kernels, one case each (bytes = algorithmic reads + writes): RoPE, SwiGLU,
+    GELU, embedding, bias-gradient column sum, sum of squares, direct / GEMM convolution, pooling, the MoE
+    router and the vision filters. Runs on the CPU paths too (tiny sizes) so that the calls stay checked
+    where there is no GPU."""
+    from . import conv as C
+    from ..parallel.ep import _RouterTopK
+    from ..vision import kernels as VK
+
+    cuda = torch.cuda.is_available()
+    dev = "cuda" if cuda else "cpu"
+    _, bw_peak, tag = peaks()
+    big = cuda and not small
+    rows_out = []
+
+    once = os.environ.get("MOMIJO_BENCH_ONCE", "0") == "1"   # one launch per kernel: for a profiler capture
+
+    def run(name, fn, nbytes, **extra):
+        if cuda and once:
+            fn()
+            torch.cuda.synchronize()
+            med = float("nan")
+        elif cuda:
+            med, _ = cuda_time_ms(fn)
+        else:
+            fn()
+            med = float("nan")
+        r = {"op": name, "ms": med, "GBs": nbytes / med / 1e6 if cuda else float("nan"),
+             f"frac_of_{tag}_bw": nbytes / (med * 1e-3) / bw_peak if cuda else float("nan")}
+        r.update(extra)
+        rows_out.append(r)
+
+    R, Cc = (32768, 4096) if big else ((8192, 4096) if cuda else (64, 128))
+    dt = bf16
+    x = torch.randn(R, Cc, device=dev).to(dt)
+    # RoPE in place on 32 heads of 128
+    D = 128
+    T = 4096 if cuda else 64
+    tab = ops.rope_table(T, D, 10000.0, x.device)
+    run("rope", lambda: ops.rope_inplace(x, tab, 0, Cc // D, D, T), 2.0 * R * Cc * 2, rows=R, cols=Cc)
+    gu = torch.randn(R, 2 * Cc, device=dev).to(dt).requires_grad_(True)
+    run("swiglu_fwd", lambda: ops.swiglu(gu), 3.0 * R * Cc * 2, rows=R, cols=Cc)
+    y = ops.swiglu(gu)
+    dy = torch.randn_like(y)
+    run("swiglu_bwd", lambda: y.backward(dy, retain_graph=True), 5.0 * R * Cc * 2, rows=R, cols=Cc)
+    xa = x.detach().clone().requires_grad_(True)
+    run("gelu_fwd", lambda: ops.activation(xa, "gelu"), 2.0 * R * Cc * 2, rows=R, cols=Cc)
+    ya = ops.activation(xa, "gelu")
+    dya = torch.randn_like(ya)
+    run("gelu_bwd", lambda: ya.backward(dya, retain_graph=True), 3.0 * R * Cc * 2, rows=R, cols=Cc)
+    # embedding gather + scatter-add
+    V, Ce = (50304, 1024) if cuda else (512, 64)
+    ntok = 65536 if cuda else 256
+    wte = torch.randn(V, Ce, device=dev).to(dt).requires_grad_(True)
+    tok = torch.randint(0, V, (ntok // 1024 if cuda else 1, 1024 if cuda else ntok), device=dev)
+    run("embedding_fwd", lambda: ops.embedding(tok, wte), 2.0 * ntok * Ce * 2, tokens=ntok, C=Ce)
+    e = ops.embedding(tok, wte)
+    de = torch.randn_like(e)
+    run("embedding_bwd", lambda: e.backward(de, retain_graph=True), 3.0 * ntok * Ce * 2, tokens=ntok, C=Ce)
+    # bias gradient (column sum) and gradient norm
+    from .functional import _colsum
+    xc = torch.randn(R, 2048 if cuda else 64, device=dev).to(dt)
+    run("colsum", lambda: _colsum(xc), 1.0 * xc.numel() * 2, rows=R, cols=xc.shape[1])
+    g = torch.randn(R * Cc, device=dev).to(dt)
+    run("sq_norm", lambda: ops.sq_norm(g), 1.0 * g.numel() * 2, n=g.numel())
+    # convolution and pooling (NCHW)
+    N_, Ci, H, Co = (32, 64, 56, 64) if cuda else (2, 4, 8, 4)
+    xi = torch.randn(N_, Ci, H, H, device=dev)
+    wc = torch.randn(Co, Ci, 3, 3, device=dev) * 0.05
+    conv_bytes = 4.0 * (xi.numel() + N_ * Co * H * H)
+    run("conv2d_fp32_direct", lambda: C.conv2d(xi, wc, None, (1, 1), (1, 1)), conv_bytes,
+        flops=2.0 * N_ * Co * H * H * Ci * 9)
+    xb, wb = xi.to(dt), wc.to(dt)
+    run("conv2d_bf16_im2col_gemm", lambda: C.conv2d(xb, wb, None, (1, 1), (1, 1)), conv_bytes / 2,
+        flops=2.0 * N_ * Co * H * H * Ci * 9)
+    run("max_pool2d", lambda: C.max_pool2d(xi, (2, 2)), 4.0 * xi.numel() * 1.25)
+    run("avg_pool2d", lambda: C.avg_pool2d(xi, (2, 2)), 4.0 * xi.numel() * 1.25)
+    # MoE router: softmax, top-6 of 64, renormalise, counts, auxiliary loss
+    n_r, E, k = (65536, 64, 6) if cuda else (128, 8, 2)
+    lg = torch.randn(n_r, E, device=dev).to(dt if cuda else torch.float32)
+    if cuda:
+        run("moe_router", lambda: _RouterTopK.apply(lg, k, 0.01), 1.0 * n_r * E * 2 + n_r * k * 8, tokens=n_r)
+    # vision filters on one 2048 x 2048 RGB image (uint8, HWC)
+    hw = 2048 if cuda else 32
+    img = torch.randint(0, 256, (hw, hw, 3), dtype=torch.uint8, device=dev)
+    gray = torch.randint(0, 256, (hw, hw, 1), dtype=torch.uint8, device=dev)
+    if cuda:
+        px = float(hw * hw)
+        run("vision_resize_bilinear_x0.5", lambda: VK.resize(img, hw // 2, hw // 2, True), px * 3 * 1.25)
+        run("vision_to_gray", lambda: VK.to_gray(img), px * 4)
+        run("vision_gaussian_5x5", lambda: VK.gaussian_blur(img, 5, 5, 1.0), px * 3 * 4)
+        run("vision_median_3", lambda: VK.median(img, 3), px * 3 * 2)
+        run("vision_bilateral_r2", lambda: VK.bilateral(img, 2, 25.0, 2.0), px * 3 * 2)
+        run("vision_sobel", lambda: VK.deriv3(gray, 0), px * 2)
+        run("vision_canny", lambda: VK.canny(gray, 50, 150), px * 2)
+        run("vision_erode_3", lambda: VK.morph(gray, 3, False), px * 2)
+        run("vision_clahe", lambda: VK.clahe_plane(gray[..., 0].contiguous(), 2.0, 8), px * 2)
+        bw = (gray[..., 0] > 127).to(torch.uint8).contiguous()
+        run("vision_connected_components", lambda: VK.connected_components(bw, 4), px * 5)
+    return rows_out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", default="all")
     ap.add_argument("--small", action="store_true")
     a = ap.parse_args()
     table = {"gemm": bench_gemm, "attn": bench_attn, "attn_kernel": bench_attn_kernel, "norm": bench_norm, "ce": bench_ce,
-             "adamw": bench_adamw}
+             "adamw": bench_adamw, "misc": bench_misc}
     for name, fn in table.items():
         if a.op in ("all", name):
             for r in fn(a.small):
