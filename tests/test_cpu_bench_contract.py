@@ -1,0 +1,27 @@
+"""The benchmark's command-line contract that needs no GPU: the reference arm reports why it cannot run, and
+the argument parser accepts the driver's flags."""
+import json
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_reference_arm_prints_unavailable_and_exits_zero():
+    r = subprocess.run([sys.executable, "bench.py", "--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "1"],
+                       cwd=ROOT, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and isinstance(line["unavailable"], str) and line["unavailable"]
+    assert "\n" not in line["unavailable"]
+
+
+def test_help_lists_the_driver_flags_and_the_configs():
+    r = subprocess.run([sys.executable, "bench.py", "--help"], cwd=ROOT, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0
+    for flag in ("--gpus", "--steps", "--warmup", "--impl", "--config", "--baseline", "--zero-stage",
+                 "--tp-fuse-min-rows", "--torch-variant"):
+        assert flag in r.stdout, flag
+    for cfg in ("gpt2", "llama8b-tp", "moe16b-ep", "llama13b-pptp"):
+        assert cfg in r.stdout, cfg

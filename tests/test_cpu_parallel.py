@@ -117,3 +117,14 @@ def test_two_rank_parity(worker, tmp_path):
     out = str(tmp_path / "ok.txt")
     mp.spawn(worker, args=(2, _free_port(), out), nprocs=2, join=True)
     assert open(out).read() == "ok"
+
+
+def test_tensor_parallel_fusion_threshold_default_and_env(monkeypatch):
+    """Products under ``fuse_min_rows`` gathered rows take the two-launch forms; the default comes from the
+    measurements at micro-batch sizes, the environment variable overrides it."""
+    from momijo_b200.parallel.tp import TPContext
+
+    monkeypatch.delenv("MOMIJO_TP_FUSE_MIN_ROWS", raising=False)
+    assert TPContext.single().fuse_min_rows == 8192
+    monkeypatch.setenv("MOMIJO_TP_FUSE_MIN_ROWS", "0")
+    assert TPContext.single().fuse_min_rows == 0
