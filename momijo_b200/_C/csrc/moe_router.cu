@@ -2,7 +2,9 @@
 // per-expert assignment counts and probability sums, and the load-balance auxiliary loss
 //   aux = coef * E * sum_e (count_e / (n * k)) * (psum_e / n)
 // in two launches (token pass + a one-block fold), plus the matching backward pass. The reference has no
-// mixture-of-experts layer; this follows the usual top-k softmax router with the Switch-style auxiliary loss.
+// mixture-of-experts layer (its layer set is legacy/src/momijo/learn/nn/layers.mojo and nn/*.mojo; its only
+// softmax is the last-dimension one, legacy/src/momijo/tensor/math.mojo:447-461); this follows the usual
+// top-k softmax router with the Switch-style auxiliary loss.
 //
 // One warp per token, lane l owns experts l, l + 32, ... (E <= 256). Counts and probability sums are kept
 // per warp in shared memory (a lane only ever touches its own experts), folded per block in warp order and

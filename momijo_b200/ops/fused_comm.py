@@ -3,6 +3,11 @@ GEMM with a reduce-scatter epilogue) and of the MoE dispatch / combine kernels.
 
 All buffers that peers touch live in the symmetric heap of a ``PeerComm``. A call site owns a
 small amount of state (flags, signal slots, epoch counter) kept in a ``FusedSite``.
+
+No counterpart in the reference: its collectives return their input unchanged
+(legacy/src/momijo/learn/distributed/collective.mojo:163-232) and its sharding helpers only slice lists
+(legacy/src/momijo/learn/distributed/sharding.mojo:130-168); these are the kernels that stand where
+``allgather_list`` / ``reduce_scatter_list`` would move data.
 """
 from __future__ import annotations
 

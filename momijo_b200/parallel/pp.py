@@ -1,6 +1,7 @@
 """Pipeline parallelism: stage wrapper and the 1F1B schedule.
 
-The reference has no pipeline parallelism (``learn/data/pipeline.mojo`` is an input pipeline).
+The reference has no pipeline parallelism (legacy/src/momijo/learn/data/pipeline.mojo is an input pipeline;
+its process group asserts a single rank, legacy/src/momijo/learn/distributed/collective.mojo:74-78).
 Inter-stage activations and gradients travel over torch.distributed point-to-point (NCCL on GPUs,
 gloo on CPU) issued asynchronously, so transfers overlap with compute:
 
