@@ -572,3 +572,58 @@ class ShardedDataParallel(nn.Module):
     def state_dict_sharded(self) -> str:
         """Same JSON shape as ``ZeroStage1.state_dict``."""
         return json.dumps({"world_size": self.world, "rank": self.rank})
+
+    # ---- checkpoint / resume ----
+    def is_cuda_engine(self) -> bool:
+        return bool(self.is_cuda) if self.world > 1 else self.flat.param.is_cuda
+
+    def save_checkpoint(self, base: str, extra: Optional[dict] = None) -> None:
+        """Optimizer state (fp32 master weights, AdamW moments, step count) as an MNP checkpoint, one blob per
+        rank (``<base>.rank<r>of<W>.bin``); every rank calls it. See ``parallel.zero_ckpt``."""
+        from . import zero_ckpt
+
+        if self.world > 1 and self.is_cuda:
+            torch.cuda.current_stream().wait_stream(self.side)
+        zero_ckpt.save(self, base, extra)
+
+    def load_checkpoint(self, base: str) -> dict:
+        """Restore from ``save_checkpoint`` output of a run with any world size (the per-parameter pieces are
+        re-split for this run's shards), rebuild the bf16 parameters from the master weights, return ``extra``."""
+        from . import zero_ckpt
+
+        return zero_ckpt.load(self, base)
+
+    def republish_from_master(self) -> None:
+        """bf16 parameters := fp32 master weights, on every rank (after a load, or after editing the master
+        weights in place). Collective."""
+        with torch.no_grad():
+            if self.world == 1:
+                self.flat.param.copy_(self.master.to(self.flat.param.dtype))
+                self.flat.mark_fresh()
+                return
+            R = self.rank
+            if self.is_cuda:
+                torch.cuda.current_stream().wait_stream(self.side)
+            for b in self.buckets:
+                mine = self.master[b.moff:b.moff + b.shard].to(self.dtype)
+                if self.pshard is not None:
+                    self.pshard[b.moff:b.moff + b.shard].copy_(mine)
+                if self.stage <= 2:
+                    b.pview[R * b.shard:(R + 1) * b.shard].copy_(mine)
+            if self.is_cuda:
+                ev = torch.cuda.Event()
+                ev.record()
+            with self._side():
+                if self.is_cuda:
+                    self.side.wait_event(ev)
+                self.comm.barrier()   # every rank's shards are in place before anyone gathers
+                for b in self.buckets:
+                    self._after_update(b)
+            if self.is_cuda:
+                torch.cuda.current_stream().wait_stream(self.side)
+            if self.stage == 3:
+                self._pslot_holds = [None] * len(self._pslot_holds)
+            for b in self.buckets:
+                b.launched = False
+            for p in self.params:
+                p._mg_fresh = True

@@ -1,0 +1,104 @@
+"""Checkpoint / resume of ShardedDataParallel: the optimizer state written per rank in the MNP layout is
+restored by a run with the same or another world size, and training continues as if never interrupted."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from test_cpu_zero_stages import ROOT, _data, _free_port, _net
+
+
+def _step(eng, xs, ys, s, lo, hi):
+    dt = next(eng.module.parameters()).dtype   # a single-rank engine re-homes its parameters as bf16
+    loss = ((eng(xs[s, lo:hi].to(dt)).float() - ys[s, lo:hi]) ** 2).mean()
+    loss.backward()
+    eng.step()
+
+
+def test_single_rank_resume_is_exact(tmp_path):
+    from momijo_b200.parallel import AdamWConfig, ShardedDataParallel
+
+    xs, ys = _data()
+    cfg = AdamWConfig(lr=1e-2, weight_decay=0.1)
+    a = ShardedDataParallel(_net(), cfg)
+    for s in range(2):
+        _step(a, xs, ys, s, 0, 8)
+    base = str(tmp_path / "ck" / "opt")
+    a.save_checkpoint(base, extra={"note": "after two steps"})
+    assert os.path.exists(base + ".json") and os.path.exists(base + ".bin")
+    _step(a, xs, ys, 2, 0, 8)
+    want = a.materialize()
+
+    b = ShardedDataParallel(_net(), cfg)
+    extra = b.load_checkpoint(base)
+    assert extra["note"] == "after two steps" and extra["step_count"] == 2 and b.step_count == 2
+    _step(b, xs, ys, 2, 0, 8)
+    got = b.materialize()
+    for k in want:
+        assert torch.equal(got[k], want[k]), k
+
+
+def _worker(rank, world, port, tmp, stage):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    from momijo_b200.parallel import AdamWConfig, ShardedDataParallel
+    from momijo_b200.parallel.peer import TorchDistComm
+
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    xs, ys = _data()
+    cfg = AdamWConfig(lr=1e-2, weight_decay=0.1)
+    lo, hi = rank * 4, rank * 4 + 4
+    base = os.path.join(tmp, "opt")
+
+    def make():
+        return ShardedDataParallel(_net(), cfg, stage=stage, comm=TorchDistComm(), window=2, grad_slots=2)
+
+    a = make()
+    for s in range(2):
+        _step(a, xs, ys, s, lo, hi)
+    a.save_checkpoint(base)
+    assert os.path.exists(f"{base}.rank{rank}of{world}.bin")
+    _step(a, xs, ys, 2, lo, hi)
+    want = a.materialize()
+
+    # same world size: exact continuation
+    b = make()
+    extra = b.load_checkpoint(base)
+    assert extra["world"] == world and b.step_count == 2
+    _step(b, xs, ys, 2, lo, hi)
+    got = b.materialize()
+    for k in want:
+        assert torch.equal(got[k], want[k]), (stage, k)
+
+    # one rank reads the two-rank checkpoint (the pieces are re-split for its single flat buffer), writes
+    # it again as a one-rank checkpoint, and two ranks read that: every element of master / m / v comes back
+    from momijo_b200.parallel.zero_ckpt import owned_pieces
+
+    fresh = make()
+    fresh.load_checkpoint(base)
+    params_after_load = fresh.materialize()       # fp32 parameters republished from the master weights
+    base1 = os.path.join(tmp, "opt_one_rank")
+    if rank == 0:
+        c = ShardedDataParallel(_net(), cfg)
+        c.load_checkpoint(base)
+        assert c.step_count == 2
+        for name, lo_, hi_, at in owned_pieces(c):
+            assert torch.equal(c.master[at:at + hi_ - lo_], params_after_load[name].reshape(-1)[lo_:hi_]), name
+        c.save_checkpoint(base1)
+    dist.barrier()
+    d = make()
+    d.load_checkpoint(base1)
+    for k in ("master", "m", "v"):
+        assert torch.equal(getattr(d, k), getattr(fresh, k)), (stage, k)
+    assert d.step_count == 2
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("stage", [1, 3])
+def test_two_rank_resume_and_resharding(tmp_path, stage):
+    port = _free_port()
+    mp.spawn(_worker, args=(2, port, str(tmp_path), stage), nprocs=2, join=True)
