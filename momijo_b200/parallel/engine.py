@@ -93,3 +93,26 @@ class HybridEngine(nn.Module):
             self.dp.step(lr)
         if self.local is not None:
             self.local.step(lr)
+
+    # ---- checkpoint / resume ----
+    def save_checkpoint(self, base: str, extra: Optional[dict] = None) -> None:
+        """Optimizer state of both parts in the MNP layout: the local part as ``<base>.local<global rank>``
+        (every process owns different local parameters), the data-parallel part as ``<base>.dp`` with one blob
+        per rank of its group. Every process calls it."""
+        g = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+        if self.local is not None:
+            self.local.save_checkpoint(f"{base}.local{g}", extra)
+        if self.dp is not None:
+            self.dp.save_checkpoint(f"{base}.dp", extra)
+
+    def load_checkpoint(self, base: str) -> dict:
+        """Restore what ``save_checkpoint`` wrote. The local part needs the layout it was written with (same
+        tensor / expert / pipeline split, same global ranks); the data-parallel part may come from a group of
+        another size."""
+        g = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+        extra = {}
+        if self.local is not None:
+            extra = self.local.load_checkpoint(f"{base}.local{g}")
+        if self.dp is not None:
+            extra = self.dp.load_checkpoint(f"{base}.dp") or extra
+        return extra
