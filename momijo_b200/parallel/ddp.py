@@ -237,5 +237,32 @@ class DistributedDataParallel(nn.Module):
 
     step_and_sync = step
 
+    # ---- checkpoint / resume ----
+    def save_checkpoint(self, base: str, extra: Optional[dict] = None) -> None:
+        """Every rank holds the same optimizer state, so rank 0 writes it (MNP layout, per-parameter
+        ``master`` / ``m`` / ``v`` tensors, step count in ``extra``) and the others wait. The file can also be
+        read by ``ShardedDataParallel.load_checkpoint`` of any world size."""
+        from . import zero_ckpt
+
+        if self.rank == 0:
+            zero_ckpt.save_replicated(self, base, extra)
+        if self.world > 1:
+            if self.comm is not None:
+                self.comm.host_barrier()
+            else:
+                dist.barrier(self.group)
+
+    def load_checkpoint(self, base: str) -> dict:
+        """Restore from ``save_checkpoint`` (or from a sharded engine's checkpoint of any world size) and rebuild
+        the bf16 parameters from the master weights."""
+        from . import zero_ckpt
+
+        extra = zero_ckpt.read_into(self, base, zero_ckpt.flat_pieces(self))
+        self.step_count = int(extra.get("step_count", self.step_count))
+        with torch.no_grad():
+            self.flat.param.copy_(self.master.to(self.flat.param.dtype))
+        self.flat.mark_fresh()
+        return extra
+
     def zero_grad(self):
         self.flat.mark_fresh()

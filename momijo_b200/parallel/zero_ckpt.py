@@ -59,16 +59,45 @@ class _State:
         return self._t
 
 
+def flat_pieces(engine) -> Iterator[Tuple[str, int, int, int]]:
+    """The pieces of an engine that keeps the whole optimizer state in one ``FlatParams`` layout (bucketed data
+    parallel, single rank): every parameter in full."""
+    names = _names(engine)
+    lay = engine.flat.layout
+    for p, off in zip(lay.params, lay.offsets):
+        yield names[id(p)], 0, p.numel(), off
+
+
+def _collect(engine, pieces):
+    state = {"master": engine.master, "m": engine.m, "v": engine.v}
+    tensors, ranges = OrderedDict(), {}
+    for name, lo, hi, at in pieces:
+        ranges[name] = [lo, hi]
+        for k in KINDS:
+            tensors[f"{k}::{name}"] = state[k][at:at + hi - lo]
+    return tensors, ranges
+
+
+def save_replicated(engine, base: str, extra: dict | None = None) -> None:
+    """One writer: an engine whose ranks all hold the same full optimizer state (``DistributedDataParallel``)."""
+    from ..learn.utils.checkpoint import save_state_dict
+
+    tensors, ranges = _collect(engine, flat_pieces(engine))
+    meta = {"engine": type(engine).__name__, "world": 1, "step_count": engine.step_count, "lr": engine.optim.lr}
+    meta.update(extra or {})
+    d = os.path.dirname(base)
+    if d:
+        os.makedirs(d, exist_ok=True)
+    if engine.master.is_cuda:
+        torch.cuda.synchronize()
+    save_state_dict(_State(tensors), base, extra=meta, shard_ranges=ranges)
+
+
 def save(engine, base: str, extra: dict | None = None) -> None:
     """Write this rank's part of the optimizer state. Every rank calls it with the same ``base``."""
     from ..learn.utils.checkpoint import save_state_dict
 
-    state = {"master": engine.master, "m": engine.m, "v": engine.v}
-    tensors, ranges = OrderedDict(), {}
-    for name, lo, hi, at in owned_pieces(engine):
-        ranges[name] = [lo, hi]
-        for k in KINDS:
-            tensors[f"{k}::{name}"] = state[k][at:at + hi - lo]
+    tensors, ranges = _collect(engine, owned_pieces(engine))
     meta = {"engine": "ShardedDataParallel", "stage": engine.stage, "world": engine.world,
             "step_count": engine.step_count, "lr": engine.lr,
             "betas": list(engine.optim.betas), "eps": engine.optim.eps, "weight_decay": engine.optim.weight_decay}
@@ -108,6 +137,16 @@ def _writer_headers(base: str) -> List[Tuple[dict, str]]:
 def load(engine, base: str) -> dict:
     """Restore the optimizer state from a checkpoint written by any world size, republish the bf16 parameters
     from the restored master weights and return the checkpoint's ``extra`` dict. Collective over the ranks."""
+    extra = read_into(engine, base, owned_pieces(engine))
+    engine.step_count = int(extra.get("step_count", engine.step_count))
+    if "lr" in extra:
+        engine.lr = float(extra["lr"])
+    engine.republish_from_master()
+    return extra
+
+
+def read_into(engine, base: str, pieces) -> dict:
+    """Fill ``engine.master / m / v`` at the given pieces from whatever ranks wrote ``base``; returns ``extra``."""
     from ..learn.utils.checkpoint import read_blob_tensor
 
     writers = _writer_headers(base)
@@ -119,7 +158,7 @@ def load(engine, base: str) -> dict:
     state = {"master": engine.master, "m": engine.m, "v": engine.v}
     cache: Dict[Tuple[int, str], torch.Tensor] = {}
     with torch.no_grad():
-        for name, lo, hi, at in owned_pieces(engine):
+        for name, lo, hi, at in pieces:
             covered = 0
             for wi, (ranges, ent, blob) in enumerate(index):
                 if name not in ranges:
@@ -139,9 +178,4 @@ def load(engine, base: str) -> dict:
             if covered != hi - lo:
                 raise KeyError(f"{base}: elements [{lo}, {hi}) of {name} are covered {covered} times over")
             cache = {k_: v_ for k_, v_ in cache.items() if not k_[1].endswith("::" + name)}
-    extra = writers[0][0].get("extra", {})
-    engine.step_count = int(extra.get("step_count", engine.step_count))
-    if "lr" in extra:
-        engine.lr = float(extra["lr"])
-    engine.republish_from_master()
-    return extra
+    return writers[0][0].get("extra", {})

@@ -147,3 +147,42 @@ def _hybrid_worker(rank, world, port, tmp):
 def test_hybrid_engine_resume(tmp_path):
     port = _free_port()
     mp.spawn(_hybrid_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+
+
+def _ddp_worker(rank, world, port, tmp):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    from momijo_b200.parallel import AdamWConfig, DistributedDataParallel, ShardedDataParallel
+    from momijo_b200.parallel.peer import TorchDistComm
+
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    xs, ys = _data()
+    cfg = AdamWConfig(lr=1e-2, weight_decay=0.1)
+    lo, hi = rank * 4, rank * 4 + 4
+    base = os.path.join(tmp, "ddp")
+    a = DistributedDataParallel(_net(), cfg, dtype=torch.float32)
+    for s in range(2):
+        _step(a, xs, ys, s, lo, hi)
+    a.save_checkpoint(base, extra={"epoch": 7})
+    assert os.path.exists(base + ".bin")
+    _step(a, xs, ys, 2, lo, hi)
+    b = DistributedDataParallel(_net(), cfg, dtype=torch.float32)
+    extra = b.load_checkpoint(base)
+    assert extra["epoch"] == 7 and b.step_count == 2
+    _step(b, xs, ys, 2, lo, hi)
+    assert torch.equal(a.flat.param, b.flat.param)
+    # the same file restores a sharded engine: its step then matches the replicated one's
+    c = ShardedDataParallel(_net(), cfg, stage=2, comm=TorchDistComm(), window=2, grad_slots=2)
+    c.load_checkpoint(base)
+    _step(c, xs, ys, 2, lo, hi)
+    got = c.materialize()
+    for n, p in a.module.named_parameters():
+        assert torch.allclose(got[n], p.detach(), rtol=0, atol=2e-6), n
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_ddp_resume_and_load_into_sharded_engine(tmp_path):
+    port = _free_port()
+    mp.spawn(_ddp_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
