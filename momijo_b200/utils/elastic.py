@@ -132,8 +132,13 @@ def guarded_step(step_fn: Callable[[], object], detector: Optional[FailureDetect
         raise
     except Exception as e:  # DeviceTimeout, DistBackendError / collective timeout, injected faults
         name = type(e).__name__
+        msg = str(e).lower()
+        # what a vanished peer looks like from a collective: a timeout, or the transport's own words for a
+        # closed connection (gloo: "Connection reset by peer", "Connection closed by peer", "Read error")
+        lost = ("timeout", "timed out", "connection reset", "connection closed", "broken pipe", "read error",
+                "write error", "socket closed")
         if name in ("DeviceTimeout", "DistBackendError", "DistNetworkError", "InjectedFault") or \
-                "timeout" in str(e).lower() or "timed out" in str(e).lower():
+                any(w in msg for w in lost):
             dead = detector.dead_ranks() if detector is not None else []
             raise RankFailure(f"{name}: {e}", dead) from e
         raise

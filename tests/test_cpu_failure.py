@@ -154,3 +154,86 @@ def test_gloo_rank_exit_is_detected(tmp_path):
     out0, _ = procs[0].communicate(timeout=120)
     procs[1].communicate(timeout=120)
     assert "DETECTED" in out0, out0
+
+
+_ELASTIC_WORKER = r"""
+import os, sys, datetime
+import torch, torch.distributed as dist
+sys.path.insert(0, os.path.join(os.environ["REPO_ROOT"], "tests"))
+from test_cpu_zero_stages import _net, _data
+from momijo_b200.parallel import AdamWConfig, ShardedDataParallel
+from momijo_b200.parallel.peer import TorchDistComm
+from momijo_b200.parallel.zero_ckpt import owned_pieces
+from momijo_b200.utils.elastic import RankFailure, run_elastic
+
+rank0, world0 = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+base = os.environ["CKPT_BASE"]
+dist.init_process_group("gloo", rank=rank0, world_size=world0, timeout=datetime.timedelta(seconds=4))
+xs, ys = _data()
+cfg = AdamWConfig(lr=1e-2, weight_decay=0.1)
+snap = {}
+
+def make_state(rank, world):
+    comm = TorchDistComm() if world > 1 else None
+    return {"eng": ShardedDataParallel(_net(), cfg, stage=3, comm=comm, window=2, grad_slots=2),
+            "rank": rank, "world": world}
+
+def train_step(st, step):
+    eng, r, w = st["eng"], st["rank"], st["world"]
+    if step == 2 and w == 2 and r == 1:
+        os._exit(0)                      # leaves between steps: nothing of its own is in flight
+    per = 8 // w
+    dt = next(eng.module.parameters()).dtype
+    x, y = xs[step % 4, r * per:(r + 1) * per].to(dt), ys[step % 4, r * per:(r + 1) * per]
+    loss = ((eng(x).float() - y) ** 2).mean()
+    loss.backward()
+    eng.step()
+    st["loss"] = float(loss)
+
+def save(st, step):
+    st["eng"].save_checkpoint(base, extra={"step": step})
+    if st["world"] == 2:
+        snap["params"] = st["eng"].materialize()      # collective, every rank still present
+        snap["step"] = step
+
+def load(st):
+    if not (os.path.exists(base + ".json") or os.path.exists(base + ".rank0of2.json")):
+        return 0
+    extra = st["eng"].load_checkpoint(base)
+    if st["world"] == 1 and "params" in snap:
+        eng = st["eng"]
+        assert extra["step"] == snap["step"] == 2, (extra, snap["step"])
+        for name, lo, hi, at in owned_pieces(eng):     # the two ranks' pieces, re-split for one rank
+            assert torch.equal(eng.master[at:at + hi - lo], snap["params"][name].reshape(-1)[lo:hi]), name
+        print("RESHARDED_OK", flush=True)
+    return int(extra["step"])
+
+def rebuild(failure):
+    print("DETECTED", type(failure).__name__, flush=True)
+    return 0, 1                          # carry on alone
+
+state, restarts = run_elastic(make_state, train_step, save, load, rebuild, total_steps=5, rank=rank0, world=world0)
+print("DONE restarts", restarts, "steps", state["eng"].step_count, "loss_finite", state["loss"] == state["loss"], flush=True)
+os._exit(0)
+"""
+
+
+def test_elastic_restart_shrinks_the_sharded_engine(tmp_path):
+    """Two gloo ranks train with ShardedDataParallel and checkpoint every step; rank 1 leaves between steps; rank 0
+    sees its next collective fail, rebuilds as a single rank, reads the two-rank checkpoint (re-split) and
+    finishes the run."""
+    script = tmp_path / "elastic_worker.py"
+    script.write_text(_ELASTIC_WORKER)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    port = 29920 + os.getpid() % 60
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   PYTHONPATH=root, REPO_ROOT=root, CKPT_BASE=str(tmp_path / "ck" / "opt"))
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    out0, _ = procs[0].communicate(timeout=240)
+    procs[1].communicate(timeout=240)
+    assert "DETECTED RankFailure" in out0, out0[-3000:]
+    assert "RESHARDED_OK" in out0, out0[-3000:]
+    assert "DONE restarts 1 steps 5 loss_finite True" in out0, out0[-3000:]
