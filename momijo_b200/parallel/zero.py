@@ -593,6 +593,55 @@ class ShardedDataParallel(nn.Module):
 
         return zero_ckpt.load(self, base)
 
+    def load_full_parameters(self, named: dict, reset_moments: bool = True) -> None:
+        """Take parameter values from full tensors (``name -> tensor`` as ``module.named_parameters()`` names
+        them: a pretrained model, ``materialize()`` of another engine): every rank copies the pieces it owns
+        into its fp32 master weights, the AdamW moments restart from zero unless told otherwise, and the bf16
+        parameters are republished. Collective."""
+        from .zero_ckpt import owned_pieces
+
+        with torch.no_grad():
+            for name, lo, hi, at in owned_pieces(self):
+                src = named[name].detach().reshape(-1)[lo:hi]
+                self.master[at:at + hi - lo].copy_(src.to(device=self.master.device, dtype=torch.float32))
+            if reset_moments:
+                self.m.zero_()
+                self.v.zero_()
+        self.republish_from_master()
+
+    def save_weights(self, base: str, extra: Optional[dict] = None) -> None:
+        """The model's parameters as ONE ordinary MNP checkpoint (``<base>.json`` + ``<base>.bin``, tensors under
+        their ``named_parameters`` names), whatever the stage: rank 0 writes what ``materialize()`` collects,
+        so that ``learn.utils.checkpoint.load_state_dict`` of an unsharded model, or ``load_weights`` of an
+        engine of any world size, can read it. Collective."""
+        from ..learn.utils.checkpoint import save_state_dict
+        from .zero_ckpt import _State
+
+        full = self.materialize()
+        if self.rank == 0:
+            import os
+            d = os.path.dirname(base)
+            if d:
+                os.makedirs(d, exist_ok=True)
+            save_state_dict(_State(full), base, extra=extra)
+        if self.world > 1:
+            self.comm.host_barrier()
+
+    def load_weights(self, base: str, reset_moments: bool = True) -> dict:
+        """Read a ``save_weights`` file (or any MNP checkpoint whose tensors carry this module's parameter
+        names) into the engine; returns the file's ``extra``. Collective."""
+        import json as _json
+        from ..learn.utils.checkpoint import read_blob_tensor
+
+        h = _json.load(open(base + ".json"))
+        blob = h["files"]["blob"]
+        import os
+        if not os.path.exists(blob):
+            blob = base + ".bin"
+        named = {e["name"]: read_blob_tensor(blob, e) for e in h.get("tensors", [])}
+        self.load_full_parameters(named, reset_moments)
+        return h.get("extra", {})
+
     def republish_from_master(self) -> None:
         """bf16 parameters := fp32 master weights, on every rank (after a load, or after editing the master
         weights in place). Collective."""

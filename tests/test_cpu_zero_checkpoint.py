@@ -186,3 +186,47 @@ def _ddp_worker(rank, world, port, tmp):
 def test_ddp_resume_and_load_into_sharded_engine(tmp_path):
     port = _free_port()
     mp.spawn(_ddp_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+
+
+def _weights_worker(rank, world, port, tmp):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    from momijo_b200.learn.utils.checkpoint import load_state_dict
+    from momijo_b200.parallel import AdamWConfig, ShardedDataParallel
+    from momijo_b200.parallel.peer import TorchDistComm
+
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    xs, ys = _data()
+    cfg = AdamWConfig(lr=1e-2, weight_decay=0.1)
+    lo, hi = rank * 4, rank * 4 + 4
+    base = os.path.join(tmp, "w", "model")
+    a = ShardedDataParallel(_net(), cfg, stage=3, comm=TorchDistComm(), window=2, grad_slots=2)
+    for s in range(2):
+        _step(a, xs, ys, s, lo, hi)
+    a.save_weights(base, extra={"tag": "two steps"})
+    want = a.materialize()
+    # an unsharded model reads the file through the ordinary MNP loader
+    plain = _net()
+    assert load_state_dict(plain, base)
+    for n, p in plain.named_parameters():
+        assert torch.equal(p.detach(), want[n]), n
+    # another engine (other stage) takes the same weights; its moments start from zero
+    torch.manual_seed(123)
+    other = _net()
+    for p in other.parameters():
+        p.data.normal_()
+    b = ShardedDataParallel(other, cfg, stage=1, comm=TorchDistComm())
+    assert b.load_weights(base)["tag"] == "two steps"
+    got = b.materialize()
+    for k in want:
+        assert torch.equal(got[k], want[k]), k
+    assert float(b.m.abs().sum()) == 0.0 and float(b.v.abs().sum()) == 0.0
+    _step(b, xs, ys, 2, lo, hi)    # and trains on
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_save_weights_is_an_ordinary_checkpoint_and_loads_into_any_engine(tmp_path):
+    port = _free_port()
+    mp.spawn(_weights_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
