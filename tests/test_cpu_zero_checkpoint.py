@@ -230,3 +230,25 @@ def _weights_worker(rank, world, port, tmp):
 def test_save_weights_is_an_ordinary_checkpoint_and_loads_into_any_engine(tmp_path):
     port = _free_port()
     mp.spawn(_weights_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+
+
+def test_model_checkpoint_callback_writes_engine_weights_and_optimizer_state(tmp_path):
+    from momijo_b200.learn.callbacks.model_checkpoint import ModelCheckpoint
+    from momijo_b200.parallel import AdamWConfig, ShardedDataParallel
+
+    xs, ys = _data()
+    cfg = AdamWConfig(lr=1e-2, weight_decay=0.1)
+    a = ShardedDataParallel(_net(), cfg)
+    for s in range(2):
+        _step(a, xs, ys, s, 0, 8)
+    cb = ModelCheckpoint(str(tmp_path / "run"))
+    path = cb.save(a, step=2, extra={"epoch": 0})
+    assert os.path.exists(path + ".json") and os.path.exists(path + ".optim.bin")
+    last = os.path.join(str(tmp_path / "run"), "last.mnp")
+    _step(a, xs, ys, 2, 0, 8)
+    b = ShardedDataParallel(_net(), cfg)
+    b.load_checkpoint(last + ".optim")     # master weights, moments and step: everything a resume needs
+    _step(b, xs, ys, 2, 0, 8)
+    wa, wb = a.materialize(), b.materialize()
+    for k in wa:
+        assert torch.equal(wa[k], wb[k]), k
