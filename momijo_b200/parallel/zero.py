@@ -149,6 +149,7 @@ class ShardedDataParallel(nn.Module):
         self.fused_comm_ctas = 4
         self.side_blocks = 2 * 148   # grid limit of kernels that run beside the backward pass
         self._sync_enabled = True
+        self._accum = None   # stages 2-3: accumulated micro-batch gradients of the unit buckets
         if self.world == 1:
             self._init_single(params, grad_dtype)
         else:
@@ -360,21 +361,45 @@ class ShardedDataParallel(nn.Module):
             b = self.unit_buckets[i]
             if self.stage == 3 and self.is_cuda:
                 b.use_ev.record()
-            if self._sync_enabled and self.overlap and not b.launched:
+            if not self._sync_enabled:
+                if self.stage >= 2:
+                    self._stash_micro_batch(b)
+                return
+            if self.overlap and not b.launched:
                 self._launch(b)
         return hook
 
     @contextlib.contextmanager
     def no_sync(self):
         """Backward passes inside this context only accumulate gradients (gradient accumulation over
-        micro-batches); the last backward pass runs outside it. Needs resident gradients (stage 1)."""
-        if self.world > 1 and self.stage >= 2:
-            raise NotImplementedError("gradient accumulation needs the full gradient buffer: use stage=1")
+        micro-batches); the last backward pass runs outside it and is followed by ``step()``.
+
+        Stage 1 keeps the full gradient buffer anyway and the kernels add into it. Stages 2 and 3 hold a
+        unit's gradients only in a rotating pool slot, so inside this context every unit's gradients are
+        moved, right after its backward pass, into a full-size accumulation buffer that exists only while
+        micro-batches are being accumulated (it is allocated on first use and released by ``step()``); the
+        last backward pass adds the accumulated part back before its reduce-scatter. The memory saving of
+        stage 2 therefore does not hold during accumulation."""
         old, self._sync_enabled = self._sync_enabled, False
         try:
             yield
         finally:
             self._sync_enabled = old
+
+    def _stash_micro_batch(self, b: _Bucket):
+        """Move the gradients of unit bucket ``b`` (in its pool slot) into the accumulation buffer and mark
+        the slot as free for the next writer."""
+        self._finalize_grads(b)
+        if self._accum is None:
+            self._accum = torch.zeros(sum(u.size for u in self.unit_buckets), dtype=self.dtype, device=self.device)
+            self._accum_off, off = {}, 0
+            for u in self.unit_buckets:
+                self._accum_off[u.idx] = off
+                off += u.size
+        o = self._accum_off[b.idx]
+        self._accum[o:o + b.size].add_(b.gview)
+        for p in b.params:
+            p._mg_fresh = True   # the next micro-batch starts this slot afresh
 
     # ---- parameter window (stage 3) ----
     def _gather_params(self, b: _Bucket, forward: bool = False):
@@ -426,6 +451,9 @@ class ShardedDataParallel(nn.Module):
 
     def _launch(self, b: _Bucket):
         self._finalize_grads(b)
+        if self._accum is not None and b.unit is not None:
+            o = self._accum_off[b.idx]
+            b.gview.add_(self._accum[o:o + b.size])
         clip = self.grad_clip is not None
         if self.is_cuda:
             ev = torch.cuda.Event()
@@ -499,6 +527,7 @@ class ShardedDataParallel(nn.Module):
         if self.is_cuda:
             torch.cuda.current_stream().wait_stream(self.side)
         self.step_count += 1
+        self._accum = None
         for b in self.buckets:
             b.launched = False
         if self.stage == 3:

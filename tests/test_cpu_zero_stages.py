@@ -174,3 +174,46 @@ def test_bucketed_ddp_overlaps_and_matches_plain_adamw(tmp_path):
     # first step learns how gradients arrive; afterwards the five block buckets leave during backward
     assert got["sent"][0] == 0 and all(n == 5 for n in got["sent"][1:]), got["sent"]
     assert got["modes"].count("native") == 5
+
+
+def _accum_worker(rank, world, port, out, stage):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    from momijo_b200.parallel import AdamWConfig, ShardedDataParallel
+    from momijo_b200.parallel.peer import TorchDistComm
+
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    xs, ys = _data()
+    eng = ShardedDataParallel(_net(), AdamWConfig(lr=1e-2, weight_decay=0.1), stage=stage, comm=TorchDistComm(),
+                              window=2, grad_slots=2)
+    lo = rank * 4
+    for s in range(xs.shape[0]):
+        # this rank's four rows as two micro-batches of two: the first only accumulates
+        with eng.no_sync():
+            (((eng(xs[s, lo:lo + 2]) - ys[s, lo:lo + 2]) ** 2).mean() / 2).backward()
+        assert eng._accum is not None or stage == 1
+        (((eng(xs[s, lo + 2:lo + 4]) - ys[s, lo + 2:lo + 4]) ** 2).mean() / 2).backward()
+        eng.step()
+        assert eng._accum is None
+    full = eng.materialize()
+    if rank == 0:
+        torch.save({"params": full}, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("stage", [1, 2, 3])
+def test_gradient_accumulation_over_micro_batches_matches_the_full_batch(tmp_path, stage):
+    xs, ys = _data()
+    net = _net()
+    opt = torch.optim.AdamW(net.parameters(), lr=1e-2, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.1)
+    for s in range(xs.shape[0]):
+        opt.zero_grad()
+        ((net(xs[s]) - ys[s]) ** 2).mean().backward()
+        opt.step()
+    out = str(tmp_path / "a.pt")
+    mp.spawn(_accum_worker, args=(2, _free_port(), out, stage), nprocs=2, join=True)
+    got = torch.load(out)
+    for name, p in net.named_parameters():
+        assert torch.allclose(got["params"][name], p.detach(), atol=3e-5), (stage, name)
