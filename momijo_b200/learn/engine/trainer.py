@@ -10,6 +10,7 @@ end), gradient accumulation rule ``(step + 1) % grad_accum_steps == 0``, the sca
 """
 from __future__ import annotations
 
+import contextlib
 import math
 
 import torch
@@ -140,7 +141,12 @@ class Trainer:
             loss = raw / self.grad_accum_steps
             scaled = scaler.scale(loss) if scaler is not None else loss
             if isinstance(scaled, torch.Tensor) and scaled.requires_grad:
-                scaled.backward()
+                # a data-parallel engine exchanges gradients from inside its backward pass: micro-batches that
+                # only accumulate run under its no_sync()
+                last_micro = (step + 1) % self.grad_accum_steps == 0
+                hold = model.no_sync() if (not last_micro and hasattr(model, "no_sync")) else contextlib.nullcontext()
+                with hold:
+                    scaled.backward()
             if (step + 1) % self.grad_accum_steps == 0 and opt is not None:
                 if scaler is not None:
                     params = getattr(opt, "params", None) or []

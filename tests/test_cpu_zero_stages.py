@@ -217,3 +217,57 @@ def test_gradient_accumulation_over_micro_batches_matches_the_full_batch(tmp_pat
     got = torch.load(out)
     for name, p in net.named_parameters():
         assert torch.allclose(got["params"][name], p.detach(), atol=3e-5), (stage, name)
+
+
+class _Loader:
+    """The loader protocol of the fit loop: ``dataset.__len__``, ``batch_size``, ``get_batch(step)``."""
+
+    def __init__(self, xs, ys):
+        self.xs, self.ys = xs, ys
+        self.dataset = list(range(xs.shape[0] * xs.shape[1]))
+        self.batch_size = xs.shape[1]
+
+    def get_batch(self, step):
+        return self.xs[step], self.ys[step]
+
+
+def _trainer_worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    from momijo_b200.learn.engine.trainer import Trainer
+    from momijo_b200.parallel import AdamWConfig, ShardedDataParallel
+    from momijo_b200.parallel.peer import TorchDistComm
+
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    xs, ys = _data()                                   # 4 steps x 8 rows
+    lo = rank * 4
+    # two micro-batches of two rows per optimizer step and rank
+    mx = xs[:, lo:lo + 4].reshape(8, 2, 8)
+    my = ys[:, lo:lo + 4].reshape(8, 2, 4)
+    eng = ShardedDataParallel(_net(), AdamWConfig(lr=1e-2, weight_decay=0.1), stage=3, comm=TorchDistComm(),
+                              window=2, grad_slots=2)
+    tr = Trainer(epochs=1, grad_accum_steps=2, verbose=False)
+    tr.set_optimizer(eng).set_loss(lambda p, t: ((p - t) ** 2).mean())
+    tr.fit(eng, _Loader(mx, my))
+    assert eng.step_count == 4
+    full = eng.materialize()
+    if rank == 0:
+        torch.save({"params": full}, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_fit_loop_accumulates_micro_batches_through_a_sharded_engine(tmp_path):
+    xs, ys = _data()
+    net = _net()
+    opt = torch.optim.AdamW(net.parameters(), lr=1e-2, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.1)
+    for s in range(xs.shape[0]):
+        opt.zero_grad()
+        ((net(xs[s]) - ys[s]) ** 2).mean().backward()
+        opt.step()
+    out = str(tmp_path / "t.pt")
+    mp.spawn(_trainer_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    got = torch.load(out)
+    for name, p in net.named_parameters():
+        assert torch.allclose(got["params"][name], p.detach(), atol=3e-5), name
