@@ -76,9 +76,23 @@ def bce_with_logits(logits, target, pos_weight=None, reduction="mean"):
     return _reduce(loss, reduction)
 
 
-def kl_div(log_p, q, reduction="mean"):
-    """sum q * (log q - log_p)."""
-    return _reduce(torch.where(q > 0, q * (q.clamp_min(1e-38).log() - log_p), torch.zeros_like(q)), reduction)
+def kl_div(p, q, eps: float = 1e-12, reduction: str = "sum", log_input: bool = False):
+    """KL(p || q) = sum p * log(p / q) over all elements, both arguments probabilities clipped to ``[eps, 1]``
+    (legacy/src/momijo/learn/losses/losses.mojo:172-177: full sum, no mean).
+
+    ``log_input=True`` gives the other common convention instead: the first argument holds
+    log-probabilities of the model and the second the target probabilities, and the result is
+    ``q * (log q - log_p)`` reduced by ``reduction`` ("sum", "mean" over elements, "batchmean", "none")."""
+    if log_input:
+        v = torch.where(q > 0, q * (q.clamp_min(1e-38).log() - p), torch.zeros_like(q))
+        if reduction == "batchmean":
+            return v.sum() / v.shape[0]
+        return _reduce(v, reduction)
+    pp, qq = p.clamp(eps, 1.0), q.clamp(eps, 1.0)
+    v = pp * (pp / qq).clamp_min(eps).log()
+    if reduction == "batchmean":
+        return v.sum() / v.shape[0]
+    return _reduce(v, reduction)
 
 
 def nll_loss(log_probs, target, class_weight=None, reduction="mean"):

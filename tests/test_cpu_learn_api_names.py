@@ -119,3 +119,17 @@ def test_utils(tmp_path):
     assert randomness.randint(3, 0, 10) == randomness.randint(3, 0, 10)
     assert sorted(randomness.permutation(1, 5)) == [0, 1, 2, 3, 4]
     assert L.utils.checkpoint.exists_checkpoint_at(str(tmp_path), "none") is False
+
+
+def test_kl_div_follows_the_reference_and_offers_the_log_input_form():
+    import torch.nn.functional as F
+    from momijo_b200.learn.losses import kl_div
+
+    torch.manual_seed(0)
+    p, q = torch.softmax(torch.randn(4, 5), -1), torch.softmax(torch.randn(4, 5), -1)
+    want = float((p * (p / q).log()).sum())          # sum p log(p / q): losses.mojo:172-177
+    assert abs(float(kl_div(p, q)) - want) < 1e-6
+    assert float(kl_div(p, p)) == 0.0
+    lp = torch.log_softmax(torch.randn(4, 5), -1)
+    assert abs(float(kl_div(lp, q, log_input=True, reduction="batchmean")) -
+               float(F.kl_div(lp, q, reduction="batchmean"))) < 1e-6
