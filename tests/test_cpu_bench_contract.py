@@ -25,3 +25,19 @@ def test_help_lists_the_driver_flags_and_the_configs():
         assert flag in r.stdout, flag
     for cfg in ("gpt2", "llama8b-tp", "moe16b-ep", "llama13b-pptp"):
         assert cfg in r.stdout, cfg
+
+
+def test_misc_kernel_benchmark_calls_stay_valid_without_a_gpu():
+    """The microbenchmark of the smaller kernels walks the same front ends on CPU tensors (tiny sizes), so a renamed
+    argument shows up here and not only on a GPU box."""
+    import torch
+
+    if torch.cuda.is_available():
+        import pytest
+        pytest.skip("the GPU form runs full sizes; covered by the profile")
+    from momijo_b200.ops.bench_kernels import bench_misc
+
+    rows = bench_misc(True)
+    names = {r["op"] for r in rows}
+    assert {"rope", "swiglu_fwd", "swiglu_bwd", "gelu_fwd", "embedding_bwd", "colsum", "sq_norm",
+            "conv2d_fp32_direct", "max_pool2d", "avg_pool2d"} <= names
