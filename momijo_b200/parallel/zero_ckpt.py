@@ -118,14 +118,23 @@ def save(engine, base: str, extra: dict | None = None) -> None:
 def _writer_headers(base: str) -> List[Tuple[dict, str]]:
     """Headers (parsed) and blob paths of every rank that wrote ``base``."""
     out = []
-    sharded = sorted(glob.glob(glob.escape(base) + ".rank*of*.json"),
-                     key=lambda f: int(re.search(r"\.rank(\d+)of\d+\.json$", f).group(1)))
-    if sharded:
-        world = int(re.search(r"of(\d+)\.json$", sharded[0]).group(1))
-        files = [f for f in sharded if f.endswith(f"of{world}.json")]
-        if len(files) != world:
-            raise FileNotFoundError(f"{base}: found {len(files)} of {world} rank files")
-        for f in files:
+    by_world: Dict[int, List[Tuple[int, str]]] = {}
+    for f in glob.glob(glob.escape(base) + ".rank*of*.json"):
+        m = re.search(r"\.rank(\d+)of(\d+)\.json$", f)
+        if m:
+            by_world.setdefault(int(m.group(2)), []).append((int(m.group(1)), f))
+    if by_world:
+        # several world sizes may have written to the same base over time: the newest complete set wins
+        complete = {w: sorted(fs) for w, fs in by_world.items() if len(fs) == w}
+        if not complete:
+            w, fs = next(iter(by_world.items()))
+            raise FileNotFoundError(f"{base}: found {len(fs)} of {w} rank files")
+        world = max(complete, key=lambda w: max(os.path.getmtime(f) for _, f in complete[w]))
+        single = base + ".json"
+        if os.path.exists(single) and os.path.getmtime(single) > max(os.path.getmtime(f) for _, f in complete[world]):
+            out.append((json.load(open(single)), base + ".bin"))
+            return out
+        for _, f in complete[world]:
             out.append((json.load(open(f)), f[:-len(".json")] + ".bin"))
     elif os.path.exists(base + ".json"):
         out.append((json.load(open(base + ".json")), base + ".bin"))
