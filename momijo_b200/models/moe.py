@@ -56,7 +56,7 @@ class MoEConfig:
 
 
 class MoEBlock(nn.Module):
-    def __init__(self, cfg: MoEConfig, dispatcher=None):
+    def __init__(self, cfg: MoEConfig, dispatcher=None, group=None):
         super().__init__()
         c, dt = cfg.d_model, cfg.dtype
         self.cfg = cfg
@@ -68,7 +68,7 @@ class MoEBlock(nn.Module):
         nn.init.normal_(self.wqkv, 0.0, cfg.init_std)
         nn.init.normal_(self.wo, 0.0, cfg.init_std)
         self.moe = MoELayer(c, cfg.d_ff_expert, cfg.n_experts, cfg.top_k, cfg.n_shared, cfg.aux_coef,
-                            dispatcher, dtype=dt, init_std=cfg.init_std)
+                            dispatcher, dtype=dt, init_std=cfg.init_std, group=group)
 
     def forward(self, delta, res, B, T):
         cfg = self.cfg
@@ -87,9 +87,11 @@ class MoEBlock(nn.Module):
 
 class MoEDecoder(nn.Module):
     """``forward(tokens, targets)`` -> (cross-entropy + auxiliary loss). ``comm``: the peer
-    communicator of the expert-parallel group (None: every expert on this rank)."""
+    communicator of the expert-parallel group; ``group``: a torch.distributed process group instead (tokens
+    travel by ``all_to_all_single``: any backend, no capacity limit); neither: every expert on this rank."""
 
-    def __init__(self, cfg: MoEConfig, comm=None, max_tokens: int = 16384, capacity_factor: float = 2.0):
+    def __init__(self, cfg: MoEConfig, comm=None, max_tokens: int = 16384, capacity_factor: float = 2.0,
+                 group=None):
         super().__init__()
         self.cfg = cfg
         self.dispatcher = None
@@ -99,7 +101,8 @@ class MoEDecoder(nn.Module):
         dt = cfg.dtype
         self.wte = nn.Parameter(torch.empty(ops.pad_vocab(cfg.vocab_size), cfg.d_model, dtype=dt))
         nn.init.normal_(self.wte, 0.0, cfg.init_std)
-        self.blocks = nn.ModuleList([MoEBlock(cfg, self.dispatcher) for _ in range(cfg.n_layer)])
+        self.blocks = nn.ModuleList([MoEBlock(cfg, self.dispatcher, group if comm is None else None)
+                                     for _ in range(cfg.n_layer)])
         self.final_norm = nn.Parameter(torch.ones(cfg.d_model, dtype=dt))
         self.lm_head = nn.Parameter(torch.empty(ops.pad_vocab(cfg.vocab_size), cfg.d_model, dtype=dt))
         nn.init.normal_(self.lm_head, 0.0, cfg.init_std)

@@ -262,6 +262,30 @@ class _RouterTopK(torch.autograd.Function):
         return dl, None, None
 
 
+class _AllToAllRows(torch.autograd.Function):
+    """``all_to_all_single`` of row blocks with given split sizes; the gradient travels the opposite way."""
+
+    @staticmethod
+    def forward(ctx, x, in_splits, out_splits, group):
+        import torch.distributed as dist
+
+        ctx.splits, ctx.group = (in_splits, out_splits), group
+        out = x.new_empty((sum(out_splits),) + tuple(x.shape[1:]))
+        dist.all_to_all_single(out, x.contiguous(), output_split_sizes=out_splits, input_split_sizes=in_splits,
+                               group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        import torch.distributed as dist
+
+        in_splits, out_splits = ctx.splits
+        dx = dy.new_empty((sum(in_splits),) + tuple(dy.shape[1:]))
+        dist.all_to_all_single(dx, dy.contiguous(), output_split_sizes=in_splits, input_split_sizes=out_splits,
+                               group=ctx.group)
+        return dx, None, None, None
+
+
 class TopKRouter(nn.Module):
     """Softmax router with top-k selection, renormalised weights and the load-balance auxiliary
     loss ``aux = coef * E * sum_e f_e * P_e`` (f_e: fraction of assignments, P_e: mean router
@@ -293,11 +317,21 @@ class MoELayer(nn.Module):
 
     def __init__(self, hidden: int, ffn: int, n_experts: int, top_k: int, n_shared: int = 0,
                  aux_coef: float = 0.01, dispatcher: Optional[MoEDispatcher] = None, world: int = 1,
-                 rank: int = 0, dtype=bf16, init_std: float = 0.02):
+                 rank: int = 0, dtype=bf16, init_std: float = 0.02, group=None):
+        """``dispatcher``: the peer-memory dispatch / combine kernels (CUDA, one NVSwitch domain).
+        ``group``: a torch.distributed process group instead: tokens travel by ``all_to_all_single`` (any
+        backend: gloo on CPU, NCCL across nodes), the experts run as plain matrix products. Neither: one
+        rank holds every expert."""
         super().__init__()
         self.disp = dispatcher
-        self.world = dispatcher.comm.world if dispatcher is not None else world
-        self.rank = dispatcher.comm.rank if dispatcher is not None else rank
+        self.group = group
+        if dispatcher is not None:
+            self.world, self.rank = dispatcher.comm.world, dispatcher.comm.rank
+        elif group is not None:
+            import torch.distributed as dist
+            self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        else:
+            self.world, self.rank = world, rank
         if n_experts % self.world:
             raise ValueError("experts must divide evenly over ranks")
         self.E, self.k, self.H, self.F = n_experts, top_k, hidden, ffn
@@ -318,11 +352,53 @@ class MoELayer(nn.Module):
         w, idx, aux = self.router(x)
         if self.disp is not None and x.is_cuda and x.dtype == bf16:
             y = _ExpertsEP.apply(x, w, idx, self.w_gu, self.w_down, self.disp)
+        elif self.group is not None and self.world > 1:
+            y = self._experts_all_to_all(x, w, idx)
         else:
             y = self._experts_reference(x, w, idx)
         if self.shared is not None:
             y = y + self.shared(x)
         return y, aux
+
+    def _experts_all_to_all(self, x, w, idx):
+        """Expert parallelism over torch.distributed: assignments sorted by expert (experts of one rank are
+        adjacent, so this also groups them by destination), per-expert counts exchanged first, rows sent
+        with ``all_to_all_single``, every local expert applied to its rows, results sent back the same way
+        and summed into their tokens with the gate weights. No capacity limit: nothing is dropped."""
+        import torch.distributed as dist
+
+        W, epr, k = self.world, self.epr, self.k
+        n = x.shape[0]
+        flat_e = idx.reshape(-1).long()
+        order = torch.argsort(flat_e, stable=True)
+        tok = torch.div(order, k, rounding_mode="floor")
+        counts = torch.bincount(flat_e, minlength=self.E)                 # assignments per expert, [E]
+        recv_counts = torch.empty_like(counts)
+        dist.all_to_all_single(recv_counts, counts, group=self.group)      # [W, epr]: from each source rank
+        in_splits = counts.view(W, epr).sum(1).tolist()
+        out_splits = recv_counts.view(W, epr).sum(1).tolist()
+        rows = _AllToAllRows.apply(x[tok], in_splits, out_splits, self.group)
+        # received rows come as (source rank, local expert) runs: bring each expert's rows together
+        rc = recv_counts.view(W, epr)
+        local_e = torch.repeat_interleave(torch.arange(epr, device=x.device).repeat(W), rc.reshape(-1))
+        by_e = torch.argsort(local_e, stable=True)
+        per_e = rc.sum(0).tolist()
+        outs, start = [], 0
+        sorted_rows = rows[by_e]
+        for j in range(epr):
+            r = sorted_rows[start:start + per_e[j]]
+            start += per_e[j]
+            h = r @ self.w_gu[j].t().to(r.dtype)
+            g, u = h.chunk(2, -1)
+            outs.append((torch.nn.functional.silu(g) * u) @ self.w_down[j].t().to(r.dtype))
+        y_sorted = torch.cat(outs) if outs else rows.new_zeros((0, self.H))
+        y_recv = torch.empty_like(y_sorted)
+        y_recv[by_e] = y_sorted                                            # back to arrival order
+        back = _AllToAllRows.apply(y_recv, out_splits, in_splits, self.group)
+        gate = w.reshape(-1)[order].to(torch.float32)
+        out = torch.zeros((n, self.H), dtype=torch.float32, device=x.device)
+        out = out.index_add(0, tok, back.float() * gate[:, None])
+        return out.to(x.dtype)
 
     def _experts_reference(self, x, w, idx):
         """Dense evaluation with plain torch (single rank holds every expert); used on CPU."""
