@@ -130,7 +130,11 @@ class ShardedDataParallel(nn.Module):
         whose loss is a per-rank mean needs 1/world here). ``grad_clip``: clip by the global gradient
         norm; the update of every bucket then waits for the norm (reduce-scatter during backward, one
         scalar all-reduce, AdamW afterwards). ``units``: the modules that get a bucket each.
-        ``grad_dtype`` (single rank only): torch.float32 accumulates micro-batch gradients in fp32."""
+        ``grad_dtype`` (single rank only): torch.float32 accumulates micro-batch gradients in fp32.
+        ``overlap``: update each unit's bucket from its backward hook (default). A loop that may decide to
+        skip a step after the backward pass (a ``GradScaler`` that found an overflow) needs ``overlap=False``:
+        with it every bucket is reduced and updated inside ``step()`` and not calling ``step()`` leaves the
+        parameters untouched."""
         super().__init__()
         if stage not in (1, 2, 3):
             raise ValueError("stage must be 1, 2 or 3")
